@@ -1,0 +1,137 @@
+/*
+ * pratchya_b200 -- C ABI of the sm_100a implementation of pratchya's FP8
+ * block-quantization path (quantize / dequantize / block-scaled FP8 matmul).
+ *
+ * The reference has no FFI: its ops are jitted Python functions in
+ * pratchya/_qualia/_qarr.py.  Each entry point below names the reference
+ * function it replaces; a JAX host binds them as jax.ffi custom calls, the
+ * bundled Python host binds them with ctypes.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer owned by the caller unless stated;
+ *   - `stream` is a cudaStream_t passed as void*; calls are asynchronous on it,
+ *     never synchronise the host and never touch the default stream;
+ *   - the library allocates nothing: scratch memory is a caller buffer whose
+ *     size the matching *_workspace_size() call returns;
+ *   - every function returns a pb_status; pb_last_error() gives the text of
+ *     the calling thread's last failure.  No C++ exception crosses this ABI.
+ *
+ * Quantized triple of an array x[batch, rows, cols] on grid (a, b)
+ * (identical to the reference's (value, sc_fp8, sc_fp32), _qarr.py:500-506):
+ *   q    : uint8  [batch, rows, cols]   fp8 bytes (e4m3fn, or e5m2 extension)
+ *   sc8  : uint8  [batch, M, K]         float8_e8m0fnu bytes, one per block
+ *   sc32 : float  [batch, M]            fp32 amax, one per super-group
+ * with Nb = rows*cols/(a*b) blocks numbered row-major, K = gcd(max(1,a*b/16), Nb),
+ * M = Nb/K.  `batch` is the reference's per-leading-index scan (_qarr.py:38-42).
+ */
+#ifndef PRATCHYA_B200_H_
+#define PRATCHYA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define PB_API __attribute__((visibility("default")))
+#else
+#define PB_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum pb_status {
+  PB_OK = 0,
+  PB_ERR_NULL_POINTER = 1,
+  PB_ERR_BAD_SHAPE = 2,        /* non-positive, or rows % a / cols % b != 0 (the reference's reshape fails too) */
+  PB_ERR_BAD_GRID = 3,
+  PB_ERR_BAD_DTYPE = 4,
+  PB_ERR_WORKSPACE_TOO_SMALL = 5,
+  PB_ERR_CUDA = 6,             /* a CUDA runtime/driver call failed; text in pb_last_error() */
+  PB_ERR_DEVICE_TIMEOUT = 7,   /* a bounded device-side wait ran out (read back via pb_gemm_check) */
+  PB_ERR_UNSUPPORTED = 8,
+  PB_ERR_MISALIGNED = 9
+} pb_status;
+
+/* element types of dense (unquantized) arrays */
+enum { PB_F32 = 0, PB_BF16 = 1 };
+/* fp8 storage formats.  E4M3 is the reference's; E5M2 swaps only the final cast. */
+enum { PB_E4M3 = 0, PB_E5M2 = 1 };
+
+PB_API int pb_version(void);
+PB_API const char* pb_last_error(void);
+PB_API const char* pb_status_string(int status);
+
+/* (M, K) of the scale arrays for one [rows, cols] slice.  _qarr.py:474-480. */
+PB_API int pb_group_geometry(int64_t rows, int64_t cols, int a, int b, int64_t* M, int64_t* K);
+
+/* ---- quantize: replaces quantize_impl(x, tgrid), _qarr.py:458-506 (and the
+ *      per-leading-index scan of QArrayImpl.__quantize, :34-44, via `batch`).
+ *      x is [batch, rows, cols] of x_dtype (PB_F32 | PB_BF16), row-major, 16-byte aligned. */
+PB_API size_t pb_quantize_workspace_size(int64_t batch, int64_t rows, int64_t cols, int a, int b);
+PB_API int pb_quantize(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols,
+                int a, int b, int out_format,
+                void* q, uint8_t* sc8, float* sc32,
+                void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- quantize of the transpose without materialising it: the triple of
+ *      quantize_impl(swapaxes(x,-1,-2), (1, b)) as used by fp8_matmul_bwd,
+ *      _qarr.py:784-789.  x is [batch, rows, cols]; q is [batch, cols, rows]. */
+PB_API size_t pb_quantize_transposed_workspace_size(int64_t batch, int64_t rows, int64_t cols, int b);
+PB_API int pb_quantize_transposed(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols,
+                           int b, int out_format,
+                           void* q_t, uint8_t* sc8, float* sc32,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- dequantize: replaces dequantize_impl(x_fp8, sc_fp8, sc_fp32, dtype, tgrid),
+ *      _qarr.py:541-569.  out is [batch, rows, cols] of out_dtype. */
+PB_API int pb_dequantize(const void* q, int q_format, const uint8_t* sc8, const float* sc32,
+                  int64_t batch, int64_t rows, int64_t cols, int a, int b,
+                  int out_dtype, void* out, void* stream);
+
+/* ---- cotangent of dequantize: g * x_sc / 128, dequantize_impl_bwd, _qarr.py:575-601.
+ *      g and out are [batch, rows, cols] of `dtype`. */
+PB_API int pb_dequantize_bwd(const void* g, int dtype, const uint8_t* sc8, const float* sc32,
+                      int64_t batch, int64_t rows, int64_t cols, int a, int b,
+                      void* out, void* stream);
+
+/* ---- block-scaled FP8 matmul.
+ * A GEMM operand is a K-major quantized matrix: bytes [rows, depth] (depth = the
+ * contraction length, contiguous), one e8m0 byte per (row-block, 128-deep block)
+ * and one fp32 factor per super-group, exactly as pb_quantize lays them out for
+ * the grids (1,128) (per-row scales) and (128,128) (per-tile scales).
+ *
+ *   D[m, n] = sum_k dq(A)[m, k] * dq(B)[n, k]        fp32 accumulate
+ *
+ * pb_gemm_tn covers all three matmuls of the reference's training triple:
+ *   forward  matmul_impl, _qarr.py:605-608 : A = Q(x,(1,128)),   B = the weight's bytes transposed
+ *   dgrad    matmul_impl_bwd g @ W^T, :621  : A = Q(g,(1,128)),   B = the weight as stored [K,N] (N is the depth)
+ *   wgrad    fp8_matmul_bwd x^T @ g, :789   : A = Q(x^T,(1,128)), B = Q(g^T,(1,128))
+ */
+typedef struct pb_operand {
+  const void* q;          /* fp8 bytes [rows, depth], row pitch = depth, 16-byte aligned */
+  const uint8_t* sc8;     /* e8m0 bytes [M, K] as produced by pb_quantize on `grid` */
+  const float* sc32;      /* fp32 [M] */
+  int64_t rows;           /* M for operand A, N for operand B */
+  int64_t depth;          /* contraction length, multiple of 128 */
+  int grid_a, grid_b;     /* (1,128) or (128,128); blocks are counted on the [rows, depth] view */
+  int format;             /* PB_E4M3 | PB_E5M2 */
+  int transposed_blocks;  /* 1: sc8/sc32 were produced on the [depth, rows] view of the same bytes' transpose
+                             (a (128,128) weight used without re-quantizing); 0 otherwise */
+} pb_operand;
+
+PB_API size_t pb_gemm_workspace_size(const pb_operand* a, const pb_operand* b);
+PB_API int pb_gemm_tn(const pb_operand* a, const pb_operand* b,
+               void* d, int d_dtype, int64_t ldd,
+               void* workspace, size_t workspace_bytes, void* stream);
+/* Reads (and clears) the device status word of the last GEMMs launched on this
+ * device; synchronises `stream`.  PB_OK or PB_ERR_DEVICE_TIMEOUT. */
+PB_API int pb_gemm_check(void* stream);
+
+/* byte transpose [rows, cols] -> [cols, rows] of an fp8 matrix (weight prepared for the forward GEMM) */
+PB_API int pb_transpose_bytes(const void* src, int64_t rows, int64_t cols, void* dst, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PRATCHYA_B200_H_ */

@@ -1,0 +1,80 @@
+"""ctypes binding of libpratchya_b200.so (the C ABI declared in include/pratchya_b200.h).
+
+There is no CPU fallback: if the library has not been built, or CUDA is not
+usable, the ops raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libpratchya_b200.so"
+_lib = None
+
+PB_F32, PB_BF16 = 0, 1
+PB_E4M3, PB_E5M2 = 0, 1
+
+
+class PbError(RuntimeError):
+    def __init__(self, status: int, text: str):
+        super().__init__(f"pratchya_b200 status {status}: {text}")
+        self.status = status
+
+
+class Operand(C.Structure):
+    """Mirror of `pb_operand`."""
+    _fields_ = [
+        ("q", C.c_void_p), ("sc8", C.c_void_p), ("sc32", C.c_void_p),
+        ("rows", C.c_int64), ("depth", C.c_int64),
+        ("grid_a", C.c_int), ("grid_b", C.c_int), ("format", C.c_int), ("transposed_blocks", C.c_int),
+    ]
+
+
+_i64, _int, _ptr, _sz = C.c_int64, C.c_int, C.c_void_p, C.c_size_t
+_SIGNATURES = {
+    "pb_version": (C.c_int, []),
+    "pb_last_error": (C.c_char_p, []),
+    "pb_status_string": (C.c_char_p, [_int]),
+    "pb_group_geometry": (_int, [_i64, _i64, _int, _int, C.POINTER(_i64), C.POINTER(_i64)]),
+    "pb_quantize_workspace_size": (_sz, [_i64, _i64, _i64, _int, _int]),
+    "pb_quantize": (_int, [_ptr, _int, _i64, _i64, _i64, _int, _int, _int, _ptr, _ptr, _ptr, _ptr, _sz, _ptr]),
+    "pb_quantize_transposed_workspace_size": (_sz, [_i64, _i64, _i64, _int]),
+    "pb_quantize_transposed": (_int, [_ptr, _int, _i64, _i64, _i64, _int, _int, _ptr, _ptr, _ptr, _ptr, _sz, _ptr]),
+    "pb_dequantize": (_int, [_ptr, _int, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _int, _ptr, _ptr]),
+    "pb_dequantize_bwd": (_int, [_ptr, _int, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr]),
+    "pb_gemm_workspace_size": (_sz, [C.POINTER(Operand), C.POINTER(Operand)]),
+    "pb_gemm_tn": (_int, [C.POINTER(Operand), C.POINTER(Operand), _ptr, _int, _i64, _ptr, _sz, _ptr]),
+    "pb_gemm_check": (_int, [_ptr]),
+    "pb_transpose_bytes": (_int, [_ptr, _i64, _i64, _ptr, _ptr]),
+    "pb_debug_division_check": (_int, [C.c_uint64, C.c_uint64, _ptr, _ptr]),
+}
+
+# every symbol include/pratchya_b200.h declares (checked by the CPU test-suite)
+DECLARED_SYMBOLS = tuple(k for k in _SIGNATURES if not k.startswith("pb_debug"))
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def load():
+    """Loads the shared library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise RuntimeError(
+                f"{_LIB_PATH} is missing: build it with `python -m pratchya_b200.csrc.build` "
+                "(there is no CPU fallback for the pratchya_b200 ops)")
+        lib = C.CDLL(str(_LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(lib, name, None)
+            if fn is None:
+                continue          # reported by the symbol test; calling it raises AttributeError
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def check(status: int):
+    if status != 0:
+        raise PbError(status, load().pb_last_error().decode(errors="replace"))

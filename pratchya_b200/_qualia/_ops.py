@@ -1,0 +1,259 @@
+"""Functional quant ops on torch CUDA tensors, same names and argument meaning as
+pratchya/_qualia/_qarr.py (quantize_impl :459, dequantize_impl :542, matmul_impl :605,
+matmul_mixed_impl :645, rmatmul_mixed_impl :680, the seven elementwise impls :757-763).
+
+Every op runs in libpratchya_b200.so on the tensor's device and the current torch
+stream.  torch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import math
+from typing import Tuple
+
+import torch
+
+from .. import _lib
+from .._lib import PB_BF16, PB_E4M3, PB_E5M2, PB_F32, Operand, check
+
+E4M3 = torch.float8_e4m3fn
+E5M2 = torch.float8_e5m2
+E8M0 = torch.float8_e8m0fnu
+_FMT_CODE = {"e4m3": PB_E4M3, "e5m2": PB_E5M2}
+_FMT_DTYPE = {"e4m3": E4M3, "e5m2": E5M2}
+_DTYPE_FMT = {E4M3: PB_E4M3, E5M2: PB_E5M2}
+_DENSE_CODE = {torch.float32: PB_F32, torch.bfloat16: PB_BF16}
+
+
+def group_geometry(rows: int, cols: int, tgrid) -> Tuple[int, int]:
+    """(M, K) of the scale arrays, _qarr.py:474-480."""
+    a, b = tgrid
+    if rows % a or cols % b:
+        raise ValueError(f"shape ({rows},{cols}) is not divisible by tgrid {tuple(tgrid)}")
+    nb = (rows * cols) // (a * b)
+    k = math.gcd(max(1, (a * b) // 16), nb)
+    return nb // k, k
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, what: str):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"{what} must be a CUDA tensor: pratchya_b200 has no CPU path")
+
+
+def _as_2d(shape):
+    """The reference's rank promotion, _qarr.py:460-464."""
+    if len(shape) == 0:
+        return (1, 1)
+    if len(shape) == 1:
+        return (1, shape[0])
+    return tuple(shape)
+
+
+def _dense_input(x: torch.Tensor) -> torch.Tensor:
+    if x.dtype not in _DENSE_CODE:
+        x = x.to(torch.float32)          # QArrayImpl casts to f32 before quantizing, _qarr.py:29
+    return x.contiguous()
+
+
+def quantize_impl(x: torch.Tensor, tgrid=(128, 128), out_format: str = "e4m3"):
+    """Block-quantizes the last two dims of `x`; leading dims are independent slices.
+
+    Returns (value fp8 [x.shape], sc_fp8 e8m0 [..., M, K], sc_fp32 f32 [..., M, 1, 1]),
+    the triple of _qarr.py:458-506.  `out_format="e5m2"` is an extension that swaps
+    only the final cast.
+    """
+    _require_cuda(x, "quantize_impl input")
+    lib = _lib.load()
+    orig_shape = tuple(x.shape)
+    shape = _as_2d(orig_shape)
+    a, b = int(tgrid[0]), int(tgrid[1])
+    rows, cols = shape[-2], shape[-1]
+    m, k = group_geometry(rows, cols, (a, b))
+    lead = shape[:-2]
+    batch = math.prod(lead)
+    x = _dense_input(x)
+    with torch.cuda.device(x.device):
+        q = torch.empty(orig_shape, dtype=_FMT_DTYPE[out_format], device=x.device)
+        sc8 = torch.empty((*lead, m, k), dtype=E8M0, device=x.device)
+        sc32 = torch.empty((*lead, m, 1, 1), dtype=torch.float32, device=x.device)
+        if x.numel() == 0:
+            return q, sc8, sc32
+        ws_bytes = lib.pb_quantize_workspace_size(batch, rows, cols, a, b)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
+        check(lib.pb_quantize(x.data_ptr(), _DENSE_CODE[x.dtype], batch, rows, cols, a, b, _FMT_CODE[out_format],
+                              q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(),
+                              ws.data_ptr() if ws is not None else None, ws_bytes, _stream(x)))
+    return q, sc8, sc32
+
+
+def quantize_transposed_impl(x: torch.Tensor, b: int = 128, out_format: str = "e4m3"):
+    """The triple of quantize_impl(swapaxes(x, -1, -2), (1, b)) without materialising the
+    transpose (the operands fp8_matmul_bwd builds, _qarr.py:784-789)."""
+    _require_cuda(x, "quantize_transposed_impl input")
+    lib = _lib.load()
+    if x.dim() < 2:
+        raise ValueError("quantize_transposed_impl needs at least 2 dims")
+    rows, cols = x.shape[-2], x.shape[-1]
+    lead = tuple(x.shape[:-2])
+    batch = math.prod(lead)
+    m, k = group_geometry(cols, rows, (1, b))
+    x = _dense_input(x)
+    with torch.cuda.device(x.device):
+        q = torch.empty((*lead, cols, rows), dtype=_FMT_DTYPE[out_format], device=x.device)
+        sc8 = torch.empty((*lead, m, k), dtype=E8M0, device=x.device)
+        sc32 = torch.empty((*lead, m, 1, 1), dtype=torch.float32, device=x.device)
+        if x.numel() == 0:
+            return q, sc8, sc32
+        ws_bytes = lib.pb_quantize_transposed_workspace_size(batch, rows, cols, b)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
+        check(lib.pb_quantize_transposed(x.data_ptr(), _DENSE_CODE[x.dtype], batch, rows, cols, b, _FMT_CODE[out_format],
+                                         q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(),
+                                         ws.data_ptr() if ws is not None else None, ws_bytes, _stream(x)))
+    return q, sc8, sc32
+
+
+def dequantize_impl(x_fp8: torch.Tensor, sc_fp8: torch.Tensor, sc_fp32: torch.Tensor, dtype, tgrid):
+    """_qarr.py:541-569.  (M, K) come from sc_fp8's last two dims, as in the reference (:550)."""
+    _require_cuda(x_fp8, "dequantize_impl input")
+    lib = _lib.load()
+    orig_shape = tuple(x_fp8.shape)
+    shape = _as_2d(orig_shape)
+    a, b = int(tgrid[0]), int(tgrid[1])
+    rows, cols = shape[-2], shape[-1]
+    m, k = group_geometry(rows, cols, (a, b))
+    if tuple(sc_fp8.shape[-2:]) != (m, k):
+        raise ValueError(f"sc_fp8 has shape {tuple(sc_fp8.shape)}, tgrid {(a, b)} on {shape} needs (..., {m}, {k})")
+    batch = math.prod(shape[:-2])
+    kernel_dtype = dtype if dtype in _DENSE_CODE else torch.float32
+    x_fp8, sc_fp8, sc_fp32 = x_fp8.contiguous(), sc_fp8.contiguous(), sc_fp32.contiguous()
+    with torch.cuda.device(x_fp8.device):
+        out = torch.empty(orig_shape, dtype=kernel_dtype, device=x_fp8.device)
+        if out.numel():
+            check(lib.pb_dequantize(x_fp8.data_ptr(), _DTYPE_FMT[x_fp8.dtype], sc_fp8.data_ptr(), sc_fp32.data_ptr(),
+                                    batch, rows, cols, a, b, _DENSE_CODE[kernel_dtype], out.data_ptr(), _stream(x_fp8)))
+    return out if kernel_dtype == dtype else out.to(dtype)
+
+
+def dequantize_impl_bwd(sc_fp8: torch.Tensor, sc_fp32: torch.Tensor, g_out: torch.Tensor, tgrid):
+    """Cotangent of the fp8 value: g * x_sc / 128 in g's dtype, _qarr.py:575-601."""
+    _require_cuda(g_out, "dequantize_impl_bwd input")
+    lib = _lib.load()
+    orig_shape = tuple(g_out.shape)
+    shape = _as_2d(orig_shape)
+    a, b = int(tgrid[0]), int(tgrid[1])
+    rows, cols = shape[-2], shape[-1]
+    batch = math.prod(shape[:-2])
+    g = g_out if g_out.dtype in _DENSE_CODE else g_out.to(torch.float32)
+    g = g.contiguous()
+    with torch.cuda.device(g.device):
+        out = torch.empty_like(g)
+        if out.numel():
+            check(lib.pb_dequantize_bwd(g.data_ptr(), _DENSE_CODE[g.dtype], sc_fp8.contiguous().data_ptr(),
+                                        sc_fp32.contiguous().data_ptr(), batch, rows, cols, a, b, out.data_ptr(), _stream(g)))
+    return out.to(g_out.dtype)
+
+
+# ---- matmuls ---------------------------------------------------------------------------
+
+def _tensor_core_eligible(x_fp8, y_fp8, grid_x, grid_y) -> bool:
+    if x_fp8.dim() != 2 or y_fp8.dim() != 2:
+        return False
+    mm, kk = x_fp8.shape
+    k2, nn = y_fp8.shape
+    return (tuple(grid_x) == (1, 128) and tuple(grid_y) == (128, 128) and kk == k2
+            and kk % 128 == 0 and nn % 128 == 0 and mm >= 1
+            and group_geometry(mm, kk, grid_x)[1] == 8)
+
+
+def transpose_bytes(q: torch.Tensor) -> torch.Tensor:
+    """[rows, cols] fp8 bytes -> [cols, rows] (a weight prepared for the forward GEMM)."""
+    lib = _lib.load()
+    rows, cols = q.shape
+    q = q.contiguous()
+    with torch.cuda.device(q.device):
+        out = torch.empty((cols, rows), dtype=q.dtype, device=q.device)
+        check(lib.pb_transpose_bytes(q.data_ptr(), rows, cols, out.data_ptr(), _stream(q)))
+    return out
+
+
+def _operand(q, sc8, sc32, rows, depth, grid, transposed_blocks=0) -> Operand:
+    return Operand(q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(), rows, depth,
+                   grid[0], grid[1], _DTYPE_FMT[q.dtype], transposed_blocks)
+
+
+def gemm_tn(a: Operand, b: Operand, out_dtype, device, keep_alive=()) -> torch.Tensor:
+    """D[m, n] = sum_k dq(A)[m, k] * dq(B)[n, k] on the tcgen05 kernel."""
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        d = torch.empty((a.rows, b.rows), dtype=out_dtype, device=device)
+        ws_bytes = lib.pb_gemm_workspace_size(a, b)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=device)
+        check(lib.pb_gemm_tn(a, b, d.data_ptr(), _DENSE_CODE[out_dtype], b.rows, ws.data_ptr(), ws_bytes,
+                             torch.cuda.current_stream(device).cuda_stream))
+    return d
+
+
+def matmul_impl(x_fp8, x_sc8, x_sc32, y_fp8, y_sc8, y_sc32, block_grid_x, block_grid_y,
+                y_fp8_t=None, out_dtype=torch.float32):
+    """dq(X) @ dq(Y) with fp32 accumulation, _qarr.py:605-608.
+
+    (1,128) x (128,128) operands run on the block-scaled tcgen05 kernel (`y_fp8_t`, the
+    byte-transposed weight, is built here when the caller has not cached it).  Other
+    grids follow the reference literally: dequantize both, then an fp32 matmul.
+    """
+    _require_cuda(x_fp8, "matmul_impl input")
+    if _tensor_core_eligible(x_fp8, y_fp8, block_grid_x, block_grid_y):
+        mm, kk = x_fp8.shape
+        nn = y_fp8.shape[1]
+        if y_fp8_t is None:
+            y_fp8_t = transpose_bytes(y_fp8)
+        x_fp8, x_sc8, x_sc32 = x_fp8.contiguous(), x_sc8.contiguous(), x_sc32.contiguous()
+        y_sc8, y_sc32 = y_sc8.contiguous(), y_sc32.contiguous()
+        a = _operand(x_fp8, x_sc8, x_sc32, mm, kk, (1, 128))
+        b = _operand(y_fp8_t, y_sc8, y_sc32, nn, kk, (128, 128), transposed_blocks=1)
+        return gemm_tn(a, b, out_dtype, x_fp8.device)
+    x = dequantize_impl(x_fp8, x_sc8, x_sc32, torch.float32, block_grid_x)
+    y = dequantize_impl(y_fp8, y_sc8, y_sc32, torch.float32, block_grid_y)
+    return _matmul_f32(x, y).to(out_dtype)
+
+
+def _matmul_f32(x, y):
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        return torch.matmul(x, y)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def matmul_mixed_impl(x_fp8, x_sc8, x_sc32, y_f32, block_grid_x):
+    """_qarr.py:645-647."""
+    x = dequantize_impl(x_fp8, x_sc8, x_sc32, torch.float32, block_grid_x)
+    return _matmul_f32(x, y_f32.to(torch.float32))
+
+
+def rmatmul_mixed_impl(x_f32, y_fp8, y_sc8, y_sc32, block_grid_y):
+    """_qarr.py:680-682."""
+    y = dequantize_impl(y_fp8, y_sc8, y_sc32, torch.float32, block_grid_y)
+    return _matmul_f32(x_f32.to(torch.float32), y)
+
+
+def make_elementwise_impl(op):
+    """_qarr.py:715-720: dequantize both operands on the same grid, apply `op`, f32 out."""
+    def impl(x_fp8, x_sc8, x_sc32, y_fp8, y_sc8, y_sc32, tgrid):
+        x = dequantize_impl(x_fp8, x_sc8, x_sc32, torch.float32, tgrid)
+        y = dequantize_impl(y_fp8, y_sc8, y_sc32, torch.float32, tgrid)
+        return op(x, y)
+    return impl
+
+
+add_impl = make_elementwise_impl(torch.add)
+mul_impl = make_elementwise_impl(torch.mul)
+sub_impl = make_elementwise_impl(torch.sub)
+truediv_impl = make_elementwise_impl(torch.div)
+floordiv_impl = make_elementwise_impl(torch.floor_divide)
+mod_impl = make_elementwise_impl(torch.remainder)
+pow_impl = make_elementwise_impl(torch.pow)

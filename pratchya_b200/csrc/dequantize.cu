@@ -1,0 +1,145 @@
+// Dequantizer and its cotangent (sm_100a).
+// Replace dequantize_impl / dequantize_impl_bwd, pratchya/_qualia/_qarr.py:541-601:
+//   out = f32(bf16(q)) * (f32(sc8 << 23) * sc32) / 128      (no 1e-7 floor on this side)
+// Pure streaming: each thread converts 16 (or 1) consecutive elements of a row.
+#include "common.cuh"
+
+namespace pb {
+namespace {
+
+struct DqDims {
+  VecIndexer idx;
+  FastDiv by_K;
+  uint32_t total_vecs;
+};
+
+__device__ __forceinline__ float block_multiplier(const DqDims& d, const uint8_t* __restrict__ sc8,
+                                                  const float* __restrict__ sc32, uint32_t i) {
+  const uint32_t blk = d.idx.block_of(i);
+  // f32(sc8 << 23) * sc32, _qarr.py:562-563.  blk / K indexes sc32 across the batch because Nb = M*K.
+  return __fmul_rn(e8m0_to_f32(__ldg(sc8 + blk)), __ldg(sc32 + d.by_K.div(blk)));
+}
+
+// (v * x_sc) / 128 with the reference's association, _qarr.py:564 and :597
+__device__ __forceinline__ float apply_scale(float v, float x_sc) { return __fmul_rn(__fmul_rn(v, x_sc), 0.0078125f); }
+
+template <typename OutT> __device__ __forceinline__ void store16(OutT* p, const float (&v)[16]);
+template <> __device__ __forceinline__ void store16<float>(float* p, const float (&v)[16]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) __stcs(reinterpret_cast<float4*>(p) + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+}
+template <> __device__ __forceinline__ void store16<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[16]) {
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+    __stcs(reinterpret_cast<uint4*>(p) + j, make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
+                                                        pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7])));
+}
+
+template <typename OutT, int FMT, int VEC>
+__global__ void __launch_bounds__(256)
+dequantize_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sc8, const float* __restrict__ sc32,
+                  OutT* __restrict__ out, DqDims d) {
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < d.total_vecs; i += stride) {
+    const float x_sc = block_multiplier(d, sc8, sc32, i);
+    if constexpr (VEC == 16) {
+      const uint4 w = __ldcs(reinterpret_cast<const uint4*>(q) + i);
+      const uint32_t in[4] = {w.x, w.y, w.z, w.w};
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 lo = fp8x2_to_f32x2<FMT>((uint16_t)(in[j] & 0xffffu));
+        const float2 hi = fp8x2_to_f32x2<FMT>((uint16_t)(in[j] >> 16));
+        v[4 * j + 0] = apply_scale(lo.x, x_sc); v[4 * j + 1] = apply_scale(lo.y, x_sc);
+        v[4 * j + 2] = apply_scale(hi.x, x_sc); v[4 * j + 3] = apply_scale(hi.y, x_sc);
+      }
+      store16<OutT>(out + (size_t)i * 16, v);
+    } else {
+      const float2 f = fp8x2_to_f32x2<FMT>((uint16_t)q[i]);
+      out[i] = Elem<OutT>::from_f32(apply_scale(f.x, x_sc));
+    }
+  }
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256)
+dequantize_bwd_kernel(const T* __restrict__ g, const uint8_t* __restrict__ sc8, const float* __restrict__ sc32,
+                      T* __restrict__ out, DqDims d) {
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < d.total_vecs; i += stride) {
+    const float x_sc = block_multiplier(d, sc8, sc32, i);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j)
+      out[(size_t)i * VEC + j] = Elem<T>::from_f32(apply_scale(Elem<T>::to_f32(g[(size_t)i * VEC + j]), x_sc));
+  }
+}
+
+int dq_grid(int64_t vecs) {
+  const int64_t need = (vecs + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  return (int)(need < cap ? (need > 0 ? need : 1) : cap);
+}
+
+template <typename OutT, int FMT>
+int launch_dq(const uint8_t* q, const uint8_t* sc8, const float* sc32, OutT* out, const Geometry& g, int64_t batch, cudaStream_t st) {
+  const int64_t total = batch * g.rows * g.cols;
+  const bool vec16 = (g.b % 16 == 0) && (reinterpret_cast<uintptr_t>(q) % 16 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0);
+  const int vec = vec16 ? 16 : 1;
+  if (total / vec > kMaxIndexed || batch * g.rows > kMaxIndexed)
+    return fail(PB_ERR_UNSUPPORTED, "pb_dequantize: %lld elements exceed the 31-bit index range of this kernel", (long long)total);
+  DqDims d{VecIndexer(g.cols, g.a, g.b, vec), FastDiv((uint32_t)g.K), (uint32_t)(total / vec)};
+  if (vec16) dequantize_kernel<OutT, FMT, 16><<<dq_grid(d.total_vecs), 256, 0, st>>>(q, sc8, sc32, out, d);
+  else       dequantize_kernel<OutT, FMT, 1><<<dq_grid(d.total_vecs), 256, 0, st>>>(q, sc8, sc32, out, d);
+  PB_LAUNCH_CHECK("dequantize_kernel");
+  return PB_OK;
+}
+
+}  // namespace
+}  // namespace pb
+
+using namespace pb;
+
+extern "C" int pb_dequantize(const void* q, int q_format, const uint8_t* sc8, const float* sc32,
+                             int64_t batch, int64_t rows, int64_t cols, int a, int b,
+                             int out_dtype, void* out, void* stream) {
+  if (!q || !sc8 || !sc32 || !out) return fail(PB_ERR_NULL_POINTER, "pb_dequantize: q, sc8, sc32 and out must be non-null");
+  if (batch <= 0) return fail(PB_ERR_BAD_SHAPE, "pb_dequantize: batch=%lld must be positive", (long long)batch);
+  if (q_format != PB_E4M3 && q_format != PB_E5M2) return fail(PB_ERR_BAD_DTYPE, "pb_dequantize: q_format %d is neither PB_E4M3 nor PB_E5M2", q_format);
+  if (out_dtype != PB_F32 && out_dtype != PB_BF16) return fail(PB_ERR_BAD_DTYPE, "pb_dequantize: out_dtype %d is neither PB_F32 nor PB_BF16", out_dtype);
+  Geometry g;
+  if (int s = make_geometry(rows, cols, a, b, &g)) return s;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint8_t* qb = static_cast<const uint8_t*>(q);
+  if (out_dtype == PB_F32)
+    return q_format == PB_E4M3 ? launch_dq<float, PB_E4M3>(qb, sc8, sc32, (float*)out, g, batch, st)
+                               : launch_dq<float, PB_E5M2>(qb, sc8, sc32, (float*)out, g, batch, st);
+  return q_format == PB_E4M3 ? launch_dq<__nv_bfloat16, PB_E4M3>(qb, sc8, sc32, (__nv_bfloat16*)out, g, batch, st)
+                             : launch_dq<__nv_bfloat16, PB_E5M2>(qb, sc8, sc32, (__nv_bfloat16*)out, g, batch, st);
+}
+
+extern "C" int pb_dequantize_bwd(const void* gin, int dtype, const uint8_t* sc8, const float* sc32,
+                                 int64_t batch, int64_t rows, int64_t cols, int a, int b,
+                                 void* out, void* stream) {
+  if (!gin || !sc8 || !sc32 || !out) return fail(PB_ERR_NULL_POINTER, "pb_dequantize_bwd: g, sc8, sc32 and out must be non-null");
+  if (batch <= 0) return fail(PB_ERR_BAD_SHAPE, "pb_dequantize_bwd: batch=%lld must be positive", (long long)batch);
+  if (dtype != PB_F32 && dtype != PB_BF16) return fail(PB_ERR_BAD_DTYPE, "pb_dequantize_bwd: dtype %d is neither PB_F32 nor PB_BF16", dtype);
+  Geometry g;
+  if (int s = make_geometry(rows, cols, a, b, &g)) return s;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t total = batch * rows * cols;
+  const bool vec4 = (b % 4 == 0);
+  const int vec = vec4 ? 4 : 1;
+  if (total / vec > kMaxIndexed || batch * g.rows > kMaxIndexed)
+    return fail(PB_ERR_UNSUPPORTED, "pb_dequantize_bwd: %lld elements exceed the 31-bit index range of this kernel", (long long)total);
+  DqDims d{VecIndexer(g.cols, g.a, g.b, vec), FastDiv((uint32_t)g.K), (uint32_t)(total / vec)};
+  const int grid = dq_grid(d.total_vecs);
+  if (dtype == PB_F32) {
+    if (vec4) dequantize_bwd_kernel<float, 4><<<grid, 256, 0, st>>>((const float*)gin, sc8, sc32, (float*)out, d);
+    else      dequantize_bwd_kernel<float, 1><<<grid, 256, 0, st>>>((const float*)gin, sc8, sc32, (float*)out, d);
+  } else {
+    if (vec4) dequantize_bwd_kernel<__nv_bfloat16, 4><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gin, sc8, sc32, (__nv_bfloat16*)out, d);
+    else      dequantize_bwd_kernel<__nv_bfloat16, 1><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gin, sc8, sc32, (__nv_bfloat16*)out, d);
+  }
+  PB_LAUNCH_CHECK("dequantize_bwd_kernel");
+  return PB_OK;
+}

@@ -1,0 +1,347 @@
+// Block quantizers (sm_100a).  Replace quantize_impl, pratchya/_qualia/_qarr.py:458-506.
+//
+// Two implementations, identical results:
+//   * row128: grid (1,128) with 8-block super-groups.  With a == 1 the row-major
+//     block order is the memory order, so a super-group is 1024 contiguous
+//     elements; one warp owns one super-group, keeps it in registers between the
+//     amax pass and the cast, and touches HBM once (read x, write q + scales).
+//     No scratch memory.
+//   * generic: any grid.  Three small kernels around a scratch buffer
+//     (per-block amax bits, then per-block divisors).
+#include "common.cuh"
+
+namespace pb {
+namespace {
+
+constexpr int kRowThreads = 256;
+constexpr int kGroupElems = 1024;   // 8 blocks x 128
+
+// ---------------------------------------------------------------------------------
+// Butterfly max-reduction of N per-lane values (N a power of two).  After the call
+// v[0] of a lane holds the maximum, over the 2^(log2 N + EXTRA) lanes that differ
+// from it in those low lane bits, of the value with index bitrev(lane's low log2 N bits).
+// Costs N-1+EXTRA shuffles instead of N*(log2 N + EXTRA).
+template <int N, int EXTRA>
+__device__ __forceinline__ void butterfly_max(float (&v)[N], int lane) {
+  int mask = 1;
+#pragma unroll
+  for (int n = N; n > 1; n >>= 1, mask <<= 1) {
+    const bool upper = (lane & mask) != 0;
+#pragma unroll
+    for (int i = 0; i < n / 2; ++i) {
+      const float keep = upper ? v[i + n / 2] : v[i];
+      const float send = upper ? v[i] : v[i + n / 2];
+      v[i] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, mask));
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < EXTRA; ++s, mask <<= 1) v[0] = fmaxf(v[0], __shfl_xor_sync(0xffffffffu, v[0], mask));
+}
+
+template <int BITS>
+__device__ __forceinline__ int bitrev(int x) {
+  int r = 0;
+#pragma unroll
+  for (int i = 0; i < BITS; ++i) r |= ((x >> i) & 1) << (BITS - 1 - i);
+  return r;
+}
+
+// ---------------------------------------------------------------------------------
+// bf16 input: lane l, load it -> 8 elements at (it*32 + l)*8; block = 2*it + (l >> 4).
+template <int FMT>
+__global__ void __launch_bounds__(kRowThreads)
+quantize_row128_bf16_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
+                            uint8_t* __restrict__ sc8, float* __restrict__ sc32, int64_t n_groups) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (int64_t)gridDim.x * (kRowThreads / 32);
+  for (int64_t g = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); g < n_groups; g += warps_total) {
+    const uint4* src = x + g * (kGroupElems / 8);
+    uint4 w[4];
+#pragma unroll
+    for (int it = 0; it < 4; ++it) w[it] = __ldcs(src + it * 32 + lane);
+
+    // per-load amax in the bf16 domain (exact), widened to f32
+    float m[4];
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const uint32_t a0 = w[it].x & 0x7fff7fffu, a1 = w[it].y & 0x7fff7fffu;
+      const uint32_t a2 = w[it].z & 0x7fff7fffu, a3 = w[it].w & 0x7fff7fffu;
+      __nv_bfloat162 h = __hmax2(__hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a0),
+                                         *reinterpret_cast<const __nv_bfloat162*>(&a1)),
+                                 __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a2),
+                                         *reinterpret_cast<const __nv_bfloat162*>(&a3)));
+      const uint32_t hb = *reinterpret_cast<const uint32_t*>(&h);
+      m[it] = fmaxf(__uint_as_float(hb << 16), __uint_as_float(hb & 0xffff0000u));
+    }
+    butterfly_max<4, 2>(m, lane);                 // m[0]: amax of block (it_own, half)
+    const int it_own = bitrev<2>(lane & 3);
+    float Mj = m[0];
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 1));
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 2));
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 16));
+
+    uint32_t sb; float D;
+    block_scale(m[0], Mj, sb, D);
+    const float r = __frcp_rn(D);
+    if ((lane & 12) == 0) sc8[g * 8 + 2 * it_own + (lane >> 4)] = (uint8_t)sb;
+    if (lane == 0) sc32[g] = Mj;
+
+    uint2* dst = q + g * (kGroupElems / 8);
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int srcl = (lane & 16) | bitrev<2>(it);
+      const float Di = __shfl_sync(0xffffffffu, D, srcl);
+      const float ri = __shfl_sync(0xffffffffu, r, srcl);
+      const uint32_t in[4] = {w[it].x, w[it].y, w[it].z, w[it].w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = div_hoisted_unsigned(__uint_as_float(in[j] << 16), Di, ri);
+        const float hi = div_hoisted_unsigned(__uint_as_float(in[j] & 0xffff0000u), Di, ri);
+        // sign of the input (also for -0) re-applied on the packed bf16 pair
+        const uint32_t p = (pack_bf16x2(lo, hi) & 0x7fff7fffu) | (in[j] & 0x80008000u);
+        o[j] = bf16x2_to_fp8x2<FMT>(p);
+      }
+      __stcs(dst + it * 32 + lane, make_uint2(o[0] | (o[1] << 16), o[2] | (o[3] << 16)));
+    }
+  }
+}
+
+// f32 input: lane l, load it -> 4 elements at (it*32 + l)*4; block = it.
+template <int FMT>
+__global__ void __launch_bounds__(kRowThreads)
+quantize_row128_f32_kernel(const float4* __restrict__ x, uint32_t* __restrict__ q,
+                           uint8_t* __restrict__ sc8, float* __restrict__ sc32, int64_t n_groups) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (int64_t)gridDim.x * (kRowThreads / 32);
+  for (int64_t g = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); g < n_groups; g += warps_total) {
+    const float4* src = x + g * (kGroupElems / 4);
+    float4 w[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) w[it] = __ldcs(src + it * 32 + lane);
+    float m[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it)
+      m[it] = fmaxf(fmaxf(fabsf(w[it].x), fabsf(w[it].y)), fmaxf(fabsf(w[it].z), fabsf(w[it].w)));
+    butterfly_max<8, 2>(m, lane);                 // m[0]: amax of block it_own over the warp
+    const int it_own = bitrev<3>(lane & 7);
+    float Mj = m[0];
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 1));
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 2));
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 4));
+
+    uint32_t sb; float D;
+    block_scale(m[0], Mj, sb, D);
+    const float r = __frcp_rn(D);
+    if (lane < 8) sc8[g * 8 + it_own] = (uint8_t)sb;
+    if (lane == 0) sc32[g] = Mj;
+
+    uint32_t* dst = q + g * (kGroupElems / 4);
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int srcl = bitrev<3>(it);
+      const float Di = __shfl_sync(0xffffffffu, D, srcl);
+      const float ri = __shfl_sync(0xffffffffu, r, srcl);
+      const uint32_t p0 = pack_bf16x2(div_hoisted(w[it].x, Di, ri), div_hoisted(w[it].y, Di, ri));
+      const uint32_t p1 = pack_bf16x2(div_hoisted(w[it].z, Di, ri), div_hoisted(w[it].w, Di, ri));
+      __stcs(dst + it * 32 + lane, bf16x2_to_fp8x2<FMT>(p0) | (bf16x2_to_fp8x2<FMT>(p1) << 16));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Generic path.  Scratch layout: uint32 amax_bits[batch*Nb] | float divisor[batch*Nb].
+struct GenericDims {
+  VecIndexer idx;
+  uint32_t total_vecs;
+};
+
+template <typename InT, int VEC>
+__device__ __forceinline__ void load_vec(const InT* p, float (&v)[VEC]) {
+  if constexpr (VEC == 1) {
+    v[0] = Elem<InT>::to_f32(p[0]);
+  } else if constexpr (sizeof(InT) == 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+  }
+}
+
+template <typename InT, int VEC>
+__global__ void __launch_bounds__(256)
+generic_amax_kernel(const InT* __restrict__ x, uint32_t* __restrict__ amax_bits, GenericDims d) {
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; ; i += stride) {
+    // whole warps leave together: lane 0 holds the warp's smallest index
+    const bool active = i < d.total_vecs;
+    if (__all_sync(0xffffffffu, !active)) break;
+    uint32_t bits = 0;
+    uint32_t blk = 0xffffffffu;
+    if (active) {
+      float v[VEC];
+      load_vec<InT, VEC>(x + (size_t)i * VEC, v);
+      float m = fabsf(v[0]);
+#pragma unroll
+      for (int j = 1; j < VEC; ++j) m = fmaxf(m, fabsf(v[j]));
+      bits = __float_as_uint(m);          // non-negative floats order like unsigned ints
+      blk = d.idx.block_of(i);
+    }
+    const uint32_t blk0 = __shfl_sync(0xffffffffu, blk, 0);
+    if (__all_sync(0xffffffffu, blk == blk0)) {
+      const uint32_t mx = __reduce_max_sync(0xffffffffu, bits);
+      if ((threadIdx.x & 31) == 0) atomicMax(amax_bits + blk0, mx);
+    } else if (active) {
+      atomicMax(amax_bits + blk, bits);
+    }
+  }
+}
+
+// One warp per super-group when K >= 32, else one thread per super-group.
+template <bool WARP_PER_GROUP>
+__global__ void __launch_bounds__(256)
+generic_scale_kernel(const uint32_t* __restrict__ amax_bits, float* __restrict__ divisor,
+                     uint8_t* __restrict__ sc8, float* __restrict__ sc32, int64_t n_groups, int64_t K) {
+  if constexpr (WARP_PER_GROUP) {
+    const int lane = threadIdx.x & 31;
+    const int64_t g = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (g >= n_groups) return;
+    float Mj = 0.0f;
+    for (int64_t k = lane; k < K; k += 32) Mj = fmaxf(Mj, __uint_as_float(amax_bits[g * K + k]));
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, s));
+    for (int64_t k = lane; k < K; k += 32) {
+      uint32_t sb; float D;
+      block_scale(__uint_as_float(amax_bits[g * K + k]), Mj, sb, D);
+      sc8[g * K + k] = (uint8_t)sb;
+      divisor[g * K + k] = D;
+    }
+    if (lane == 0) sc32[g] = Mj;
+  } else {
+    const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= n_groups) return;
+    float Mj = 0.0f;
+    for (int64_t k = 0; k < K; ++k) Mj = fmaxf(Mj, __uint_as_float(amax_bits[g * K + k]));
+    for (int64_t k = 0; k < K; ++k) {
+      uint32_t sb; float D;
+      block_scale(__uint_as_float(amax_bits[g * K + k]), Mj, sb, D);
+      sc8[g * K + k] = (uint8_t)sb;
+      divisor[g * K + k] = D;
+    }
+    sc32[g] = Mj;
+  }
+}
+
+template <typename InT, int VEC, int FMT>
+__global__ void __launch_bounds__(256)
+generic_apply_kernel(const InT* __restrict__ x, const float* __restrict__ divisor,
+                     uint8_t* __restrict__ q, GenericDims d) {
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < d.total_vecs; i += stride) {
+    float v[VEC];
+    load_vec<InT, VEC>(x + (size_t)i * VEC, v);
+    const float D = divisor[d.idx.block_of(i)];
+    const float r = __frcp_rn(D);
+    if constexpr (VEC == 1) {
+      const uint32_t p = pack_bf16x2(div_hoisted(v[0], D, r), 0.0f);
+      q[i] = (uint8_t)(bf16x2_to_fp8x2<FMT>(p) & 0xffu);
+    } else {
+      const uint32_t p0 = pack_bf16x2(div_hoisted(v[0], D, r), div_hoisted(v[1], D, r));
+      const uint32_t p1 = pack_bf16x2(div_hoisted(v[2], D, r), div_hoisted(v[3], D, r));
+      reinterpret_cast<uint32_t*>(q)[i] = bf16x2_to_fp8x2<FMT>(p0) | (bf16x2_to_fp8x2<FMT>(p1) << 16);
+    }
+  }
+}
+
+int grid_for(int64_t work_items, int threads, int ctas_per_sm) {
+  const int64_t need = (work_items + threads - 1) / threads;
+  const int64_t cap = (int64_t)sm_count() * ctas_per_sm;
+  return (int)(need < cap ? (need > 0 ? need : 1) : cap);
+}
+
+template <typename InT, int VEC>
+int launch_generic(const InT* x, const Geometry& g, int64_t batch, int fmt, uint8_t* q, uint8_t* sc8, float* sc32,
+                   void* workspace, cudaStream_t st) {
+  const int64_t nblk = batch * g.Nb;
+  uint32_t* amax_bits = static_cast<uint32_t*>(workspace);
+  float* divisor = reinterpret_cast<float*>(amax_bits + nblk);
+  const int64_t total = batch * g.rows * g.cols;
+  if (total / VEC > kMaxIndexed || batch * g.rows > kMaxIndexed)
+    return fail(PB_ERR_UNSUPPORTED, "pb_quantize: %lld elements exceed the 31-bit index range of the generic kernels", (long long)total);
+  GenericDims d{VecIndexer(g.cols, g.a, g.b, VEC), (uint32_t)(total / VEC)};
+  PB_CUDA_TRY(cudaMemsetAsync(amax_bits, 0, nblk * sizeof(uint32_t), st));
+  const int grid = grid_for(d.total_vecs, 256, 8);
+  generic_amax_kernel<InT, VEC><<<grid, 256, 0, st>>>(x, amax_bits, d);
+  PB_LAUNCH_CHECK("generic_amax_kernel");
+  const int64_t n_groups = batch * g.M;
+  if (g.K >= 32) {
+    generic_scale_kernel<true><<<(unsigned)((n_groups * 32 + 255) / 256), 256, 0, st>>>(amax_bits, divisor, sc8, sc32, n_groups, g.K);
+  } else {
+    generic_scale_kernel<false><<<(unsigned)((n_groups + 255) / 256), 256, 0, st>>>(amax_bits, divisor, sc8, sc32, n_groups, g.K);
+  }
+  PB_LAUNCH_CHECK("generic_scale_kernel");
+  if (fmt == PB_E4M3) generic_apply_kernel<InT, VEC, PB_E4M3><<<grid, 256, 0, st>>>(x, divisor, q, d);
+  else                generic_apply_kernel<InT, VEC, PB_E5M2><<<grid, 256, 0, st>>>(x, divisor, q, d);
+  PB_LAUNCH_CHECK("generic_apply_kernel");
+  return PB_OK;
+}
+
+bool row128_eligible(const Geometry& g) { return g.a == 1 && g.b == 128 && g.K == 8; }
+
+}  // namespace
+}  // namespace pb
+
+using namespace pb;
+
+extern "C" size_t pb_quantize_workspace_size(int64_t batch, int64_t rows, int64_t cols, int a, int b) {
+  Geometry g;
+  if (batch <= 0 || make_geometry(rows, cols, a, b, &g) != PB_OK) return 0;
+  if (row128_eligible(g)) return 0;
+  return (size_t)(batch * g.Nb) * 8;
+}
+
+extern "C" int pb_quantize(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols,
+                           int a, int b, int out_format, void* q, uint8_t* sc8, float* sc32,
+                           void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !q || !sc8 || !sc32) return fail(PB_ERR_NULL_POINTER, "pb_quantize: x, q, sc8 and sc32 must be non-null");
+  if (batch <= 0) return fail(PB_ERR_BAD_SHAPE, "pb_quantize: batch=%lld must be positive", (long long)batch);
+  if (x_dtype != PB_F32 && x_dtype != PB_BF16) return fail(PB_ERR_BAD_DTYPE, "pb_quantize: x_dtype %d is neither PB_F32 nor PB_BF16", x_dtype);
+  if (out_format != PB_E4M3 && out_format != PB_E5M2) return fail(PB_ERR_BAD_DTYPE, "pb_quantize: out_format %d is neither PB_E4M3 nor PB_E5M2", out_format);
+  Geometry g;
+  if (int s = make_geometry(rows, cols, a, b, &g)) return s;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  if (row128_eligible(g)) {
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7))
+      return fail(PB_ERR_MISALIGNED, "pb_quantize: x must be 16-byte and q 8-byte aligned");
+    const int64_t n_groups = batch * g.M;
+    const int grid = grid_for(n_groups * 32, kRowThreads, 8);
+    if (x_dtype == PB_BF16) {
+      if (out_format == PB_E4M3)
+        quantize_row128_bf16_kernel<PB_E4M3><<<grid, kRowThreads, 0, st>>>((const uint4*)x, (uint2*)q, sc8, sc32, n_groups);
+      else
+        quantize_row128_bf16_kernel<PB_E5M2><<<grid, kRowThreads, 0, st>>>((const uint4*)x, (uint2*)q, sc8, sc32, n_groups);
+    } else {
+      if (out_format == PB_E4M3)
+        quantize_row128_f32_kernel<PB_E4M3><<<grid, kRowThreads, 0, st>>>((const float4*)x, (uint32_t*)q, sc8, sc32, n_groups);
+      else
+        quantize_row128_f32_kernel<PB_E5M2><<<grid, kRowThreads, 0, st>>>((const float4*)x, (uint32_t*)q, sc8, sc32, n_groups);
+    }
+    PB_LAUNCH_CHECK("quantize_row128_kernel");
+    return PB_OK;
+  }
+
+  const size_t need = (size_t)(batch * g.Nb) * 8;
+  if (!workspace || workspace_bytes < need)
+    return fail(PB_ERR_WORKSPACE_TOO_SMALL, "pb_quantize: grid (%d,%d) needs %zu bytes of workspace, got %zu", a, b, need, workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) & 3) return fail(PB_ERR_MISALIGNED, "pb_quantize: workspace must be 4-byte aligned");
+  const bool vec4 = (b % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(q) % 4 == 0);
+  if (x_dtype == PB_BF16) {
+    return vec4 ? launch_generic<__nv_bfloat16, 4>((const __nv_bfloat16*)x, g, batch, out_format, (uint8_t*)q, sc8, sc32, workspace, st)
+                : launch_generic<__nv_bfloat16, 1>((const __nv_bfloat16*)x, g, batch, out_format, (uint8_t*)q, sc8, sc32, workspace, st);
+  }
+  return vec4 ? launch_generic<float, 4>((const float*)x, g, batch, out_format, (uint8_t*)q, sc8, sc32, workspace, st)
+              : launch_generic<float, 1>((const float*)x, g, batch, out_format, (uint8_t*)q, sc8, sc32, workspace, st);
+}

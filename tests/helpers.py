@@ -1,0 +1,58 @@
+"""Shared helpers of the parity tests (test infrastructure; may use oracle/)."""
+import ml_dtypes
+import numpy as np
+
+from oracle import qarr_oracle as oracle
+
+BF16 = ml_dtypes.bfloat16
+
+
+def synth(shape, seed, dist="normal", outliers=0.01, scale=1.0, dtype=np.float32):
+    """Seeded synthetic tensors with the value distributions of the benchmark configs:
+    N(0, scale^2) with a seeded fraction of entries multiplied by 64, or Student-t(3)."""
+    rng = np.random.default_rng(seed)
+    if dist == "student_t":
+        x = rng.standard_t(3, size=shape).astype(np.float32) * np.float32(scale)
+    else:
+        x = rng.standard_normal(shape).astype(np.float32) * np.float32(scale)
+    if outliers:
+        mask = rng.random(shape) < outliers
+        x = np.where(mask, x * np.float32(64.0), x).astype(np.float32)
+    return x.astype(dtype)
+
+
+def to_torch(x, device="cuda"):
+    import torch
+    if x.dtype == BF16:
+        return torch.from_numpy(x.view(np.uint16).copy()).view(torch.bfloat16).to(device)
+    return torch.from_numpy(np.ascontiguousarray(x)).to(device)
+
+
+def bytes_of(t):
+    """uint8 numpy view of a torch fp8/e8m0 tensor or an ml_dtypes array."""
+    import torch
+    if isinstance(t, torch.Tensor):
+        return t.contiguous().reshape(-1).view(torch.uint8).cpu().numpy().reshape(tuple(t.shape))
+    return np.ascontiguousarray(t).reshape(-1).view(np.uint8).reshape(np.shape(t))
+
+
+def from_torch(t):
+    import torch
+    if t.dtype == torch.bfloat16:
+        return t.contiguous().view(torch.uint16).cpu().numpy().view(BF16)
+    return t.cpu().numpy()
+
+
+def assert_triple_equal(got, want, what=""):
+    gq, g8, g32 = got
+    wq, w8, w32 = want
+    gq, wq = bytes_of(gq), bytes_of(wq)
+    assert gq.shape == wq.shape, f"{what}: value shape {gq.shape} vs {wq.shape}"
+    bad = np.flatnonzero(gq.reshape(-1) != wq.reshape(-1))
+    assert bad.size == 0, f"{what}: {bad.size} fp8 bytes differ, first at {bad[:5]}: got {gq.reshape(-1)[bad[:5]]} want {wq.reshape(-1)[bad[:5]]}"
+    g8, w8 = bytes_of(g8), bytes_of(w8)
+    assert g8.shape == w8.shape, f"{what}: sc8 shape {g8.shape} vs {w8.shape}"
+    assert np.array_equal(g8, w8), f"{what}: e8m0 bytes differ"
+    g32 = from_torch(g32) if not isinstance(g32, np.ndarray) else g32
+    assert g32.shape == w32.shape, f"{what}: sc32 shape {g32.shape} vs {w32.shape}"
+    assert np.array_equal(g32.view(np.uint32), w32.view(np.uint32)), f"{what}: fp32 scales differ"
