@@ -1,0 +1,591 @@
+// Block-scaled FP8 matmul for sm_100a: tcgen05.mma (kind::mxf8f6f4, block_scale) with TMEM
+// accumulators, operands staged by TMA, scale factors staged by bulk copies + tcgen05.cp.
+// Replaces the dequantize-then-f32-dot of matmul_impl / matmul_impl_bwd / fp8_matmul_bwd,
+// pratchya/_qualia/_qarr.py:605-642, :780-791.
+//
+// Scale algebra.  A quantized element is q * 2^(e-127) * M / 128 with e the block's e8m0
+// byte and M the fp32 amax of its super-group (_qarr.py:562-564).  The power-of-two part is
+// exactly what the tensor core's block scaling applies (one ue8m0 factor per row and 32-deep
+// K step; the byte of a 128-deep block is simply reused for its four K steps).  The fp32 part
+// is constant over aligned runs of P <= 8 k-blocks ("chunks") for every row of both
+// operands, so a chunk is accumulated in TMEM by the tensor core and then promoted into fp32
+// registers:  acc[m,n] += partial[m,n] * fA[m,chunk] * fB[n,chunk].
+//
+// One CTA per SM, persistent over output tiles, warp-specialised:
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocator + MMA issuer (one elected lane)
+//   warps 2..   epilogue: TMEM -> registers, chunk promotion, store of D
+// Every wait on an mbarrier is bounded; on expiry the kernel records PB_ERR_DEVICE_TIMEOUT in
+// a device status word, all roles leave their loops, TMEM is released and the kernel returns.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace pb {
+namespace {
+
+constexpr int BM = 128;        // rows of A per tile (TMEM lanes)
+constexpr int BK = 128;        // depth of one pipeline stage = one 128-byte swizzle row
+constexpr int UMMA_K = 32;     // depth of one tcgen05.mma for 8-bit operands
+constexpr int kMaxChunk = 8;   // k-blocks per promotion at most (1024-deep)
+constexpr uint32_t kTmemCols = 512;
+constexpr uint64_t kWaitBudgetNs = 2000000000ull;   // 2 s per wait before giving up
+
+template <int BN>
+struct Cfg {
+  static_assert(BN == 128 || BN == 256, "tile width");
+  static constexpr int kStages = BN == 128 ? 6 : 4;
+  static constexpr int kAccBufs = BN == 128 ? 2 : 1;
+  static constexpr int kEpiWarps = 4 * (BN / 128);
+  static constexpr int kThreads = 64 + 32 * kEpiWarps;
+  static constexpr int kABytes = BM * BK;
+  static constexpr int kBBytes = BN * BK;
+  static constexpr int kSfaBytes = 512;
+  static constexpr int kSfbBytes = 512 * (BN / 128);
+  static constexpr int kSfStage = kSfaBytes + kSfbBytes;
+  static constexpr int kStageTx = kABytes + kBBytes + kSfStage;
+  static constexpr int kSfCols = 4 + BN / 32;                    // TMEM columns of one scale-factor set
+  static constexpr int kSfColBase = kAccBufs * BN;
+  static constexpr int kOffB = kStages * kABytes;
+  static constexpr int kOffSf = kOffB + kStages * kBBytes;
+  static constexpr int kOffBar = kOffSf + kStages * kSfStage;
+  static constexpr int kNumBars = 2 * kStages + 2 * kAccBufs;
+  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;   // +1024: manual alignment slack
+};
+
+__device__ unsigned int g_gemm_status;   // 0, or PB_ERR_DEVICE_TIMEOUT once any bounded wait ran out
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false (and raises the abort flag) when the budget ran out or
+// another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitBudgetNs) {
+        *abort_flag = 1;
+        atomicExch(&g_gemm_status, (unsigned int)PB_ERR_DEVICE_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_block_scaled(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                    uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row groups
+// 1024 bytes apart.  Fields: start >> 4 at [0,14), LBO >> 4 at [16,30) (unused for swizzled
+// K-major, set to 1), SBO >> 4 at [32,46), descriptor version 1 at [46,48), layout 2 at [61,64).
+__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr & 0x3ffffu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Scale-factor atom: 32 rows of 16 bytes, no swizzle, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr & 0x3ffffu) >> 4) | ((uint64_t)(128 >> 4) << 32) | (1ull << 46);
+}
+// Instruction descriptor of kind::mxf8f6f4.block_scale: b_sf_id [4,6), a/b format [7,10)/[10,13)
+// (0 = e4m3, 1 = e5m2), both operands K-major (bits 15, 16 clear), N >> 3 at [17,23),
+// ue8m0 scales (bit 23), M >> 4 at [24,29), a_sf_id [29,31).
+__device__ __forceinline__ uint32_t instr_desc(int bn, int a_fmt, int b_fmt, uint32_t sf_id) {
+  return (sf_id << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(bn >> 3) << 17) | (1u << 23) |
+         ((uint32_t)(BM >> 4) << 24) | (sf_id << 29);
+}
+
+struct GemmParams {
+  const uint8_t* sfa;     // [KG][Mpad/128][512]
+  const uint8_t* sfb;     // [KG][Npad/128][512]
+  const float* fa;        // [nchunks][Mpad]
+  const float* fb;        // [nchunks][Npad]
+  void* d;
+  int64_t ldd;
+  int M, N, KB, P, nchunks;
+  int Mpad, Npad;
+  int tiles_m, tiles_n;
+  int a_fmt, b_fmt;
+  int d_dtype;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(Cfg<BN>::kThreads, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t s_a = s_base, s_b = s_base + C::kOffB, s_sf = s_base + C::kOffSf, s_bar = s_base + C::kOffBar;
+  auto bar_full = [&](int s) { return s_bar + 8u * s; };
+  auto bar_empty = [&](int s) { return s_bar + 8u * (C::kStages + s); };
+  auto bar_acc_full = [&](int b) { return s_bar + 8u * (2 * C::kStages + b); };
+  auto bar_acc_empty = [&](int b) { return s_bar + 8u * (2 * C::kStages + C::kAccBufs + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffBar + C::kNumBars * 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+    for (int b = 0; b < C::kAccBufs; ++b) { mbar_init(bar_acc_full(b), 1); mbar_init(bar_acc_empty(b), C::kEpiWarps); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;   // running stage counter across tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+        for (int kb = 0; kb < p.KB; ++kb, ++it) {
+          const int s = it % C::kStages;
+          if (!mbar_wait(bar_empty(s), ((it / C::kStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar_full(s), C::kStageTx);
+          tma_load_2d(s_a + s * C::kABytes, &map_a, kb * BK, m0, bar_full(s));
+          tma_load_2d(s_b + s * C::kBBytes, &map_b, kb * BK, n0, bar_full(s));
+          const int kg = kb >> 2;
+          bulk_load(s_sf + s * C::kSfStage, p.sfa + ((size_t)kg * (p.Mpad / 128) + m0 / 128) * 512, C::kSfaBytes, bar_full(s));
+          bulk_load(s_sf + s * C::kSfStage + C::kSfaBytes, p.sfb + ((size_t)kg * (p.Npad / 128) + n0 / 128) * 512, C::kSfbBytes, bar_full(s));
+        }
+      }
+      // Leave only when every copy this thread started has landed (bounded): the last
+      // kStages fills are the ones that can still be in flight.
+      const uint32_t issued = it;
+      for (uint32_t j = (issued > (uint32_t)C::kStages ? issued - C::kStages : 0); j < issued; ++j)
+        (void)mbar_wait(bar_full(j % C::kStages), (j / C::kStages) & 1u, abort_flag);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, g = 0;   // stage counter, chunk counter
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int c = 0; c < p.nchunks && ok; ++c, ++g) {
+          const int buf = g % C::kAccBufs;
+          if (!mbar_wait(bar_acc_empty(buf), ((g / C::kAccBufs) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * BN;
+          const int kb_end = min(p.KB, (c + 1) * p.P);
+          for (int kb = c * p.P; kb < kb_end; ++kb, ++it) {
+            const int s = it % C::kStages;
+            if (!mbar_wait(bar_full(s), (it / C::kStages) & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sf_col = tmem_base + C::kSfColBase + (it & 1u) * C::kSfCols;
+            const uint32_t sf_smem = s_sf + s * C::kSfStage;
+            tc_cp_sf(sf_col, sf_desc(sf_smem));
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j) tc_cp_sf(sf_col + 4 + 4 * j, sf_desc(sf_smem + C::kSfaBytes + 512 * j));
+            const uint32_t idesc = instr_desc(BN, p.a_fmt, p.b_fmt, (uint32_t)(kb & 3));
+            const uint64_t a_desc = operand_desc(s_a + s * C::kABytes);
+            const uint64_t b_desc = operand_desc(s_b + s * C::kBBytes);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              tc_mma_block_scaled(d_tmem, a_desc + (uint64_t)(k * UMMA_K >> 4), b_desc + (uint64_t)(k * UMMA_K >> 4), idesc,
+                                  sf_col, sf_col + 4, (kb > c * p.P || k > 0) ? 1u : 0u);
+            tc_commit(bar_empty(s));          // frees the stage once these MMAs have read it
+          }
+          if (ok) tc_commit(bar_acc_full(buf));   // chunk accumulated
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue
+    const int ew = warp - 2;
+    const int quarter = warp & 3;             // TMEM lanes this warp may touch
+    const int col_half = ew >> 2;             // which 128-column slice of the tile
+    const int row_in_tile = quarter * 32 + lane;
+    uint32_t g = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN + col_half * 128;
+      float acc[128];
+#pragma unroll
+      for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+      for (int c = 0; c < p.nchunks; ++c, ++g) {
+        const int buf = g % C::kAccBufs;
+        if (!mbar_wait(bar_acc_full(buf), (g / C::kAccBufs) & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const float fa = __ldg(p.fa + (size_t)c * p.Mpad + m0 + row_in_tile);
+        const float4* fb4 = reinterpret_cast<const float4*>(p.fb + (size_t)c * p.Npad + n0);
+        const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + col_half * 128;
+#pragma unroll
+        for (int part = 0; part < 4; ++part) {
+          uint32_t r[32];
+          tc_ld32(t_addr + part * 32, r);
+          tc_wait_ld();
+          if (part == 3) {
+            // all of this warp's reads of the buffer are done: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty(buf));
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 fb = __ldg(fb4 + part * 8 + j);
+            acc[part * 32 + 4 * j + 0] = fmaf(__uint_as_float(r[4 * j + 0]) * fa, fb.x, acc[part * 32 + 4 * j + 0]);
+            acc[part * 32 + 4 * j + 1] = fmaf(__uint_as_float(r[4 * j + 1]) * fa, fb.y, acc[part * 32 + 4 * j + 1]);
+            acc[part * 32 + 4 * j + 2] = fmaf(__uint_as_float(r[4 * j + 2]) * fa, fb.z, acc[part * 32 + 4 * j + 2]);
+            acc[part * 32 + 4 * j + 3] = fmaf(__uint_as_float(r[4 * j + 3]) * fa, fb.w, acc[part * 32 + 4 * j + 3]);
+          }
+        }
+      }
+      if (!ok) break;
+      // store one row segment of 128 columns per thread
+      const int row = m0 + row_in_tile;
+      if (row < p.M) {
+        if (p.d_dtype == PB_BF16) {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.d) + (size_t)row * p.ldd + n0;
+          const bool vec = ((p.ldd & 7) == 0) && (n0 + 128 <= p.N) && ((reinterpret_cast<uintptr_t>(p.d) & 15) == 0);
+          if (vec) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              *reinterpret_cast<uint4*>(dst + 8 * j) =
+                  make_uint4(pack_bf16x2(acc[8 * j], acc[8 * j + 1]), pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3]),
+                             pack_bf16x2(acc[8 * j + 4], acc[8 * j + 5]), pack_bf16x2(acc[8 * j + 6], acc[8 * j + 7]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 128; ++j)
+              if (n0 + j < p.N) dst[j] = __float2bfloat16_rn(acc[j]);
+          }
+        } else {
+          float* dst = static_cast<float*>(p.d) + (size_t)row * p.ldd + n0;
+          const bool vec = ((p.ldd & 3) == 0) && (n0 + 128 <= p.N) && ((reinterpret_cast<uintptr_t>(p.d) & 15) == 0);
+          if (vec) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              *reinterpret_cast<float4*>(dst + 4 * j) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 128; ++j)
+              if (n0 + j < p.N) dst[j] = acc[j];
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- scale preparation -----------------------------------------------------------------------
+// Rewrites one operand's (sc8, sc32) into what the main kernel consumes:
+//   sf[kg][row/128][ (row%32)*16 + ((row%128)/32)*4 + kb%4 ]   e8m0 byte of (row, kb), kg = kb/4
+//   f[chunk][row] = sc32[group of (row, chunk*P)] / 128
+struct PrepParams {
+  const uint8_t* sc8;
+  const float* sc32;
+  uint8_t* sf;
+  float* f;
+  int rows, rows_pad, KB, KG, P, nchunks;
+  int grid_a;        // 1 or 128: rows per block
+  int transposed;    // blocks numbered on the [depth, rows] view
+  int64_t Ksg;       // blocks per super-group
+};
+
+__device__ __forceinline__ int64_t flat_block(const PrepParams& q, int r, int kb) {
+  return q.transposed ? (int64_t)kb * (q.rows / 128) + r / 128 : (int64_t)(r / q.grid_a) * q.KB + kb;
+}
+
+__global__ void __launch_bounds__(256) gemm_prep_kernel(PrepParams q) {
+  const int64_t n_sf = (int64_t)q.rows_pad * q.KG * 4;
+  const int64_t n_f = (int64_t)q.rows_pad * q.nchunks;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_sf + n_f; i += stride) {
+    if (i < n_sf) {
+      // i enumerates the destination bytes in order: kg, row tile, then the 512-byte atom
+      const int within = (int)(i & 511);
+      const int64_t atom = i >> 9;
+      const int rt = (int)(atom % (q.rows_pad / 128)), kg = (int)(atom / (q.rows_pad / 128));
+      const int r = rt * 128 + ((within >> 2) & 3) * 32 + (within >> 4);
+      const int kb = kg * 4 + (within & 3);
+      uint8_t v = 0;
+      if (r < q.rows && kb < q.KB) v = q.sc8[flat_block(q, r, kb)];
+      q.sf[i] = v;
+    } else {
+      const int64_t j = i - n_sf;
+      const int r = (int)(j % q.rows_pad), c = (int)(j / q.rows_pad);
+      float v = 0.0f;
+      if (r < q.rows) v = q.sc32[flat_block(q, r, c * q.P) / q.Ksg] * 0.0078125f;
+      q.f[j] = v;
+    }
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static std::mutex mu;
+  static EncodeTiledFn fn = nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+int make_operand_map(CUtensorMap* map, const void* q, int64_t rows, int64_t depth, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {(cuuint64_t)depth, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)depth};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(q), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return PB_OK;
+}
+
+struct OperandPlan {
+  int64_t Ksg, Mgroups;
+  int P;      // largest run of k-blocks with a constant fp32 factor for every row
+};
+
+int plan_operand(const pb_operand* o, const char* name, OperandPlan* plan) {
+  if (!o->q || !o->sc8 || !o->sc32) return fail(PB_ERR_NULL_POINTER, "pb_gemm_tn: operand %s has a null pointer", name);
+  if (o->rows <= 0 || o->depth <= 0 || o->depth % BK != 0)
+    return fail(PB_ERR_BAD_SHAPE, "pb_gemm_tn: operand %s is [%lld, %lld]; depth must be a positive multiple of 128", name,
+                (long long)o->rows, (long long)o->depth);
+  if (!((o->grid_a == 1 || o->grid_a == 128) && o->grid_b == 128))
+    return fail(PB_ERR_BAD_GRID, "pb_gemm_tn: operand %s grid (%d,%d) is neither (1,128) nor (128,128)", name, o->grid_a, o->grid_b);
+  if (o->format != PB_E4M3 && o->format != PB_E5M2) return fail(PB_ERR_BAD_DTYPE, "pb_gemm_tn: operand %s format %d", name, o->format);
+  if (o->grid_a == 128 && o->rows % 128 != 0)
+    return fail(PB_ERR_BAD_SHAPE, "pb_gemm_tn: operand %s rows=%lld not divisible by its 128-row blocks", name, (long long)o->rows);
+  if (o->transposed_blocks && o->grid_a != 128)
+    return fail(PB_ERR_BAD_GRID, "pb_gemm_tn: operand %s: transposed_blocks needs a (128,128) grid", name);
+  if (reinterpret_cast<uintptr_t>(o->q) & 15) return fail(PB_ERR_MISALIGNED, "pb_gemm_tn: operand %s bytes must be 16-byte aligned", name);
+  if (o->rows > (1ll << 30) || o->depth > (1ll << 30)) return fail(PB_ERR_UNSUPPORTED, "pb_gemm_tn: operand %s is too large", name);
+  Geometry g;
+  // the scales were produced on the [rows, depth] view, or on its transpose
+  const int s = o->transposed_blocks ? make_geometry(o->depth, o->rows, 128, 128, &g) : make_geometry(o->rows, o->depth, o->grid_a, 128, &g);
+  if (s) return s;
+  plan->Ksg = g.K;
+  plan->Mgroups = g.M;
+  const int64_t KB = o->depth / BK;
+  int P = kMaxChunk;
+  if (g.M > 1) {
+    if (!o->transposed_blocks) {
+      P = (int)std::gcd((int64_t)kMaxChunk, std::gcd(g.K, KB));
+    } else {
+      const int64_t nbc = o->rows / 128;
+      P = 1;
+      for (int c = kMaxChunk; c > 1; c >>= 1)
+        if (g.K % (c * nbc) == 0) { P = c; break; }
+    }
+  }
+  plan->P = P;
+  return PB_OK;
+}
+
+struct GemmPlan {
+  OperandPlan pa, pb;
+  int P, KB, KG, nchunks, Mpad, Npad, BN;
+  size_t off_sfa, off_sfb, off_fa, off_fb, total;
+};
+
+int pick_bn() {
+  static int bn = [] {
+    const char* e = getenv("PB_GEMM_BN");
+    const int v = e ? atoi(e) : 128;
+    return v == 256 ? 256 : 128;
+  }();
+  return bn;
+}
+
+int make_plan(const pb_operand* a, const pb_operand* b, GemmPlan* gp) {
+  if (!a || !b) return fail(PB_ERR_NULL_POINTER, "pb_gemm_tn: operands must be non-null");
+  if (int s = plan_operand(a, "A", &gp->pa)) return s;
+  if (int s = plan_operand(b, "B", &gp->pb)) return s;
+  if (a->depth != b->depth)
+    return fail(PB_ERR_BAD_SHAPE, "pb_gemm_tn: contraction lengths differ (%lld vs %lld)", (long long)a->depth, (long long)b->depth);
+  gp->BN = pick_bn();
+  gp->P = gp->pa.P < gp->pb.P ? gp->pa.P : gp->pb.P;
+  gp->KB = (int)(a->depth / BK);
+  if (gp->P > gp->KB) gp->P = gp->KB;
+  gp->KG = (gp->KB + 3) / 4;
+  gp->nchunks = (gp->KB + gp->P - 1) / gp->P;
+  gp->Mpad = (int)((a->rows + 127) / 128 * 128);
+  gp->Npad = (int)((b->rows + 255) / 256 * 256);
+  auto align = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  size_t off = 0;
+  gp->off_sfa = off; off = align(off + (size_t)gp->KG * gp->Mpad * 4);
+  gp->off_sfb = off; off = align(off + (size_t)gp->KG * gp->Npad * 4);
+  gp->off_fa = off;  off = align(off + (size_t)gp->nchunks * gp->Mpad * 4);
+  gp->off_fb = off;  off = align(off + (size_t)gp->nchunks * gp->Npad * 4);
+  gp->total = off;
+  return PB_OK;
+}
+
+int launch_prep(const pb_operand* o, const OperandPlan& op, const GemmPlan& gp, int rows_pad, uint8_t* sf, float* f, cudaStream_t st) {
+  PrepParams q{o->sc8, o->sc32, sf, f, (int)o->rows, rows_pad, gp.KB, gp.KG, gp.P, gp.nchunks, o->grid_a, o->transposed_blocks, op.Ksg};
+  const int64_t items = (int64_t)rows_pad * (gp.KG * 4 + gp.nchunks);
+  const int64_t need = (items + 255) / 256;
+  const int grid = (int)(need < (int64_t)sm_count() * 8 ? need : (int64_t)sm_count() * 8);
+  gemm_prep_kernel<<<grid, 256, 0, st>>>(q);
+  PB_LAUNCH_CHECK("gemm_prep_kernel");
+  return PB_OK;
+}
+
+template <int BN>
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st) {
+  static std::mutex mu;
+  static bool configured[64] = {false};
+  int dev = 0;
+  PB_CUDA_TRY(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      PB_CUDA_TRY(cudaFuncSetAttribute(gemm_tn_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes));
+      configured[dev] = true;
+    }
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_tn_kernel<BN><<<grid, Cfg<BN>::kThreads, Cfg<BN>::kSmemBytes, st>>>(ma, mb, p);
+  PB_LAUNCH_CHECK("gemm_tn_kernel");
+  return PB_OK;
+}
+
+}  // namespace
+}  // namespace pb
+
+using namespace pb;
+
+extern "C" size_t pb_gemm_workspace_size(const pb_operand* a, const pb_operand* b) {
+  GemmPlan gp;
+  if (make_plan(a, b, &gp) != PB_OK) return 0;
+  return gp.total;
+}
+
+extern "C" int pb_gemm_tn(const pb_operand* a, const pb_operand* b, void* d, int d_dtype, int64_t ldd,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+  GemmPlan gp;
+  if (int s = make_plan(a, b, &gp)) return s;
+  if (!d) return fail(PB_ERR_NULL_POINTER, "pb_gemm_tn: d must be non-null");
+  if (d_dtype != PB_F32 && d_dtype != PB_BF16) return fail(PB_ERR_BAD_DTYPE, "pb_gemm_tn: d_dtype %d is neither PB_F32 nor PB_BF16", d_dtype);
+  if (ldd < b->rows) return fail(PB_ERR_BAD_SHAPE, "pb_gemm_tn: ldd=%lld is smaller than N=%lld", (long long)ldd, (long long)b->rows);
+  if (!workspace || workspace_bytes < gp.total)
+    return fail(PB_ERR_WORKSPACE_TOO_SMALL, "pb_gemm_tn: needs %zu bytes of workspace, got %zu", gp.total, workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(PB_ERR_MISALIGNED, "pb_gemm_tn: workspace must be 256-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+
+  if (int s = launch_prep(a, gp.pa, gp, gp.Mpad, ws + gp.off_sfa, reinterpret_cast<float*>(ws + gp.off_fa), st)) return s;
+  if (int s = launch_prep(b, gp.pb, gp, gp.Npad, ws + gp.off_sfb, reinterpret_cast<float*>(ws + gp.off_fb), st)) return s;
+
+  CUtensorMap ma, mb;
+  if (int s = make_operand_map(&ma, a->q, a->rows, a->depth, BM)) return s;
+  if (int s = make_operand_map(&mb, b->q, b->rows, b->depth, gp.BN)) return s;
+
+  GemmParams p;
+  p.sfa = ws + gp.off_sfa; p.sfb = ws + gp.off_sfb;
+  p.fa = reinterpret_cast<const float*>(ws + gp.off_fa); p.fb = reinterpret_cast<const float*>(ws + gp.off_fb);
+  p.d = d; p.ldd = ldd;
+  p.M = (int)a->rows; p.N = (int)b->rows; p.KB = gp.KB; p.P = gp.P; p.nchunks = gp.nchunks;
+  p.Mpad = gp.Mpad; p.Npad = gp.Npad;
+  p.tiles_m = gp.Mpad / BM; p.tiles_n = (int)((b->rows + gp.BN - 1) / gp.BN);
+  p.a_fmt = a->format; p.b_fmt = b->format; p.d_dtype = d_dtype;
+  return gp.BN == 256 ? launch_gemm<256>(ma, mb, p, st) : launch_gemm<128>(ma, mb, p, st);
+}
+
+extern "C" int pb_gemm_check(void* stream) {
+  PB_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  unsigned int v = 0, zero = 0;
+  PB_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(v)));
+  if (v != 0) {
+    PB_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(zero)));
+    return fail((int)v, "a bounded device-side wait in the GEMM kernel ran out");
+  }
+  return PB_OK;
+}

@@ -234,6 +234,22 @@ generic_scale_kernel(const uint32_t* __restrict__ amax_bits, float* __restrict__
   }
 }
 
+}  // namespace
+
+// Per-block amax bits -> e8m0 bytes, fp32 amax and per-block divisors (shared with the
+// transposed quantizer).
+int launch_group_scales(const uint32_t* amax_bits, float* divisor, uint8_t* sc8, float* sc32, int64_t n_groups, int64_t K, cudaStream_t st) {
+  if (K >= 32) {
+    generic_scale_kernel<true><<<(unsigned)((n_groups * 32 + 255) / 256), 256, 0, st>>>(amax_bits, divisor, sc8, sc32, n_groups, K);
+  } else {
+    generic_scale_kernel<false><<<(unsigned)((n_groups + 255) / 256), 256, 0, st>>>(amax_bits, divisor, sc8, sc32, n_groups, K);
+  }
+  PB_LAUNCH_CHECK("generic_scale_kernel");
+  return PB_OK;
+}
+
+namespace {
+
 template <typename InT, int VEC, int FMT>
 __global__ void __launch_bounds__(256)
 generic_apply_kernel(const InT* __restrict__ x, const float* __restrict__ divisor,
@@ -275,13 +291,7 @@ int launch_generic(const InT* x, const Geometry& g, int64_t batch, int fmt, uint
   const int grid = grid_for(d.total_vecs, 256, 8);
   generic_amax_kernel<InT, VEC><<<grid, 256, 0, st>>>(x, amax_bits, d);
   PB_LAUNCH_CHECK("generic_amax_kernel");
-  const int64_t n_groups = batch * g.M;
-  if (g.K >= 32) {
-    generic_scale_kernel<true><<<(unsigned)((n_groups * 32 + 255) / 256), 256, 0, st>>>(amax_bits, divisor, sc8, sc32, n_groups, g.K);
-  } else {
-    generic_scale_kernel<false><<<(unsigned)((n_groups + 255) / 256), 256, 0, st>>>(amax_bits, divisor, sc8, sc32, n_groups, g.K);
-  }
-  PB_LAUNCH_CHECK("generic_scale_kernel");
+  if (int s = launch_group_scales(amax_bits, divisor, sc8, sc32, batch * g.M, g.K, st)) return s;
   if (fmt == PB_E4M3) generic_apply_kernel<InT, VEC, PB_E4M3><<<grid, 256, 0, st>>>(x, divisor, q, d);
   else                generic_apply_kernel<InT, VEC, PB_E5M2><<<grid, 256, 0, st>>>(x, divisor, q, d);
   PB_LAUNCH_CHECK("generic_apply_kernel");

@@ -1,0 +1,174 @@
+// Quantizer of the transpose, and a plain byte transpose (sm_100a).
+//
+// pb_quantize_transposed produces the triple of quantize_impl(swapaxes(x,-1,-2), (1, b))
+// (the operands fp8_matmul_bwd builds from x^T and g, pratchya/_qualia/_qarr.py:784-789)
+// directly from x[rows, cols], without writing the transposed dense matrix:
+//   1. column-block amax: m[c][rb] = max |x[rb*b .. rb*b+b-1, c]|   (scratch, the block order of x^T)
+//   2. the shared per-super-group scale kernel (divisors into scratch, sc8 / sc32 out)
+//   3. tile transpose through shared memory, dividing on the way, coalesced byte rows out.
+#include "common.cuh"
+
+namespace pb {
+
+// defined in quantize.cu
+int launch_group_scales(const uint32_t* amax_bits, float* divisor, uint8_t* sc8, float* sc32, int64_t n_groups, int64_t K, cudaStream_t st);
+
+namespace {
+
+constexpr int kTile = 64;
+
+// grid: (cols/2 per 128 threads, row blocks, batch).  Each thread owns two adjacent columns.
+template <typename InT>
+__global__ void __launch_bounds__(128)
+column_amax_kernel(const InT* __restrict__ x, uint32_t* __restrict__ amax_bits, int rows, int cols, int b) {
+  const int c = (blockIdx.x * 128 + threadIdx.x) * 2;
+  const int rb = blockIdx.y;
+  const int nrb = rows / b;
+  const InT* src = x + ((size_t)blockIdx.z * rows + (size_t)rb * b) * cols;
+  if (c >= cols) return;
+  float m0 = 0.0f, m1 = 0.0f;
+  const bool pair = (c + 1 < cols) && ((cols & 1) == 0);
+  for (int r = 0; r < b; ++r) {
+    if (pair) {
+      if constexpr (sizeof(InT) == 2) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(src + (size_t)r * cols + c);
+        m0 = fmaxf(m0, fabsf(__uint_as_float(w << 16)));
+        m1 = fmaxf(m1, fabsf(__uint_as_float(w & 0xffff0000u)));
+      } else {
+        const float2 w = *reinterpret_cast<const float2*>(src + (size_t)r * cols + c);
+        m0 = fmaxf(m0, fabsf(w.x));
+        m1 = fmaxf(m1, fabsf(w.y));
+      }
+    } else {
+      m0 = fmaxf(m0, fabsf(Elem<InT>::to_f32(src[(size_t)r * cols + c])));
+      if (c + 1 < cols) m1 = fmaxf(m1, fabsf(Elem<InT>::to_f32(src[(size_t)r * cols + c + 1])));
+    }
+  }
+  uint32_t* dst = amax_bits + ((size_t)blockIdx.z * cols + c) * nrb + rb;
+  dst[0] = __float_as_uint(m0);
+  if (c + 1 < cols) dst[nrb] = __float_as_uint(m1);
+}
+
+// grid: (ceil(cols/64), ceil(rows/64), batch), 256 threads.  Reads a 64x64 tile of x row-wise,
+// writes 64 rows (columns of x) of 64 quantized bytes each.
+template <typename InT, int FMT>
+__global__ void __launch_bounds__(256)
+transpose_apply_kernel(const InT* __restrict__ x, const float* __restrict__ divisor, uint8_t* __restrict__ q_t,
+                       int rows, int cols, int b) {
+  __shared__ float tile[kTile][kTile + 1];
+  const int r0 = blockIdx.y * kTile, c0 = blockIdx.x * kTile;
+  const InT* src = x + (size_t)blockIdx.z * rows * cols;
+  for (int i = threadIdx.x; i < kTile * kTile; i += 256) {
+    const int r = i / kTile, c = i % kTile;
+    tile[r][c] = (r0 + r < rows && c0 + c < cols) ? Elem<InT>::to_f32(src[(size_t)(r0 + r) * cols + c0 + c]) : 0.0f;
+  }
+  __syncthreads();
+  const int nrb = rows / b;
+  uint8_t* dst = q_t + (size_t)blockIdx.z * rows * cols;
+  const float* div = divisor + (size_t)blockIdx.z * cols * nrb;
+  // thread -> (output row = column c of x, 16 consecutive source rows)
+  const int c = threadIdx.x / 4, seg = threadIdx.x % 4;
+  if (c0 + c >= cols) return;
+  uint32_t out[4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    uint32_t packed = 0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = seg * 16 + w * 4 + h * 2;
+      float v0 = 0.0f, v1 = 0.0f;
+      if (r0 + r < rows) {
+        const float D = div[(size_t)(c0 + c) * nrb + (r0 + r) / b];
+        v0 = div_hoisted(tile[r][c], D, __frcp_rn(D));
+      }
+      if (r0 + r + 1 < rows) {
+        const float D = div[(size_t)(c0 + c) * nrb + (r0 + r + 1) / b];
+        v1 = div_hoisted(tile[r + 1][c], D, __frcp_rn(D));
+      }
+      packed |= bf16x2_to_fp8x2<FMT>(pack_bf16x2(v0, v1)) << (16 * h);
+    }
+    out[w] = packed;
+  }
+  uint8_t* o = dst + (size_t)(c0 + c) * rows + r0 + seg * 16;
+  if (r0 + seg * 16 + 16 <= rows && (rows & 15) == 0 && (reinterpret_cast<uintptr_t>(q_t) & 15) == 0) {
+    *reinterpret_cast<uint4*>(o) = make_uint4(out[0], out[1], out[2], out[3]);
+  } else {
+    for (int j = 0; j < 16; ++j)
+      if (r0 + seg * 16 + j < rows) o[j] = (uint8_t)(out[j >> 2] >> (8 * (j & 3)));
+  }
+}
+
+__global__ void __launch_bounds__(256)
+transpose_bytes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int rows, int cols) {
+  __shared__ uint8_t tile[kTile][kTile + 4];
+  const int r0 = blockIdx.y * kTile, c0 = blockIdx.x * kTile;
+  for (int i = threadIdx.x; i < kTile * kTile; i += 256) {
+    const int r = i / kTile, c = i % kTile;
+    tile[r][c] = (r0 + r < rows && c0 + c < cols) ? src[(size_t)(r0 + r) * cols + c0 + c] : 0;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kTile * kTile; i += 256) {
+    const int c = i / kTile, r = i % kTile;
+    if (r0 + r < rows && c0 + c < cols) dst[(size_t)(c0 + c) * rows + r0 + r] = tile[r][c];
+  }
+}
+
+}  // namespace
+}  // namespace pb
+
+using namespace pb;
+
+extern "C" size_t pb_quantize_transposed_workspace_size(int64_t batch, int64_t rows, int64_t cols, int b) {
+  Geometry g;
+  if (batch <= 0 || make_geometry(cols, rows, 1, b, &g) != PB_OK) return 0;
+  return (size_t)(batch * g.Nb) * 8;
+}
+
+extern "C" int pb_quantize_transposed(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols,
+                                      int b, int out_format, void* q_t, uint8_t* sc8, float* sc32,
+                                      void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !q_t || !sc8 || !sc32) return fail(PB_ERR_NULL_POINTER, "pb_quantize_transposed: x, q_t, sc8 and sc32 must be non-null");
+  if (batch <= 0) return fail(PB_ERR_BAD_SHAPE, "pb_quantize_transposed: batch=%lld must be positive", (long long)batch);
+  if (x_dtype != PB_F32 && x_dtype != PB_BF16) return fail(PB_ERR_BAD_DTYPE, "pb_quantize_transposed: x_dtype %d is neither PB_F32 nor PB_BF16", x_dtype);
+  if (out_format != PB_E4M3 && out_format != PB_E5M2) return fail(PB_ERR_BAD_DTYPE, "pb_quantize_transposed: out_format %d is neither PB_E4M3 nor PB_E5M2", out_format);
+  Geometry g;   // geometry of x^T: [cols, rows] on (1, b)
+  if (int s = make_geometry(cols, rows, 1, b, &g)) return s;
+  if (rows > kMaxIndexed || cols > kMaxIndexed || batch > 65535 || rows / b > 65535 || (rows + kTile - 1) / kTile > 65535)
+    return fail(PB_ERR_UNSUPPORTED, "pb_quantize_transposed: shape [%lld, %lld, %lld] exceeds the launch limits", (long long)batch, (long long)rows, (long long)cols);
+  const size_t need = (size_t)(batch * g.Nb) * 8;
+  if (!workspace || workspace_bytes < need)
+    return fail(PB_ERR_WORKSPACE_TOO_SMALL, "pb_quantize_transposed: needs %zu bytes of workspace, got %zu", need, workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) & 3) return fail(PB_ERR_MISALIGNED, "pb_quantize_transposed: workspace must be 4-byte aligned");
+  if (reinterpret_cast<uintptr_t>(x) & 7) return fail(PB_ERR_MISALIGNED, "pb_quantize_transposed: x must be 8-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t* amax_bits = static_cast<uint32_t*>(workspace);
+  float* divisor = reinterpret_cast<float*>(amax_bits + batch * g.Nb);
+
+  const dim3 grid1((unsigned)((cols + 255) / 256), (unsigned)(rows / b), (unsigned)batch);
+  if (x_dtype == PB_BF16) column_amax_kernel<__nv_bfloat16><<<grid1, 128, 0, st>>>((const __nv_bfloat16*)x, amax_bits, (int)rows, (int)cols, b);
+  else                    column_amax_kernel<float><<<grid1, 128, 0, st>>>((const float*)x, amax_bits, (int)rows, (int)cols, b);
+  PB_LAUNCH_CHECK("column_amax_kernel");
+  if (int s = launch_group_scales(amax_bits, divisor, sc8, sc32, batch * g.M, g.K, st)) return s;
+
+  const dim3 grid3((unsigned)((cols + kTile - 1) / kTile), (unsigned)((rows + kTile - 1) / kTile), (unsigned)batch);
+  uint8_t* out = static_cast<uint8_t*>(q_t);
+  if (x_dtype == PB_BF16) {
+    if (out_format == PB_E4M3) transpose_apply_kernel<__nv_bfloat16, PB_E4M3><<<grid3, 256, 0, st>>>((const __nv_bfloat16*)x, divisor, out, (int)rows, (int)cols, b);
+    else                       transpose_apply_kernel<__nv_bfloat16, PB_E5M2><<<grid3, 256, 0, st>>>((const __nv_bfloat16*)x, divisor, out, (int)rows, (int)cols, b);
+  } else {
+    if (out_format == PB_E4M3) transpose_apply_kernel<float, PB_E4M3><<<grid3, 256, 0, st>>>((const float*)x, divisor, out, (int)rows, (int)cols, b);
+    else                       transpose_apply_kernel<float, PB_E5M2><<<grid3, 256, 0, st>>>((const float*)x, divisor, out, (int)rows, (int)cols, b);
+  }
+  PB_LAUNCH_CHECK("transpose_apply_kernel");
+  return PB_OK;
+}
+
+extern "C" int pb_transpose_bytes(const void* src, int64_t rows, int64_t cols, void* dst, void* stream) {
+  if (!src || !dst) return fail(PB_ERR_NULL_POINTER, "pb_transpose_bytes: src and dst must be non-null");
+  if (rows <= 0 || cols <= 0 || rows > kMaxIndexed || cols > kMaxIndexed || (rows + kTile - 1) / kTile > 65535)
+    return fail(PB_ERR_BAD_SHAPE, "pb_transpose_bytes: bad shape [%lld, %lld]", (long long)rows, (long long)cols);
+  const dim3 grid((unsigned)((cols + kTile - 1) / kTile), (unsigned)((rows + kTile - 1) / kTile));
+  transpose_bytes_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>((const uint8_t*)src, (uint8_t*)dst, (int)rows, (int)cols);
+  PB_LAUNCH_CHECK("transpose_bytes_kernel");
+  return PB_OK;
+}

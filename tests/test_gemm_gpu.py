@@ -1,0 +1,127 @@
+"""GPU parity of the block-scaled FP8 matmul with the oracle's dq(A) @ dq(B) on the same
+quantized operands.  Tolerance: max |got - ref| <= 1e-2 * max |ref| per output matrix, and
+<= 1e-2 relative on entries with |ref| above 5% of the matrix maximum (the tensor core sums
+exact fp8 products in fp32; the bound covers its accumulation order)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import BF16, bytes_of, from_torch, oracle, synth, to_torch
+from pratchya_b200 import _lib
+from pratchya_b200._qualia import matmul_impl, quantize_impl, quantize_transposed_impl
+from pratchya_b200._qualia import _ops
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-2
+
+
+def check_close(got, ref, what):
+    ref = np.asarray(ref, dtype=np.float64)
+    got = np.asarray(got, dtype=np.float64)
+    assert got.shape == ref.shape, f"{what}: shape {got.shape} vs {ref.shape}"
+    scale = np.abs(ref).max()
+    err = np.abs(got - ref)
+    assert err.max() <= REL_TOL * scale, f"{what}: max abs err {err.max():.3e} vs scale {scale:.3e}"
+    big = np.abs(ref) > 0.05 * scale
+    if big.any():
+        rel = (err[big] / np.abs(ref[big])).max()
+        assert rel <= REL_TOL, f"{what}: max rel err {rel:.3e}"
+    return err.max() / scale
+
+
+def gpu_triple(x, grid):
+    return quantize_impl(to_torch(x), grid)
+
+
+def np_triple(t):
+    q, s8, s32 = t
+    return (bytes_of(q).view(oracle.E4M3), bytes_of(s8), from_torch(s32))
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (128, 128, 512), (128, 256, 1024), (256, 256, 2048),
+                                   (200, 384, 1024), (1024, 1024, 2048), (384, 128, 2304), (128, 1280, 4096)])
+def test_forward_matmul_matches_oracle(built_lib, m, n, k):
+    x = synth((m, k), seed=m + n + k, outliers=0.01)
+    w = synth((k, n), seed=m * 7 + n, scale=0.02, outliers=0)
+    xq, wq = gpu_triple(x, (1, 128)), gpu_triple(w, (128, 128))
+    if oracle.group_geometry(m, k, (1, 128))[1] != 8:
+        pytest.skip("activation super-group is not 8 blocks: falls back to the literal path")
+    got = matmul_impl(*xq, *wq, (1, 128), (128, 128))
+    _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+    ref = oracle.matmul_impl(*np_triple(xq), *np_triple(wq), (1, 128), (128, 128), acc=np.float64)
+    check_close(got.cpu().numpy(), ref, f"fwd {m}x{n}x{k}")
+
+
+def test_bf16_output_and_student_t(built_lib):
+    m, n, k = 512, 512, 2048
+    x = synth((m, k), seed=1, dist="student_t", outliers=0).astype(BF16)
+    w = synth((k, n), seed=2, scale=0.02, outliers=0).astype(BF16)
+    xq, wq = gpu_triple(x, (1, 128)), gpu_triple(w, (128, 128))
+    got = matmul_impl(*xq, *wq, (1, 128), (128, 128), out_dtype=torch.bfloat16)
+    _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+    ref = oracle.matmul_impl(*np_triple(xq), *np_triple(wq), (1, 128), (128, 128), acc=np.float64)
+    check_close(from_torch(got).astype(np.float32), ref, "bf16 out")
+
+
+def test_dgrad_and_wgrad_operand_forms(built_lib):
+    """dgrad: A = Q(g,(1,128)) [M,N], B = the weight as stored [K,N] (N is the depth).
+    wgrad: A = Q(x^T,(1,128)) [K,M], B = Q(g^T,(1,128)) [N,M] (tokens are the depth)."""
+    m, n, k = 1024, 512, 256
+    x = synth((m, k), seed=3)
+    w = synth((k, n), seed=4, scale=0.02, outliers=0)
+    g = synth((m, n), seed=5, scale=1e-3, outliers=0)
+    wq = gpu_triple(w, (128, 128))
+    gq = gpu_triple(g, (1, 128))
+    a = _ops._operand(gq[0], gq[1], gq[2], m, n, (1, 128))
+    b = _ops._operand(wq[0], wq[1], wq[2], k, n, (128, 128))
+    dx = _ops.gemm_tn(a, b, torch.float32, gq[0].device)
+    _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+    g_hat = oracle.dequantize_impl(*np_triple(gq), np.float64, (1, 128))
+    w_hat = oracle.dequantize_impl(*np_triple(wq), np.float64, (128, 128))
+    check_close(dx.cpu().numpy(), g_hat @ w_hat.T, "dgrad")
+
+    xt = quantize_transposed_impl(to_torch(x), 128)
+    gt = quantize_transposed_impl(to_torch(g), 128)
+    want_xt = oracle.quantize_impl(np.ascontiguousarray(x.T), (1, 128))
+    assert np.array_equal(bytes_of(xt[0]), bytes_of(want_xt[0])) and np.array_equal(bytes_of(xt[1]), want_xt[1])
+    assert np.array_equal(from_torch(xt[2]), want_xt[2])
+    a = _ops._operand(xt[0], xt[1], xt[2], k, m, (1, 128))
+    b = _ops._operand(gt[0], gt[1], gt[2], n, m, (1, 128))
+    dw = _ops.gemm_tn(a, b, torch.float32, xt[0].device)
+    _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+    xt_hat = oracle.dequantize_impl(*np_triple(xt), np.float64, (1, 128))
+    gt_hat = oracle.dequantize_impl(*np_triple(gt), np.float64, (1, 128))
+    check_close(dw.cpu().numpy(), xt_hat @ gt_hat.T, "wgrad")
+
+
+def test_slab_supergroups_of_a_large_weight(built_lib):
+    """A weight with more than 1024 blocks has several fp32 amax slabs along the depth."""
+    m, n, k = 128, 4096, 8192          # 64 x 32 blocks -> K = 1024 blocks = 32 block rows per slab
+    x = synth((m, k), seed=6)
+    w = synth((k, n), seed=7, scale=0.02, outliers=0)
+    w[:4096] *= 8.0                     # make the two slabs differ
+    xq, wq = gpu_triple(x, (1, 128)), gpu_triple(w, (128, 128))
+    assert wq[2].numel() == 2
+    got = matmul_impl(*xq, *wq, (1, 128), (128, 128))
+    _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+    ref = oracle.matmul_impl(*np_triple(xq), *np_triple(wq), (1, 128), (128, 128), acc=np.float64)
+    check_close(got.cpu().numpy(), ref, "slabs")
+
+
+def test_literal_path_for_small_grids(built_lib):
+    x = synth((64, 96), seed=8)
+    w = synth((96, 48), seed=9, scale=0.02, outliers=0)
+    xq, wq = gpu_triple(x, (1, 16)), gpu_triple(w, (16, 16))
+    got = matmul_impl(*xq, *wq, (1, 16), (16, 16))
+    ref = oracle.matmul_impl(*np_triple(xq), *np_triple(wq), (1, 16), (16, 16), acc=np.float64)
+    check_close(got.cpu().numpy(), ref, "literal")
+
+
+def test_transposed_quantizer_bit_exact(built_lib):
+    for shape, dt in [((1024, 256), np.float32), ((2048, 192), BF16), ((1024, 100), np.float32), ((128, 64), BF16)]:
+        x = synth(shape, seed=10, outliers=0.01).astype(dt)
+        got = quantize_transposed_impl(to_torch(x), 128)
+        want = oracle.quantize_impl(np.ascontiguousarray(x.T), (1, 128))
+        assert np.array_equal(bytes_of(got[0]), bytes_of(want[0])), shape
+        assert np.array_equal(bytes_of(got[1]), want[1]) and np.array_equal(from_torch(got[2]), want[2])
