@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 block-quantization hot path (one JSON line on stdout).
+
+Workload (per GPU, weak scaling): the block-scaled FP8 GEMM forward of BASELINE.json configs[1]
+    X bf16 [8192, 2048] ~ N(0,1)  --(1,128) e4m3-->  Xq      (timed, every step)
+    W bf16 [2048, 8192] ~ N(0,0.02), quantized (128,128) once (the layer holds it quantized)
+    Y = dq(Xq) . dq(Wq), fp32 accumulation, bf16 [8192, 8192]    (timed, every step)
+A step is quantize(X) + GEMM; `value` is 2*M*N*K per step time, summed over ranks.
+Synthetic seeded inputs; the step rotates over several input/output buffer sets so that every
+step's data (201 MB per set, 800+ MB in rotation) comes from HBM, not from the 126 MB L2.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M, N, K = 8192, 8192, 2048
+FLOP_PER_STEP = 2 * M * N * K
+QUANT_BYTES_PER_ELEM = 2 + 1 + 1 / 128 + 4 / 1024          # bf16 in, fp8 out, e8m0 per 128, fp32 per 1024
+NBUF = 4
+METRIC = "fp8_block_gemm_step_tflops"
+WORKLOAD = "configs[1]: X[8192,2048] bf16 -> (1,128) e4m3; W[2048,8192] (128,128) e4m3; Y bf16 [8192,8192]"
+
+# DRAM bytes per launch from the ncu captures summarised under profiles/ (None until captured)
+GEMM_DRAM_TRAFFIC_BYTES = None
+QUANT_DRAM_TRAFFIC_BYTES = None
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()       # the exact child this object started
+        self.thread.join(timeout=2)
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU reference arm
+def cpu_sample(rows: int, seed: int = 0):
+    """One pass of the oracle (numpy restatement of the reference) over a row sample of the
+    workload: quantize X[rows, K], then dq(X) @ dq(W) in f32 for all N columns."""
+    import numpy as np
+    from oracle import qarr_oracle as oracle
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((rows, K)).astype(np.float32)
+    w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    wq = oracle.quantize_impl(w, (128, 128))
+    t0 = time.perf_counter()
+    xq = oracle.quantize_impl(x, (1, 128))
+    y = oracle.matmul_impl(*xq, *wq, (1, 128), (128, 128))
+    dt = time.perf_counter() - t0
+    return dt, float(np.abs(y).max())
+
+
+CPU_SAMPLE_ROWS = 2048      # a quarter of the workload's rows; W is the full [2048, 8192]
+
+
+def cpu_baseline(budget_s: float = 12.0):
+    rows = CPU_SAMPLE_ROWS
+    dt, _ = cpu_sample(rows)                      # warm-up / calibration
+    reps, total = 0, 0.0
+    while total < budget_s and reps < 50:
+        dt, _ = cpu_sample(rows, seed=reps + 1)
+        total += dt
+        reps += 1
+    per = total / reps
+    return {"value": 2 * rows * N * K / per / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"oracle (numpy+ml_dtypes restatement; jax is not installed, so the reference's own JAX CPU path cannot run): "
+                      f"quantize X[{rows},{K}] + dequantize both operands + f32 matmul to [{rows},{N}], mean of {reps} passes, "
+                      f"numpy BLAS threads = all cores, elementwise part single-threaded"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    rows = CPU_SAMPLE_ROWS
+    for i in range(args.warmup):
+        cpu_sample(rows, seed=100 + i)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        cpu_sample(rows, seed=i)
+    dt = time.perf_counter() - t0
+    val = 2 * rows * N * K * args.steps / dt / 1e12
+    cb = {"value": val, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+          "sample": f"each step = oracle pass over a {rows}-row sample of X (quantize + dequantize + f32 matmul against the full W[{K},{N}])"}
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "sample_rows": rows},
+        "cpu_baseline": cb, "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+    return 0
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from pratchya_b200 import _lib
+    from pratchya_b200._qualia import _ops
+    from pratchya_b200._nnx_impl import Linear
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the pratchya_b200 ops have no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)       # each rank owns its own row shard
+    xs = [torch.randn(M, K, device=dev, generator=gen, dtype=torch.float32).to(torch.bfloat16) for _ in range(NBUF)]
+    w = (torch.randn(K, N, device=dev, generator=torch.Generator(device=dev).manual_seed(7), dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    layer = Linear(K, N, (128, 128), kernel=w)                       # weight quantized once, replicated on every rank
+    wq, w_s8, w_s32 = layer.kernel.get_value(), layer.kernel.sc_fp8, layer.kernel.sc_fp32
+    w_t = layer.kernel.transposed_value()
+
+    # preallocated device buffers: the timed loop calls the C ABI only
+    xq = [torch.empty(M, K, device=dev, dtype=torch.uint8) for _ in range(NBUF)]
+    x_s8 = [torch.empty(M * K // 128, device=dev, dtype=torch.uint8) for _ in range(NBUF)]
+    x_s32 = [torch.empty(M * K // 1024, device=dev, dtype=torch.float32) for _ in range(NBUF)]
+    ys = [torch.empty(M, N, device=dev, dtype=torch.bfloat16) for _ in range(NBUF)]
+    ops_a = [_lib.Operand(xq[i].data_ptr(), x_s8[i].data_ptr(), x_s32[i].data_ptr(), M, K, 1, 128, _lib.PB_E4M3, 0) for i in range(NBUF)]
+    op_b = _lib.Operand(w_t.data_ptr(), w_s8.data_ptr(), w_s32.data_ptr(), N, K, 128, 128, _lib.PB_E4M3, 1)
+    ws_bytes = lib.pb_gemm_workspace_size(ops_a[0], op_b)
+    ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
+
+    def quantize(i):
+        _lib.check(lib.pb_quantize(xs[i].data_ptr(), _lib.PB_BF16, 1, M, K, 1, 128, _lib.PB_E4M3,
+                                   xq[i].data_ptr(), x_s8[i].data_ptr(), x_s32[i].data_ptr(), None, 0, stream))
+
+    def gemm(i):
+        _lib.check(lib.pb_gemm_tn(ops_a[i], op_b, ys[i].data_ptr(), _lib.PB_BF16, N, ws.data_ptr(), ws_bytes, stream))
+
+    def step(i):
+        quantize(i % NBUF)
+        gemm(i % NBUF)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    _lib.check(lib.pb_gemm_check(stream))
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.15)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 2)]
+    barrier()
+    ev[0].record()
+    for i in range(args.steps):
+        quantize(i % NBUF)
+        ev[2 * i + 1].record()
+        gemm(i % NBUF)
+        ev[2 * i + 2].record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = ev[0].elapsed_time(ev[2 * args.steps])
+    q_ms = statistics.mean(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(args.steps))
+    g_ms = statistics.mean(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps))
+    _lib.check(lib.pb_gemm_check(stream))
+
+    # ---- quantizer alone on the largest activation of the training configs (HBM-bound, 202 MB per launch)
+    qm, qk = 32768, 2048
+    big = [torch.randn(qm, qk, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    bq = torch.empty(qm, qk, device=dev, dtype=torch.uint8)
+    b8 = torch.empty(qm * qk // 128, device=dev, dtype=torch.uint8)
+    b32 = torch.empty(qm * qk // 1024, device=dev, dtype=torch.float32)
+
+    def big_quant(i):
+        _lib.check(lib.pb_quantize(big[i % 2].data_ptr(), _lib.PB_BF16, 1, qm, qk, 1, 128, _lib.PB_E4M3,
+                                   bq.data_ptr(), b8.data_ptr(), b32.data_ptr(), None, 0, stream))
+    for i in range(3):
+        big_quant(i)
+    torch.cuda.synchronize()
+    qe = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    reps = 20
+    qe[0].record()
+    for i in range(reps):
+        big_quant(i)
+    qe[1].record()
+    torch.cuda.synchronize()
+    big_q_ms = qe[0].elapsed_time(qe[1]) / reps
+    quant_bytes = qm * qk * QUANT_BYTES_PER_ELEM
+
+    # ---- end to end through the public API with host buffers
+    x_host = [x.cpu().pin_memory() for x in xs[:2]]
+    y_host = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    x_dev = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+
+    def e2e_step(i):
+        x_dev.copy_(x_host[i % 2], non_blocking=True)
+        y = layer.matmul(x_dev, out_dtype=torch.bfloat16)
+        y_host.copy_(y, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 10))
+    for i in range(2):
+        e2e_step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    times = torch.tensor([total_ms, e2e_ms, g_ms, q_ms, big_q_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms, g_ms, q_ms, big_q_ms = times.tolist()
+
+    if rank == 0:
+        peaks = load_peaks()
+        ms_per_step = total_ms / args.steps
+        fp8_peak = 2.0 * peaks["bf16_tflops"]
+        gemm_tflops = FLOP_PER_STEP / (g_ms * 1e-3) / 1e12
+        out = {
+            "metric": METRIC, "value": world * FLOP_PER_STEP / (ms_per_step * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "rows_per_gpu": M, "parallelism": f"row shards x{world}, no collective",
+                       "l2": f"rotation over {NBUF} buffer sets, {NBUF * (M * K * 3 + M * N * 2) / 1e6:.0f} MB > 126 MB L2"},
+            "gpu_launches": args.steps * 4,
+            "parts": {"gemm_ms": g_ms, "gemm_tflops": gemm_tflops, "quantize_ms": q_ms,
+                      "quantize_gbs_in_step": M * K * QUANT_BYTES_PER_ELEM / (q_ms * 1e-3) / 1e9,
+                      "kernels_per_step": "quantize_row128_bf16, gemm_prep x2, gemm_tn"},
+            "roofline": {"bound": "tensor", "kernel": "gemm_tn_kernel", "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s",
+                         "frac": gemm_tflops / fp8_peak, "traffic": GEMM_DRAM_TRAFFIC_BYTES,
+                         "peak_source": f"2 x bf16_tflops burst of {peaks['source']} (no FP8 figure is measured); nominal dense FP8 is 4500",
+                         "frac_of_nominal_4500": gemm_tflops / 4500.0},
+            "roofline_quantize": {"bound": "hbm", "kernel": "quantize_row128_bf16_kernel", "workload": f"X[{qm},{qk}] bf16",
+                                  "achieved": quant_bytes / (big_q_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                  "frac": quant_bytes / (big_q_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": QUANT_DRAM_TRAFFIC_BYTES,
+                                  "peak_source": f"hbm_gbs of {peaks['source']}"},
+            "e2e": {"value": world * FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
+                    "api": "pratchya_b200._nnx_impl.Linear.matmul on a device copy of pinned host X; Y copied back to pinned host memory"},
+            "clocks": clocks,
+        }
+        if world == 1:
+            out["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def run_profile_case(name: str):
+    """A few launches of one kernel on a reduced case, for `ncu --set full` captures
+    (not a benchmark: prints nothing that is a result)."""
+    import torch
+    from pratchya_b200._qualia import _ops, quantize_impl
+    torch.cuda.set_device(0)
+    if name == "quantize":
+        x = torch.randn(16384, 4096, device="cuda", dtype=torch.bfloat16)      # 134 MB in: larger than L2
+        for _ in range(4):
+            quantize_impl(x, (1, 128))
+    elif name == "dequantize":
+        x = torch.randn(16384, 4096, device="cuda", dtype=torch.bfloat16)
+        t = quantize_impl(x, (1, 128))
+        for _ in range(4):
+            _ops.dequantize_impl(*t, torch.bfloat16, (1, 128))
+    else:
+        m, n, k = 4096, 4096, 2048
+        x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(k, n, device="cuda", dtype=torch.bfloat16) * 0.02
+        xq, wq = quantize_impl(x, (1, 128)), quantize_impl(w, (128, 128))
+        for _ in range(4):
+            _ops.matmul_impl(*xq, *wq, (1, 128), (128, 128), out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    print(f"profile case {name} done")
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "quantize", "dequantize"],
+                    help="run a few launches of one kernel on a reduced case (for ncu) and exit")
+    args = ap.parse_args()
+    if args.profile_case:
+        return run_profile_case(args.profile_case)
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -47,6 +47,7 @@ _SIGNATURES = {
     "pb_gemm_check": (_int, [_ptr]),
     "pb_transpose_bytes": (_int, [_ptr, _i64, _i64, _ptr, _ptr]),
     "pb_debug_division_check": (_int, [C.c_uint64, C.c_uint64, _ptr, _ptr]),
+    "pb_debug_gemm_profile": (_int, [C.POINTER(C.c_uint64), _ptr]),
 }
 
 # every symbol include/pratchya_b200.h declares (checked by the CPU test-suite)

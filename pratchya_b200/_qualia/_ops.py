@@ -159,9 +159,11 @@ def dequantize_impl_bwd(sc_fp8: torch.Tensor, sc_fp32: torch.Tensor, g_out: torc
 # ---- matmuls ---------------------------------------------------------------------------
 
 def _tensor_core_eligible(x_fp8, y_fp8, grid_x, grid_y) -> bool:
-    if x_fp8.dim() != 2 or y_fp8.dim() != 2:
+    """(1,128) activations (any leading dims, 8-block super-groups inside every slice)
+    times a 2-D (128,128) weight."""
+    if x_fp8.dim() < 2 or y_fp8.dim() != 2:
         return False
-    mm, kk = x_fp8.shape
+    mm, kk = x_fp8.shape[-2:]
     k2, nn = y_fp8.shape
     return (tuple(grid_x) == (1, 128) and tuple(grid_y) == (128, 128) and kk == k2
             and kk % 128 == 0 and nn % 128 == 0 and mm >= 1
@@ -206,7 +208,9 @@ def matmul_impl(x_fp8, x_sc8, x_sc32, y_fp8, y_sc8, y_sc32, block_grid_x, block_
     """
     _require_cuda(x_fp8, "matmul_impl input")
     if _tensor_core_eligible(x_fp8, y_fp8, block_grid_x, block_grid_y):
-        mm, kk = x_fp8.shape
+        lead = tuple(x_fp8.shape[:-2])
+        kk = x_fp8.shape[-1]
+        mm = x_fp8.numel() // kk          # leading slices stack into rows: their super-groups are 8 blocks each
         nn = y_fp8.shape[1]
         if y_fp8_t is None:
             y_fp8_t = transpose_bytes(y_fp8)
@@ -214,7 +218,8 @@ def matmul_impl(x_fp8, x_sc8, x_sc32, y_fp8, y_sc8, y_sc32, block_grid_x, block_
         y_sc8, y_sc32 = y_sc8.contiguous(), y_sc32.contiguous()
         a = _operand(x_fp8, x_sc8, x_sc32, mm, kk, (1, 128))
         b = _operand(y_fp8_t, y_sc8, y_sc32, nn, kk, (128, 128), transposed_blocks=1)
-        return gemm_tn(a, b, out_dtype, x_fp8.device)
+        d = gemm_tn(a, b, out_dtype, x_fp8.device)
+        return d.reshape(*lead, x_fp8.shape[-2], nn) if lead else d
     x = dequantize_impl(x_fp8, x_sc8, x_sc32, torch.float32, block_grid_x)
     y = dequantize_impl(y_fp8, y_sc8, y_sc32, torch.float32, block_grid_y)
     return _matmul_f32(x, y).to(out_dtype)

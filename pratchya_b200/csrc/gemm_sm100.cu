@@ -14,7 +14,8 @@
 // One CTA per SM, persistent over output tiles, warp-specialised:
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      TMEM allocator + MMA issuer (one elected lane)
-//   warps 2..   epilogue: TMEM -> registers, chunk promotion, store of D
+//   warps 4..   epilogue warpgroups: TMEM -> registers, chunk promotion, store of D
+// (warps 2-3 only fill warpgroup 0, which gives most of its registers to the epilogue.)
 // Every wait on an mbarrier is bounded; on expiry the kernel records PB_ERR_DEVICE_TIMEOUT in
 // a device status word, all roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda.h>
@@ -40,7 +41,7 @@ struct Cfg {
   static constexpr int kStages = BN == 128 ? 6 : 4;
   static constexpr int kAccBufs = BN == 128 ? 2 : 1;
   static constexpr int kEpiWarps = 4 * (BN / 128);
-  static constexpr int kThreads = 64 + 32 * kEpiWarps;
+  static constexpr int kThreads = 128 + 32 * kEpiWarps;   // warpgroup 0: producer, MMA, two idle warps; then the epilogue warpgroups
   static constexpr int kABytes = BM * BK;
   static constexpr int kBBytes = BN * BK;
   static constexpr int kSfaBytes = 512;
@@ -57,6 +58,11 @@ struct Cfg {
 };
 
 __device__ unsigned int g_gemm_status;   // 0, or PB_ERR_DEVICE_TIMEOUT once any bounded wait ran out
+// Cycle counters summed over CTAs when GemmParams::profile is set (diagnostics only):
+// 0 producer waits for a free stage, 1 MMA waits for a full stage, 2 MMA waits for a drained
+// accumulator, 3 epilogue (first warp) waits for an accumulated chunk, 4 epilogue busy,
+// 5 CTA lifetime, 6 MMA issue (non-wait), 7 CTAs counted
+__device__ unsigned long long g_gemm_prof[8];
 
 // ---- PTX wrappers ------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -129,6 +135,14 @@ __device__ __forceinline__ void tc_mma_block_scaled(uint32_t d_tmem, uint64_t a_
       "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
 }
+// timing experiment only: the same tile without block scaling (numerically wrong for scaled data)
+__device__ __forceinline__ void tc_mma_plain(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -139,6 +153,36 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
+}
+// the same load, written straight into 32 consecutive floats of an accumulator array
+template <int OFF>
+__device__ __forceinline__ void tc_ld32f(uint32_t taddr, float (&a)[128]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=f"(a[OFF + 0]), "=f"(a[OFF + 1]), "=f"(a[OFF + 2]), "=f"(a[OFF + 3]), "=f"(a[OFF + 4]), "=f"(a[OFF + 5]), "=f"(a[OFF + 6]), "=f"(a[OFF + 7]),
+        "=f"(a[OFF + 8]), "=f"(a[OFF + 9]), "=f"(a[OFF + 10]), "=f"(a[OFF + 11]), "=f"(a[OFF + 12]), "=f"(a[OFF + 13]), "=f"(a[OFF + 14]), "=f"(a[OFF + 15]),
+        "=f"(a[OFF + 16]), "=f"(a[OFF + 17]), "=f"(a[OFF + 18]), "=f"(a[OFF + 19]), "=f"(a[OFF + 20]), "=f"(a[OFF + 21]), "=f"(a[OFF + 22]), "=f"(a[OFF + 23]),
+        "=f"(a[OFF + 24]), "=f"(a[OFF + 25]), "=f"(a[OFF + 26]), "=f"(a[OFF + 27]), "=f"(a[OFF + 28]), "=f"(a[OFF + 29]), "=f"(a[OFF + 30]), "=f"(a[OFF + 31])
+      : "r"(taddr) : "memory");
+}
+// acc[OFF .. OFF+31] += r * fa * fb[column]
+template <int OFF>
+__device__ __forceinline__ void promote(float (&acc)[128], const uint32_t (&r)[32], float fa, float s_uni, const float* fbp, int uniform) {
+  if (uniform) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc[OFF + j] = fmaf(__uint_as_float(r[j]), s_uni, acc[OFF + j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 fb = __ldg(reinterpret_cast<const float4*>(fbp + OFF) + j);
+      acc[OFF + 4 * j + 0] = fmaf(__uint_as_float(r[4 * j + 0]) * fa, fb.x, acc[OFF + 4 * j + 0]);
+      acc[OFF + 4 * j + 1] = fmaf(__uint_as_float(r[4 * j + 1]) * fa, fb.y, acc[OFF + 4 * j + 1]);
+      acc[OFF + 4 * j + 2] = fmaf(__uint_as_float(r[4 * j + 2]) * fa, fb.z, acc[OFF + 4 * j + 2]);
+      acc[OFF + 4 * j + 3] = fmaf(__uint_as_float(r[4 * j + 3]) * fa, fb.w, acc[OFF + 4 * j + 3]);
+    }
+  }
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -172,6 +216,8 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int a_fmt, b_fmt;
   int d_dtype;
+  int fb_uniform;   // B's fp32 factor is the same for all rows of B within a chunk
+  int profile;
 };
 
 template <int BN>
@@ -208,22 +254,34 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int num_tiles = p.tiles_m * p.tiles_n;
 
+  const long long t_cta0 = p.profile ? clock64() : 0;
+  // With the 256-wide tile 384 threads start with 168 registers each; the epilogue needs ~220
+  // (128 accumulators + two 32-register load buffers), warpgroup 0 almost none.
+  if (warp < 4) {
+  if (BN == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
     if (lane == 0) {
       uint32_t it = 0;   // running stage counter across tiles
+      long long waited = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
         for (int kb = 0; kb < p.KB; ++kb, ++it) {
           const int s = it % C::kStages;
+          const long long t0 = p.profile ? clock64() : 0;
           if (!mbar_wait(bar_empty(s), ((it / C::kStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-          mbar_arrive_expect_tx(bar_full(s), C::kStageTx);
+          if (p.profile) waited += clock64() - t0;
+          // the scale-factor atom of a stage covers 4 k-blocks: only the first of them carries it
+          const bool with_sf = (kb & 3) == 0;
+          mbar_arrive_expect_tx(bar_full(s), C::kABytes + C::kBBytes + (with_sf ? C::kSfStage : 0));
           tma_load_2d(s_a + s * C::kABytes, &map_a, kb * BK, m0, bar_full(s));
           tma_load_2d(s_b + s * C::kBBytes, &map_b, kb * BK, n0, bar_full(s));
-          const int kg = kb >> 2;
-          bulk_load(s_sf + s * C::kSfStage, p.sfa + ((size_t)kg * (p.Mpad / 128) + m0 / 128) * 512, C::kSfaBytes, bar_full(s));
-          bulk_load(s_sf + s * C::kSfStage + C::kSfaBytes, p.sfb + ((size_t)kg * (p.Npad / 128) + n0 / 128) * 512, C::kSfbBytes, bar_full(s));
+          if (with_sf) {
+            const int kg = kb >> 2;
+            bulk_load(s_sf + s * C::kSfStage, p.sfa + ((size_t)kg * (p.Mpad / 128) + m0 / 128) * 512, C::kSfaBytes, bar_full(s));
+            bulk_load(s_sf + s * C::kSfStage + C::kSfaBytes, p.sfb + ((size_t)kg * (p.Npad / 128) + n0 / 128) * 512, C::kSfbBytes, bar_full(s));
+          }
         }
       }
       // Leave only when every copy this thread started has landed (bounded): the last
@@ -231,80 +289,121 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t issued = it;
       for (uint32_t j = (issued > (uint32_t)C::kStages ? issued - C::kStages : 0); j < issued; ++j)
         (void)mbar_wait(bar_full(j % C::kStages), (j / C::kStages) & 1u, abort_flag);
+      if (p.profile) atomicAdd(&g_gemm_prof[0], (unsigned long long)waited);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       uint32_t it = 0, g = 0;   // stage counter, chunk counter
+      long long wait_full = 0, wait_acc = 0;
+      const long long t_begin = p.profile ? clock64() : 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         for (int c = 0; c < p.nchunks && ok; ++c, ++g) {
           const int buf = g % C::kAccBufs;
+          long long t0 = p.profile ? clock64() : 0;
           if (!mbar_wait(bar_acc_empty(buf), ((g / C::kAccBufs) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          if (p.profile) wait_acc += clock64() - t0;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
           const int kb_end = min(p.KB, (c + 1) * p.P);
           for (int kb = c * p.P; kb < kb_end; ++kb, ++it) {
             const int s = it % C::kStages;
+            t0 = p.profile ? clock64() : 0;
             if (!mbar_wait(bar_full(s), (it / C::kStages) & 1u, abort_flag)) { ok = false; break; }
+            if (p.profile) wait_full += clock64() - t0;
             tc_fence_after();
-            const uint32_t sf_col = tmem_base + C::kSfColBase + (it & 1u) * C::kSfCols;
-            const uint32_t sf_smem = s_sf + s * C::kSfStage;
-            tc_cp_sf(sf_col, sf_desc(sf_smem));
+            // scale factors of k-blocks 4j..4j+3 live in TMEM set j & 1; the MMAs of set j-2 were
+            // issued (and are ordered) before this copy
+            const uint32_t sf_col = tmem_base + C::kSfColBase + ((uint32_t)(kb >> 2) & 1u) * C::kSfCols;
+            if ((kb & 3) == 0) {
+              const uint32_t sf_smem = s_sf + s * C::kSfStage;
+              tc_cp_sf(sf_col, sf_desc(sf_smem));
 #pragma unroll
-            for (int j = 0; j < BN / 128; ++j) tc_cp_sf(sf_col + 4 + 4 * j, sf_desc(sf_smem + C::kSfaBytes + 512 * j));
+              for (int j = 0; j < BN / 128; ++j) tc_cp_sf(sf_col + 4 + 4 * j, sf_desc(sf_smem + C::kSfaBytes + 512 * j));
+            }
             const uint32_t idesc = instr_desc(BN, p.a_fmt, p.b_fmt, (uint32_t)(kb & 3));
             const uint64_t a_desc = operand_desc(s_a + s * C::kABytes);
             const uint64_t b_desc = operand_desc(s_b + s * C::kBBytes);
+            if (p.profile == 2) {
+              const uint32_t plain = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k)
+                tc_mma_plain(d_tmem, a_desc + (uint64_t)(k * UMMA_K >> 4), b_desc + (uint64_t)(k * UMMA_K >> 4), plain,
+                             (kb > c * p.P || k > 0) ? 1u : 0u);
+            } else {
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k)
               tc_mma_block_scaled(d_tmem, a_desc + (uint64_t)(k * UMMA_K >> 4), b_desc + (uint64_t)(k * UMMA_K >> 4), idesc,
                                   sf_col, sf_col + 4, (kb > c * p.P || k > 0) ? 1u : 0u);
+            }
             tc_commit(bar_empty(s));          // frees the stage once these MMAs have read it
           }
           if (ok) tc_commit(bar_acc_full(buf));   // chunk accumulated
         }
       }
+      if (p.profile) {
+        atomicAdd(&g_gemm_prof[1], (unsigned long long)wait_full);
+        atomicAdd(&g_gemm_prof[2], (unsigned long long)wait_acc);
+        atomicAdd(&g_gemm_prof[6], (unsigned long long)(clock64() - t_begin - wait_full - wait_acc));
+      }
     }
+  }
   } else {
     // ------------------------------------------------------------- epilogue
-    const int ew = warp - 2;
+    if (BN == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    const int ew = warp - 4;
     const int quarter = warp & 3;             // TMEM lanes this warp may touch
     const int col_half = ew >> 2;             // which 128-column slice of the tile
     const int row_in_tile = quarter * 32 + lane;
     uint32_t g = 0;
     bool ok = true;
+    long long wait_chunk = 0;
+    const long long t_begin = p.profile ? clock64() : 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN + col_half * 128;
       float acc[128];
-#pragma unroll
-      for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
       for (int c = 0; c < p.nchunks; ++c, ++g) {
         const int buf = g % C::kAccBufs;
+        const long long t0 = p.profile ? clock64() : 0;
         if (!mbar_wait(bar_acc_full(buf), (g / C::kAccBufs) & 1u, abort_flag)) { ok = false; break; }
+        if (p.profile) wait_chunk += clock64() - t0;
         tc_fence_after();
         const float fa = __ldg(p.fa + (size_t)c * p.Mpad + m0 + row_in_tile);
-        const float4* fb4 = reinterpret_cast<const float4*>(p.fb + (size_t)c * p.Npad + n0);
+        const float* fbp = p.fb + (size_t)c * p.Npad + n0;
+        const float s_uni = fa * __ldg(fbp);      // the whole factor when B's fp32 factor does not vary over the tile
         const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + col_half * 128;
-#pragma unroll
-        for (int part = 0; part < 4; ++part) {
-          uint32_t r[32];
-          tc_ld32(t_addr + part * 32, r);
+        auto release = [&]() {
+          // all of this warp's reads of the buffer are done: hand it back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_acc_empty(buf));
+        };
+        if (c == 0) {
+          // First chunk of a tile: straight into the accumulator registers, so the buffer goes
+          // back to the MMA warp before any arithmetic.
+          tc_ld32f<0>(t_addr, acc); tc_ld32f<32>(t_addr + 32, acc); tc_ld32f<64>(t_addr + 64, acc); tc_ld32f<96>(t_addr + 96, acc);
           tc_wait_ld();
-          if (part == 3) {
-            // all of this warp's reads of the buffer are done: hand it back to the MMA warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_acc_empty(buf));
-          }
+          release();
+          if (p.fb_uniform) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float4 fb = __ldg(fb4 + part * 8 + j);
-            acc[part * 32 + 4 * j + 0] = fmaf(__uint_as_float(r[4 * j + 0]) * fa, fb.x, acc[part * 32 + 4 * j + 0]);
-            acc[part * 32 + 4 * j + 1] = fmaf(__uint_as_float(r[4 * j + 1]) * fa, fb.y, acc[part * 32 + 4 * j + 1]);
-            acc[part * 32 + 4 * j + 2] = fmaf(__uint_as_float(r[4 * j + 2]) * fa, fb.z, acc[part * 32 + 4 * j + 2]);
-            acc[part * 32 + 4 * j + 3] = fmaf(__uint_as_float(r[4 * j + 3]) * fa, fb.w, acc[part * 32 + 4 * j + 3]);
+            for (int j = 0; j < 128; ++j) acc[j] *= s_uni;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float4 fb = __ldg(reinterpret_cast<const float4*>(fbp) + j);
+              acc[4 * j + 0] = acc[4 * j + 0] * fa * fb.x; acc[4 * j + 1] = acc[4 * j + 1] * fa * fb.y;
+              acc[4 * j + 2] = acc[4 * j + 2] * fa * fb.z; acc[4 * j + 3] = acc[4 * j + 3] * fa * fb.w;
+            }
           }
+        } else {
+          // Later chunks: 32-column parts, the load of part i+1 in flight under the arithmetic of part i.
+          uint32_t r0[32], r1[32];
+          tc_ld32(t_addr, r0);
+          tc_wait_ld(); tc_ld32(t_addr + 32, r1); promote<0>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
+          tc_wait_ld(); tc_ld32(t_addr + 64, r0); promote<32>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
+          tc_wait_ld(); tc_ld32(t_addr + 96, r1); promote<64>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
+          tc_wait_ld(); release();                promote<96>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
         }
       }
       if (!ok) break;
@@ -340,10 +439,18 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
     }
+    if (p.profile && warp == 4 && lane == 0) {
+      atomicAdd(&g_gemm_prof[3], (unsigned long long)wait_chunk);
+      atomicAdd(&g_gemm_prof[4], (unsigned long long)(clock64() - t_begin - wait_chunk));
+    }
   }
 
   tc_fence_before();
   __syncthreads();
+  if (p.profile && threadIdx.x == 0) {
+    atomicAdd(&g_gemm_prof[5], (unsigned long long)(clock64() - t_cta0));
+    atomicAdd(&g_gemm_prof[7], 1ull);
+  }
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
@@ -430,6 +537,7 @@ int make_operand_map(CUtensorMap* map, const void* q, int64_t rows, int64_t dept
 struct OperandPlan {
   int64_t Ksg, Mgroups;
   int P;      // largest run of k-blocks with a constant fp32 factor for every row
+  bool row_uniform;   // the fp32 factor of a chunk is the same for every row of the operand
 };
 
 int plan_operand(const pb_operand* o, const char* name, OperandPlan* plan) {
@@ -465,6 +573,9 @@ int plan_operand(const pb_operand* o, const char* name, OperandPlan* plan) {
     }
   }
   plan->P = P;
+  // one super-group in all, or (128,128) blocks numbered along the rows first with whole
+  // block-rows per super-group: every row then sees the same fp32 amax in a given k-block
+  plan->row_uniform = (g.M == 1) || (o->transposed_blocks && g.K % (o->rows / 128) == 0);
   return PB_OK;
 }
 
@@ -477,10 +588,15 @@ struct GemmPlan {
 int pick_bn() {
   static int bn = [] {
     const char* e = getenv("PB_GEMM_BN");
-    const int v = e ? atoi(e) : 128;
-    return v == 256 ? 256 : 128;
+    const int v = e ? atoi(e) : 256;
+    return v == 128 ? 128 : 256;
   }();
   return bn;
+}
+
+int profile_level() {   // 0 off, 1 cycle counters, 2 counters + unscaled MMA (timing experiment)
+  static const int level = [] { const char* e = getenv("PB_GEMM_PROFILE"); return e ? atoi(e) : 0; }();
+  return level;
 }
 
 int make_plan(const pb_operand* a, const pb_operand* b, GemmPlan* gp) {
@@ -576,6 +692,8 @@ extern "C" int pb_gemm_tn(const pb_operand* a, const pb_operand* b, void* d, int
   p.Mpad = gp.Mpad; p.Npad = gp.Npad;
   p.tiles_m = gp.Mpad / BM; p.tiles_n = (int)((b->rows + gp.BN - 1) / gp.BN);
   p.a_fmt = a->format; p.b_fmt = b->format; p.d_dtype = d_dtype;
+  p.fb_uniform = gp.pb.row_uniform ? 1 : 0;
+  p.profile = profile_level();
   return gp.BN == 256 ? launch_gemm<256>(ma, mb, p, st) : launch_gemm<128>(ma, mb, p, st);
 }
 
@@ -587,5 +705,16 @@ extern "C" int pb_gemm_check(void* stream) {
     PB_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(zero)));
     return fail((int)v, "a bounded device-side wait in the GEMM kernel ran out");
   }
+  return PB_OK;
+}
+
+// Not part of the reference's surface: diagnostics.  Copies (and clears) the eight cycle
+// counters the GEMM kernel accumulates when the environment sets PB_GEMM_PROFILE=1.
+extern "C" PB_API int pb_debug_gemm_profile(unsigned long long* out8, void* stream) {
+  if (!out8) return fail(PB_ERR_NULL_POINTER, "pb_debug_gemm_profile: out8 must be non-null");
+  PB_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  unsigned long long zero[8] = {0};
+  PB_CUDA_TRY(cudaMemcpyFromSymbol(out8, g_gemm_prof, sizeof(zero)));
+  PB_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_prof, zero, sizeof(zero)));
   return PB_OK;
 }
