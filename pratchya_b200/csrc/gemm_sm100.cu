@@ -220,6 +220,39 @@ struct GemmParams {
   int profile;
 };
 
+
+// One thread stores its row segment of 128 output columns (bf16 or f32), clipped to [M, N].
+__device__ __forceinline__ void store_row_segment(const GemmParams& p, const float (&acc)[128], int row, int n0) {
+  if (row >= p.M) return;
+  if (p.d_dtype == PB_BF16) {
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.d) + (size_t)row * p.ldd + n0;
+    const bool vec = ((p.ldd & 7) == 0) && (n0 + 128 <= p.N) && ((reinterpret_cast<uintptr_t>(p.d) & 15) == 0);
+    if (vec) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        *reinterpret_cast<uint4*>(dst + 8 * j) =
+            make_uint4(pack_bf16x2(acc[8 * j], acc[8 * j + 1]), pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3]),
+                       pack_bf16x2(acc[8 * j + 4], acc[8 * j + 5]), pack_bf16x2(acc[8 * j + 6], acc[8 * j + 7]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 128; ++j)
+        if (n0 + j < p.N) dst[j] = __float2bfloat16_rn(acc[j]);
+    }
+  } else {
+    float* dst = static_cast<float*>(p.d) + (size_t)row * p.ldd + n0;
+    const bool vec = ((p.ldd & 3) == 0) && (n0 + 128 <= p.N) && ((reinterpret_cast<uintptr_t>(p.d) & 15) == 0);
+    if (vec) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        *reinterpret_cast<float4*>(dst + 4 * j) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 128; ++j)
+        if (n0 + j < p.N) dst[j] = acc[j];
+    }
+  }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
@@ -274,6 +307,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (p.profile) waited += clock64() - t0;
           // the scale-factor atom of a stage covers 4 k-blocks: only the first of them carries it
           const bool with_sf = (kb & 3) == 0;
+          if (p.profile == 3) { mbar_arrive(bar_full(s)); continue; }   // timing experiment: no data movement
           mbar_arrive_expect_tx(bar_full(s), C::kABytes + C::kBBytes + (with_sf ? C::kSfStage : 0));
           tma_load_2d(s_a + s * C::kABytes, &map_a, kb * BK, m0, bar_full(s));
           tma_load_2d(s_b + s * C::kBBytes, &map_b, kb * BK, n0, bar_full(s));
@@ -365,13 +399,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       float acc[128];
       for (int c = 0; c < p.nchunks; ++c, ++g) {
         const int buf = g % C::kAccBufs;
+        // the chunk's fp32 factors do not depend on the MMAs: fetch them before waiting
+        const float fa = __ldg(p.fa + (size_t)c * p.Mpad + m0 + row_in_tile);
+        const float* fbp = p.fb + (size_t)c * p.Npad + n0;
+        const float s_uni = fa * __ldg(fbp);      // the whole factor when B's fp32 factor does not vary over the tile
         const long long t0 = p.profile ? clock64() : 0;
         if (!mbar_wait(bar_acc_full(buf), (g / C::kAccBufs) & 1u, abort_flag)) { ok = false; break; }
         if (p.profile) wait_chunk += clock64() - t0;
         tc_fence_after();
-        const float fa = __ldg(p.fa + (size_t)c * p.Mpad + m0 + row_in_tile);
-        const float* fbp = p.fb + (size_t)c * p.Npad + n0;
-        const float s_uni = fa * __ldg(fbp);      // the whole factor when B's fp32 factor does not vary over the tile
         const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + col_half * 128;
         auto release = [&]() {
           // all of this warp's reads of the buffer are done: hand it back to the MMA warp
@@ -407,37 +442,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
       if (!ok) break;
-      // store one row segment of 128 columns per thread
-      const int row = m0 + row_in_tile;
-      if (row < p.M) {
-        if (p.d_dtype == PB_BF16) {
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.d) + (size_t)row * p.ldd + n0;
-          const bool vec = ((p.ldd & 7) == 0) && (n0 + 128 <= p.N) && ((reinterpret_cast<uintptr_t>(p.d) & 15) == 0);
-          if (vec) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              *reinterpret_cast<uint4*>(dst + 8 * j) =
-                  make_uint4(pack_bf16x2(acc[8 * j], acc[8 * j + 1]), pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3]),
-                             pack_bf16x2(acc[8 * j + 4], acc[8 * j + 5]), pack_bf16x2(acc[8 * j + 6], acc[8 * j + 7]));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 128; ++j)
-              if (n0 + j < p.N) dst[j] = __float2bfloat16_rn(acc[j]);
-          }
-        } else {
-          float* dst = static_cast<float*>(p.d) + (size_t)row * p.ldd + n0;
-          const bool vec = ((p.ldd & 3) == 0) && (n0 + 128 <= p.N) && ((reinterpret_cast<uintptr_t>(p.d) & 15) == 0);
-          if (vec) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              *reinterpret_cast<float4*>(dst + 4 * j) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 128; ++j)
-              if (n0 + j < p.N) dst[j] = acc[j];
-          }
-        }
-      }
+      store_row_segment(p, acc, m0 + row_in_tile, n0);
     }
     if (p.profile && warp == 4 && lane == 0) {
       atomicAdd(&g_gemm_prof[3], (unsigned long long)wait_chunk);
@@ -454,6 +459,262 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+
+// ==============================================================================================
+// CTA-pair variant: tcgen05.mma.cta_group::2 on 256x256 output tiles.  Each CTA of a 2-CTA
+// cluster owns 128 rows of the tile (its own TMEM accumulator) and stages its own 128 rows of A
+// and its own 128 of the tile's 256 rows of B, so a k-block costs each SM 32 KB of TMA writes
+// and 32 KB of tensor-core reads of shared memory instead of 48 + 48 KB: the single-CTA tile is
+// bound by that shared-memory traffic.  The leader CTA (cluster rank 0) issues every MMA and
+// scale-factor copy for the pair; all TMA loads of both CTAs complete on the leader's barrier.
+struct Cfg2 {
+  static constexpr int BN = 256;
+  static constexpr int kStages = 6;
+  static constexpr int kEpiWarps = 8;
+  static constexpr int kThreads = 128 + 32 * kEpiWarps;
+  static constexpr int kABytes = BM * BK;            // this CTA's 128 rows of A
+  static constexpr int kBBytes = 128 * BK;           // this CTA's half of the tile's B rows
+  static constexpr int kSfaBytes = 512;              // scale factors of this CTA's A rows
+  static constexpr int kSfbBytes = 1024;             // scale factors of all 256 B rows (each CTA needs them all)
+  static constexpr int kSfStage = kSfaBytes + kSfbBytes;
+  static constexpr int kSfCols = 4 + BN / 32;
+  static constexpr int kSfColBase = BN;
+  static constexpr int kOffB = kStages * kABytes;
+  static constexpr int kOffSf = kOffB + kStages * kBBytes;
+  static constexpr int kOffBar = kOffSf + kStages * kSfStage;
+  static constexpr int kNumBars = 2 * kStages + 2;
+  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load whose completion is signalled on a barrier of either CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tc2_commit(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tc2_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc2_mma_block_scaled(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                     uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
+// as instr_desc, for the pair: M = 256
+__device__ __forceinline__ uint32_t instr_desc_pair(int a_fmt, int b_fmt, uint32_t sf_id) {
+  return (sf_id << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(256 >> 3) << 17) | (1u << 23) |
+         ((uint32_t)(256 >> 4) << 24) | (sf_id << 29);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg2::kThreads, 1)
+gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                    const GemmParams p) {
+  using C = Cfg2;
+  constexpr int BN = C::BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t s_a = s_base, s_b = s_base + C::kOffB, s_sf = s_base + C::kOffSf, s_bar = s_base + C::kOffBar;
+  auto bar_full = [&](int s) { return s_bar + 8u * s; };                       // used in the leader only
+  auto bar_empty = [&](int s) { return s_bar + 8u * (C::kStages + s); };       // one per CTA
+  const uint32_t bar_acc_full = s_bar + 8u * (2 * C::kStages);                 // one per CTA
+  const uint32_t bar_acc_empty = s_bar + 8u * (2 * C::kStages + 1);            // used in the leader only
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffBar + C::kNumBars * 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+    mbar_init(bar_acc_full, 1);
+    mbar_init(bar_acc_empty, 2 * C::kEpiWarps);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // both CTAs' barriers are initialised before any remote signal
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;          // 256 x 256 tiles
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int m0 = (tile % p.tiles_m) * 256 + (int)rank * 128;     // this CTA's rows of A and D
+        const int n0 = (tile / p.tiles_m) * BN;
+        for (int kb = 0; kb < p.KB; ++kb, ++it) {
+          const int s = it % C::kStages;
+          if (!mbar_wait(bar_empty(s), ((it / C::kStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          const bool with_sf = (kb & 3) == 0;
+          const uint32_t full = map_to_cta(bar_full(s), 0);
+          if (p.profile == 3) { if (leader) mbar_arrive(bar_full(s)); continue; }   // timing experiment: no data movement
+          if (leader) mbar_arrive_expect_tx(bar_full(s), 2 * (C::kABytes + C::kBBytes + (with_sf ? C::kSfStage : 0)));
+          tma_load_2d_pair(s_a + s * C::kABytes, &map_a, kb * BK, m0, full);
+          tma_load_2d_pair(s_b + s * C::kBBytes, &map_b, kb * BK, n0 + (int)rank * 128, full);
+          if (with_sf) {
+            const int kg = kb >> 2;
+            tma_load_2d_pair(s_sf + s * C::kSfStage, &map_sfa, 0, kg * (p.Mpad / 128) + m0 / 128, full);
+            tma_load_2d_pair(s_sf + s * C::kSfStage + C::kSfaBytes, &map_sfb, 0, kg * (p.Npad / 128) + n0 / 128, full);
+          }
+        }
+      }
+    }
+  } else if (warp == 1 && leader) {
+    // ------------------------------------------------------------- MMA issuer (leader CTA only)
+    if (lane == 0) {
+      uint32_t it = 0, g = 0;
+      long long wait_full = 0, wait_acc = 0;
+      const long long t_begin = p.profile ? clock64() : 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        for (int c = 0; c < p.nchunks && ok; ++c, ++g) {
+          long long t0 = p.profile ? clock64() : 0;
+          if (!mbar_wait(bar_acc_empty, (g & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          if (p.profile) wait_acc += clock64() - t0;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base;
+          const int kb_end = min(p.KB, (c + 1) * p.P);
+          for (int kb = c * p.P; kb < kb_end; ++kb, ++it) {
+            const int s = it % C::kStages;
+            t0 = p.profile ? clock64() : 0;
+            if (!mbar_wait(bar_full(s), (it / C::kStages) & 1u, abort_flag)) { ok = false; break; }
+            if (p.profile) wait_full += clock64() - t0;
+            tc_fence_after();
+            const uint32_t sf_col = tmem_base + C::kSfColBase + ((uint32_t)(kb >> 2) & 1u) * C::kSfCols;
+            if ((kb & 3) == 0) {
+              const uint32_t sf_smem = s_sf + s * C::kSfStage;
+              tc2_cp_sf(sf_col, sf_desc(sf_smem));
+              tc2_cp_sf(sf_col + 4, sf_desc(sf_smem + C::kSfaBytes));
+              tc2_cp_sf(sf_col + 8, sf_desc(sf_smem + C::kSfaBytes + 512));
+            }
+            const uint32_t idesc = instr_desc_pair(p.a_fmt, p.b_fmt, (uint32_t)(kb & 3));
+            const uint64_t a_desc = operand_desc(s_a + s * C::kABytes);
+            const uint64_t b_desc = operand_desc(s_b + s * C::kBBytes);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              tc2_mma_block_scaled(d_tmem, a_desc + (uint64_t)(k * UMMA_K >> 4), b_desc + (uint64_t)(k * UMMA_K >> 4), idesc,
+                                   sf_col, sf_col + 4, (kb > c * p.P || k > 0) ? 1u : 0u);
+            // free the stage in both CTAs once these MMAs have read it
+            tc2_commit(bar_empty(s));
+            tc2_commit(map_to_cta(bar_empty(s), 1));
+          }
+          if (ok) {
+            tc2_commit(bar_acc_full);
+            tc2_commit(map_to_cta(bar_acc_full, 1));
+          }
+        }
+      }
+      if (p.profile) {
+        atomicAdd(&g_gemm_prof[1], (unsigned long long)wait_full);
+        atomicAdd(&g_gemm_prof[2], (unsigned long long)wait_acc);
+        atomicAdd(&g_gemm_prof[6], (unsigned long long)(clock64() - t_begin - wait_full - wait_acc));
+        atomicAdd(&g_gemm_prof[7], 1ull);
+      }
+    }
+  }
+  } else {
+    // ------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    const int ew = warp - 4;
+    const int quarter = warp & 3;
+    const int col_half = ew >> 2;
+    const int row_in_tile = quarter * 32 + lane;
+    const uint32_t acc_empty_leader = map_to_cta(bar_acc_empty, 0);
+    uint32_t g = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      const int m0 = (tile % p.tiles_m) * 256 + (int)rank * 128, n0 = (tile / p.tiles_m) * BN + col_half * 128;
+      float acc[128];
+      for (int c = 0; c < p.nchunks; ++c, ++g) {
+        const float fa = __ldg(p.fa + (size_t)c * p.Mpad + m0 + row_in_tile);
+        const float* fbp = p.fb + (size_t)c * p.Npad + n0;
+        const float s_uni = fa * __ldg(fbp);
+        if (!mbar_wait(bar_acc_full, g & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + col_half * 128;
+        auto release = [&]() {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        };
+        if (c == 0) {
+          tc_ld32f<0>(t_addr, acc); tc_ld32f<32>(t_addr + 32, acc); tc_ld32f<64>(t_addr + 64, acc); tc_ld32f<96>(t_addr + 96, acc);
+          tc_wait_ld();
+          release();
+          if (p.fb_uniform) {
+#pragma unroll
+            for (int j = 0; j < 128; ++j) acc[j] *= s_uni;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float4 fb = __ldg(reinterpret_cast<const float4*>(fbp) + j);
+              acc[4 * j + 0] = acc[4 * j + 0] * fa * fb.x; acc[4 * j + 1] = acc[4 * j + 1] * fa * fb.y;
+              acc[4 * j + 2] = acc[4 * j + 2] * fa * fb.z; acc[4 * j + 3] = acc[4 * j + 3] * fa * fb.w;
+            }
+          }
+        } else {
+          uint32_t r0[32], r1[32];
+          tc_ld32(t_addr, r0);
+          tc_wait_ld(); tc_ld32(t_addr + 32, r1); promote<0>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
+          tc_wait_ld(); tc_ld32(t_addr + 64, r0); promote<32>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
+          tc_wait_ld(); tc_ld32(t_addr + 96, r1); promote<64>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
+          tc_wait_ld(); release();                promote<96>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
+        }
+      }
+      if (!ok) break;
+      store_row_segment(p, acc, m0 + row_in_tile, n0);
+    }
+  }
+
+  // Neither CTA may leave (or free TMEM) while its partner can still signal its barriers, read
+  // its shared memory or write its TMEM.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -534,6 +795,21 @@ int make_operand_map(CUtensorMap* map, const void* q, int64_t rows, int64_t dept
   return PB_OK;
 }
 
+// Scale-factor atoms as a 2-D tensor of 32-bit words: [atoms, 128 words]; a box is `atoms_per_box` atoms.
+int make_sf_map(CUtensorMap* map, const void* sf, int64_t atoms, int atoms_per_box) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {128, (cuuint64_t)atoms};
+  const cuuint64_t strides[1] = {512};
+  const cuuint32_t box[2] = {128, (cuuint32_t)atoms_per_box};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(sf), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled (scale factors) failed with CUresult %d", (int)r);
+  return PB_OK;
+}
+
 struct OperandPlan {
   int64_t Ksg, Mgroups;
   int P;      // largest run of k-blocks with a constant fp32 factor for every row
@@ -582,8 +858,14 @@ int plan_operand(const pb_operand* o, const char* name, OperandPlan* plan) {
 struct GemmPlan {
   OperandPlan pa, pb;
   int P, KB, KG, nchunks, Mpad, Npad, BN;
+  bool pair;      // CTA-pair kernel (256 x 256 tiles) instead of the single-CTA one
   size_t off_sfa, off_sfb, off_fa, off_fb, total;
 };
+
+bool pick_pair() {      // PB_GEMM_MODE=pair selects the CTA-pair kernel (the single-CTA one measures faster so far)
+  static const bool pair = [] { const char* e = getenv("PB_GEMM_MODE"); return e && e[0] == 'p'; }();
+  return pair;
+}
 
 int pick_bn() {
   static int bn = [] {
@@ -605,13 +887,14 @@ int make_plan(const pb_operand* a, const pb_operand* b, GemmPlan* gp) {
   if (int s = plan_operand(b, "B", &gp->pb)) return s;
   if (a->depth != b->depth)
     return fail(PB_ERR_BAD_SHAPE, "pb_gemm_tn: contraction lengths differ (%lld vs %lld)", (long long)a->depth, (long long)b->depth);
-  gp->BN = pick_bn();
+  gp->pair = pick_pair() && a->rows > 128;
+  gp->BN = gp->pair ? 256 : pick_bn();
   gp->P = gp->pa.P < gp->pb.P ? gp->pa.P : gp->pb.P;
   gp->KB = (int)(a->depth / BK);
   if (gp->P > gp->KB) gp->P = gp->KB;
   gp->KG = (gp->KB + 3) / 4;
   gp->nchunks = (gp->KB + gp->P - 1) / gp->P;
-  gp->Mpad = (int)((a->rows + 127) / 128 * 128);
+  gp->Mpad = (int)((a->rows + 255) / 256 * 256);
   gp->Npad = (int)((b->rows + 255) / 256 * 256);
   auto align = [](size_t v) { return (v + 255) & ~(size_t)255; };
   size_t off = 0;
@@ -653,6 +936,27 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
   return PB_OK;
 }
 
+int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msfa, const CUtensorMap& msfb,
+                     const GemmParams& p, cudaStream_t st) {
+  static std::mutex mu;
+  static bool configured[64] = {false};
+  int dev = 0;
+  PB_CUDA_TRY(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      PB_CUDA_TRY(cudaFuncSetAttribute(gemm_tn_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::kSmemBytes));
+      configured[dev] = true;
+    }
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int pairs = sm_count() / 2;
+  const int grid = 2 * (tiles < pairs ? tiles : pairs);
+  gemm_tn_pair_kernel<<<grid, Cfg2::kThreads, Cfg2::kSmemBytes, st>>>(ma, mb, msfa, msfb, p);
+  PB_LAUNCH_CHECK("gemm_tn_pair_kernel");
+  return PB_OK;
+}
+
 }  // namespace
 }  // namespace pb
 
@@ -682,7 +986,7 @@ extern "C" int pb_gemm_tn(const pb_operand* a, const pb_operand* b, void* d, int
 
   CUtensorMap ma, mb;
   if (int s = make_operand_map(&ma, a->q, a->rows, a->depth, BM)) return s;
-  if (int s = make_operand_map(&mb, b->q, b->rows, b->depth, gp.BN)) return s;
+  if (int s = make_operand_map(&mb, b->q, b->rows, b->depth, gp.pair ? 128 : gp.BN)) return s;
 
   GemmParams p;
   p.sfa = ws + gp.off_sfa; p.sfb = ws + gp.off_sfb;
@@ -690,10 +994,16 @@ extern "C" int pb_gemm_tn(const pb_operand* a, const pb_operand* b, void* d, int
   p.d = d; p.ldd = ldd;
   p.M = (int)a->rows; p.N = (int)b->rows; p.KB = gp.KB; p.P = gp.P; p.nchunks = gp.nchunks;
   p.Mpad = gp.Mpad; p.Npad = gp.Npad;
-  p.tiles_m = gp.Mpad / BM; p.tiles_n = (int)((b->rows + gp.BN - 1) / gp.BN);
+  p.tiles_m = gp.Mpad / (gp.pair ? 256 : BM); p.tiles_n = (int)((b->rows + gp.BN - 1) / gp.BN);
   p.a_fmt = a->format; p.b_fmt = b->format; p.d_dtype = d_dtype;
   p.fb_uniform = gp.pb.row_uniform ? 1 : 0;
   p.profile = profile_level();
+  if (gp.pair) {
+    CUtensorMap msfa, msfb;
+    if (int s = make_sf_map(&msfa, ws + gp.off_sfa, (int64_t)gp.KG * (gp.Mpad / 128), 1)) return s;
+    if (int s = make_sf_map(&msfb, ws + gp.off_sfb, (int64_t)gp.KG * (gp.Npad / 128), 2)) return s;
+    return launch_gemm_pair(ma, mb, msfa, msfb, p, st);
+  }
   return gp.BN == 256 ? launch_gemm<256>(ma, mb, p, st) : launch_gemm<128>(ma, mb, p, st);
 }
 
