@@ -74,6 +74,20 @@ PB_API int pb_quantize(const void* x, int x_dtype, int64_t batch, int64_t rows, 
                 void* q, uint8_t* sc8, float* sc32,
                 void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- quantize for callers that can neither pass nor allocate scratch memory.  It has no
+ *      counterpart in the reference.  Same arguments and results as pb_quantize, minus the
+ *      workspace: the scratch is a 512 KiB device array built into the library (held by every
+ *      GPU that loads it until the process exits), so batch * (rows*cols/(a*b)) must not exceed
+ *      65536 blocks; larger inputs return PB_ERR_UNSUPPORTED.  The call allocates nothing
+ *      (no cudaMalloc/cudaFree, no allocating library routine).  The first call on each device
+ *      looks up the array's device address (cudaGetSymbolAddress) and caches it: make that
+ *      first call outside any stream capture.  All calls share the one array, which keeps what
+ *      the last call wrote; each call clears what it reads before use, but two calls that
+ *      overlap on the GPU (different streams) race on it. */
+PB_API int pb_quantize_static(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols,
+                       int a, int b, int out_format,
+                       void* q, uint8_t* sc8, float* sc32, void* stream);
+
 /* ---- quantize of the transpose without materialising it: the triple of
  *      quantize_impl(swapaxes(x,-1,-2), (1, b)) as used by fp8_matmul_bwd,
  *      _qarr.py:784-789.  x is [batch, rows, cols]; q is [batch, cols, rows]. */

@@ -38,6 +38,7 @@ _SIGNATURES = {
     "pb_group_geometry": (_int, [_i64, _i64, _int, _int, C.POINTER(_i64), C.POINTER(_i64)]),
     "pb_quantize_workspace_size": (_sz, [_i64, _i64, _i64, _int, _int]),
     "pb_quantize": (_int, [_ptr, _int, _i64, _i64, _i64, _int, _int, _int, _ptr, _ptr, _ptr, _ptr, _sz, _ptr]),
+    "pb_quantize_static": (_int, [_ptr, _int, _i64, _i64, _i64, _int, _int, _int, _ptr, _ptr, _ptr, _ptr]),
     "pb_quantize_transposed_workspace_size": (_sz, [_i64, _i64, _i64, _int]),
     "pb_quantize_transposed": (_int, [_ptr, _int, _i64, _i64, _i64, _int, _int, _ptr, _ptr, _ptr, _ptr, _sz, _ptr]),
     "pb_dequantize": (_int, [_ptr, _int, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _int, _ptr, _ptr]),

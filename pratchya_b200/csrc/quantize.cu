@@ -8,6 +8,8 @@
 //     No scratch memory.
 //   * generic: any grid.  Three small kernels around a scratch buffer
 //     (per-block amax bits, then per-block divisors).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace pb {
@@ -354,4 +356,60 @@ extern "C" int pb_quantize(const void* x, int x_dtype, int64_t batch, int64_t ro
   }
   return vec4 ? launch_generic<float, 4>((const float*)x, g, batch, out_format, (uint8_t*)q, sc8, sc32, workspace, st)
               : launch_generic<float, 1>((const float*)x, g, batch, out_format, (uint8_t*)q, sc8, sc32, workspace, st);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Quantize without any caller-provided or library-allocated scratch.
+//
+// Some hosts of this library may not allocate device memory around a call: an XLA custom call
+// that was registered without a scratch result, code running while a CUDA graph is being
+// captured or replayed with fixed buffers, or a runtime whose allocator must not be re-entered
+// from inside an op.  For them the scratch the generic quantizer needs (8 bytes per block: the
+// block amax bits and the per-block divisors) lives in a fixed device array that is part of this
+// library's image.  Every GPU that loads the library holds these 512 KiB until the process exits.
+namespace pb {
+namespace {
+
+constexpr int64_t kStaticScratchBlocks = 65536;          // largest batch * Nb this entry point accepts
+static __device__ __align__(256) unsigned char g_quantize_scratch[kStaticScratchBlocks * 8];
+
+// Device address of g_quantize_scratch on the current device.  In host code the array's name
+// is only a handle for the runtime, not an address a kernel can use; the real address is
+// looked up once per device (with that device current) and cached.
+int static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  PB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(PB_ERR_UNSUPPORTED, "pb_quantize_static: device ordinal %d is out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* p = nullptr;
+    PB_CUDA_TRY(cudaGetSymbolAddress(&p, g_quantize_scratch));
+    cached[dev] = p;
+  }
+  *out = cached[dev];
+  return PB_OK;
+}
+
+}  // namespace
+}  // namespace pb
+
+extern "C" int pb_quantize_static(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols,
+                                  int a, int b, int out_format, void* q, uint8_t* sc8, float* sc32, void* stream) {
+  Geometry g;
+  if (batch <= 0) return fail(PB_ERR_BAD_SHAPE, "pb_quantize_static: batch=%lld must be positive", (long long)batch);
+  if (int s = make_geometry(rows, cols, a, b, &g)) return s;
+  if (row128_eligible(g))      // this grid needs no scratch at all
+    return pb_quantize(x, x_dtype, batch, rows, cols, a, b, out_format, q, sc8, sc32, nullptr, 0, stream);
+  if (batch * g.Nb > kStaticScratchBlocks)
+    return fail(PB_ERR_UNSUPPORTED,
+                "pb_quantize_static: %lld blocks exceed the built-in scratch of %lld blocks; use pb_quantize with a caller workspace",
+                (long long)(batch * g.Nb), (long long)kStaticScratchBlocks);
+  void* scratch = nullptr;
+  if (int s = static_scratch_address(&scratch)) return s;
+  // pb_quantize clears the amax half of the scratch itself (cudaMemsetAsync on `stream`), so
+  // whatever the previous call left behind is never read.
+  return pb_quantize(x, x_dtype, batch, rows, cols, a, b, out_format, q, sc8, sc32, scratch,
+                     (size_t)kStaticScratchBlocks * 8, stream);
 }
