@@ -91,9 +91,9 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 // Bounded wait.  Returns false (and raises the abort flag) when the budget ran out or
-// another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+// another role already aborted.  The common case
+// (the phase has already completed) costs one try_wait; only a miss reads the timer.
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
   const uint64_t t0 = global_timer_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -106,6 +106,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
@@ -255,7 +259,8 @@ __device__ __forceinline__ void store_row_segment(const GemmParams& p, const flo
 
 template <int BN>
 __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1)
-gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ GemmParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -328,48 +333,59 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0) {
+      // This thread is the kernel's critical resource: a tcgen05.mma costs ~75 cycles to issue, so
+      // the four of a k-block leave ~200 cycles of the tensor core's 512 for everything else here.
       uint32_t it = 0, g = 0;   // stage counter, chunk counter
       long long wait_full = 0, wait_acc = 0;
-      const long long t_begin = p.profile ? clock64() : 0;
+      const int prof = p.profile;
+      const long long t_begin = prof ? clock64() : 0;
+      const int KB = p.KB, P = p.P, nchunks = p.nchunks;
+      const uint32_t idesc0 = instr_desc(BN, p.a_fmt, p.b_fmt, 0u);
+      const uint64_t a_desc0 = operand_desc(s_a), b_desc0 = operand_desc(s_b);
+      const uint32_t sf_tmem0 = tmem_base + C::kSfColBase;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        for (int c = 0; c < p.nchunks && ok; ++c, ++g) {
+        for (int c = 0; c < nchunks && ok; ++c, ++g) {
           const int buf = g % C::kAccBufs;
-          long long t0 = p.profile ? clock64() : 0;
+          long long t0 = prof ? clock64() : 0;
           if (!mbar_wait(bar_acc_empty(buf), ((g / C::kAccBufs) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-          if (p.profile) wait_acc += clock64() - t0;
+          if (prof) wait_acc += clock64() - t0;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
-          const int kb_end = min(p.KB, (c + 1) * p.P);
-          for (int kb = c * p.P; kb < kb_end; ++kb, ++it) {
-            const int s = it % C::kStages;
-            t0 = p.profile ? clock64() : 0;
+          const int kb_end = min(KB, (c + 1) * P);
+          uint32_t accumulate = 0;
+          for (int kb = c * P; kb < kb_end; ++kb, ++it) {
+            const uint32_t s = it % C::kStages;
+            if (prof) t0 = clock64();
             if (!mbar_wait(bar_full(s), (it / C::kStages) & 1u, abort_flag)) { ok = false; break; }
-            if (p.profile) wait_full += clock64() - t0;
-            tc_fence_after();
+            if (prof) wait_full += clock64() - t0;
             // scale factors of k-blocks 4j..4j+3 live in TMEM set j & 1; the MMAs of set j-2 were
             // issued (and are ordered) before this copy
-            const uint32_t sf_col = tmem_base + C::kSfColBase + ((uint32_t)(kb >> 2) & 1u) * C::kSfCols;
+            const uint32_t sf_col = sf_tmem0 + ((uint32_t)(kb >> 2) & 1u) * C::kSfCols;
             if ((kb & 3) == 0) {
-              const uint32_t sf_smem = s_sf + s * C::kSfStage;
-              tc_cp_sf(sf_col, sf_desc(sf_smem));
+              const uint64_t sd = sf_desc(s_sf + s * C::kSfStage);
+              tc_cp_sf(sf_col, sd);
 #pragma unroll
-              for (int j = 0; j < BN / 128; ++j) tc_cp_sf(sf_col + 4 + 4 * j, sf_desc(sf_smem + C::kSfaBytes + 512 * j));
+              for (int j = 0; j < BN / 128; ++j) tc_cp_sf(sf_col + 4 + 4 * j, sd + (uint64_t)((C::kSfaBytes + 512 * j) >> 4));
             }
-            const uint32_t idesc = instr_desc(BN, p.a_fmt, p.b_fmt, (uint32_t)(kb & 3));
-            const uint64_t a_desc = operand_desc(s_a + s * C::kABytes);
-            const uint64_t b_desc = operand_desc(s_b + s * C::kBBytes);
-            if (p.profile == 2) {
+            const uint32_t sfid = (uint32_t)kb & 3u;
+            const uint32_t idesc = idesc0 | (sfid << 4) | (sfid << 29);
+            const uint64_t a_desc = a_desc0 + (uint64_t)(s * (C::kABytes >> 4));
+            const uint64_t b_desc = b_desc0 + (uint64_t)(s * (C::kBBytes >> 4));
+            if (prof == 2) {
               const uint32_t plain = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 #pragma unroll
-              for (int k = 0; k < BK / UMMA_K; ++k)
-                tc_mma_plain(d_tmem, a_desc + (uint64_t)(k * UMMA_K >> 4), b_desc + (uint64_t)(k * UMMA_K >> 4), plain,
-                             (kb > c * p.P || k > 0) ? 1u : 0u);
+              for (int k = 0; k < BK / UMMA_K; ++k) {
+                tc_mma_plain(d_tmem, a_desc + (uint64_t)(k * UMMA_K >> 4), b_desc + (uint64_t)(k * UMMA_K >> 4), plain, accumulate);
+                accumulate = 1;
+              }
             } else {
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k)
-              tc_mma_block_scaled(d_tmem, a_desc + (uint64_t)(k * UMMA_K >> 4), b_desc + (uint64_t)(k * UMMA_K >> 4), idesc,
-                                  sf_col, sf_col + 4, (kb > c * p.P || k > 0) ? 1u : 0u);
+              for (int k = 0; k < BK / UMMA_K; ++k) {
+                tc_mma_block_scaled(d_tmem, a_desc + (uint64_t)(k * UMMA_K >> 4), b_desc + (uint64_t)(k * UMMA_K >> 4), idesc,
+                                    sf_col, sf_col + 4, accumulate);
+                accumulate = 1;
+              }
             }
             tc_commit(bar_empty(s));          // frees the stage once these MMAs have read it
           }
@@ -535,7 +551,7 @@ __device__ __forceinline__ uint32_t instr_desc_pair(int a_fmt, int b_fmt, uint32
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg2::kThreads, 1)
 gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                    const GemmParams p) {
+                    const __grid_constant__ GemmParams p) {
   using C = Cfg2;
   constexpr int BN = C::BN;
   extern __shared__ uint8_t smem_raw[];
