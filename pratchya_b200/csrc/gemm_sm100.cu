@@ -33,7 +33,6 @@ constexpr int BK = 128;        // depth of one pipeline stage = one 128-byte swi
 constexpr int UMMA_K = 32;     // depth of one tcgen05.mma for 8-bit operands
 constexpr int kMaxChunk = 8;   // k-blocks per promotion at most (1024-deep)
 constexpr uint32_t kTmemCols = 512;
-constexpr uint64_t kWaitBudgetNs = 2000000000ull;   // 2 s per wait before giving up
 
 template <int BN>
 struct Cfg {
@@ -85,31 +84,44 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
+// The same test, letting the hardware park the warp for up to `ns` nanoseconds (it resumes when
+// the phase completes): a parked warp does not compete for issue slots with the MMA warp.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+  return ok != 0;
 }
-// Bounded wait.  Returns false (and raises the abort flag) when the budget ran out or
-// another role already aborted.  The common case
-// (the phase has already completed) costs one try_wait; only a miss reads the timer.
-__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  const uint64_t t0 = global_timer_ns();
-  for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 255u) == 0) {
-      if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitBudgetNs) {
-        *abort_flag = 1;
-        atomicExch(&g_gemm_status, (unsigned int)PB_ERR_DEVICE_TIMEOUT);
-        return false;
-      }
-    }
-  }
-}
+// Bounded wait.  Returns false (and raises the abort flag) when the poll budget ran out or
+// another role already aborted.  The budget is a poll count, not a clock: 2^24 polls take at
+// least half a second even if the hardware never parks the warp (and ~30 s if every poll parks
+// for its full 2 us), while a healthy wait in this kernel lasts microseconds.  Counting keeps the
+// slow path to a handful of registers, which matters in the MMA-issuing thread.
+constexpr uint32_t kWaitPolls = 1u << 24;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, abort_flag);
+  // The whole poll loop is one PTX block: the compiler sees a single opaque instruction, so the
+  // loops that wait (the MMA issue loop above all) keep their state in registers.
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .u32 n;\n\t"
+      "mov.u32 n, 0;\n"
+      "WAIT_%=:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 2000;\n\t"
+      "@p bra DONE_%=;\n\t"
+      "add.u32 n, n, 1;\n\t"
+      "setp.lt.u32 p, n, %3;\n\t"
+      "@p bra WAIT_%=;\n\t"
+      "setp.ne.u32 p, n, n;\n"          // budget exhausted: p = false
+      "DONE_%=:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(kWaitPolls) : "memory");
+  if (ok) return true;
+  *abort_flag = 1;
+  atomicExch(&g_gemm_status, (unsigned int)PB_ERR_DEVICE_TIMEOUT);
+  return false;
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
@@ -138,14 +150,6 @@ __device__ __forceinline__ void tc_mma_block_scaled(uint32_t d_tmem, uint64_t a_
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
-}
-// timing experiment only: the same tile without block scaling (numerically wrong for scaled data)
-__device__ __forceinline__ void tc_mma_plain(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -208,6 +212,26 @@ __device__ __forceinline__ uint32_t instr_desc(int bn, int a_fmt, int b_fmt, uin
          ((uint32_t)(BM >> 4) << 24) | (sf_id << 29);
 }
 
+// 32-bit forms for the MMA-issuing thread: the upper descriptor word never changes, so only the
+// low word (address >> 4, plus the LBO field) is carried and advanced.
+constexpr uint32_t kOperandDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);   // SBO, version 1, 128-byte swizzle
+constexpr uint32_t kSfDescHi = (uint32_t)(128 >> 4) | (1u << 14);                      // SBO, version 1, no swizzle
+__device__ __forceinline__ uint32_t operand_desc_lo(uint32_t smem_addr) { return ((smem_addr & 0x3ffffu) >> 4) | (1u << 16); }
+__device__ __forceinline__ uint32_t sf_desc_lo(uint32_t smem_addr) { return (smem_addr & 0x3ffffu) >> 4; }
+__device__ __forceinline__ void tc_cp_sf_lo(uint32_t taddr, uint32_t desc_lo) {
+  asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n\t}"
+               ::"r"(taddr), "r"(desc_lo), "r"(kSfDescHi));
+}
+__device__ __forceinline__ void tc_mma_block_scaled_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                       uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %7};\n\tmov.b64 db, {%2, %7};\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], da, db, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "r"(kOperandDescHi));
+}
+
 struct GemmParams {
   const uint8_t* sfa;     // [KG][Mpad/128][512]
   const uint8_t* sfb;     // [KG][Npad/128][512]
@@ -257,7 +281,7 @@ __device__ __forceinline__ void store_row_segment(const GemmParams& p, const flo
   }
 }
 
-template <int BN>
+template <int BN, bool PROF>
 __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ GemmParams p) {
@@ -291,15 +315,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_tiles = p.tiles_m * p.tiles_n;
-
-  const long long t_cta0 = p.profile ? clock64() : 0;
+  const long long t_cta0 = PROF ? clock64() : 0;
   // With the 256-wide tile 384 threads start with 168 registers each; the epilogue needs ~220
   // (128 accumulators + two 32-register load buffers), warpgroup 0 almost none.
   if (warp < 4) {
-  if (BN == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-  if (warp == 0) {
-    // ------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    if (BN == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp == 0 && lane == 0) {
+      // ------------------------------------------------------------- TMA producer
       uint32_t it = 0;   // running stage counter across tiles
       long long waited = 0;
       bool ok = true;
@@ -307,12 +329,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
         for (int kb = 0; kb < p.KB; ++kb, ++it) {
           const int s = it % C::kStages;
-          const long long t0 = p.profile ? clock64() : 0;
+          const long long t0 = PROF ? clock64() : 0;
           if (!mbar_wait(bar_empty(s), ((it / C::kStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-          if (p.profile) waited += clock64() - t0;
+          if (PROF) waited += clock64() - t0;
           // the scale-factor atom of a stage covers 4 k-blocks: only the first of them carries it
           const bool with_sf = (kb & 3) == 0;
-          if (p.profile == 3) { mbar_arrive(bar_full(s)); continue; }   // timing experiment: no data movement
           mbar_arrive_expect_tx(bar_full(s), C::kABytes + C::kBBytes + (with_sf ? C::kSfStage : 0));
           tma_load_2d(s_a + s * C::kABytes, &map_a, kb * BK, m0, bar_full(s));
           tma_load_2d(s_b + s * C::kBBytes, &map_b, kb * BK, n0, bar_full(s));
@@ -328,80 +349,70 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t issued = it;
       for (uint32_t j = (issued > (uint32_t)C::kStages ? issued - C::kStages : 0); j < issued; ++j)
         (void)mbar_wait(bar_full(j % C::kStages), (j / C::kStages) & 1u, abort_flag);
-      if (p.profile) atomicAdd(&g_gemm_prof[0], (unsigned long long)waited);
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      // This thread is the kernel's critical resource: a tcgen05.mma costs ~75 cycles to issue, so
-      // the four of a k-block leave ~200 cycles of the tensor core's 512 for everything else here.
-      uint32_t it = 0, g = 0;   // stage counter, chunk counter
-      long long wait_full = 0, wait_acc = 0;
-      const int prof = p.profile;
-      const long long t_begin = prof ? clock64() : 0;
+      if (PROF) atomicAdd(&g_gemm_prof[0], (unsigned long long)waited);
+    } else if (warp == 1 && lane == 0) {
+      // ------------------------------------------------------------- MMA issuer
+      // This one thread is the kernel's critical resource.  It runs alone on its scheduler, so
+      // every dependent instruction costs its full latency, and a tcgen05.mma takes ~75 cycles to
+      // issue: the four of a k-block leave ~200 of the tensor core's 512 cycles for everything
+      // else.  Hence: no divisions, 32-bit descriptor arithmetic, incremental stage state.
       const int KB = p.KB, P = p.P, nchunks = p.nchunks;
       const uint32_t idesc0 = instr_desc(BN, p.a_fmt, p.b_fmt, 0u);
-      const uint64_t a_desc0 = operand_desc(s_a), b_desc0 = operand_desc(s_b);
+      const uint32_t a_lo0 = operand_desc_lo(s_a), b_lo0 = operand_desc_lo(s_b);
       const uint32_t sf_tmem0 = tmem_base + C::kSfColBase;
+      uint32_t s = 0, phase = 0;                 // pipeline stage and the parity of its current fill
+      uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full(0), empty = bar_empty(0), sf_lo = sf_desc_lo(s_sf);
+      uint32_t g = 0;                            // chunk counter
+      long long wait_full = 0, wait_acc = 0;
+      const long long t_begin = PROF ? clock64() : 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         for (int c = 0; c < nchunks && ok; ++c, ++g) {
           const int buf = g % C::kAccBufs;
-          long long t0 = prof ? clock64() : 0;
+          long long t0 = PROF ? clock64() : 0;
           if (!mbar_wait(bar_acc_empty(buf), ((g / C::kAccBufs) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-          if (prof) wait_acc += clock64() - t0;
+          if (PROF) wait_acc += clock64() - t0;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
           const int kb_end = min(KB, (c + 1) * P);
           uint32_t accumulate = 0;
-          for (int kb = c * P; kb < kb_end; ++kb, ++it) {
-            const uint32_t s = it % C::kStages;
-            if (prof) t0 = clock64();
-            if (!mbar_wait(bar_full(s), (it / C::kStages) & 1u, abort_flag)) { ok = false; break; }
-            if (prof) wait_full += clock64() - t0;
+          for (int kb = c * P; kb < kb_end; ++kb) {
+            if (PROF) t0 = clock64();
+            if (!mbar_wait(full, phase, abort_flag)) { ok = false; break; }
+            if (PROF) wait_full += clock64() - t0;
             // scale factors of k-blocks 4j..4j+3 live in TMEM set j & 1; the MMAs of set j-2 were
             // issued (and are ordered) before this copy
             const uint32_t sf_col = sf_tmem0 + ((uint32_t)(kb >> 2) & 1u) * C::kSfCols;
             if ((kb & 3) == 0) {
-              const uint64_t sd = sf_desc(s_sf + s * C::kSfStage);
-              tc_cp_sf(sf_col, sd);
+              tc_cp_sf_lo(sf_col, sf_lo);
 #pragma unroll
-              for (int j = 0; j < BN / 128; ++j) tc_cp_sf(sf_col + 4 + 4 * j, sd + (uint64_t)((C::kSfaBytes + 512 * j) >> 4));
+              for (int j = 0; j < BN / 128; ++j) tc_cp_sf_lo(sf_col + 4 + 4 * j, sf_lo + ((C::kSfaBytes + 512 * j) >> 4));
             }
-            const uint32_t sfid = (uint32_t)kb & 3u;
-            const uint32_t idesc = idesc0 | (sfid << 4) | (sfid << 29);
-            const uint64_t a_desc = a_desc0 + (uint64_t)(s * (C::kABytes >> 4));
-            const uint64_t b_desc = b_desc0 + (uint64_t)(s * (C::kBBytes >> 4));
-            if (prof == 2) {
-              const uint32_t plain = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            const uint32_t idesc = idesc0 + ((uint32_t)kb & 3u) * ((1u << 4) | (1u << 29));
 #pragma unroll
-              for (int k = 0; k < BK / UMMA_K; ++k) {
-                tc_mma_plain(d_tmem, a_desc + (uint64_t)(k * UMMA_K >> 4), b_desc + (uint64_t)(k * UMMA_K >> 4), plain, accumulate);
-                accumulate = 1;
-              }
-            } else {
-#pragma unroll
-              for (int k = 0; k < BK / UMMA_K; ++k) {
-                tc_mma_block_scaled(d_tmem, a_desc + (uint64_t)(k * UMMA_K >> 4), b_desc + (uint64_t)(k * UMMA_K >> 4), idesc,
-                                    sf_col, sf_col + 4, accumulate);
-                accumulate = 1;
-              }
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              tc_mma_block_scaled_lo(d_tmem, a_lo + (k * UMMA_K >> 4), b_lo + (k * UMMA_K >> 4), idesc, sf_col, sf_col + 4, accumulate);
+              accumulate = 1;
             }
-            tc_commit(bar_empty(s));          // frees the stage once these MMAs have read it
+            tc_commit(empty);          // frees the stage once these MMAs have read it
+            ++s; a_lo += C::kABytes >> 4; b_lo += C::kBBytes >> 4; full += 8; empty += 8; sf_lo += C::kSfStage >> 4;
+            if (s == C::kStages) {
+              s = 0; phase ^= 1u;
+              a_lo = a_lo0; b_lo = b_lo0; full = bar_full(0); empty = bar_empty(0); sf_lo = sf_desc_lo(s_sf);
+            }
           }
           if (ok) tc_commit(bar_acc_full(buf));   // chunk accumulated
         }
       }
-      if (p.profile) {
+      if (PROF) {
         atomicAdd(&g_gemm_prof[1], (unsigned long long)wait_full);
         atomicAdd(&g_gemm_prof[2], (unsigned long long)wait_acc);
         atomicAdd(&g_gemm_prof[6], (unsigned long long)(clock64() - t_begin - wait_full - wait_acc));
       }
     }
-  }
   } else {
     // ------------------------------------------------------------- epilogue
-    if (BN == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    if (BN == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int ew = warp - 4;
     const int quarter = warp & 3;             // TMEM lanes this warp may touch
     const int col_half = ew >> 2;             // which 128-column slice of the tile
@@ -409,7 +420,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t g = 0;
     bool ok = true;
     long long wait_chunk = 0;
-    const long long t_begin = p.profile ? clock64() : 0;
+    const long long t_begin = PROF ? clock64() : 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN + col_half * 128;
       float acc[128];
@@ -419,9 +430,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const float fa = __ldg(p.fa + (size_t)c * p.Mpad + m0 + row_in_tile);
         const float* fbp = p.fb + (size_t)c * p.Npad + n0;
         const float s_uni = fa * __ldg(fbp);      // the whole factor when B's fp32 factor does not vary over the tile
-        const long long t0 = p.profile ? clock64() : 0;
+        const long long t0 = PROF ? clock64() : 0;
         if (!mbar_wait(bar_acc_full(buf), (g / C::kAccBufs) & 1u, abort_flag)) { ok = false; break; }
-        if (p.profile) wait_chunk += clock64() - t0;
+        if (PROF) wait_chunk += clock64() - t0;
         tc_fence_after();
         const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + col_half * 128;
         auto release = [&]() {
@@ -460,7 +471,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!ok) break;
       store_row_segment(p, acc, m0 + row_in_tile, n0);
     }
-    if (p.profile && warp == 4 && lane == 0) {
+    if (PROF && warp == 4 && lane == 0) {
       atomicAdd(&g_gemm_prof[3], (unsigned long long)wait_chunk);
       atomicAdd(&g_gemm_prof[4], (unsigned long long)(clock64() - t_begin - wait_chunk));
     }
@@ -468,7 +479,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
-  if (p.profile && threadIdx.x == 0) {
+  if (PROF && threadIdx.x == 0) {
     atomicAdd(&g_gemm_prof[5], (unsigned long long)(clock64() - t_cta0));
     atomicAdd(&g_gemm_prof[7], 1ull);
   }
@@ -477,7 +488,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
-
 
 // ==============================================================================================
 // CTA-pair variant: tcgen05.mma.cta_group::2 on 256x256 output tiles.  Each CTA of a 2-CTA
@@ -590,7 +600,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
 
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer (both CTAs)
     if (lane == 0) {
@@ -671,7 +681,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
   } else {
     // ------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int ew = warp - 4;
     const int quarter = warp & 3;
     const int col_half = ew >> 2;
@@ -892,7 +902,7 @@ int pick_bn() {
   return bn;
 }
 
-int profile_level() {   // 0 off, 1 cycle counters, 2 counters + unscaled MMA (timing experiment)
+int profile_level() {   // 0 off, 1 per-role cycle counters (PB_GEMM_PROFILE=1)
   static const int level = [] { const char* e = getenv("PB_GEMM_PROFILE"); return e ? atoi(e) : 0; }();
   return level;
 }
@@ -932,7 +942,7 @@ int launch_prep(const pb_operand* o, const OperandPlan& op, const GemmPlan& gp, 
   return PB_OK;
 }
 
-template <int BN>
+template <int BN, bool PROF>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st) {
   static std::mutex mu;
   static bool configured[64] = {false};
@@ -941,13 +951,13 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
   {
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-      PB_CUDA_TRY(cudaFuncSetAttribute(gemm_tn_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes));
+      PB_CUDA_TRY(cudaFuncSetAttribute(gemm_tn_kernel<BN, PROF>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes));
       configured[dev] = true;
     }
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_tn_kernel<BN><<<grid, Cfg<BN>::kThreads, Cfg<BN>::kSmemBytes, st>>>(ma, mb, p);
+  gemm_tn_kernel<BN, PROF><<<grid, Cfg<BN>::kThreads, Cfg<BN>::kSmemBytes, st>>>(ma, mb, p);
   PB_LAUNCH_CHECK("gemm_tn_kernel");
   return PB_OK;
 }
@@ -1020,7 +1030,8 @@ extern "C" int pb_gemm_tn(const pb_operand* a, const pb_operand* b, void* d, int
     if (int s = make_sf_map(&msfb, ws + gp.off_sfb, (int64_t)gp.KG * (gp.Npad / 128), 2)) return s;
     return launch_gemm_pair(ma, mb, msfa, msfb, p, st);
   }
-  return gp.BN == 256 ? launch_gemm<256>(ma, mb, p, st) : launch_gemm<128>(ma, mb, p, st);
+  if (p.profile) return gp.BN == 256 ? launch_gemm<256, true>(ma, mb, p, st) : launch_gemm<128, true>(ma, mb, p, st);
+  return gp.BN == 256 ? launch_gemm<256, false>(ma, mb, p, st) : launch_gemm<128, false>(ma, mb, p, st);
 }
 
 extern "C" int pb_gemm_check(void* stream) {
