@@ -552,6 +552,19 @@ __device__ __forceinline__ void tc2_mma_block_scaled(uint32_t d_tmem, uint64_t a
       "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
 }
+__device__ __forceinline__ void tc2_cp_sf_lo(uint32_t taddr, uint32_t desc_lo) {
+  asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d;\n\t}"
+               ::"r"(taddr), "r"(desc_lo), "r"(kSfDescHi));
+}
+__device__ __forceinline__ void tc2_mma_block_scaled_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                        uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %7};\n\tmov.b64 db, {%2, %7};\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], da, db, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "r"(kOperandDescHi));
+}
 // as instr_desc, for the pair: M = 256
 __device__ __forceinline__ uint32_t instr_desc_pair(int a_fmt, int b_fmt, uint32_t sf_id) {
   return (sf_id << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(256 >> 3) << 17) | (1u << 23) |
@@ -614,7 +627,6 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (!mbar_wait(bar_empty(s), ((it / C::kStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
           const bool with_sf = (kb & 3) == 0;
           const uint32_t full = map_to_cta(bar_full(s), 0);
-          if (p.profile == 3) { if (leader) mbar_arrive(bar_full(s)); continue; }   // timing experiment: no data movement
           if (leader) mbar_arrive_expect_tx(bar_full(s), 2 * (C::kABytes + C::kBBytes + (with_sf ? C::kSfStage : 0)));
           tma_load_2d_pair(s_a + s * C::kABytes, &map_a, kb * BK, m0, full);
           tma_load_2d_pair(s_b + s * C::kBBytes, &map_b, kb * BK, n0 + (int)rank * 128, full);
@@ -629,45 +641,55 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else if (warp == 1 && leader) {
     // ------------------------------------------------------------- MMA issuer (leader CTA only)
     if (lane == 0) {
-      uint32_t it = 0, g = 0;
+      // same lean issue loop as the single-CTA kernel: 32-bit descriptor words, incremental stage state
+      const int prof = p.profile;
+      const int KB = p.KB, P = p.P, nchunks = p.nchunks;
+      const uint32_t idesc0 = instr_desc_pair(p.a_fmt, p.b_fmt, 0u);
+      const uint32_t a_lo0 = operand_desc_lo(s_a), b_lo0 = operand_desc_lo(s_b);
+      const uint32_t sf_tmem0 = tmem_base + C::kSfColBase;
+      const uint32_t empty_peer0 = map_to_cta(bar_empty(0), 1), acc_full_peer = map_to_cta(bar_acc_full, 1);
+      uint32_t s = 0, phase = 0;
+      uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full(0), empty = bar_empty(0), empty_peer = empty_peer0, sf_lo = sf_desc_lo(s_sf);
+      uint32_t g = 0;
       long long wait_full = 0, wait_acc = 0;
-      const long long t_begin = p.profile ? clock64() : 0;
+      const long long t_begin = prof ? clock64() : 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        for (int c = 0; c < p.nchunks && ok; ++c, ++g) {
-          long long t0 = p.profile ? clock64() : 0;
+        for (int c = 0; c < nchunks && ok; ++c, ++g) {
+          long long t0 = prof ? clock64() : 0;
           if (!mbar_wait(bar_acc_empty, (g & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-          if (p.profile) wait_acc += clock64() - t0;
+          if (prof) wait_acc += clock64() - t0;
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base;
-          const int kb_end = min(p.KB, (c + 1) * p.P);
-          for (int kb = c * p.P; kb < kb_end; ++kb, ++it) {
-            const int s = it % C::kStages;
-            t0 = p.profile ? clock64() : 0;
-            if (!mbar_wait(bar_full(s), (it / C::kStages) & 1u, abort_flag)) { ok = false; break; }
-            if (p.profile) wait_full += clock64() - t0;
-            tc_fence_after();
-            const uint32_t sf_col = tmem_base + C::kSfColBase + ((uint32_t)(kb >> 2) & 1u) * C::kSfCols;
+          const int kb_end = min(KB, (c + 1) * P);
+          uint32_t accumulate = 0;
+          for (int kb = c * P; kb < kb_end; ++kb) {
+            if (prof) t0 = clock64();
+            if (!mbar_wait(full, phase, abort_flag)) { ok = false; break; }
+            if (prof) wait_full += clock64() - t0;
+            const uint32_t sf_col = sf_tmem0 + ((uint32_t)(kb >> 2) & 1u) * C::kSfCols;
             if ((kb & 3) == 0) {
-              const uint32_t sf_smem = s_sf + s * C::kSfStage;
-              tc2_cp_sf(sf_col, sf_desc(sf_smem));
-              tc2_cp_sf(sf_col + 4, sf_desc(sf_smem + C::kSfaBytes));
-              tc2_cp_sf(sf_col + 8, sf_desc(sf_smem + C::kSfaBytes + 512));
+              tc2_cp_sf_lo(sf_col, sf_lo);
+              tc2_cp_sf_lo(sf_col + 4, sf_lo + (C::kSfaBytes >> 4));
+              tc2_cp_sf_lo(sf_col + 8, sf_lo + ((C::kSfaBytes + 512) >> 4));
             }
-            const uint32_t idesc = instr_desc_pair(p.a_fmt, p.b_fmt, (uint32_t)(kb & 3));
-            const uint64_t a_desc = operand_desc(s_a + s * C::kABytes);
-            const uint64_t b_desc = operand_desc(s_b + s * C::kBBytes);
+            const uint32_t idesc = idesc0 + ((uint32_t)kb & 3u) * ((1u << 4) | (1u << 29));
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k)
-              tc2_mma_block_scaled(d_tmem, a_desc + (uint64_t)(k * UMMA_K >> 4), b_desc + (uint64_t)(k * UMMA_K >> 4), idesc,
-                                   sf_col, sf_col + 4, (kb > c * p.P || k > 0) ? 1u : 0u);
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              tc2_mma_block_scaled_lo(tmem_base, a_lo + (k * UMMA_K >> 4), b_lo + (k * UMMA_K >> 4), idesc, sf_col, sf_col + 4, accumulate);
+              accumulate = 1;
+            }
             // free the stage in both CTAs once these MMAs have read it
-            tc2_commit(bar_empty(s));
-            tc2_commit(map_to_cta(bar_empty(s), 1));
+            tc2_commit(empty);
+            tc2_commit(empty_peer);
+            ++s; a_lo += C::kABytes >> 4; b_lo += C::kBBytes >> 4; full += 8; empty += 8; empty_peer += 8; sf_lo += C::kSfStage >> 4;
+            if (s == C::kStages) {
+              s = 0; phase ^= 1u;
+              a_lo = a_lo0; b_lo = b_lo0; full = bar_full(0); empty = bar_empty(0); empty_peer = empty_peer0; sf_lo = sf_desc_lo(s_sf);
+            }
           }
           if (ok) {
             tc2_commit(bar_acc_full);
-            tc2_commit(map_to_cta(bar_acc_full, 1));
+            tc2_commit(acc_full_peer);
           }
         }
       }
