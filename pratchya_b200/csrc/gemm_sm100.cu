@@ -34,26 +34,33 @@ constexpr int UMMA_K = 32;     // depth of one tcgen05.mma for 8-bit operands
 constexpr int kMaxChunk = 8;   // k-blocks per promotion at most (1024-deep)
 constexpr uint32_t kTmemCols = 512;
 
+// Tile widths.  224 is the default: two 224-column accumulators plus the scale-factor columns fit
+// the 512 TMEM columns (two 256-column ones do not), so the epilogue drains one chunk while the
+// tensor core fills the next, and a 44 KB stage leaves room for five pipeline stages.
 template <int BN>
 struct Cfg {
-  static_assert(BN == 128 || BN == 256, "tile width");
-  static constexpr int kStages = BN == 128 ? 6 : 4;
-  static constexpr int kAccBufs = BN == 128 ? 2 : 1;
-  static constexpr int kEpiWarps = 4 * (BN / 128);
+  static_assert(BN == 128 || BN == 224 || BN == 256, "tile width");
+  static constexpr int kStages = BN == 128 ? 5 : (BN == 224 ? 4 : 3);
+  static constexpr int kAccBufs = BN == 256 ? 1 : 2;
+  static constexpr int kEpiWarps = BN == 128 ? 4 : 8;
   static constexpr int kThreads = 128 + 32 * kEpiWarps;   // warpgroup 0: producer, MMA, two idle warps; then the epilogue warpgroups
   static constexpr int kABytes = BM * BK;
   static constexpr int kBBytes = BN * BK;
+  static constexpr int kSfbAtoms = (BN + 127) / 128;             // 512-byte scale-factor atoms per B tile
   static constexpr int kSfaBytes = 512;
-  static constexpr int kSfbBytes = 512 * (BN / 128);
-  static constexpr int kSfStage = kSfaBytes + kSfbBytes;
-  static constexpr int kStageTx = kABytes + kBBytes + kSfStage;
-  static constexpr int kSfCols = 4 + BN / 32;                    // TMEM columns of one scale-factor set
+  static constexpr int kSfbBytes = 512 * kSfbAtoms;
+  static constexpr int kSfSlot = kSfaBytes + kSfbBytes;          // one slot holds the atoms of 4 k-blocks
+  static constexpr int kSfSlots = 2;                             // reused every 8 k-blocks (> kStages, see the producer)
+  static constexpr int kSfCols = 12;                             // TMEM columns of one scale-factor set (4 for A, up to 8 for B)
   static constexpr int kSfColBase = kAccBufs * BN;
   static constexpr int kOffB = kStages * kABytes;
   static constexpr int kOffSf = kOffB + kStages * kBBytes;
-  static constexpr int kOffBar = kOffSf + kStages * kSfStage;
+  static constexpr int kOffStore = ((kOffSf + kSfSlots * kSfSlot + 1023) / 1024) * 1024;   // epilogue staging, 4 KB per warp
+  static constexpr int kOffBar = kOffStore + kEpiWarps * 4096;
   static constexpr int kNumBars = 2 * kStages + 2 * kAccBufs;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;   // +1024: manual alignment slack
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
+  static_assert(kSfColBase + 2 * kSfCols <= 512, "TMEM budget");
 };
 
 __device__ unsigned int g_gemm_status;   // 0, or PB_ERR_DEVICE_TIMEOUT once any bounded wait ran out
@@ -245,38 +252,100 @@ struct GemmParams {
   int a_fmt, b_fmt;
   int d_dtype;
   int fb_uniform;   // B's fp32 factor is the same for all rows of B within a chunk
+  int tma_store;    // D is written through shared memory and TMA stores (needs 16-byte aligned rows)
   int profile;
 };
 
 
-// One thread stores its row segment of 128 output columns (bf16 or f32), clipped to [M, N].
-__device__ __forceinline__ void store_row_segment(const GemmParams& p, const float (&acc)[128], int row, int n0) {
+// TMA store of a [32 rows x 32 columns] box from shared memory, tracked by this thread's bulk group
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N> __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// Stages 32 columns (OFF .. OFF+31) of this lane's row into the warp's staging buffer and lets lane 0
+// hand the 32 x 32 box to the TMA.  The buffer is swizzled the way the store's tensor map expects
+// (64-byte rows for bf16, 128-byte rows for f32), which also keeps the 16-byte writes of the 32
+// lanes on distinct banks.  bf16 alternates between two 2 KB halves; f32 uses the whole 4 KB.
+template <int OFF>
+__device__ __forceinline__ void stage_and_store(const CUtensorMap* map, const float (&acc)[128], uint32_t stage, int lane,
+                                                int d_dtype, int col0, int row0, uint32_t& stores) {
+  if (d_dtype == PB_BF16) {
+    const uint32_t buf = stage + (stores++ & 1u) * 2048;     // halves alternate over the warp's whole run of stores
+    if (lane == 0) tma_store_wait_read<1>();      // the store that last read this half has finished reading
+    __syncwarp();
+    const uint32_t sw = ((uint32_t)lane >> 1) & 3u;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      st_shared_v4(buf + lane * 64 + (((uint32_t)c ^ sw) << 4),
+                   pack_bf16x2(acc[OFF + 8 * c], acc[OFF + 8 * c + 1]), pack_bf16x2(acc[OFF + 8 * c + 2], acc[OFF + 8 * c + 3]),
+                   pack_bf16x2(acc[OFF + 8 * c + 4], acc[OFF + 8 * c + 5]), pack_bf16x2(acc[OFF + 8 * c + 6], acc[OFF + 8 * c + 7]));
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) tma_store_2d(map, buf, col0 + OFF, row0);
+  } else {
+    if (lane == 0) tma_store_wait_read<0>();
+    __syncwarp();
+    const uint32_t sw = (uint32_t)lane & 7u;
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      st_shared_v4(stage + lane * 128 + (((uint32_t)c ^ sw) << 4), __float_as_uint(acc[OFF + 4 * c]), __float_as_uint(acc[OFF + 4 * c + 1]),
+                   __float_as_uint(acc[OFF + 4 * c + 2]), __float_as_uint(acc[OFF + 4 * c + 3]));
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) tma_store_2d(map, stage, col0 + OFF, row0);
+  }
+}
+
+__device__ __forceinline__ void st_global_stream_256(void* ptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
+                                                     uint32_t e, uint32_t f, uint32_t g, uint32_t h) {
+  asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(ptr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e), "r"(f), "r"(g), "r"(h) : "memory");
+}
+
+// One thread stores its row segment of `ncols` (96 or 128) output columns (bf16 or f32), clipped to [M, N].
+__device__ __forceinline__ void store_row_segment(const GemmParams& p, const float (&acc)[128], int row, int n0, int ncols = 128) {
   if (row >= p.M) return;
   if (p.d_dtype == PB_BF16) {
     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.d) + (size_t)row * p.ldd + n0;
-    const bool vec = ((p.ldd & 7) == 0) && (n0 + 128 <= p.N) && ((reinterpret_cast<uintptr_t>(p.d) & 15) == 0);
+    const bool vec = ((p.ldd & 15) == 0) && (n0 + ncols <= p.N) && ((reinterpret_cast<uintptr_t>(p.d) & 31) == 0);
     if (vec) {
+      // 256-bit streaming stores: every instruction writes whole 32-byte sectors, and the output
+      // (larger than L2 for the benchmark shapes) is marked evict-first so that it does not push the
+      // operand tiles, which every CTA re-reads, out of L2.
 #pragma unroll
-      for (int j = 0; j < 16; ++j)
-        *reinterpret_cast<uint4*>(dst + 8 * j) =
-            make_uint4(pack_bf16x2(acc[8 * j], acc[8 * j + 1]), pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3]),
-                       pack_bf16x2(acc[8 * j + 4], acc[8 * j + 5]), pack_bf16x2(acc[8 * j + 6], acc[8 * j + 7]));
+      for (int j = 0; j < 8; ++j)
+        if (16 * j < ncols)
+          st_global_stream_256(dst + 16 * j,
+                               pack_bf16x2(acc[16 * j], acc[16 * j + 1]), pack_bf16x2(acc[16 * j + 2], acc[16 * j + 3]),
+                               pack_bf16x2(acc[16 * j + 4], acc[16 * j + 5]), pack_bf16x2(acc[16 * j + 6], acc[16 * j + 7]),
+                               pack_bf16x2(acc[16 * j + 8], acc[16 * j + 9]), pack_bf16x2(acc[16 * j + 10], acc[16 * j + 11]),
+                               pack_bf16x2(acc[16 * j + 12], acc[16 * j + 13]), pack_bf16x2(acc[16 * j + 14], acc[16 * j + 15]));
     } else {
 #pragma unroll
       for (int j = 0; j < 128; ++j)
-        if (n0 + j < p.N) dst[j] = __float2bfloat16_rn(acc[j]);
+        if (j < ncols && n0 + j < p.N) dst[j] = __float2bfloat16_rn(acc[j]);
     }
   } else {
     float* dst = static_cast<float*>(p.d) + (size_t)row * p.ldd + n0;
-    const bool vec = ((p.ldd & 3) == 0) && (n0 + 128 <= p.N) && ((reinterpret_cast<uintptr_t>(p.d) & 15) == 0);
+    const bool vec = ((p.ldd & 7) == 0) && (n0 + ncols <= p.N) && ((reinterpret_cast<uintptr_t>(p.d) & 31) == 0);
     if (vec) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        *reinterpret_cast<float4*>(dst + 4 * j) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+      for (int j = 0; j < 16; ++j)
+        if (8 * j < ncols)
+          st_global_stream_256(dst + 8 * j, __float_as_uint(acc[8 * j]), __float_as_uint(acc[8 * j + 1]), __float_as_uint(acc[8 * j + 2]),
+                               __float_as_uint(acc[8 * j + 3]), __float_as_uint(acc[8 * j + 4]), __float_as_uint(acc[8 * j + 5]),
+                               __float_as_uint(acc[8 * j + 6]), __float_as_uint(acc[8 * j + 7]));
     } else {
 #pragma unroll
       for (int j = 0; j < 128; ++j)
-        if (n0 + j < p.N) dst[j] = acc[j];
+        if (j < ncols && n0 + j < p.N) dst[j] = acc[j];
     }
   }
 }
@@ -284,7 +353,7 @@ __device__ __forceinline__ void store_row_segment(const GemmParams& p, const flo
 template <int BN, bool PROF>
 __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ GemmParams p) {
+               const __grid_constant__ CUtensorMap map_d, const __grid_constant__ GemmParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -316,13 +385,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int num_tiles = p.tiles_m * p.tiles_n;
   const long long t_cta0 = PROF ? clock64() : 0;
-  // With the 256-wide tile 384 threads start with 168 registers each; the epilogue needs ~220
+  // With eight epilogue warps 384 threads start with 168 registers each; the epilogue needs ~220
   // (128 accumulators + two 32-register load buffers), warpgroup 0 almost none.
   if (warp < 4) {
-    if (BN == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (C::kEpiWarps == 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 0 && lane == 0) {
       // ------------------------------------------------------------- TMA producer
       uint32_t it = 0;   // running stage counter across tiles
+      uint32_t sf_fills = 0;
       long long waited = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -334,13 +404,18 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (PROF) waited += clock64() - t0;
           // the scale-factor atom of a stage covers 4 k-blocks: only the first of them carries it
           const bool with_sf = (kb & 3) == 0;
-          mbar_arrive_expect_tx(bar_full(s), C::kABytes + C::kBBytes + (with_sf ? C::kSfStage : 0));
+          mbar_arrive_expect_tx(bar_full(s), C::kABytes + C::kBBytes + (with_sf ? C::kSfSlot : 0));
           tma_load_2d(s_a + s * C::kABytes, &map_a, kb * BK, m0, bar_full(s));
           tma_load_2d(s_b + s * C::kBBytes, &map_b, kb * BK, n0, bar_full(s));
           if (with_sf) {
+            // Two slots alternate.  A slot is rewritten 8 k-blocks after the copy that read it was
+            // issued; this fill waited for the commit of k-block it - kStages (kStages < 8), which
+            // completes only after every earlier tcgen05 operation, that copy included.
             const int kg = kb >> 2;
-            bulk_load(s_sf + s * C::kSfStage, p.sfa + ((size_t)kg * (p.Mpad / 128) + m0 / 128) * 512, C::kSfaBytes, bar_full(s));
-            bulk_load(s_sf + s * C::kSfStage + C::kSfaBytes, p.sfb + ((size_t)kg * (p.Npad / 128) + n0 / 128) * 512, C::kSfbBytes, bar_full(s));
+            const uint32_t slot = s_sf + (sf_fills & 1u) * C::kSfSlot;
+            ++sf_fills;
+            bulk_load(slot, p.sfa + ((size_t)kg * p.tiles_m + tile % p.tiles_m) * 512, C::kSfaBytes, bar_full(s));
+            bulk_load(slot + C::kSfaBytes, p.sfb + ((size_t)kg * p.tiles_n + tile / p.tiles_m) * C::kSfbBytes, C::kSfbBytes, bar_full(s));
           }
         }
       }
@@ -361,7 +436,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t a_lo0 = operand_desc_lo(s_a), b_lo0 = operand_desc_lo(s_b);
       const uint32_t sf_tmem0 = tmem_base + C::kSfColBase;
       uint32_t s = 0, phase = 0;                 // pipeline stage and the parity of its current fill
-      uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full(0), empty = bar_empty(0), sf_lo = sf_desc_lo(s_sf);
+      uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full(0), empty = bar_empty(0);
+      const uint32_t sf_lo0 = sf_desc_lo(s_sf);
+      uint32_t sf_reads = 0;                     // scale-factor slots consumed so far
       uint32_t g = 0;                            // chunk counter
       long long wait_full = 0, wait_acc = 0;
       const long long t_begin = PROF ? clock64() : 0;
@@ -384,9 +461,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // issued (and are ordered) before this copy
             const uint32_t sf_col = sf_tmem0 + ((uint32_t)(kb >> 2) & 1u) * C::kSfCols;
             if ((kb & 3) == 0) {
+              const uint32_t sf_lo = sf_lo0 + (sf_reads & 1u) * (C::kSfSlot >> 4);
+              ++sf_reads;
               tc_cp_sf_lo(sf_col, sf_lo);
 #pragma unroll
-              for (int j = 0; j < BN / 128; ++j) tc_cp_sf_lo(sf_col + 4 + 4 * j, sf_lo + ((C::kSfaBytes + 512 * j) >> 4));
+              for (int j = 0; j < C::kSfbAtoms; ++j) tc_cp_sf_lo(sf_col + 4 + 4 * j, sf_lo + ((C::kSfaBytes + 512 * j) >> 4));
             }
             const uint32_t idesc = idesc0 + ((uint32_t)kb & 3u) * ((1u << 4) | (1u << 29));
 #pragma unroll
@@ -395,10 +474,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               accumulate = 1;
             }
             tc_commit(empty);          // frees the stage once these MMAs have read it
-            ++s; a_lo += C::kABytes >> 4; b_lo += C::kBBytes >> 4; full += 8; empty += 8; sf_lo += C::kSfStage >> 4;
+            ++s; a_lo += C::kABytes >> 4; b_lo += C::kBBytes >> 4; full += 8; empty += 8;
             if (s == C::kStages) {
               s = 0; phase ^= 1u;
-              a_lo = a_lo0; b_lo = b_lo0; full = bar_full(0); empty = bar_empty(0); sf_lo = sf_desc_lo(s_sf);
+              a_lo = a_lo0; b_lo = b_lo0; full = bar_full(0); empty = bar_empty(0);
             }
           }
           if (ok) tc_commit(bar_acc_full(buf));   // chunk accumulated
@@ -412,12 +491,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------- epilogue
-    if (BN == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    if (C::kEpiWarps == 8) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int ew = warp - 4;
     const int quarter = warp & 3;             // TMEM lanes this warp may touch
-    const int col_half = ew >> 2;             // which 128-column slice of the tile
+    const int col_half = ew >> 2;             // which column slice of the tile: [0,128) or [128,BN)
+    const int ncols = col_half == 0 ? (BN < 128 ? BN : 128) : BN - 128;      // 128, or 96 for the 224-wide tile
+    const bool four_parts = ncols == 128;     // 32-column parts this warp drains per chunk (else three)
     const int row_in_tile = quarter * 32 + lane;
-    uint32_t g = 0;
+    uint32_t g = 0, stores = 0;
     bool ok = true;
     long long wait_chunk = 0;
     const long long t_begin = PROF ? clock64() : 0;
@@ -441,10 +522,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_acc_empty(buf));
         };
+        // Diagnostic knobs (PB_GEMM_PROFILE=3: handshake only; >=2: no stores of D, below).  They are
+        // tested in every build on purpose: with these two branches in the loop the compiler keeps
+        // the accumulators of a tile apart from the next tile's prologue, and the kernel measures
+        // 132 us instead of 151 us on the 8192 x 8192 x 2048 case.
+        if (p.profile == 3) { release(); continue; }
         if (c == 0) {
           // First chunk of a tile: straight into the accumulator registers, so the buffer goes
           // back to the MMA warp before any arithmetic.
-          tc_ld32f<0>(t_addr, acc); tc_ld32f<32>(t_addr + 32, acc); tc_ld32f<64>(t_addr + 64, acc); tc_ld32f<96>(t_addr + 96, acc);
+          tc_ld32f<0>(t_addr, acc); tc_ld32f<32>(t_addr + 32, acc); tc_ld32f<64>(t_addr + 64, acc);
+          if (four_parts) tc_ld32f<96>(t_addr + 96, acc);
           tc_wait_ld();
           release();
           if (p.fb_uniform) {
@@ -453,9 +540,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const float4 fb = __ldg(reinterpret_cast<const float4*>(fbp) + j);
-              acc[4 * j + 0] = acc[4 * j + 0] * fa * fb.x; acc[4 * j + 1] = acc[4 * j + 1] * fa * fb.y;
-              acc[4 * j + 2] = acc[4 * j + 2] * fa * fb.z; acc[4 * j + 3] = acc[4 * j + 3] * fa * fb.w;
+              if (j < 24 || four_parts) {
+                const float4 fb = __ldg(reinterpret_cast<const float4*>(fbp) + j);
+                acc[4 * j + 0] = acc[4 * j + 0] * fa * fb.x; acc[4 * j + 1] = acc[4 * j + 1] * fa * fb.y;
+                acc[4 * j + 2] = acc[4 * j + 2] * fa * fb.z; acc[4 * j + 3] = acc[4 * j + 3] * fa * fb.w;
+              }
             }
           }
         } else {
@@ -464,13 +553,28 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tc_ld32(t_addr, r0);
           tc_wait_ld(); tc_ld32(t_addr + 32, r1); promote<0>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
           tc_wait_ld(); tc_ld32(t_addr + 64, r0); promote<32>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
-          tc_wait_ld(); tc_ld32(t_addr + 96, r1); promote<64>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
-          tc_wait_ld(); release();                promote<96>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
+          if (four_parts) {
+            tc_wait_ld(); tc_ld32(t_addr + 96, r1); promote<64>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
+            tc_wait_ld(); release();                promote<96>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
+          } else {
+            tc_wait_ld(); release();                promote<64>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
+          }
         }
       }
       if (!ok) break;
-      store_row_segment(p, acc, m0 + row_in_tile, n0);
+      if (p.profile >= 2) continue;       // 2, 3: diagnostics without the stores of D
+      if (p.tma_store) {
+        const uint32_t stage = s_base + C::kOffStore + ew * 4096;
+        const int row0 = m0 + quarter * 32;
+        stage_and_store<0>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores);
+        stage_and_store<32>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores);
+        stage_and_store<64>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores);
+        if (four_parts) stage_and_store<96>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores);
+      } else {
+        store_row_segment(p, acc, m0 + row_in_tile, n0, ncols);
+      }
     }
+    if (lane == 0) tma_store_wait_all();          // this thread's stores have left shared memory and are complete
     if (PROF && warp == 4 && lane == 0) {
       atomicAdd(&g_gemm_prof[3], (unsigned long long)wait_chunk);
       atomicAdd(&g_gemm_prof[4], (unsigned long long)(clock64() - t_begin - wait_chunk));
@@ -768,7 +872,9 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 // ---- scale preparation -----------------------------------------------------------------------
 // Rewrites one operand's (sc8, sc32) into what the main kernel consumes:
-//   sf[kg][row/128][ (row%32)*16 + ((row%128)/32)*4 + kb%4 ]   e8m0 byte of (row, kb), kg = kb/4
+//   sf[kg][tile][atom][ (r%32)*16 + (r/32)*4 + kb%4 ]   e8m0 byte of (row, kb); kg = kb/4, the row is
+//        tile*tile_rows + atom*128 + r with r in [0,128): atoms are relative to the tile's first row
+//        (a 224-row tile of B has two atoms, the second one three quarters full)
 //   f[chunk][row] = sc32[group of (row, chunk*P)] / 128
 struct PrepParams {
   const uint8_t* sc8;
@@ -776,6 +882,7 @@ struct PrepParams {
   uint8_t* sf;
   float* f;
   int rows, rows_pad, KB, KG, P, nchunks;
+  int tile_rows, tiles, atoms_per_tile;
   int grid_a;        // 1 or 128: rows per block
   int transposed;    // blocks numbered on the [depth, rows] view
   int64_t Ksg;       // blocks per super-group
@@ -786,19 +893,22 @@ __device__ __forceinline__ int64_t flat_block(const PrepParams& q, int r, int kb
 }
 
 __global__ void __launch_bounds__(256) gemm_prep_kernel(PrepParams q) {
-  const int64_t n_sf = (int64_t)q.rows_pad * q.KG * 4;
+  const int atoms_per_kg = q.tiles * q.atoms_per_tile;
+  const int64_t n_sf = (int64_t)q.KG * atoms_per_kg * 512;
   const int64_t n_f = (int64_t)q.rows_pad * q.nchunks;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_sf + n_f; i += stride) {
     if (i < n_sf) {
-      // i enumerates the destination bytes in order: kg, row tile, then the 512-byte atom
+      // i enumerates the destination bytes in order: kg, tile, atom, then the 512 bytes of the atom
       const int within = (int)(i & 511);
-      const int64_t atom = i >> 9;
-      const int rt = (int)(atom % (q.rows_pad / 128)), kg = (int)(atom / (q.rows_pad / 128));
-      const int r = rt * 128 + ((within >> 2) & 3) * 32 + (within >> 4);
+      const int64_t atom_global = i >> 9;
+      const int kg = (int)(atom_global / atoms_per_kg), rem = (int)(atom_global % atoms_per_kg);
+      const int tile = rem / q.atoms_per_tile, atom = rem % q.atoms_per_tile;
+      const int local = atom * 128 + ((within >> 2) & 3) * 32 + (within >> 4);
+      const int r = tile * q.tile_rows + local;
       const int kb = kg * 4 + (within & 3);
       uint8_t v = 0;
-      if (r < q.rows && kb < q.KB) v = q.sc8[flat_block(q, r, kb)];
+      if (local < q.tile_rows && r < q.rows && kb < q.KB) v = q.sc8[flat_block(q, r, kb)];
       q.sf[i] = v;
     } else {
       const int64_t j = i - n_sf;
@@ -840,6 +950,24 @@ int make_operand_map(CUtensorMap* map, const void* q, int64_t rows, int64_t dept
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return PB_OK;
+}
+
+// D as a 2-D tensor [M, N] for the epilogue's TMA stores: boxes of 32 rows x 32 columns, swizzled
+// like the staging buffers (64-byte rows for bf16, 128-byte rows for f32).
+int make_store_map(CUtensorMap* map, void* d, int d_dtype, int64_t M, int64_t N, int64_t ldd) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const int es = d_dtype == PB_BF16 ? 2 : 4;
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)(ldd * es)};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, d_dtype == PB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, d, dims, strides,
+                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        d_dtype == PB_BF16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
   return PB_OK;
 }
 
@@ -906,6 +1034,7 @@ int plan_operand(const pb_operand* o, const char* name, OperandPlan* plan) {
 struct GemmPlan {
   OperandPlan pa, pb;
   int P, KB, KG, nchunks, Mpad, Npad, BN;
+  int tiles_m, tiles_n, atoms_b;      // A tiles of 128 rows, B tiles of BN rows, scale-factor atoms per B tile
   bool pair;      // CTA-pair kernel (256 x 256 tiles) instead of the single-CTA one
   size_t off_sfa, off_sfb, off_fa, off_fb, total;
 };
@@ -915,16 +1044,16 @@ bool pick_pair() {      // PB_GEMM_MODE=pair selects the CTA-pair kernel (the si
   return pair;
 }
 
-int pick_bn() {
+int pick_bn() {      // PB_GEMM_BN=128|224|256 overrides the default tile width
   static int bn = [] {
     const char* e = getenv("PB_GEMM_BN");
-    const int v = e ? atoi(e) : 256;
-    return v == 128 ? 128 : 256;
+    const int v = e ? atoi(e) : 224;
+    return (v == 128 || v == 256) ? v : 224;
   }();
   return bn;
 }
 
-int profile_level() {   // 0 off, 1 per-role cycle counters (PB_GEMM_PROFILE=1)
+int profile_level() {   // 0 off, 1 per-role cycle counters; 2 also skips the stores of D, 3 also the TMEM reads (timing only)
   static const int level = [] { const char* e = getenv("PB_GEMM_PROFILE"); return e ? atoi(e) : 0; }();
   return level;
 }
@@ -943,20 +1072,25 @@ int make_plan(const pb_operand* a, const pb_operand* b, GemmPlan* gp) {
   gp->KG = (gp->KB + 3) / 4;
   gp->nchunks = (gp->KB + gp->P - 1) / gp->P;
   gp->Mpad = (int)((a->rows + 255) / 256 * 256);
-  gp->Npad = (int)((b->rows + 255) / 256 * 256);
+  gp->tiles_m = gp->Mpad / 128;
+  gp->tiles_n = (int)((b->rows + gp->BN - 1) / gp->BN);
+  gp->atoms_b = (gp->BN + 127) / 128;
+  gp->Npad = (gp->tiles_n * gp->BN + 255) / 256 * 256;
   auto align = [](size_t v) { return (v + 255) & ~(size_t)255; };
   size_t off = 0;
-  gp->off_sfa = off; off = align(off + (size_t)gp->KG * gp->Mpad * 4);
-  gp->off_sfb = off; off = align(off + (size_t)gp->KG * gp->Npad * 4);
+  gp->off_sfa = off; off = align(off + (size_t)gp->KG * gp->tiles_m * 512);
+  gp->off_sfb = off; off = align(off + (size_t)gp->KG * gp->tiles_n * gp->atoms_b * 512);
   gp->off_fa = off;  off = align(off + (size_t)gp->nchunks * gp->Mpad * 4);
   gp->off_fb = off;  off = align(off + (size_t)gp->nchunks * gp->Npad * 4);
   gp->total = off;
   return PB_OK;
 }
 
-int launch_prep(const pb_operand* o, const OperandPlan& op, const GemmPlan& gp, int rows_pad, uint8_t* sf, float* f, cudaStream_t st) {
-  PrepParams q{o->sc8, o->sc32, sf, f, (int)o->rows, rows_pad, gp.KB, gp.KG, gp.P, gp.nchunks, o->grid_a, o->transposed_blocks, op.Ksg};
-  const int64_t items = (int64_t)rows_pad * (gp.KG * 4 + gp.nchunks);
+int launch_prep(const pb_operand* o, const OperandPlan& op, const GemmPlan& gp, int rows_pad, int tile_rows, int tiles, int atoms_per_tile,
+                uint8_t* sf, float* f, cudaStream_t st) {
+  PrepParams q{o->sc8, o->sc32, sf, f, (int)o->rows, rows_pad, gp.KB, gp.KG, gp.P, gp.nchunks, tile_rows, tiles, atoms_per_tile,
+               o->grid_a, o->transposed_blocks, op.Ksg};
+  const int64_t items = (int64_t)gp.KG * tiles * atoms_per_tile * 512 + (int64_t)rows_pad * gp.nchunks;
   const int64_t need = (items + 255) / 256;
   const int grid = (int)(need < (int64_t)sm_count() * 8 ? need : (int64_t)sm_count() * 8);
   gemm_prep_kernel<<<grid, 256, 0, st>>>(q);
@@ -965,7 +1099,7 @@ int launch_prep(const pb_operand* o, const OperandPlan& op, const GemmPlan& gp, 
 }
 
 template <int BN, bool PROF>
-int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st) {
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const GemmParams& p, cudaStream_t st) {
   static std::mutex mu;
   static bool configured[64] = {false};
   int dev = 0;
@@ -979,7 +1113,7 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_tn_kernel<BN, PROF><<<grid, Cfg<BN>::kThreads, Cfg<BN>::kSmemBytes, st>>>(ma, mb, p);
+  gemm_tn_kernel<BN, PROF><<<grid, Cfg<BN>::kThreads, Cfg<BN>::kSmemBytes, st>>>(ma, mb, md, p);
   PB_LAUNCH_CHECK("gemm_tn_kernel");
   return PB_OK;
 }
@@ -1029,8 +1163,8 @@ extern "C" int pb_gemm_tn(const pb_operand* a, const pb_operand* b, void* d, int
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
 
-  if (int s = launch_prep(a, gp.pa, gp, gp.Mpad, ws + gp.off_sfa, reinterpret_cast<float*>(ws + gp.off_fa), st)) return s;
-  if (int s = launch_prep(b, gp.pb, gp, gp.Npad, ws + gp.off_sfb, reinterpret_cast<float*>(ws + gp.off_fb), st)) return s;
+  if (int s = launch_prep(a, gp.pa, gp, gp.Mpad, 128, gp.tiles_m, 1, ws + gp.off_sfa, reinterpret_cast<float*>(ws + gp.off_fa), st)) return s;
+  if (int s = launch_prep(b, gp.pb, gp, gp.Npad, gp.BN, gp.tiles_n, gp.atoms_b, ws + gp.off_sfb, reinterpret_cast<float*>(ws + gp.off_fb), st)) return s;
 
   CUtensorMap ma, mb;
   if (int s = make_operand_map(&ma, a->q, a->rows, a->depth, BM)) return s;
@@ -1042,18 +1176,30 @@ extern "C" int pb_gemm_tn(const pb_operand* a, const pb_operand* b, void* d, int
   p.d = d; p.ldd = ldd;
   p.M = (int)a->rows; p.N = (int)b->rows; p.KB = gp.KB; p.P = gp.P; p.nchunks = gp.nchunks;
   p.Mpad = gp.Mpad; p.Npad = gp.Npad;
-  p.tiles_m = gp.Mpad / (gp.pair ? 256 : BM); p.tiles_n = (int)((b->rows + gp.BN - 1) / gp.BN);
+  p.tiles_m = gp.pair ? gp.Mpad / 256 : gp.tiles_m; p.tiles_n = gp.tiles_n;
   p.a_fmt = a->format; p.b_fmt = b->format; p.d_dtype = d_dtype;
   p.fb_uniform = gp.pb.row_uniform ? 1 : 0;
+  p.tma_store = 0;
   p.profile = profile_level();
   if (gp.pair) {
     CUtensorMap msfa, msfb;
-    if (int s = make_sf_map(&msfa, ws + gp.off_sfa, (int64_t)gp.KG * (gp.Mpad / 128), 1)) return s;
-    if (int s = make_sf_map(&msfb, ws + gp.off_sfb, (int64_t)gp.KG * (gp.Npad / 128), 2)) return s;
+    if (int s = make_sf_map(&msfa, ws + gp.off_sfa, (int64_t)gp.KG * gp.tiles_m, 1)) return s;
+    if (int s = make_sf_map(&msfb, ws + gp.off_sfb, (int64_t)gp.KG * gp.tiles_n * 2, 2)) return s;
     return launch_gemm_pair(ma, mb, msfa, msfb, p, st);
   }
-  if (p.profile) return gp.BN == 256 ? launch_gemm<256, true>(ma, mb, p, st) : launch_gemm<128, true>(ma, mb, p, st);
-  return gp.BN == 256 ? launch_gemm<256, false>(ma, mb, p, st) : launch_gemm<128, false>(ma, mb, p, st);
+  // D goes out through TMA stores when its rows are 16-byte aligned; otherwise by direct stores
+  CUtensorMap md = ma;
+  const int es = d_dtype == PB_BF16 ? 2 : 4;
+  p.tma_store = ((reinterpret_cast<uintptr_t>(d) & 15) == 0 && (ldd * es) % 16 == 0) ? 1 : 0;
+  if (p.tma_store) {
+    if (int s = make_store_map(&md, d, d_dtype, a->rows, b->rows, ldd)) return s;
+  }
+  if (p.profile) {
+    if (gp.BN == 224) return launch_gemm<224, true>(ma, mb, md, p, st);
+    return gp.BN == 256 ? launch_gemm<256, true>(ma, mb, md, p, st) : launch_gemm<128, true>(ma, mb, md, p, st);
+  }
+  if (gp.BN == 224) return launch_gemm<224, false>(ma, mb, md, p, st);
+  return gp.BN == 256 ? launch_gemm<256, false>(ma, mb, md, p, st) : launch_gemm<128, false>(ma, mb, md, p, st);
 }
 
 extern "C" int pb_gemm_check(void* stream) {
