@@ -36,8 +36,8 @@ WORKLOAD = "configs[1]: X[8192,2048] bf16 -> (1,128) e4m3; W[2048,8192] (128,128
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised
 # under profiles/.  Quantizer: profiles/quantize_row128_bf16_X16384x4096.md, the same 67.1 M elements as the
 # X[32768,2048] launch timed here (134.2 MB read + 30.2 MB written before the kernel ends; the rest of the
-# 67.9 MB output is written back from L2 later).  GEMM: profiles/gemm_tn_8192x8192x2048_dram.md.
-GEMM_DRAM_TRAFFIC_BYTES = None
+# 67.9 MB output is written back from L2 later).  GEMM: the benchmark launch itself, second table of profiles/gemm_tn_4096x4096x2048.md.
+GEMM_DRAM_TRAFFIC_BYTES = 121.0e6
 QUANT_DRAM_TRAFFIC_BYTES = 164.4e6
 
 
@@ -325,6 +325,13 @@ def run_profile_case(name: str):
         t = quantize_impl(x, (1, 128))
         for _ in range(4):
             _ops.dequantize_impl(*t, torch.bfloat16, (1, 128))
+    elif name == "gemm_full":
+        m, n, k = M, N, K                                   # the benchmark's own launch, for DRAM-byte counters only
+        x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(k, n, device="cuda", dtype=torch.bfloat16) * 0.02
+        xq, wq = quantize_impl(x, (1, 128)), quantize_impl(w, (128, 128))
+        for _ in range(3):
+            _ops.matmul_impl(*xq, *wq, (1, 128), (128, 128), out_dtype=torch.bfloat16)
     else:
         m, n, k = 4096, 4096, 2048
         x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
@@ -343,7 +350,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "quantize", "dequantize"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "dequantize"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
     args = ap.parse_args()
     if args.profile_case:
