@@ -89,6 +89,15 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU reference arm
+def _use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core."""
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=os.cpu_count())
+    except Exception:
+        pass
+
+
 def cpu_sample(rows: int, seed: int = 0):
     """One pass of the oracle (numpy restatement of the reference) over a row sample of the
     workload: quantize X[rows, K], then dq(X) @ dq(W) in f32 for all N columns."""
@@ -109,6 +118,7 @@ CPU_SAMPLE_ROWS = 2048      # a quarter of the workload's rows; W is the full [2
 
 
 def cpu_baseline(budget_s: float = 12.0):
+    _use_all_host_threads()
     rows = CPU_SAMPLE_ROWS
     dt, _ = cpu_sample(rows)                      # warm-up / calibration
     reps, total = 0, 0.0
@@ -127,6 +137,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    _use_all_host_threads()
     rows = CPU_SAMPLE_ROWS
     for i in range(args.warmup):
         cpu_sample(rows, seed=100 + i)
