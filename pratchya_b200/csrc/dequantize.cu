@@ -35,26 +35,44 @@ template <> __device__ __forceinline__ void store16<__nv_bfloat16>(__nv_bfloat16
                                                         pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7])));
 }
 
+template <typename OutT, int FMT>
+__device__ __forceinline__ void dequantize16(const uint4 w, float x_sc, OutT* dst) {
+  const uint32_t in[4] = {w.x, w.y, w.z, w.w};
+  float v[16];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 lo = fp8x2_to_f32x2<FMT>((uint16_t)(in[j] & 0xffffu));
+    const float2 hi = fp8x2_to_f32x2<FMT>((uint16_t)(in[j] >> 16));
+    v[4 * j + 0] = apply_scale(lo.x, x_sc); v[4 * j + 1] = apply_scale(lo.y, x_sc);
+    v[4 * j + 2] = apply_scale(hi.x, x_sc); v[4 * j + 3] = apply_scale(hi.y, x_sc);
+  }
+  store16<OutT>(dst, v);
+}
+
 template <typename OutT, int FMT, int VEC>
 __global__ void __launch_bounds__(256)
 dequantize_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sc8, const float* __restrict__ sc32,
                   OutT* __restrict__ out, DqDims d) {
   const uint32_t stride = gridDim.x * blockDim.x;
-  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < d.total_vecs; i += stride) {
-    const float x_sc = block_multiplier(d, sc8, sc32, i);
-    if constexpr (VEC == 16) {
-      const uint4 w = __ldcs(reinterpret_cast<const uint4*>(q) + i);
-      const uint32_t in[4] = {w.x, w.y, w.z, w.w};
-      float v[16];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 lo = fp8x2_to_f32x2<FMT>((uint16_t)(in[j] & 0xffffu));
-        const float2 hi = fp8x2_to_f32x2<FMT>((uint16_t)(in[j] >> 16));
-        v[4 * j + 0] = apply_scale(lo.x, x_sc); v[4 * j + 1] = apply_scale(lo.y, x_sc);
-        v[4 * j + 2] = apply_scale(hi.x, x_sc); v[4 * j + 3] = apply_scale(hi.y, x_sc);
-      }
-      store16<OutT>(out + (size_t)i * 16, v);
-    } else {
+  if constexpr (VEC == 16) {
+    // two 16-byte vectors per iteration: both loads (and their scale lookups) are in flight together
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + stride < d.total_vecs; i += 2 * stride) {
+      const uint32_t i2 = i + stride;
+      const uint4 w0 = __ldcs(reinterpret_cast<const uint4*>(q) + i);
+      const uint4 w1 = __ldcs(reinterpret_cast<const uint4*>(q) + i2);
+      const float s0 = block_multiplier(d, sc8, sc32, i);
+      const float s1 = block_multiplier(d, sc8, sc32, i2);
+      dequantize16<OutT, FMT>(w0, s0, out + (size_t)i * 16);
+      dequantize16<OutT, FMT>(w1, s1, out + (size_t)i2 * 16);
+    }
+    if (i < d.total_vecs) {
+      const uint4 w0 = __ldcs(reinterpret_cast<const uint4*>(q) + i);
+      dequantize16<OutT, FMT>(w0, block_multiplier(d, sc8, sc32, i), out + (size_t)i * 16);
+    }
+  } else {
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < d.total_vecs; i += stride) {
+      const float x_sc = block_multiplier(d, sc8, sc32, i);
       const float2 f = fp8x2_to_f32x2<FMT>((uint16_t)q[i]);
       out[i] = Elem<OutT>::from_f32(apply_scale(f.x, x_sc));
     }
