@@ -355,6 +355,72 @@ def run_profile_case(name: str):
     return 0
 
 
+def run_triple():
+    """BASELINE.json configs[2] on one GPU, one projection at a time: forward, dgrad and wgrad of a
+    d_model=2048 layer at M = 32768 tokens with their quantizers.  Prints one JSON object (not
+    the benchmark line): device times per part, CUDA events, inputs seeded and resident in HBM."""
+    import torch
+    from pratchya_b200 import _lib
+    from pratchya_b200._qualia import _ops
+    torch.cuda.set_device(0)
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    tokens = 32768
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    out = {"config": "configs[2]: M=32768 tokens, d_model=2048, W~N(0,0.02), X~N(0,1), dY~N(0,1e-3); dY in e4m3 (reference dtype) unless noted",
+           "layers": {}}
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        _lib.check(lib.pb_gemm_check(stream))
+        return a.elapsed_time(b) / reps
+
+    for name, (k_in, n_out) in {"attn 2048->2048": (2048, 2048), "ffn up 2048->8192": (2048, 8192), "ffn down 8192->2048": (8192, 2048)}.items():
+        x = torch.randn(tokens, k_in, device="cuda", generator=gen).to(torch.bfloat16)
+        w = (torch.randn(k_in, n_out, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+        dy = (torch.randn(tokens, n_out, device="cuda", generator=gen) * 1e-3).to(torch.bfloat16)
+        wq = _ops.quantize_impl(w, (128, 128))
+        wt = _ops.transpose_bytes(wq[0])
+        xq = _ops.quantize_impl(x, (1, 128))
+        gq = _ops.quantize_impl(dy, (1, 128))
+        xt = _ops.quantize_transposed_impl(x, 128)
+        gt = _ops.quantize_transposed_impl(dy, 128)
+        dev = x.device
+        op = _ops._operand
+        parts = {}
+        flop = 2.0 * tokens * k_in * n_out
+        ms = timed(lambda: _ops.gemm_tn(op(xq[0], xq[1], xq[2], tokens, k_in, (1, 128)), op(wt, wq[1], wq[2], n_out, k_in, (128, 128), 1), torch.bfloat16, dev))
+        parts["fwd_gemm"] = {"ms": ms, "tflops": flop / ms / 1e9}
+        ms = timed(lambda: _ops.gemm_tn(op(gq[0], gq[1], gq[2], tokens, n_out, (1, 128)), op(wq[0], wq[1], wq[2], k_in, n_out, (128, 128)), torch.bfloat16, dev))
+        parts["dgrad_gemm"] = {"ms": ms, "tflops": flop / ms / 1e9}
+        ms = timed(lambda: _ops.gemm_tn(op(xt[0], xt[1], xt[2], k_in, tokens, (1, 128)), op(gt[0], gt[1], gt[2], n_out, tokens, (1, 128)), torch.float32, dev))
+        parts["wgrad_gemm"] = {"ms": ms, "tflops": flop / ms / 1e9}
+        ms = timed(lambda: _ops.quantize_impl(x, (1, 128)))
+        parts["quantize_x_1x128"] = {"ms": ms, "gbs": tokens * k_in * QUANT_BYTES_PER_ELEM / ms / 1e6}
+        ms = timed(lambda: _ops.quantize_transposed_impl(x, 128))
+        parts["quantize_xT_1x128"] = {"ms": ms, "gbs": tokens * k_in * QUANT_BYTES_PER_ELEM / ms / 1e6}
+        ms = timed(lambda: _ops.quantize_impl(dy, (1, 128)))
+        parts["quantize_dy_1x128"] = {"ms": ms, "gbs": tokens * n_out * QUANT_BYTES_PER_ELEM / ms / 1e6}
+        ms = timed(lambda: _ops.quantize_impl(dy, (1, 128), out_format="e5m2"))
+        parts["quantize_dy_1x128_e5m2"] = {"ms": ms, "gbs": tokens * n_out * QUANT_BYTES_PER_ELEM / ms / 1e6}
+        ms = timed(lambda: _ops.quantize_transposed_impl(dy, 128))
+        parts["quantize_dyT_1x128"] = {"ms": ms, "gbs": tokens * n_out * QUANT_BYTES_PER_ELEM / ms / 1e6}
+        ms = timed(lambda: _ops.quantize_impl(w, (128, 128)))
+        parts["quantize_w_128x128"] = {"ms": ms, "gbs": k_in * n_out * QUANT_BYTES_PER_ELEM / ms / 1e6}
+        out["layers"][name] = parts
+        del x, w, dy, xq, gq, xt, gt
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -363,7 +429,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "dequantize"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
+    ap.add_argument("--triple", action="store_true", help="time the forward/dgrad/wgrad parts of BASELINE configs[2] and exit")
     args = ap.parse_args()
+    if args.triple:
+        return run_triple()
     if args.profile_case:
         return run_profile_case(args.profile_case)
     if args.impl == "reference":

@@ -98,6 +98,94 @@ transpose_apply_kernel(const InT* __restrict__ x, const float* __restrict__ divi
   }
 }
 
+
+// ---- vectorised variants (cols a multiple of the tile width, 16-byte aligned rows) -------------
+// Column-block amax: a CTA owns one 128-row block of kAmaxCols channels.  Each lane keeps VEC
+// channels, each warp 16 of the 128 rows (16 independent 128-bit loads per lane), then the eight
+// warps are reduced through shared memory.
+template <typename InT> struct Vec16 { static constexpr int n = 16 / (int)sizeof(InT); };
+
+template <typename InT>
+__global__ void __launch_bounds__(256)
+column_amax128_kernel(const InT* __restrict__ x, uint32_t* __restrict__ amax_bits, int rows, int cols) {
+  constexpr int VEC = Vec16<InT>::n;
+  constexpr int kCols = 32 * VEC;
+  __shared__ float red[8][kCols];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c0 = blockIdx.x * kCols + lane * VEC;
+  const int rb = blockIdx.y, nrb = rows / 128;
+  const InT* src = x + ((size_t)blockIdx.z * rows + (size_t)rb * 128 + warp * 16) * cols + c0;
+  float m[VEC];
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) m[j] = 0.0f;
+  uint4 w[16];
+#pragma unroll
+  for (int r = 0; r < 16; ++r) w[r] = __ldcs(reinterpret_cast<const uint4*>(src + (size_t)r * cols));
+#pragma unroll
+  for (int r = 0; r < 16; ++r) {
+    const uint32_t in[4] = {w[r].x, w[r].y, w[r].z, w[r].w};
+    if constexpr (sizeof(InT) == 2) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        m[2 * j] = fmaxf(m[2 * j], fabsf(__uint_as_float(in[j] << 16)));
+        m[2 * j + 1] = fmaxf(m[2 * j + 1], fabsf(__uint_as_float(in[j] & 0xffff0000u)));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) m[j] = fmaxf(m[j], fabsf(__uint_as_float(in[j])));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) red[warp][lane * VEC + j] = m[j];
+  __syncthreads();
+  for (int c = threadIdx.x; c < kCols; c += 256) {
+    float v = red[0][c];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) v = fmaxf(v, red[k][c]);
+    amax_bits[((size_t)blockIdx.z * cols + blockIdx.x * kCols + c) * nrb + rb] = __float_as_uint(v);
+  }
+}
+
+// Apply + transpose: a CTA owns 128 rows (one block row) x 64 channels.  The tile is loaded with
+// 128-bit loads into shared memory; then thread (channel, segment) walks 32 rows down its channel
+// (consecutive lanes = consecutive channels: conflict-free), quantizes with the block's divisor and
+// writes one whole 32-byte sector of the transposed output.
+template <typename InT, int FMT>
+__global__ void __launch_bounds__(256)
+transpose_apply128_kernel(const InT* __restrict__ x, const float* __restrict__ divisor, uint8_t* __restrict__ q_t,
+                          int rows, int cols) {
+  constexpr int VEC = Vec16<InT>::n;
+  constexpr int kPitch = 64 + VEC;                   // elements per tile row, padded
+  __shared__ __align__(16) InT tile[128 * kPitch];
+  const int r0 = blockIdx.y * 128, c0 = blockIdx.x * 64;
+  const InT* src = x + (size_t)blockIdx.z * rows * cols + (size_t)r0 * cols + c0;
+  constexpr int kThreadsPerRow = 64 / VEC;           // 8 (bf16) or 16 (f32)
+  constexpr int kRowsPerPass = 256 / kThreadsPerRow;
+  const int lr = threadIdx.x / kThreadsPerRow, lc = (threadIdx.x % kThreadsPerRow) * VEC;
+#pragma unroll
+  for (int p = 0; p < 128 / kRowsPerPass; ++p) {
+    const int r = p * kRowsPerPass + lr;
+    const uint4 v = __ldcs(reinterpret_cast<const uint4*>(src + (size_t)r * cols + lc));
+    *reinterpret_cast<uint4*>(&tile[r * kPitch + lc]) = v;
+  }
+  __syncthreads();
+  const int c = threadIdx.x & 63, seg = threadIdx.x >> 6;      // 4 segments of 32 rows
+  const int nrb = rows / 128;
+  const float D = divisor[((size_t)blockIdx.z * cols + c0 + c) * nrb + blockIdx.y];
+  const float rcp = __frcp_rn(D);
+  uint32_t out[8];
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = div_hoisted(Elem<InT>::to_f32(tile[(seg * 32 + w * 4 + j) * kPitch + c]), D, rcp);
+    out[w] = bf16x2_to_fp8x2<FMT>(pack_bf16x2(v[0], v[1])) | (bf16x2_to_fp8x2<FMT>(pack_bf16x2(v[2], v[3])) << 16);
+  }
+  uint8_t* o = q_t + (size_t)blockIdx.z * rows * cols + (size_t)(c0 + c) * rows + r0 + seg * 32;
+  asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(o), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7]) : "memory");
+}
+
 __global__ void __launch_bounds__(256)
 transpose_bytes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int rows, int cols) {
   __shared__ uint8_t tile[kTile][kTile + 4];
@@ -144,6 +232,28 @@ extern "C" int pb_quantize_transposed(const void* x, int x_dtype, int64_t batch,
   uint32_t* amax_bits = static_cast<uint32_t*>(workspace);
   float* divisor = reinterpret_cast<float*>(amax_bits + batch * g.Nb);
 
+  uint8_t* out = static_cast<uint8_t*>(q_t);
+  const int vec = x_dtype == PB_BF16 ? 8 : 4;
+  const bool fast = b == 128 && cols % (32 * vec) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(q_t) & 31) == 0 && rows % 32 == 0 && cols / 64 <= 65535;
+  if (fast) {
+    const dim3 ga((unsigned)(cols / (32 * vec)), (unsigned)(rows / 128), (unsigned)batch);
+    if (x_dtype == PB_BF16) column_amax128_kernel<__nv_bfloat16><<<ga, 256, 0, st>>>((const __nv_bfloat16*)x, amax_bits, (int)rows, (int)cols);
+    else                    column_amax128_kernel<float><<<ga, 256, 0, st>>>((const float*)x, amax_bits, (int)rows, (int)cols);
+    PB_LAUNCH_CHECK("column_amax128_kernel");
+    if (int s = launch_group_scales(amax_bits, divisor, sc8, sc32, batch * g.M, g.K, st)) return s;
+    const dim3 gc((unsigned)(cols / 64), (unsigned)(rows / 128), (unsigned)batch);
+    if (x_dtype == PB_BF16) {
+      if (out_format == PB_E4M3) transpose_apply128_kernel<__nv_bfloat16, PB_E4M3><<<gc, 256, 0, st>>>((const __nv_bfloat16*)x, divisor, out, (int)rows, (int)cols);
+      else                       transpose_apply128_kernel<__nv_bfloat16, PB_E5M2><<<gc, 256, 0, st>>>((const __nv_bfloat16*)x, divisor, out, (int)rows, (int)cols);
+    } else {
+      if (out_format == PB_E4M3) transpose_apply128_kernel<float, PB_E4M3><<<gc, 256, 0, st>>>((const float*)x, divisor, out, (int)rows, (int)cols);
+      else                       transpose_apply128_kernel<float, PB_E5M2><<<gc, 256, 0, st>>>((const float*)x, divisor, out, (int)rows, (int)cols);
+    }
+    PB_LAUNCH_CHECK("transpose_apply128_kernel");
+    return PB_OK;
+  }
+
   const dim3 grid1((unsigned)((cols + 255) / 256), (unsigned)(rows / b), (unsigned)batch);
   if (x_dtype == PB_BF16) column_amax_kernel<__nv_bfloat16><<<grid1, 128, 0, st>>>((const __nv_bfloat16*)x, amax_bits, (int)rows, (int)cols, b);
   else                    column_amax_kernel<float><<<grid1, 128, 0, st>>>((const float*)x, amax_bits, (int)rows, (int)cols, b);
@@ -151,7 +261,6 @@ extern "C" int pb_quantize_transposed(const void* x, int x_dtype, int64_t batch,
   if (int s = launch_group_scales(amax_bits, divisor, sc8, sc32, batch * g.M, g.K, st)) return s;
 
   const dim3 grid3((unsigned)((cols + kTile - 1) / kTile), (unsigned)((rows + kTile - 1) / kTile), (unsigned)batch);
-  uint8_t* out = static_cast<uint8_t*>(q_t);
   if (x_dtype == PB_BF16) {
     if (out_format == PB_E4M3) transpose_apply_kernel<__nv_bfloat16, PB_E4M3><<<grid3, 256, 0, st>>>((const __nv_bfloat16*)x, divisor, out, (int)rows, (int)cols, b);
     else                       transpose_apply_kernel<__nv_bfloat16, PB_E5M2><<<grid3, 256, 0, st>>>((const __nv_bfloat16*)x, divisor, out, (int)rows, (int)cols, b);
