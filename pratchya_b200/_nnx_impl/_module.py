@@ -57,3 +57,82 @@ class LowRankFFN:
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         return self.up(torch.tanh(self.down(x)))
+
+
+class _LinearFn(torch.autograd.Function):
+    """Differentiable FP8 linear layer: forward and the custom-VJP chain of the reference
+    (dequantize_impl_bwd -> quantize_impl_bwd -> matmul_impl_bwd -> quantize_impl_bwd,
+    pratchya/_qualia/_qarr.py:575-601, 514-526, 616-640) on the tensor-core kernels.
+
+    recipe "fp8" (default): dY is quantized on (1,128) for dgrad, and both X^T and dY^T are
+    quantized on (1,128) along the tokens for wgrad (the operands of fp8_matmul_bwd, :784-789);
+    the reference's matmul_impl_bwd keeps dY in f32, which no tensor-core K-block can consume.
+    recipe "reference": the literal f32 dots on dequantized operands (library matmul).
+    In both, dX is quantized on (1,a) and dequantized again, and dW is quantized on the weight's
+    grid, as the reference returns them (:637-640, :522-526)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, grid, fake_quant_output, recipe, grad_format):
+        a, b = grid
+        x2 = x.reshape(-1, x.shape[-1])
+        wq = _ops.quantize_impl(weight, grid)
+        xq = _ops.quantize_impl(x2, (1, a))
+        eligible = _ops._tensor_core_eligible(xq[0], wq[0], (1, a), grid)
+        w_t = _ops.transpose_bytes(wq[0]) if eligible else None
+        y = _ops.matmul_impl(*xq, *wq, (1, a), grid, y_fp8_t=w_t, out_dtype=torch.float32)
+        ctx.grid, ctx.recipe, ctx.grad_format, ctx.fake = grid, recipe, grad_format, fake_quant_output
+        ctx.x_shape, ctx.x_dtype, ctx.w_dtype = x.shape, x.dtype, weight.dtype
+        saved = [*xq, *wq]
+        if recipe == "fp8" and eligible and x2.shape[0] % 1024 == 0:
+            saved += list(_ops.quantize_transposed_impl(x2, 128))      # X^T on (1,128) for wgrad; x itself is not kept
+            ctx.have_xt = True
+        else:
+            ctx.have_xt = False
+        if fake_quant_output:
+            yq = _ops.quantize_impl(y, (1, b))
+            y = _ops.dequantize_impl(*yq, x.dtype, (1, b))
+            saved += [yq[1], yq[2]]
+        else:
+            y = y.to(x.dtype)
+        ctx.save_for_backward(*saved)
+        return y.reshape(*x.shape[:-1], weight.shape[1])
+
+    @staticmethod
+    def backward(ctx, g_y):
+        a, b = ctx.grid
+        saved = list(ctx.saved_tensors)
+        xq, wq = saved[0:3], saved[3:6]
+        pos = 6
+        xt = None
+        if ctx.have_xt:
+            xt, pos = saved[6:9], 9
+        g = g_y.reshape(-1, g_y.shape[-1]).contiguous()
+        if ctx.fake:                                    # cotangent of the output's dequantize, :575-601
+            g = _ops.dequantize_impl_bwd(saved[pos], saved[pos + 1], g, (1, b))
+        m, k = xq[0].shape
+        n = wq[0].shape[1]
+        if xt is not None:
+            gq = _ops.quantize_impl(g, (1, 128), out_format=ctx.grad_format)
+            gt = _ops.quantize_transposed_impl(g, 128, out_format=ctx.grad_format)
+            op = _ops._operand
+            gx = _ops.gemm_tn(op(gq[0], gq[1], gq[2], m, n, (1, 128)), op(wq[0], wq[1], wq[2], k, n, (128, 128)), torch.float32, g.device)
+            gw = _ops.gemm_tn(op(xt[0], xt[1], xt[2], k, m, (1, 128)), op(gt[0], gt[1], gt[2], n, m, (1, 128)), torch.float32, g.device)
+        else:
+            x_hat = _ops.dequantize_impl(*xq, torch.float32, (1, a))
+            w_hat = _ops.dequantize_impl(*wq, torch.float32, ctx.grid)
+            g32 = g.to(torch.float32)
+            gx = _ops._matmul_f32(g32, w_hat.t())
+            gw = _ops._matmul_f32(x_hat.t(), g32)
+        gx = _ops.dequantize_impl(*_ops.quantize_impl(gx, (1, a)), torch.float32, (1, a))        # :637 then :522-526
+        gw = _ops.dequantize_impl(*_ops.quantize_impl(gw, ctx.grid), torch.float32, ctx.grid)    # :638; the optimizer dequantizes it
+        return gx.reshape(ctx.x_shape).to(ctx.x_dtype), gw.to(ctx.w_dtype), None, None, None, None
+
+
+def linear_fp8(x: torch.Tensor, weight: torch.Tensor, tgrid=(128, 128), *, fake_quant_output: bool = True,
+               recipe: str = "fp8", grad_format: str = "e4m3") -> torch.Tensor:
+    """y = Linear(x) with a dense master `weight` [fan_in, fan_out] that is quantized on `tgrid` in
+    the forward pass; differentiable in x and weight.  `grad_format="e5m2"` stores dY in e5m2
+    (an extension: the reference has no e5m2 anywhere)."""
+    if recipe not in ("fp8", "reference"):
+        raise ValueError("recipe must be 'fp8' or 'reference'")
+    return _LinearFn.apply(x, weight, (int(tgrid[0]), int(tgrid[1])), fake_quant_output, recipe, grad_format)
