@@ -594,29 +594,34 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ==============================================================================================
-// CTA-pair variant: tcgen05.mma.cta_group::2 on 256x256 output tiles.  Each CTA of a 2-CTA
-// cluster owns 128 rows of the tile (its own TMEM accumulator) and stages its own 128 rows of A
-// and its own 128 of the tile's 256 rows of B, so a k-block costs each SM 32 KB of TMA writes
-// and 32 KB of tensor-core reads of shared memory instead of 48 + 48 KB: the single-CTA tile is
-// bound by that shared-memory traffic.  The leader CTA (cluster rank 0) issues every MMA and
+// CTA-pair variant: tcgen05.mma.cta_group::2 on 256 x 224 output tiles.  Each CTA of a 2-CTA
+// cluster owns 128 rows of the tile (its own TMEM accumulators) and stages its own 128 rows of A
+// and its own 112 of the tile's 224 rows of B, so a k-block moves 30 KB from L2 into each SM
+// instead of 44 KB: the single-CTA kernel is bound by that L2-to-SM traffic (about 9 TB/s summed
+// over the chip at 2.1 PFLOP/s).  The leader CTA (cluster rank 0) issues every MMA and
 // scale-factor copy for the pair; all TMA loads of both CTAs complete on the leader's barrier.
 struct Cfg2 {
-  static constexpr int BN = 256;
+  static constexpr int BN = 224;
   static constexpr int kStages = 6;
+  static constexpr int kAccBufs = 2;
   static constexpr int kEpiWarps = 8;
   static constexpr int kThreads = 128 + 32 * kEpiWarps;
   static constexpr int kABytes = BM * BK;            // this CTA's 128 rows of A
-  static constexpr int kBBytes = 128 * BK;           // this CTA's half of the tile's B rows
+  static constexpr int kBBytes = (BN / 2) * BK;      // this CTA's half of the tile's B rows
   static constexpr int kSfaBytes = 512;              // scale factors of this CTA's A rows
-  static constexpr int kSfbBytes = 1024;             // scale factors of all 256 B rows (each CTA needs them all)
-  static constexpr int kSfStage = kSfaBytes + kSfbBytes;
-  static constexpr int kSfCols = 4 + BN / 32;
-  static constexpr int kSfColBase = BN;
+  static constexpr int kSfbBytes = 1024;             // scale factors of all 224 B rows (each CTA needs them all)
+  static constexpr int kSfSlot = kSfaBytes + kSfbBytes;
+  static constexpr int kSfSlots = 2;
+  static constexpr int kSfCols = 12;
+  static constexpr int kSfColBase = kAccBufs * BN;
   static constexpr int kOffB = kStages * kABytes;
   static constexpr int kOffSf = kOffB + kStages * kBBytes;
-  static constexpr int kOffBar = kOffSf + kStages * kSfStage;
-  static constexpr int kNumBars = 2 * kStages + 2;
+  static constexpr int kOffStore = ((kOffSf + kSfSlots * kSfSlot + 1023) / 1024) * 1024;
+  static constexpr int kOffBar = kOffStore + kEpiWarps * 4096;
+  static constexpr int kNumBars = 2 * kStages + 2 * kAccBufs;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
+  static_assert(kSfColBase + 2 * kSfCols <= 512, "TMEM budget");
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -645,16 +650,10 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
 __device__ __forceinline__ void tc2_commit(uint32_t cluster_bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
-__device__ __forceinline__ void tc2_cp_sf(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-__device__ __forceinline__ void tc2_mma_block_scaled(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                     uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+// one commit that arrives on the barrier at this shared-memory offset in both CTAs of the pair
+__device__ __forceinline__ void tc2_commit_both(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
 __device__ __forceinline__ void tc2_cp_sf_lo(uint32_t taddr, uint32_t desc_lo) {
   asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d;\n\t}"
@@ -670,25 +669,26 @@ __device__ __forceinline__ void tc2_mma_block_scaled_lo(uint32_t d_tmem, uint32_
       ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "r"(kOperandDescHi));
 }
 // as instr_desc, for the pair: M = 256
-__device__ __forceinline__ uint32_t instr_desc_pair(int a_fmt, int b_fmt, uint32_t sf_id) {
-  return (sf_id << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(256 >> 3) << 17) | (1u << 23) |
+__device__ __forceinline__ uint32_t instr_desc_pair(int bn, int a_fmt, int b_fmt, uint32_t sf_id) {
+  return (sf_id << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(bn >> 3) << 17) | (1u << 23) |
          ((uint32_t)(256 >> 4) << 24) | (sf_id << 29);
 }
 
+template <bool PROF>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg2::kThreads, 1)
 gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                    const __grid_constant__ GemmParams p) {
+                    const __grid_constant__ CUtensorMap map_d, const __grid_constant__ GemmParams p) {
   using C = Cfg2;
   constexpr int BN = C::BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t s_base = smem_u32(smem);
   const uint32_t s_a = s_base, s_b = s_base + C::kOffB, s_sf = s_base + C::kOffSf, s_bar = s_base + C::kOffBar;
-  auto bar_full = [&](int s) { return s_bar + 8u * s; };                       // used in the leader only
-  auto bar_empty = [&](int s) { return s_bar + 8u * (C::kStages + s); };       // one per CTA
-  const uint32_t bar_acc_full = s_bar + 8u * (2 * C::kStages);                 // one per CTA
-  const uint32_t bar_acc_empty = s_bar + 8u * (2 * C::kStages + 1);            // used in the leader only
+  auto bar_full = [&](int s) { return s_bar + 8u * s; };                                    // used in the leader only
+  auto bar_empty = [&](int s) { return s_bar + 8u * (C::kStages + s); };                    // one set per CTA
+  auto bar_acc_full = [&](int b) { return s_bar + 8u * (2 * C::kStages + b); };             // one set per CTA
+  auto bar_acc_empty = [&](int b) { return s_bar + 8u * (2 * C::kStages + C::kAccBufs + b); };   // used in the leader only
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffBar + C::kNumBars * 8);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -698,8 +698,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
-    mbar_init(bar_acc_full, 1);
-    mbar_init(bar_acc_empty, 2 * C::kEpiWarps);
+    for (int b = 0; b < C::kAccBufs; ++b) { mbar_init(bar_acc_full(b), 1); mbar_init(bar_acc_empty(b), 2 * C::kEpiWarps); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -713,65 +712,67 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;          // 256 x 256 tiles
+  const int num_tiles = p.tiles_m * p.tiles_n;          // 256 x 224 tiles
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
 
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-  if (warp == 0) {
-    // ------------------------------------------------------------- TMA producer (both CTAs)
-    if (lane == 0) {
-      uint32_t it = 0;
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp == 0 && lane == 0) {
+      // ------------------------------------------------------------- TMA producer (both CTAs)
+      uint32_t it = 0, sf_fills = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const int m0 = (tile % p.tiles_m) * 256 + (int)rank * 128;     // this CTA's rows of A and D
-        const int n0 = (tile / p.tiles_m) * BN;
+        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        const int m0 = tm * 256 + (int)rank * 128;          // this CTA's rows of A and D
+        const int n0 = tn * BN;
         for (int kb = 0; kb < p.KB; ++kb, ++it) {
           const int s = it % C::kStages;
           if (!mbar_wait(bar_empty(s), ((it / C::kStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
           const bool with_sf = (kb & 3) == 0;
           const uint32_t full = map_to_cta(bar_full(s), 0);
-          if (leader) mbar_arrive_expect_tx(bar_full(s), 2 * (C::kABytes + C::kBBytes + (with_sf ? C::kSfStage : 0)));
+          if (leader) mbar_arrive_expect_tx(bar_full(s), 2 * (C::kABytes + C::kBBytes + (with_sf ? C::kSfSlot : 0)));
           tma_load_2d_pair(s_a + s * C::kABytes, &map_a, kb * BK, m0, full);
-          tma_load_2d_pair(s_b + s * C::kBBytes, &map_b, kb * BK, n0 + (int)rank * 128, full);
+          tma_load_2d_pair(s_b + s * C::kBBytes, &map_b, kb * BK, n0 + (int)rank * (BN / 2), full);
           if (with_sf) {
             const int kg = kb >> 2;
-            tma_load_2d_pair(s_sf + s * C::kSfStage, &map_sfa, 0, kg * (p.Mpad / 128) + m0 / 128, full);
-            tma_load_2d_pair(s_sf + s * C::kSfStage + C::kSfaBytes, &map_sfb, 0, kg * (p.Npad / 128) + n0 / 128, full);
+            const uint32_t slot = s_sf + (sf_fills & 1u) * C::kSfSlot;      // see the single-CTA producer for the reuse argument
+            ++sf_fills;
+            tma_load_2d_pair(slot, &map_sfa, 0, kg * (2 * p.tiles_m) + 2 * tm + (int)rank, full);
+            tma_load_2d_pair(slot + C::kSfaBytes, &map_sfb, 0, (kg * p.tiles_n + tn) * 2, full);
           }
         }
       }
-    }
-  } else if (warp == 1 && leader) {
-    // ------------------------------------------------------------- MMA issuer (leader CTA only)
-    if (lane == 0) {
-      // same lean issue loop as the single-CTA kernel: 32-bit descriptor words, incremental stage state
-      const int prof = p.profile;
+    } else if (warp == 1 && lane == 0 && leader) {
+      // ------------------------------------------------------------- MMA issuer (leader CTA only)
       const int KB = p.KB, P = p.P, nchunks = p.nchunks;
-      const uint32_t idesc0 = instr_desc_pair(p.a_fmt, p.b_fmt, 0u);
+      const uint32_t idesc0 = instr_desc_pair(BN, p.a_fmt, p.b_fmt, 0u);
       const uint32_t a_lo0 = operand_desc_lo(s_a), b_lo0 = operand_desc_lo(s_b);
       const uint32_t sf_tmem0 = tmem_base + C::kSfColBase;
-      const uint32_t empty_peer0 = map_to_cta(bar_empty(0), 1), acc_full_peer = map_to_cta(bar_acc_full, 1);
-      uint32_t s = 0, phase = 0;
-      uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full(0), empty = bar_empty(0), empty_peer = empty_peer0, sf_lo = sf_desc_lo(s_sf);
-      uint32_t g = 0;
+      const uint32_t sf_lo0 = sf_desc_lo(s_sf);
+      const uint32_t empty_peer0 = map_to_cta(bar_empty(0), 1);
+      uint32_t s = 0, phase = 0, sf_reads = 0, g = 0;
+      uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full(0), empty = bar_empty(0), empty_peer = empty_peer0;
       long long wait_full = 0, wait_acc = 0;
-      const long long t_begin = prof ? clock64() : 0;
+      const long long t_begin = PROF ? clock64() : 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         for (int c = 0; c < nchunks && ok; ++c, ++g) {
-          long long t0 = prof ? clock64() : 0;
-          if (!mbar_wait(bar_acc_empty, (g & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-          if (prof) wait_acc += clock64() - t0;
+          const int buf = g % C::kAccBufs;
+          long long t0 = PROF ? clock64() : 0;
+          if (!mbar_wait(bar_acc_empty(buf), ((g / C::kAccBufs) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          if (PROF) wait_acc += clock64() - t0;
           tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * BN;
           const int kb_end = min(KB, (c + 1) * P);
           uint32_t accumulate = 0;
           for (int kb = c * P; kb < kb_end; ++kb) {
-            if (prof) t0 = clock64();
+            if (PROF) t0 = clock64();
             if (!mbar_wait(full, phase, abort_flag)) { ok = false; break; }
-            if (prof) wait_full += clock64() - t0;
+            if (PROF) wait_full += clock64() - t0;
             const uint32_t sf_col = sf_tmem0 + ((uint32_t)(kb >> 2) & 1u) * C::kSfCols;
             if ((kb & 3) == 0) {
+              const uint32_t sf_lo = sf_lo0 + (sf_reads & 1u) * (C::kSfSlot >> 4);
+              ++sf_reads;
               tc2_cp_sf_lo(sf_col, sf_lo);
               tc2_cp_sf_lo(sf_col + 4, sf_lo + (C::kSfaBytes >> 4));
               tc2_cp_sf_lo(sf_col + 8, sf_lo + ((C::kSfaBytes + 512) >> 4));
@@ -779,59 +780,60 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint32_t idesc = idesc0 + ((uint32_t)kb & 3u) * ((1u << 4) | (1u << 29));
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
-              tc2_mma_block_scaled_lo(tmem_base, a_lo + (k * UMMA_K >> 4), b_lo + (k * UMMA_K >> 4), idesc, sf_col, sf_col + 4, accumulate);
+              tc2_mma_block_scaled_lo(d_tmem, a_lo + (k * UMMA_K >> 4), b_lo + (k * UMMA_K >> 4), idesc, sf_col, sf_col + 4, accumulate);
               accumulate = 1;
             }
-            // free the stage in both CTAs once these MMAs have read it
-            tc2_commit(empty);
-            tc2_commit(empty_peer);
-            ++s; a_lo += C::kABytes >> 4; b_lo += C::kBBytes >> 4; full += 8; empty += 8; empty_peer += 8; sf_lo += C::kSfStage >> 4;
+            tc2_commit_both(empty);     // free the stage in both CTAs once these MMAs have read it
+            ++s; a_lo += C::kABytes >> 4; b_lo += C::kBBytes >> 4; full += 8; empty += 8; empty_peer += 8;
             if (s == C::kStages) {
               s = 0; phase ^= 1u;
-              a_lo = a_lo0; b_lo = b_lo0; full = bar_full(0); empty = bar_empty(0); empty_peer = empty_peer0; sf_lo = sf_desc_lo(s_sf);
+              a_lo = a_lo0; b_lo = b_lo0; full = bar_full(0); empty = bar_empty(0); empty_peer = empty_peer0;
             }
           }
           if (ok) {
-            tc2_commit(bar_acc_full);
-            tc2_commit(acc_full_peer);
+            tc2_commit_both(bar_acc_full(buf));
           }
         }
       }
-      if (p.profile) {
+      if (PROF) {
         atomicAdd(&g_gemm_prof[1], (unsigned long long)wait_full);
         atomicAdd(&g_gemm_prof[2], (unsigned long long)wait_acc);
         atomicAdd(&g_gemm_prof[6], (unsigned long long)(clock64() - t_begin - wait_full - wait_acc));
         atomicAdd(&g_gemm_prof[7], 1ull);
       }
     }
-  }
   } else {
     // ------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int ew = warp - 4;
     const int quarter = warp & 3;
     const int col_half = ew >> 2;
+    const int ncols = col_half == 0 ? 128 : BN - 128;
+    const bool four_parts = ncols == 128;
     const int row_in_tile = quarter * 32 + lane;
-    const uint32_t acc_empty_leader = map_to_cta(bar_acc_empty, 0);
-    uint32_t g = 0;
+    uint32_t g = 0, stores = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       const int m0 = (tile % p.tiles_m) * 256 + (int)rank * 128, n0 = (tile / p.tiles_m) * BN + col_half * 128;
       float acc[128];
       for (int c = 0; c < p.nchunks; ++c, ++g) {
+        const int buf = g % C::kAccBufs;
         const float fa = __ldg(p.fa + (size_t)c * p.Mpad + m0 + row_in_tile);
         const float* fbp = p.fb + (size_t)c * p.Npad + n0;
         const float s_uni = fa * __ldg(fbp);
-        if (!mbar_wait(bar_acc_full, g & 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(bar_acc_full(buf), (g / C::kAccBufs) & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + col_half * 128;
+        const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + col_half * 128;
+        const uint32_t acc_empty_leader = map_to_cta(bar_acc_empty(buf), 0);
         auto release = [&]() {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         };
+        if (p.profile == 3) { release(); continue; }     // diagnostic knobs, see the single-CTA kernel
         if (c == 0) {
-          tc_ld32f<0>(t_addr, acc); tc_ld32f<32>(t_addr + 32, acc); tc_ld32f<64>(t_addr + 64, acc); tc_ld32f<96>(t_addr + 96, acc);
+          tc_ld32f<0>(t_addr, acc); tc_ld32f<32>(t_addr + 32, acc); tc_ld32f<64>(t_addr + 64, acc);
+          if (four_parts) tc_ld32f<96>(t_addr + 96, acc);
           tc_wait_ld();
           release();
           if (p.fb_uniform) {
@@ -840,9 +842,11 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const float4 fb = __ldg(reinterpret_cast<const float4*>(fbp) + j);
-              acc[4 * j + 0] = acc[4 * j + 0] * fa * fb.x; acc[4 * j + 1] = acc[4 * j + 1] * fa * fb.y;
-              acc[4 * j + 2] = acc[4 * j + 2] * fa * fb.z; acc[4 * j + 3] = acc[4 * j + 3] * fa * fb.w;
+              if (j < 24 || four_parts) {
+                const float4 fb = __ldg(reinterpret_cast<const float4*>(fbp) + j);
+                acc[4 * j + 0] = acc[4 * j + 0] * fa * fb.x; acc[4 * j + 1] = acc[4 * j + 1] * fa * fb.y;
+                acc[4 * j + 2] = acc[4 * j + 2] * fa * fb.z; acc[4 * j + 3] = acc[4 * j + 3] * fa * fb.w;
+              }
             }
           }
         } else {
@@ -850,13 +854,28 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           tc_ld32(t_addr, r0);
           tc_wait_ld(); tc_ld32(t_addr + 32, r1); promote<0>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
           tc_wait_ld(); tc_ld32(t_addr + 64, r0); promote<32>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
-          tc_wait_ld(); tc_ld32(t_addr + 96, r1); promote<64>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
-          tc_wait_ld(); release();                promote<96>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
+          if (four_parts) {
+            tc_wait_ld(); tc_ld32(t_addr + 96, r1); promote<64>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
+            tc_wait_ld(); release();                promote<96>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
+          } else {
+            tc_wait_ld(); release();                promote<64>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
+          }
         }
       }
       if (!ok) break;
-      store_row_segment(p, acc, m0 + row_in_tile, n0);
+      if (p.profile >= 2) continue;
+      if (p.tma_store) {
+        const uint32_t stage = s_base + C::kOffStore + ew * 4096;
+        const int row0 = m0 + quarter * 32;
+        stage_and_store<0>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores);
+        stage_and_store<32>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores);
+        stage_and_store<64>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores);
+        if (four_parts) stage_and_store<96>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores);
+      } else {
+        store_row_segment(p, acc, m0 + row_in_tile, n0, ncols);
+      }
     }
+    if (lane == 0) tma_store_wait_all();
   }
 
   // Neither CTA may leave (or free TMEM) while its partner can still signal its barriers, read
@@ -1039,8 +1058,8 @@ struct GemmPlan {
   size_t off_sfa, off_sfb, off_fa, off_fb, total;
 };
 
-bool pick_pair() {      // PB_GEMM_MODE=pair selects the CTA-pair kernel (the single-CTA one measures faster so far)
-  static const bool pair = [] { const char* e = getenv("PB_GEMM_MODE"); return e && e[0] == 'p'; }();
+bool pick_pair() {      // the CTA-pair kernel is the default; PB_GEMM_MODE=single selects the single-CTA one
+  static const bool pair = [] { const char* e = getenv("PB_GEMM_MODE"); return !(e && e[0] == 's'); }();
   return pair;
 }
 
@@ -1065,7 +1084,7 @@ int make_plan(const pb_operand* a, const pb_operand* b, GemmPlan* gp) {
   if (a->depth != b->depth)
     return fail(PB_ERR_BAD_SHAPE, "pb_gemm_tn: contraction lengths differ (%lld vs %lld)", (long long)a->depth, (long long)b->depth);
   gp->pair = pick_pair() && a->rows > 128;
-  gp->BN = gp->pair ? 256 : pick_bn();
+  gp->BN = gp->pair ? Cfg2::BN : pick_bn();
   gp->P = gp->pa.P < gp->pb.P ? gp->pa.P : gp->pb.P;
   gp->KB = (int)(a->depth / BK);
   if (gp->P > gp->KB) gp->P = gp->KB;
@@ -1118,8 +1137,9 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
   return PB_OK;
 }
 
+template <bool PROF>
 int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msfa, const CUtensorMap& msfb,
-                     const GemmParams& p, cudaStream_t st) {
+                     const CUtensorMap& md, const GemmParams& p, cudaStream_t st) {
   static std::mutex mu;
   static bool configured[64] = {false};
   int dev = 0;
@@ -1127,14 +1147,14 @@ int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   {
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-      PB_CUDA_TRY(cudaFuncSetAttribute(gemm_tn_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::kSmemBytes));
+      PB_CUDA_TRY(cudaFuncSetAttribute(gemm_tn_pair_kernel<PROF>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::kSmemBytes));
       configured[dev] = true;
     }
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = sm_count() / 2;
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  gemm_tn_pair_kernel<<<grid, Cfg2::kThreads, Cfg2::kSmemBytes, st>>>(ma, mb, msfa, msfb, p);
+  gemm_tn_pair_kernel<PROF><<<grid, Cfg2::kThreads, Cfg2::kSmemBytes, st>>>(ma, mb, msfa, msfb, md, p);
   PB_LAUNCH_CHECK("gemm_tn_pair_kernel");
   return PB_OK;
 }
@@ -1168,7 +1188,7 @@ extern "C" int pb_gemm_tn(const pb_operand* a, const pb_operand* b, void* d, int
 
   CUtensorMap ma, mb;
   if (int s = make_operand_map(&ma, a->q, a->rows, a->depth, BM)) return s;
-  if (int s = make_operand_map(&mb, b->q, b->rows, b->depth, gp.pair ? 128 : gp.BN)) return s;
+  if (int s = make_operand_map(&mb, b->q, b->rows, b->depth, gp.pair ? Cfg2::BN / 2 : gp.BN)) return s;
 
   GemmParams p;
   p.sfa = ws + gp.off_sfa; p.sfb = ws + gp.off_sfb;
@@ -1181,18 +1201,18 @@ extern "C" int pb_gemm_tn(const pb_operand* a, const pb_operand* b, void* d, int
   p.fb_uniform = gp.pb.row_uniform ? 1 : 0;
   p.tma_store = 0;
   p.profile = profile_level();
-  if (gp.pair) {
-    CUtensorMap msfa, msfb;
-    if (int s = make_sf_map(&msfa, ws + gp.off_sfa, (int64_t)gp.KG * gp.tiles_m, 1)) return s;
-    if (int s = make_sf_map(&msfb, ws + gp.off_sfb, (int64_t)gp.KG * gp.tiles_n * 2, 2)) return s;
-    return launch_gemm_pair(ma, mb, msfa, msfb, p, st);
-  }
   // D goes out through TMA stores when its rows are 16-byte aligned; otherwise by direct stores
   CUtensorMap md = ma;
   const int es = d_dtype == PB_BF16 ? 2 : 4;
   p.tma_store = ((reinterpret_cast<uintptr_t>(d) & 15) == 0 && (ldd * es) % 16 == 0) ? 1 : 0;
   if (p.tma_store) {
     if (int s = make_store_map(&md, d, d_dtype, a->rows, b->rows, ldd)) return s;
+  }
+  if (gp.pair) {
+    CUtensorMap msfa, msfb;
+    if (int s = make_sf_map(&msfa, ws + gp.off_sfa, (int64_t)gp.KG * gp.tiles_m, 1)) return s;
+    if (int s = make_sf_map(&msfb, ws + gp.off_sfb, (int64_t)gp.KG * gp.tiles_n * 2, 2)) return s;
+    return p.profile ? launch_gemm_pair<true>(ma, mb, msfa, msfb, md, p, st) : launch_gemm_pair<false>(ma, mb, msfa, msfb, md, p, st);
   }
   if (p.profile) {
     if (gp.BN == 224) return launch_gemm<224, true>(ma, mb, md, p, st);
