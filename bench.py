@@ -299,8 +299,8 @@ def run_ours(args):
             "gpu_launches": args.steps * 4,
             "parts": {"gemm_ms": g_ms, "gemm_tflops": gemm_tflops, "quantize_ms": q_ms,
                       "quantize_gbs_in_step": M * K * QUANT_BYTES_PER_ELEM / (q_ms * 1e-3) / 1e9,
-                      "kernels_per_step": "quantize_row128_bf16, gemm_prep x2, gemm_tn"},
-            "roofline": {"bound": "tensor", "kernel": "gemm_tn_kernel", "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s",
+                      "kernels_per_step": "quantize_row128_bf16, gemm_prep x2, gemm_tn_pair"},
+            "roofline": {"bound": "tensor", "kernel": "gemm_tn_pair_kernel", "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s",
                          "frac": gemm_tflops / fp8_peak, "traffic": GEMM_DRAM_TRAFFIC_BYTES,
                          "peak_source": f"2 x bf16_tflops burst of {peaks['source']} (no FP8 figure is measured); nominal dense FP8 is 4500",
                          "frac_of_nominal_4500": gemm_tflops / 4500.0},
