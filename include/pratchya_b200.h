@@ -138,6 +138,30 @@ PB_API size_t pb_gemm_workspace_size(const pb_operand* a, const pb_operand* b);
 PB_API int pb_gemm_tn(const pb_operand* a, const pb_operand* b,
                void* d, int d_dtype, int64_t ldd,
                void* workspace, size_t workspace_bytes, void* stream);
+/* pb_gemm_tn with the re-tiling of the scales skipped for operands whose prepared scales are
+ * already in `workspace` (no counterpart in the reference: it saves the two small launches that
+ * pb_gemm_tn spends on them in a step like Linear.__call__, pratchya/_nnx_impl/_module.py:46-50,
+ * where the weight's scales do not change between calls).
+ *   PB_GEMM_A_PREPARED  A's scales were written by pb_quantize_for_gemm into this workspace.
+ *   PB_GEMM_B_PREPARED  an earlier pb_gemm_tn / pb_gemm_tn_ex with the same B (bytes may differ, sc8
+ *                       and sc32 may not), the same A shape and grid and this workspace has run, and
+ *                       nothing else has written the workspace since.
+ * flags = 0 is pb_gemm_tn. PB_GEMM_A_PREPARED on an operand pair whose fp32 factors do not hold
+ * for eight k-blocks at a time returns PB_ERR_UNSUPPORTED. */
+#define PB_GEMM_A_PREPARED 1u
+#define PB_GEMM_B_PREPARED 2u
+PB_API int pb_gemm_tn_ex(const pb_operand* a, const pb_operand* b,
+                  void* d, int d_dtype, int64_t ldd,
+                  void* workspace, size_t workspace_bytes, unsigned int flags, void* stream);
+/* quantize_impl (pratchya/_qualia/_qarr.py:458-506) on the (1,128) grid for an activation
+ * x[rows, cols] that is about to be operand A of pb_gemm_tn_ex against `b`: the same q, sc8 and
+ * sc32 as pb_quantize, and in the same pass A's scales in the layout the GEMM kernel reads, written
+ * into `gemm_workspace` (size from pb_gemm_workspace_size(a, b)).  cols must be a multiple of
+ * 1024 (whole super-groups of eight blocks per row); PB_ERR_UNSUPPORTED when b's scales do not
+ * allow promotion every eight k-blocks.  Follow it with pb_gemm_tn_ex(..., PB_GEMM_A_PREPARED ...). */
+PB_API int pb_quantize_for_gemm(const void* x, int x_dtype, int64_t rows, int64_t cols, int out_format,
+                         void* q, uint8_t* sc8, float* sc32,
+                         const pb_operand* b, void* gemm_workspace, size_t gemm_workspace_bytes, void* stream);
 /* Reads (and clears) the device status word of the last GEMMs launched on this
  * device; synchronises `stream`.  PB_OK or PB_ERR_DEVICE_TIMEOUT. */
 PB_API int pb_gemm_check(void* stream);

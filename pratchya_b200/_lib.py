@@ -15,6 +15,9 @@ PB_F32, PB_BF16 = 0, 1
 PB_E4M3, PB_E5M2 = 0, 1
 
 
+PB_ERR_UNSUPPORTED = 8
+
+
 class PbError(RuntimeError):
     def __init__(self, status: int, text: str):
         super().__init__(f"pratchya_b200 status {status}: {text}")
@@ -45,6 +48,8 @@ _SIGNATURES = {
     "pb_dequantize_bwd": (_int, [_ptr, _int, _ptr, _ptr, _i64, _i64, _i64, _int, _int, _ptr, _ptr]),
     "pb_gemm_workspace_size": (_sz, [C.POINTER(Operand), C.POINTER(Operand)]),
     "pb_gemm_tn": (_int, [C.POINTER(Operand), C.POINTER(Operand), _ptr, _int, _i64, _ptr, _sz, _ptr]),
+    "pb_gemm_tn_ex": (_int, [C.POINTER(Operand), C.POINTER(Operand), _ptr, _int, _i64, _ptr, _sz, C.c_uint, _ptr]),
+    "pb_quantize_for_gemm": (_int, [_ptr, _int, _i64, _i64, _int, _ptr, _ptr, _ptr, C.POINTER(Operand), _ptr, _sz, _ptr]),
     "pb_gemm_check": (_int, [_ptr]),
     "pb_transpose_bytes": (_int, [_ptr, _i64, _i64, _ptr, _ptr]),
     "pb_debug_division_check": (_int, [C.c_uint64, C.c_uint64, _ptr, _ptr]),

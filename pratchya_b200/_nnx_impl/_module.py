@@ -8,6 +8,7 @@ import math
 
 import torch
 
+from .. import _lib
 from .._qualia import _ops
 from .._qualia._qarr import QArrayImpl
 
@@ -31,6 +32,8 @@ class Linear:
         if kernel is None:
             kernel = lecun_normal(fan_in, fan_out, generator=generator, device=device, dtype=dtype)
         self.kernel = kernel if isinstance(kernel, QArrayImpl) else QArrayImpl(kernel, tuple(tgrid))
+        self._steps = {}       # (rows, out dtype) -> LinearStep, or None where the fused path does not apply
+        self._steps_kernel = self.kernel
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         a, _ = self.kernel.tgrid
@@ -41,10 +44,39 @@ class Linear:
         """dq(Q(x, (1,a))) @ dq(W) accumulated in fp32, returned in `out_dtype` (default x.dtype)."""
         a, _ = self.kernel.tgrid
         k = self.kernel
+        step = self._fused_step(x, out_dtype or x.dtype)
+        if step is not None:
+            d, _ = step(x)
+            return d.reshape(*x.shape[:-1], d.shape[-1])
         xq = _ops.quantize_impl(x, (1, a))
         y_t = k.transposed_value() if _ops._tensor_core_eligible(xq[0], k.get_value(), (1, a), k.tgrid) else None
         return _ops.matmul_impl(*xq, k.get_value(), k.sc_fp8, k.sc_fp32, (1, a), k.tgrid, y_fp8_t=y_t,
                                 out_dtype=out_dtype or x.dtype)
+
+
+    def _fused_step(self, x, out_dtype):
+        """The two-launch path (quantizer that also lays out the GEMM's scales, weight prepared once)
+        for 2-D-stackable bf16/f32 inputs against a (128,128) weight; None where it does not apply."""
+        k = self.kernel
+        kk = x.shape[-1] if x.dim() >= 1 else 0
+        if (k.tgrid != (128, 128) or x.dim() < 2 or kk == 0 or kk % 1024 != 0 or not x.is_cuda
+                or k.get_value().dim() != 2 or k.get_value().shape[1] % 16 != 0
+                or out_dtype not in (torch.float32, torch.bfloat16)):
+            return None
+        if self._steps_kernel is not k:      # the kernel was replaced: its prepared scales are stale
+            self._steps, self._steps_kernel = {}, k
+        rows = x.numel() // kk
+        key = (rows, out_dtype)
+        if key not in self._steps:
+            try:
+                step = _ops.LinearStep(k.transposed_value(), k.sc_fp8, k.sc_fp32, rows, out_dtype)
+                step(torch.zeros((rows, kk), dtype=torch.bfloat16, device=x.device))     # plan check + weight preparation
+                self._steps[key] = step
+            except _lib.PbError as e:
+                if e.status != _lib.PB_ERR_UNSUPPORTED:
+                    raise
+                self._steps[key] = None
+        return self._steps[key]
 
 
 class LowRankFFN:

@@ -198,6 +198,72 @@ def gemm_tn(a: Operand, b: Operand, out_dtype, device, keep_alive=()) -> torch.T
     return d
 
 
+GEMM_A_PREPARED = 1
+GEMM_B_PREPARED = 2
+
+
+class LinearStep:
+    """quantize(x, (1,128)) followed by dq(x) @ dq(W) for one fixed weight and batch size.
+
+    The two calls of Linear.__call__ (_module.py:46-50) with the per-call re-tiling of the scales
+    taken out: the quantizer writes the activation's scales in the GEMM's layout as it goes
+    (pb_quantize_for_gemm), and the weight's are prepared by the first call and reused until
+    `refresh_weight()` says that its scales changed.  Two launches per call instead of four.
+
+    `w_t` is the byte-transposed fp8 weight [n, k]; `w_sc8`/`w_sc32` its scales from quantizing
+    the stored [k, n] matrix on (128,128).  Results are bit-identical to quantize_impl + matmul_impl.
+    """
+
+    def __init__(self, w_t, w_sc8, w_sc32, rows: int, out_dtype=torch.bfloat16, out_format: str = "e4m3"):
+        _require_cuda(w_t, "LinearStep weight")
+        self.n, self.k = int(w_t.shape[0]), int(w_t.shape[1])
+        self.rows, self.out_dtype, self.out_format = int(rows), out_dtype, out_format
+        if self.k % 1024 != 0:
+            raise ValueError(f"LinearStep needs a contraction length that is a multiple of 1024, got {self.k}")
+        self._keep = (w_t, w_sc8.contiguous(), w_sc32.contiguous())
+        self.b = _operand(w_t, self._keep[1], self._keep[2], self.n, self.k, (128, 128), transposed_blocks=1)
+        lib = _lib.load()
+        dev = w_t.device
+        with torch.cuda.device(dev):
+            # the workspace size depends on the shapes and grids only: a placeholder A describes them
+            ph = torch.empty(16, dtype=torch.uint8, device=dev)
+            a = Operand(ph.data_ptr(), ph.data_ptr(), ph.data_ptr(), self.rows, self.k, 1, 128, _FMT_CODE[out_format], 0)
+            self.ws_bytes = lib.pb_gemm_workspace_size(a, self.b)
+            if self.ws_bytes == 0:
+                raise _lib.PbError(2, lib.pb_last_error().decode(errors="replace"))
+            self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=dev)
+        self._b_ready = False
+
+    def refresh_weight(self):
+        """The weight's scales changed (an optimizer step re-quantized it): prepare them again next call."""
+        self._b_ready = False
+
+    def __call__(self, x: torch.Tensor, out=None, triple=None):
+        lib = _lib.load()
+        x = _dense_input(x)
+        if x.numel() != self.rows * self.k or x.shape[-1] != self.k:
+            raise ValueError(f"LinearStep was planned for [{self.rows}, {self.k}], got {tuple(x.shape)}")
+        dev = x.device
+        with torch.cuda.device(dev):
+            if triple is None:
+                q = torch.empty((self.rows, self.k), dtype=_FMT_DTYPE[self.out_format], device=dev)
+                sc8 = torch.empty((self.rows * self.k // 1024, 8), dtype=E8M0, device=dev)
+                sc32 = torch.empty((self.rows * self.k // 1024, 1, 1), dtype=torch.float32, device=dev)
+            else:
+                q, sc8, sc32 = triple
+            d = out if out is not None else torch.empty((self.rows, self.n), dtype=self.out_dtype, device=dev)
+            st = torch.cuda.current_stream(dev).cuda_stream
+            check(lib.pb_quantize_for_gemm(x.data_ptr(), _DENSE_CODE[x.dtype], self.rows, self.k, _FMT_CODE[self.out_format],
+                                           q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(), self.b,
+                                           self.ws.data_ptr(), self.ws_bytes, st))
+            a = _operand(q, sc8, sc32, self.rows, self.k, (1, 128))
+            flags = GEMM_A_PREPARED | (GEMM_B_PREPARED if self._b_ready else 0)
+            check(lib.pb_gemm_tn_ex(a, self.b, d.data_ptr(), _DENSE_CODE[self.out_dtype], self.n,
+                                    self.ws.data_ptr(), self.ws_bytes, flags, st))
+            self._b_ready = True
+        return d, (q, sc8, sc32)
+
+
 def matmul_impl(x_fp8, x_sc8, x_sc32, y_fp8, y_sc8, y_sc32, block_grid_x, block_grid_y,
                 y_fp8_t=None, out_dtype=torch.float32):
     """dq(X) @ dq(Y) with fp32 accumulation, _qarr.py:605-608.

@@ -1160,6 +1160,31 @@ int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
 }
 
 }  // namespace
+
+// Where the A operand's prepared scales live inside the workspace of the GEMM (a x b): used by
+// the row quantizer that writes them directly.  The quantizer covers one super-group of eight
+// k-blocks per warp, so the plan must promote in chunks of eight.
+int gemm_a_prep_location(const pb_operand* a, const pb_operand* b, void* workspace, size_t workspace_bytes,
+                         uint8_t** sf, float** f, uint32_t* tiles, uint32_t* Mpad, void* stream) {
+  GemmPlan gp;
+  if (int s = make_plan(a, b, &gp)) return s;
+  if (gp.P != kMaxChunk)
+    return fail(PB_ERR_UNSUPPORTED, "pb_quantize_for_gemm: this operand pair promotes every %d k-blocks, the fused preparation needs %d", gp.P, kMaxChunk);
+  if (!workspace || workspace_bytes < gp.total)
+    return fail(PB_ERR_WORKSPACE_TOO_SMALL, "pb_quantize_for_gemm: needs %zu bytes of GEMM workspace, got %zu", gp.total, workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(PB_ERR_MISALIGNED, "pb_quantize_for_gemm: workspace must be 256-byte aligned");
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  if (gp.Mpad != a->rows) {      // rows of padding are never written by the quantizer: give them zeros
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    PB_CUDA_TRY(cudaMemsetAsync(ws + gp.off_sfa, 0, (size_t)gp.KG * gp.tiles_m * 512, st));
+    PB_CUDA_TRY(cudaMemsetAsync(ws + gp.off_fa, 0, (size_t)gp.nchunks * gp.Mpad * 4, st));
+  }
+  *sf = ws + gp.off_sfa;
+  *f = reinterpret_cast<float*>(ws + gp.off_fa);
+  *tiles = (uint32_t)gp.tiles_m;
+  *Mpad = (uint32_t)gp.Mpad;
+  return PB_OK;
+}
 }  // namespace pb
 
 using namespace pb;
@@ -1172,8 +1197,17 @@ extern "C" size_t pb_gemm_workspace_size(const pb_operand* a, const pb_operand* 
 
 extern "C" int pb_gemm_tn(const pb_operand* a, const pb_operand* b, void* d, int d_dtype, int64_t ldd,
                           void* workspace, size_t workspace_bytes, void* stream) {
+  return pb_gemm_tn_ex(a, b, d, d_dtype, ldd, workspace, workspace_bytes, 0u, stream);
+}
+
+extern "C" int pb_gemm_tn_ex(const pb_operand* a, const pb_operand* b, void* d, int d_dtype, int64_t ldd,
+                             void* workspace, size_t workspace_bytes, unsigned int flags, void* stream) {
   GemmPlan gp;
   if (int s = make_plan(a, b, &gp)) return s;
+  if (flags & ~(unsigned)(PB_GEMM_A_PREPARED | PB_GEMM_B_PREPARED))
+    return fail(PB_ERR_UNSUPPORTED, "pb_gemm_tn_ex: unknown flag bits 0x%x", flags);
+  if ((flags & PB_GEMM_A_PREPARED) && gp.P != kMaxChunk)
+    return fail(PB_ERR_UNSUPPORTED, "pb_gemm_tn_ex: PB_GEMM_A_PREPARED needs a plan that promotes every %d k-blocks (this one: %d)", kMaxChunk, gp.P);
   if (!d) return fail(PB_ERR_NULL_POINTER, "pb_gemm_tn: d must be non-null");
   if (d_dtype != PB_F32 && d_dtype != PB_BF16) return fail(PB_ERR_BAD_DTYPE, "pb_gemm_tn: d_dtype %d is neither PB_F32 nor PB_BF16", d_dtype);
   if (ldd < b->rows) return fail(PB_ERR_BAD_SHAPE, "pb_gemm_tn: ldd=%lld is smaller than N=%lld", (long long)ldd, (long long)b->rows);
@@ -1183,8 +1217,10 @@ extern "C" int pb_gemm_tn(const pb_operand* a, const pb_operand* b, void* d, int
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
 
-  if (int s = launch_prep(a, gp.pa, gp, gp.Mpad, 128, gp.tiles_m, 1, ws + gp.off_sfa, reinterpret_cast<float*>(ws + gp.off_fa), st)) return s;
-  if (int s = launch_prep(b, gp.pb, gp, gp.Npad, gp.BN, gp.tiles_n, gp.atoms_b, ws + gp.off_sfb, reinterpret_cast<float*>(ws + gp.off_fb), st)) return s;
+  if (!(flags & PB_GEMM_A_PREPARED))
+    if (int s = launch_prep(a, gp.pa, gp, gp.Mpad, 128, gp.tiles_m, 1, ws + gp.off_sfa, reinterpret_cast<float*>(ws + gp.off_fa), st)) return s;
+  if (!(flags & PB_GEMM_B_PREPARED))
+    if (int s = launch_prep(b, gp.pb, gp, gp.Npad, gp.BN, gp.tiles_n, gp.atoms_b, ws + gp.off_sfb, reinterpret_cast<float*>(ws + gp.off_fb), st)) return s;
 
   CUtensorMap ma, mb;
   if (int s = make_operand_map(&ma, a->q, a->rows, a->depth, BM)) return s;

@@ -48,12 +48,33 @@ __device__ __forceinline__ int bitrev(int x) {
   return r;
 }
 
+// Optional second output of the row quantizer: the same scales in the layout the GEMM kernel
+// consumes for its A operand (512-byte scale-factor atoms and one fp32 factor per row and
+// 1024-deep chunk), so that a following pb_gemm_tn_ex need not re-tile them.  Needs whole
+// super-groups per row (cols % 1024 == 0).
+struct GemmPrepOut {
+  uint8_t* sf;      // [kg][row tile of 128][512]; null: not requested
+  float* f;         // [chunk][Mpad]
+  uint32_t KB;      // 128-deep blocks per row
+  uint32_t tiles;   // row tiles of 128 (atoms per kg)
+  uint32_t Mpad;
+};
+__device__ __forceinline__ void write_gemm_prep(const GemmPrepOut& o, int64_t g, int blk, uint32_t sb, float Mj, bool write_byte, bool write_factor) {
+  const uint32_t flat = (uint32_t)g * 8u;               // first block of this super-group
+  const uint32_t row = flat / o.KB, kb0 = flat - row * o.KB;
+  if (write_byte) {
+    const uint32_t kb = kb0 + (uint32_t)blk;
+    o.sf[((size_t)(kb >> 2) * o.tiles + (row >> 7)) * 512 + (row & 31u) * 16 + ((row & 127u) >> 5) * 4 + (kb & 3u)] = (uint8_t)sb;
+  }
+  if (write_factor) o.f[(size_t)(kb0 >> 3) * o.Mpad + row] = Mj * 0.0078125f;
+}
+
 // ---------------------------------------------------------------------------------
 // bf16 input: lane l, load it -> 8 elements at (it*32 + l)*8; block = 2*it + (l >> 4).
-template <int FMT, int MINB>
+template <int FMT, int MINB, bool PREP>
 __global__ void __launch_bounds__(kRowThreads, MINB)
 quantize_row128_bf16_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
-                            uint8_t* __restrict__ sc8, float* __restrict__ sc32, int64_t n_groups) {
+                            uint8_t* __restrict__ sc8, float* __restrict__ sc32, int64_t n_groups, const GemmPrepOut prep) {
   const int lane = threadIdx.x & 31;
   const int64_t warps_total = (int64_t)gridDim.x * (kRowThreads / 32);
   for (int64_t g = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); g < n_groups; g += warps_total) {
@@ -87,6 +108,7 @@ quantize_row128_bf16_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
     const float r = __frcp_rn(D);
     if ((lane & 12) == 0) sc8[g * 8 + 2 * it_own + (lane >> 4)] = (uint8_t)sb;
     if (lane == 0) sc32[g] = Mj;
+    if (PREP) write_gemm_prep(prep, g, 2 * it_own + (lane >> 4), sb, Mj, (lane & 12) == 0, lane == 0);
 
     uint2* dst = q + g * (kGroupElems / 8);
 #pragma unroll
@@ -110,10 +132,10 @@ quantize_row128_bf16_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
 }
 
 // f32 input: lane l, load it -> 4 elements at (it*32 + l)*4; block = it.
-template <int FMT>
+template <int FMT, bool PREP>
 __global__ void __launch_bounds__(kRowThreads)
 quantize_row128_f32_kernel(const float4* __restrict__ x, uint32_t* __restrict__ q,
-                           uint8_t* __restrict__ sc8, float* __restrict__ sc32, int64_t n_groups) {
+                           uint8_t* __restrict__ sc8, float* __restrict__ sc32, int64_t n_groups, const GemmPrepOut prep) {
   const int lane = threadIdx.x & 31;
   const int64_t warps_total = (int64_t)gridDim.x * (kRowThreads / 32);
   for (int64_t g = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); g < n_groups; g += warps_total) {
@@ -137,6 +159,7 @@ quantize_row128_f32_kernel(const float4* __restrict__ x, uint32_t* __restrict__ 
     const float r = __frcp_rn(D);
     if (lane < 8) sc8[g * 8 + it_own] = (uint8_t)sb;
     if (lane == 0) sc32[g] = Mj;
+    if (PREP) write_gemm_prep(prep, g, it_own, sb, Mj, lane < 8, lane == 0);
 
     uint32_t* dst = q + g * (kGroupElems / 4);
 #pragma unroll
@@ -314,9 +337,15 @@ extern "C" size_t pb_quantize_workspace_size(int64_t batch, int64_t rows, int64_
   return (size_t)(batch * g.Nb) * 8;
 }
 
-extern "C" int pb_quantize(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols,
-                           int a, int b, int out_format, void* q, uint8_t* sc8, float* sc32,
-                           void* workspace, size_t workspace_bytes, void* stream) {
+namespace pb {
+// defined in gemm_sm100.cu: where the A operand's prepared scales live inside a GEMM workspace
+int gemm_a_prep_location(const pb_operand* a, const pb_operand* b, void* workspace, size_t workspace_bytes,
+                         uint8_t** sf, float** f, uint32_t* tiles, uint32_t* Mpad, void* stream);
+}
+
+static int quantize_entry(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols,
+                          int a, int b, int out_format, void* q, uint8_t* sc8, float* sc32,
+                          void* workspace, size_t workspace_bytes, void* stream, const GemmPrepOut& prep) {
   if (!x || !q || !sc8 || !sc32) return fail(PB_ERR_NULL_POINTER, "pb_quantize: x, q, sc8 and sc32 must be non-null");
   if (batch <= 0) return fail(PB_ERR_BAD_SHAPE, "pb_quantize: batch=%lld must be positive", (long long)batch);
   if (x_dtype != PB_F32 && x_dtype != PB_BF16) return fail(PB_ERR_BAD_DTYPE, "pb_quantize: x_dtype %d is neither PB_F32 nor PB_BF16", x_dtype);
@@ -330,19 +359,28 @@ extern "C" int pb_quantize(const void* x, int x_dtype, int64_t batch, int64_t ro
       return fail(PB_ERR_MISALIGNED, "pb_quantize: x must be 16-byte and q 8-byte aligned");
     const int64_t n_groups = batch * g.M;
     const int grid = grid_for(n_groups * 32, kRowThreads, 8);
+    // 40 registers per thread (6 CTAs of 256 threads per SM) measures the same as the compiler's
+    // unconstrained 49; an unconstrained single CTA per SM (96 registers) is 15 % slower.
+    const bool e4 = out_format == PB_E4M3;
+#define PB_ROW128_LAUNCH(KERNEL, XT, QT) KERNEL<<<grid, kRowThreads, 0, st>>>((const XT*)x, (QT*)q, sc8, sc32, n_groups, prep)
     if (x_dtype == PB_BF16) {
-      // 40 registers per thread (6 CTAs of 256 threads per SM) measures the same as the compiler's
-      // unconstrained 49; an unconstrained single CTA per SM (96 registers) is 15 % slower.
-      if (out_format == PB_E4M3)
-        quantize_row128_bf16_kernel<PB_E4M3, 6><<<grid, kRowThreads, 0, st>>>((const uint4*)x, (uint2*)q, sc8, sc32, n_groups);
-      else
-        quantize_row128_bf16_kernel<PB_E5M2, 6><<<grid, kRowThreads, 0, st>>>((const uint4*)x, (uint2*)q, sc8, sc32, n_groups);
+      if (prep.sf) {
+        if (e4) PB_ROW128_LAUNCH((quantize_row128_bf16_kernel<PB_E4M3, 6, true>), uint4, uint2);
+        else    PB_ROW128_LAUNCH((quantize_row128_bf16_kernel<PB_E5M2, 6, true>), uint4, uint2);
+      } else {
+        if (e4) PB_ROW128_LAUNCH((quantize_row128_bf16_kernel<PB_E4M3, 6, false>), uint4, uint2);
+        else    PB_ROW128_LAUNCH((quantize_row128_bf16_kernel<PB_E5M2, 6, false>), uint4, uint2);
+      }
     } else {
-      if (out_format == PB_E4M3)
-        quantize_row128_f32_kernel<PB_E4M3><<<grid, kRowThreads, 0, st>>>((const float4*)x, (uint32_t*)q, sc8, sc32, n_groups);
-      else
-        quantize_row128_f32_kernel<PB_E5M2><<<grid, kRowThreads, 0, st>>>((const float4*)x, (uint32_t*)q, sc8, sc32, n_groups);
+      if (prep.sf) {
+        if (e4) PB_ROW128_LAUNCH((quantize_row128_f32_kernel<PB_E4M3, true>), float4, uint32_t);
+        else    PB_ROW128_LAUNCH((quantize_row128_f32_kernel<PB_E5M2, true>), float4, uint32_t);
+      } else {
+        if (e4) PB_ROW128_LAUNCH((quantize_row128_f32_kernel<PB_E4M3, false>), float4, uint32_t);
+        else    PB_ROW128_LAUNCH((quantize_row128_f32_kernel<PB_E5M2, false>), float4, uint32_t);
+      }
     }
+#undef PB_ROW128_LAUNCH
     PB_LAUNCH_CHECK("quantize_row128_kernel");
     return PB_OK;
   }
@@ -358,6 +396,28 @@ extern "C" int pb_quantize(const void* x, int x_dtype, int64_t batch, int64_t ro
   }
   return vec4 ? launch_generic<float, 4>((const float*)x, g, batch, out_format, (uint8_t*)q, sc8, sc32, workspace, st)
               : launch_generic<float, 1>((const float*)x, g, batch, out_format, (uint8_t*)q, sc8, sc32, workspace, st);
+}
+
+extern "C" int pb_quantize(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols,
+                           int a, int b, int out_format, void* q, uint8_t* sc8, float* sc32,
+                           void* workspace, size_t workspace_bytes, void* stream) {
+  return quantize_entry(x, x_dtype, batch, rows, cols, a, b, out_format, q, sc8, sc32, workspace, workspace_bytes, stream,
+                        GemmPrepOut{nullptr, nullptr, 1, 1, 0});
+}
+
+extern "C" int pb_quantize_for_gemm(const void* x, int x_dtype, int64_t rows, int64_t cols, int out_format,
+                                    void* q, uint8_t* sc8, float* sc32,
+                                    const pb_operand* b, void* gemm_workspace, size_t gemm_workspace_bytes, void* stream) {
+  if (cols <= 0 || cols % 1024 != 0)
+    return fail(PB_ERR_BAD_SHAPE, "pb_quantize_for_gemm: cols=%lld must be a positive multiple of 1024", (long long)cols);
+  GemmPrepOut prep{nullptr, nullptr, (uint32_t)(cols / 128), 0, 0};
+  if (!x || !q || !sc8 || !sc32) return fail(PB_ERR_NULL_POINTER, "pb_quantize_for_gemm: x, q, sc8 and sc32 must be non-null");
+  if (rows <= 0 || rows * (cols / 128) > kMaxIndexed) return fail(PB_ERR_UNSUPPORTED, "pb_quantize_for_gemm: rows=%lld is out of range", (long long)rows);
+  pb_operand a_op;
+  a_op.q = q; a_op.sc8 = sc8; a_op.sc32 = sc32; a_op.rows = rows; a_op.depth = cols;
+  a_op.grid_a = 1; a_op.grid_b = 128; a_op.format = out_format; a_op.transposed_blocks = 0;
+  if (int s = pb::gemm_a_prep_location(&a_op, b, gemm_workspace, gemm_workspace_bytes, &prep.sf, &prep.f, &prep.tiles, &prep.Mpad, stream)) return s;
+  return quantize_entry(x, x_dtype, 1, rows, cols, 1, 128, out_format, q, sc8, sc32, nullptr, 0, stream, prep);
 }
 
 // ---------------------------------------------------------------------------------------------

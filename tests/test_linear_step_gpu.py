@@ -1,0 +1,105 @@
+"""GPU parity of the two-launch linear step (pb_quantize_for_gemm + pb_gemm_tn_ex) with the
+four-launch path it shortens (pb_quantize + pb_gemm_tn) and with the oracle.
+
+Bit-exact: the quantized triple against the oracle's quantize_impl and against pb_quantize, and
+the product against pb_gemm_tn on the same triple (same kernel, same scales, so the same bits).
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import BF16, assert_triple_equal, bytes_of, from_torch, oracle, synth, to_torch
+from pratchya_b200 import _lib
+from pratchya_b200._nnx_impl import Linear
+from pratchya_b200._qualia import LinearStep, matmul_impl, quantize_impl
+from pratchya_b200._qualia import _ops
+
+pytestmark = pytest.mark.gpu
+
+
+def weight(k, n, seed):
+    w = synth((k, n), seed=seed, scale=0.02, outliers=0)
+    wq = quantize_impl(to_torch(w), (128, 128))
+    return wq, _ops.transpose_bytes(wq[0])
+
+
+def np_triple(t):
+    q, s8, s32 = t
+    return (bytes_of(q), bytes_of(s8), from_torch(s32))
+
+
+@pytest.mark.parametrize("m,n,k,dtype", [(256, 1024, 1024, np.float32), (128, 2048, 2048, BF16), (200, 1024, 2048, BF16),
+                                         (1000, 2048, 1024, np.float32), (2048, 8192, 2048, BF16)])
+def test_step_equals_separate_calls_and_oracle(built_lib, m, n, k, dtype):
+    x = synth((m, k), seed=m + k, outliers=0.01).astype(dtype)
+    wq, w_t = weight(k, n, seed=n)
+    step = LinearStep(w_t, wq[1], wq[2], rows=m, out_dtype=torch.float32)
+    xt = to_torch(x)
+    for call in range(3):          # first call prepares the weight's scales, later ones reuse them
+        d, triple = step(xt)
+        _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+        want = quantize_impl(xt, (1, 128))
+        assert_triple_equal(np_triple(triple), np_triple(want), f"call {call}: fused quantizer vs pb_quantize")
+        ref = matmul_impl(*want, *wq, (1, 128), (128, 128), y_fp8_t=w_t)
+        assert torch.equal(d, ref), f"call {call}: two-launch product differs from pb_gemm_tn"
+    oq = oracle.quantize_impl(np.asarray(x), (1, 128))
+    assert_triple_equal(np_triple(triple), (oq[0].view(np.uint8), oq[1].view(np.uint8), oq[2]), "fused quantizer vs oracle")
+
+
+def test_step_sees_new_activations_and_refreshed_weight(built_lib):
+    m, n, k = 384, 1024, 1024
+    wq, w_t = weight(k, n, seed=5)
+    step = LinearStep(w_t, wq[1], wq[2], rows=m, out_dtype=torch.bfloat16)
+    for seed in (1, 2):
+        xt = to_torch(synth((m, k), seed=seed, scale=10.0 ** seed).astype(BF16))
+        d, _ = step(xt)
+        ref = matmul_impl(*quantize_impl(xt, (1, 128)), *wq, (1, 128), (128, 128), y_fp8_t=w_t, out_dtype=torch.bfloat16)
+        assert torch.equal(d, ref)
+    # new weight scales in the same buffers: stale until refresh_weight()
+    wq2, w_t2 = weight(k, n, seed=6)
+    w_t.copy_(w_t2); wq[1].copy_(wq2[1]); wq[2].copy_(wq2[2] * 4)
+    step.refresh_weight()
+    d, _ = step(xt)
+    ref = matmul_impl(*quantize_impl(xt, (1, 128)), wq2[0], wq2[1], wq2[2] * 4, (1, 128), (128, 128), y_fp8_t=w_t2,
+                      out_dtype=torch.bfloat16)
+    assert torch.equal(d, ref)
+
+
+def test_linear_matmul_uses_the_step_and_matches(built_lib):
+    k, n = 1024, 512
+    lin = Linear(k, n, (128, 128), generator=torch.Generator(device="cuda").manual_seed(3))
+    x = to_torch(synth((2, 96, k), seed=9))
+    y = lin.matmul(x)
+    assert lin._steps and all(v is not None for v in lin._steps.values())
+    kq = lin.kernel
+    ref = matmul_impl(*quantize_impl(x, (1, 128)), kq.get_value(), kq.sc_fp8, kq.sc_fp32, (1, 128), (128, 128))
+    assert y.shape == (2, 96, n)
+    assert torch.equal(y, ref)
+
+
+def test_rejections(built_lib):
+    wq, w_t = weight(1024, 256, seed=1)
+    with pytest.raises(ValueError):
+        LinearStep(w_t[:, :512].contiguous(), wq[1], wq[2], rows=128)          # depth 512: not whole super-groups
+    step = LinearStep(w_t, wq[1], wq[2], rows=128)
+    with pytest.raises(ValueError):
+        step(torch.zeros((64, 1024), device="cuda"))
+    # unknown flag bits
+    xq = quantize_impl(torch.zeros((128, 1024), device="cuda"), (1, 128))
+    a = _ops._operand(*xq, 128, 1024, (1, 128))
+    d = torch.empty((128, 256), device="cuda")
+    st = built_lib.pb_gemm_tn_ex(a, step.b, d.data_ptr(), 0, 256, step.ws.data_ptr(), step.ws_bytes, 8, None)
+    assert st == _lib.PB_ERR_UNSUPPORTED
+    # a weight whose super-groups do not span eight k-blocks of every row: the fused preparation refuses
+    wq3, w_t3 = weight(1024, 384, seed=2)         # 8 x 3 blocks in super-groups of 8: no run of k-blocks shares a factor
+    step3 = LinearStep(w_t3, wq3[1], wq3[2], rows=128)
+    with pytest.raises(_lib.PbError) as e:
+        step3(torch.zeros((128, 1024), device="cuda"))
+    assert e.value.status == _lib.PB_ERR_UNSUPPORTED
+    # Linear falls back to the four-launch path for such a weight
+    lin = Linear(1024, 384, (128, 128), generator=torch.Generator(device="cuda").manual_seed(4))
+    x = to_torch(synth((128, 1024), seed=3))
+    y = lin.matmul(x)
+    assert list(lin._steps.values()) == [None]
+    kq = lin.kernel
+    assert torch.equal(y, matmul_impl(*quantize_impl(x, (1, 128)), kq.get_value(), kq.sc_fp8, kq.sc_fp32, (1, 128), (128, 128)))
