@@ -251,6 +251,7 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int a_fmt, b_fmt;
   int d_dtype;
+  int band;         // pair kernel: tile rows per band; a band's tiles are visited column by column before the next band
   int fb_uniform;   // B's fp32 factor is the same for all rows of B within a chunk
   int tma_store;    // D is written through shared memory and TMA stores (needs 16-byte aligned rows)
   int profile;
@@ -603,6 +604,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 struct Cfg2 {
   static constexpr int BN = 224;
   static constexpr int kStages = 6;
+  static constexpr int kSlots = kStages / 2;         // the pipeline moves in pairs of stages
   static constexpr int kAccBufs = 2;
   static constexpr int kEpiWarps = 8;
   static constexpr int kThreads = 128 + 32 * kEpiWarps;
@@ -674,6 +676,18 @@ __device__ __forceinline__ uint32_t instr_desc_pair(int bn, int a_fmt, int b_fmt
          ((uint32_t)(256 >> 4) << 24) | (sf_id << 29);
 }
 
+// Tile order of the pair kernel.  Tiles are numbered band by band: a band is `p.band` tile rows,
+// walked down its tile rows first and then across the tile columns, so that the band's rows of A
+// and all of B stay in L2 while the band is worked through (with one band spanning all of M, a
+// 32768-row A is evicted between two columns and read from DRAM once per tile column).
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
+  const int per_band = p.band * p.tiles_n;
+  const int b = tile / per_band, within = tile - b * per_band;
+  const int rows = min(p.band, p.tiles_m - b * p.band);
+  tn = within / rows;
+  tm = b * p.band + (within - tn * rows);
+}
+
 template <bool PROF>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg2::kThreads, 1)
 gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -719,39 +733,67 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 0 && lane == 0) {
       // ------------------------------------------------------------- TMA producer (both CTAs)
+      // The pipeline moves in steps of two k-blocks (one inside a chunk's odd tail): slot q is the
+      // stage pair (2q, 2q+1) with one full and one empty barrier.  Half as many waits and commits
+      // in the MMA thread, the same bytes in flight.
       uint32_t it = 0, sf_fills = 0;
       bool ok = true;
+      long long prod_wait = 0;
+      const long long prod_begin = PROF ? clock64() : 0;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        int tm, tn;
+        tile_coords(p, tile, tm, tn);
         const int m0 = tm * 256 + (int)rank * 128;          // this CTA's rows of A and D
-        const int n0 = tn * BN;
-        for (int kb = 0; kb < p.KB; ++kb, ++it) {
-          const int s = it % C::kStages;
-          if (!mbar_wait(bar_empty(s), ((it / C::kStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-          const bool with_sf = (kb & 3) == 0;
-          const uint32_t full = map_to_cta(bar_full(s), 0);
-          if (leader) mbar_arrive_expect_tx(bar_full(s), 2 * (C::kABytes + C::kBBytes + (with_sf ? C::kSfSlot : 0)));
-          tma_load_2d_pair(s_a + s * C::kABytes, &map_a, kb * BK, m0, full);
-          tma_load_2d_pair(s_b + s * C::kBBytes, &map_b, kb * BK, n0 + (int)rank * (BN / 2), full);
-          if (with_sf) {
-            const int kg = kb >> 2;
-            const uint32_t slot = s_sf + (sf_fills & 1u) * C::kSfSlot;      // see the single-CTA producer for the reuse argument
-            ++sf_fills;
-            tma_load_2d_pair(slot, &map_sfa, 0, kg * (2 * p.tiles_m) + 2 * tm + (int)rank, full);
-            tma_load_2d_pair(slot + C::kSfaBytes, &map_sfb, 0, (kg * p.tiles_n + tn) * 2, full);
+        const int nb0 = tn * BN + (int)rank * (BN / 2);     // this CTA's half of the tile's B rows
+        for (int c = 0; c < p.nchunks && ok; ++c) {
+          const int kb_end = min(p.KB, (c + 1) * p.P);
+          for (int kb = c * p.P; kb < kb_end; kb += 2, ++it) {
+            const int q = it % C::kSlots;
+            const long long tw = PROF ? clock64() : 0;
+            if (!mbar_wait(bar_empty(q), ((it / C::kSlots) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+            if (PROF) prod_wait += clock64() - tw;
+            const bool two = kb + 1 < kb_end;
+            const bool with_sf = (kb & 3) == 0;             // a step of two starts at an even k-block: only its first can open a group of four
+            const uint32_t full = map_to_cta(bar_full(q), 0);
+            if (leader) mbar_arrive_expect_tx(bar_full(q), 2 * ((two ? 2 : 1) * (C::kABytes + C::kBBytes) + (with_sf ? C::kSfSlot : 0)));
+            const int s = 2 * q;
+            tma_load_2d_pair(s_a + s * C::kABytes, &map_a, kb * BK, m0, full);
+            tma_load_2d_pair(s_b + s * C::kBBytes, &map_b, kb * BK, nb0, full);
+            if (with_sf) {
+              // Two slots alternate.  A slot is rewritten 8 k-blocks after the copy that read it was
+              // issued; this fill waited for the commit of the step kSlots before this one, which
+              // came after that copy in the MMA thread and completes only after every earlier
+              // tcgen05 operation of that thread.
+              const int kg = kb >> 2;
+              const uint32_t slot = s_sf + (sf_fills & 1u) * C::kSfSlot;
+              ++sf_fills;
+              tma_load_2d_pair(slot, &map_sfa, 0, kg * (2 * p.tiles_m) + 2 * tm + (int)rank, full);
+              tma_load_2d_pair(slot + C::kSfaBytes, &map_sfb, 0, (kg * p.tiles_n + tn) * 2, full);
+            }
+            if (two) {
+              tma_load_2d_pair(s_a + (s + 1) * C::kABytes, &map_a, (kb + 1) * BK, m0, full);
+              tma_load_2d_pair(s_b + (s + 1) * C::kBBytes, &map_b, (kb + 1) * BK, nb0, full);
+            }
           }
         }
       }
+      if (PROF && leader) {      // slots 0 and 3: the producer's time waiting for a free slot, and the rest of its time
+        atomicAdd(&g_gemm_prof[0], (unsigned long long)prod_wait);
+        atomicAdd(&g_gemm_prof[3], (unsigned long long)(clock64() - prod_begin - prod_wait));
+      }
     } else if (warp == 1 && lane == 0 && leader) {
       // ------------------------------------------------------------- MMA issuer (leader CTA only)
+      // Issuing is what bounds this kernel: an MMA takes the thread ~72 cycles to issue and the
+      // tensor core 112 to run, but a barrier wait costs ~130, a commit ~65 and the three
+      // scale-factor copies ~350, during which a short MMA queue runs dry.  Eight MMAs per wait and
+      // commit keep enough work queued to cover them.
       const int KB = p.KB, P = p.P, nchunks = p.nchunks;
       const uint32_t idesc0 = instr_desc_pair(BN, p.a_fmt, p.b_fmt, 0u);
       const uint32_t a_lo0 = operand_desc_lo(s_a), b_lo0 = operand_desc_lo(s_b);
       const uint32_t sf_tmem0 = tmem_base + C::kSfColBase;
       const uint32_t sf_lo0 = sf_desc_lo(s_sf);
-      const uint32_t empty_peer0 = map_to_cta(bar_empty(0), 1);
-      uint32_t s = 0, phase = 0, sf_reads = 0, g = 0;
-      uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full(0), empty = bar_empty(0), empty_peer = empty_peer0;
+      uint32_t q = 0, phase = 0, sf_reads = 0, g = 0;
+      uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full(0), empty = bar_empty(0);
       long long wait_full = 0, wait_acc = 0;
       const long long t_begin = PROF ? clock64() : 0;
       bool ok = true;
@@ -765,7 +807,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const uint32_t d_tmem = tmem_base + buf * BN;
           const int kb_end = min(KB, (c + 1) * P);
           uint32_t accumulate = 0;
-          for (int kb = c * P; kb < kb_end; ++kb) {
+          for (int kb = c * P; kb < kb_end; kb += 2) {
             if (PROF) t0 = clock64();
             if (!mbar_wait(full, phase, abort_flag)) { ok = false; break; }
             if (PROF) wait_full += clock64() - t0;
@@ -783,11 +825,18 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               tc2_mma_block_scaled_lo(d_tmem, a_lo + (k * UMMA_K >> 4), b_lo + (k * UMMA_K >> 4), idesc, sf_col, sf_col + 4, accumulate);
               accumulate = 1;
             }
-            tc2_commit_both(empty);     // free the stage in both CTAs once these MMAs have read it
-            ++s; a_lo += C::kABytes >> 4; b_lo += C::kBBytes >> 4; full += 8; empty += 8; empty_peer += 8;
-            if (s == C::kStages) {
-              s = 0; phase ^= 1u;
-              a_lo = a_lo0; b_lo = b_lo0; full = bar_full(0); empty = bar_empty(0); empty_peer = empty_peer0;
+            if (kb + 1 < kb_end) {
+              const uint32_t idesc1 = idesc + ((1u << 4) | (1u << 29));
+              const uint32_t a1 = a_lo + (C::kABytes >> 4), b1 = b_lo + (C::kBBytes >> 4);
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k)
+                tc2_mma_block_scaled_lo(d_tmem, a1 + (k * UMMA_K >> 4), b1 + (k * UMMA_K >> 4), idesc1, sf_col, sf_col + 4, 1u);
+            }
+            tc2_commit_both(empty);     // free the stage pair in both CTAs once these MMAs have read it
+            ++q; a_lo += 2 * (C::kABytes >> 4); b_lo += 2 * (C::kBBytes >> 4); full += 8; empty += 8;
+            if (q == C::kSlots) {
+              q = 0; phase ^= 1u;
+              a_lo = a_lo0; b_lo = b_lo0; full = bar_full(0); empty = bar_empty(0);
             }
           }
           if (ok) {
@@ -814,7 +863,9 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t g = 0, stores = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-      const int m0 = (tile % p.tiles_m) * 256 + (int)rank * 128, n0 = (tile / p.tiles_m) * BN + col_half * 128;
+      int tm, tn;
+      tile_coords(p, tile, tm, tn);
+      const int m0 = tm * 256 + (int)rank * 128, n0 = tn * BN + col_half * 128;
       float acc[128];
       for (int c = 0; c < p.nchunks; ++c, ++g) {
         const int buf = g % C::kAccBufs;
@@ -1235,6 +1286,15 @@ extern "C" int pb_gemm_tn_ex(const pb_operand* a, const pb_operand* b, void* d, 
   p.tiles_m = gp.pair ? gp.Mpad / 256 : gp.tiles_m; p.tiles_n = gp.tiles_n;
   p.a_fmt = a->format; p.b_fmt = b->format; p.d_dtype = d_dtype;
   p.fb_uniform = gp.pb.row_uniform ? 1 : 0;
+  {
+    // band height: about 16 MB of A rows (they and B, at most a few tens of MB, then share the 126 MB L2 with the stream of D)
+    static const int forced = [] { const char* e = getenv("PB_GEMM_BAND"); return e ? atoi(e) : 0; }();
+    int band = (int)((16ll << 20) / (256 * a->depth));
+    if (forced > 0) band = forced;
+    if (band < 4) band = 4;
+    if (band > p.tiles_m) band = p.tiles_m;
+    p.band = band;
+  }
   p.tma_store = 0;
   p.profile = profile_level();
   // D goes out through TMA stores when its rows are 16-byte aligned; otherwise by direct stores
