@@ -68,7 +68,7 @@ __device__ unsigned int g_gemm_status;   // 0, or PB_ERR_DEVICE_TIMEOUT once any
 // 0 producer waits for a free stage, 1 MMA waits for a full stage, 2 MMA waits for a drained
 // accumulator, 3 epilogue (first warp) waits for an accumulated chunk, 4 epilogue busy,
 // 5 CTA lifetime, 6 MMA issue (non-wait), 7 CTAs counted
-__device__ unsigned long long g_gemm_prof[8];
+__device__ unsigned long long g_gemm_prof[16];
 
 // ---- PTX wrappers ------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -251,6 +251,7 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int a_fmt, b_fmt;
   int d_dtype;
+  int diag;         // timing experiments in the profiling build of the pair kernel: 1 skips the loads of B, 2 those of A, 4 those of the scale factors
   int band;         // pair kernel: tile rows per band; a band's tiles are visited column by column before the next band
   int fb_uniform;   // B's fp32 factor is the same for all rows of B within a chunk
   int tma_store;    // D is written through shared memory and TMA stores (needs 16-byte aligned rows)
@@ -728,6 +729,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   const int num_tiles = p.tiles_m * p.tiles_n;          // 256 x 224 tiles
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  long long life_c0 = 0; unsigned long long life_n0 = 0;
+  if (PROF && threadIdx.x == 96) { life_c0 = clock64(); asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(life_n0)); }
 
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
@@ -755,11 +758,12 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const bool two = kb + 1 < kb_end;
             const bool with_sf = (kb & 3) == 0;             // a step of two starts at an even k-block: only its first can open a group of four
             const uint32_t full = map_to_cta(bar_full(q), 0);
-            if (leader) mbar_arrive_expect_tx(bar_full(q), 2 * ((two ? 2 : 1) * (C::kABytes + C::kBBytes) + (with_sf ? C::kSfSlot : 0)));
+            const bool ld_a = !(PROF && (p.diag & 2)), ld_b = !(PROF && (p.diag & 1)), ld_sf = !(PROF && (p.diag & 4));
+            if (leader) mbar_arrive_expect_tx(bar_full(q), 2 * ((two ? 2 : 1) * ((ld_a ? C::kABytes : 0) + (ld_b ? C::kBBytes : 0)) + (with_sf && ld_sf ? C::kSfSlot : 0)));
             const int s = 2 * q;
-            tma_load_2d_pair(s_a + s * C::kABytes, &map_a, kb * BK, m0, full);
-            tma_load_2d_pair(s_b + s * C::kBBytes, &map_b, kb * BK, nb0, full);
-            if (with_sf) {
+            if (ld_a) tma_load_2d_pair(s_a + s * C::kABytes, &map_a, kb * BK, m0, full);
+            if (ld_b) tma_load_2d_pair(s_b + s * C::kBBytes, &map_b, kb * BK, nb0, full);
+            if (with_sf && ld_sf) {
               // Two slots alternate.  A slot is rewritten 8 k-blocks after the copy that read it was
               // issued; this fill waited for the commit of the step kSlots before this one, which
               // came after that copy in the MMA thread and completes only after every earlier
@@ -771,8 +775,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               tma_load_2d_pair(slot + C::kSfaBytes, &map_sfb, 0, (kg * p.tiles_n + tn) * 2, full);
             }
             if (two) {
-              tma_load_2d_pair(s_a + (s + 1) * C::kABytes, &map_a, (kb + 1) * BK, m0, full);
-              tma_load_2d_pair(s_b + (s + 1) * C::kBBytes, &map_b, (kb + 1) * BK, nb0, full);
+              if (ld_a) tma_load_2d_pair(s_a + (s + 1) * C::kABytes, &map_a, (kb + 1) * BK, m0, full);
+              if (ld_b) tma_load_2d_pair(s_b + (s + 1) * C::kBBytes, &map_b, (kb + 1) * BK, nb0, full);
             }
           }
         }
@@ -933,6 +937,12 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   // its shared memory or write its TMEM.
   tc_fence_before();
   __syncthreads();
+  if (PROF && threadIdx.x == 96 && leader) {       // slots 13-15: this CTA's life in SM cycles and in nanoseconds
+    unsigned long long n1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(n1));
+    atomicAdd(&g_gemm_prof[13], (unsigned long long)(clock64() - life_c0));
+    atomicAdd(&g_gemm_prof[14], n1 - life_n0);
+    atomicAdd(&g_gemm_prof[15], 1ull);
+  }
   cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
@@ -1297,6 +1307,7 @@ extern "C" int pb_gemm_tn_ex(const pb_operand* a, const pb_operand* b, void* d, 
   }
   p.tma_store = 0;
   p.profile = profile_level();
+  p.diag = [] { const char* e = getenv("PB_GEMM_DIAG"); return e ? atoi(e) : 0; }();
   // D goes out through TMA stores when its rows are 16-byte aligned; otherwise by direct stores
   CUtensorMap md = ma;
   const int es = d_dtype == PB_BF16 ? 2 : 4;
@@ -1331,10 +1342,11 @@ extern "C" int pb_gemm_check(void* stream) {
 
 // Not part of the reference's surface: diagnostics.  Copies (and clears) the eight cycle
 // counters the GEMM kernel accumulates when the environment sets PB_GEMM_PROFILE=1.
-extern "C" PB_API int pb_debug_gemm_profile(unsigned long long* out8, void* stream) {
-  if (!out8) return fail(PB_ERR_NULL_POINTER, "pb_debug_gemm_profile: out8 must be non-null");
+extern "C" PB_API int pb_debug_gemm_profile(unsigned long long* out16, void* stream) {
+  unsigned long long* out8 = out16;
+  if (!out8) return fail(PB_ERR_NULL_POINTER, "pb_debug_gemm_profile: out16 must be non-null");
   PB_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
-  unsigned long long zero[8] = {0};
+  unsigned long long zero[16] = {0};
   PB_CUDA_TRY(cudaMemcpyFromSymbol(out8, g_gemm_prof, sizeof(zero)));
   PB_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_prof, zero, sizeof(zero)));
   return PB_OK;
