@@ -162,6 +162,13 @@ PB_API int pb_gemm_tn_ex(const pb_operand* a, const pb_operand* b,
 PB_API int pb_quantize_for_gemm(const void* x, int x_dtype, int64_t rows, int64_t cols, int out_format,
                          void* q, uint8_t* sc8, float* sc32,
                          const pb_operand* b, void* gemm_workspace, size_t gemm_workspace_bytes, void* stream);
+/* out = dequantize(quantize(x)) in one pass: what Linear.__call__ does to its f32 product,
+ * `(x_q @ kernel).astype(x.dtype)` (pratchya/_nnx_impl/_module.py:46-50; the product is wrapped as
+ * QArrayImpl(out, (1, b)), pratchya/_qualia/_qarr.py:104-105, and read back by astype, :339-342).
+ * Same bits as pb_quantize followed by pb_dequantize.  f32 input on the (1,128) grid with whole
+ * super-groups of eight blocks only; anything else returns PB_ERR_UNSUPPORTED (use the two calls). */
+PB_API int pb_fake_quantize(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols, int a, int b,
+                     int out_format, void* out, int out_dtype, void* stream);
 /* Reads (and clears) the device status word of the last GEMMs launched on this
  * device; synchronises `stream`.  PB_OK or PB_ERR_DEVICE_TIMEOUT. */
 PB_API int pb_gemm_check(void* stream);

@@ -36,7 +36,12 @@ class Linear:
         self._steps_kernel = self.kernel
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
-        a, _ = self.kernel.tgrid
+        a, b = self.kernel.tgrid
+        if isinstance(x, torch.Tensor) and x.dim() >= 2 and x.is_cuda and self.kernel.get_value().dim() == 2:
+            # the same three reference steps with fewer passes: quantize x and multiply (two launches
+            # where the fused step applies), then quantize-and-dequantize the f32 product in one
+            y = self.matmul(x, out_dtype=torch.float32)
+            return _ops.fake_quantize_impl(y, (1, b), x.dtype)
         x_q = QArrayImpl(x, (1, a))
         return (x_q @ self.kernel).astype(x.dtype)
 

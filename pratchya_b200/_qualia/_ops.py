@@ -137,6 +137,27 @@ def dequantize_impl(x_fp8: torch.Tensor, sc_fp8: torch.Tensor, sc_fp32: torch.Te
     return out if kernel_dtype == dtype else out.to(dtype)
 
 
+def fake_quantize_impl(x: torch.Tensor, tgrid, dtype, out_format: str = "e4m3") -> torch.Tensor:
+    """dequantize_impl(*quantize_impl(x, tgrid), dtype, tgrid) -- QArrayImpl(x, tgrid).astype(dtype),
+    _qarr.py:29 and :339-342 -- in one pass where the library has a fused kernel (f32 input on the
+    (1,128) grid with whole 8-block super-groups), otherwise by the two calls.  Same bits either way."""
+    _require_cuda(x, "fake_quantize_impl input")
+    lib = _lib.load()
+    shape = _as_2d(tuple(x.shape))
+    a, b = int(tgrid[0]), int(tgrid[1])
+    rows, cols = shape[-2], shape[-1]
+    fused = (x.dtype == torch.float32 and dtype in _DENSE_CODE and (a, b) == (1, 128) and x.numel() > 0
+             and group_geometry(rows, cols, (a, b))[1] == 8)
+    if not fused:
+        return dequantize_impl(*quantize_impl(x, tgrid, out_format), dtype, tgrid)
+    x = x.contiguous()
+    with torch.cuda.device(x.device):
+        out = torch.empty(tuple(x.shape), dtype=dtype, device=x.device)
+        check(lib.pb_fake_quantize(x.data_ptr(), _DENSE_CODE[x.dtype], math.prod(shape[:-2]), rows, cols, a, b,
+                                   _FMT_CODE[out_format], out.data_ptr(), _DENSE_CODE[dtype], _stream(x)))
+    return out
+
+
 def dequantize_impl_bwd(sc_fp8: torch.Tensor, sc_fp32: torch.Tensor, g_out: torch.Tensor, tgrid):
     """Cotangent of the fp8 value: g * x_sc / 128 in g's dtype, _qarr.py:575-601."""
     _require_cuda(g_out, "dequantize_impl_bwd input")

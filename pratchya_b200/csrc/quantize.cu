@@ -174,6 +174,65 @@ quantize_row128_f32_kernel(const float4* __restrict__ x, uint32_t* __restrict__ 
   }
 }
 
+// Quantize and dequantize in one pass (f32 input, grid (1,128), 8-block super-groups): what
+// `(x_q @ kernel).astype(dtype)` does to the f32 product in Linear.__call__
+// (pratchya/_nnx_impl/_module.py:46-50 through QArrayImpl.__matmul__, _qarr.py:104-105, and
+// astype/dequantize, :339-342, :46-59): out = dq(q(x)).  The arithmetic is the quantizer's above
+// followed by the dequantizer's (fp8 -> f32 exactly, times f32(sc8<<23)*sc32, divided by 128,
+// rounded to the output type), so the result has the bits of pb_quantize + pb_dequantize.
+template <typename OutT> struct Out4;
+template <> struct Out4<float> {
+  using vec = float4;
+  static __device__ __forceinline__ vec make(float a, float b, float c, float d) { return make_float4(a, b, c, d); }
+};
+template <> struct Out4<__nv_bfloat16> {
+  using vec = uint2;
+  static __device__ __forceinline__ vec make(float a, float b, float c, float d) { return make_uint2(pack_bf16x2(a, b), pack_bf16x2(c, d)); }
+};
+
+template <int FMT, typename OutT>
+__global__ void __launch_bounds__(kRowThreads)
+fake_quantize_row128_f32_kernel(const float4* __restrict__ x, typename Out4<OutT>::vec* __restrict__ out, int64_t n_groups) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (int64_t)gridDim.x * (kRowThreads / 32);
+  for (int64_t g = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); g < n_groups; g += warps_total) {
+    const float4* src = x + g * (kGroupElems / 4);
+    float4 w[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) w[it] = __ldcs(src + it * 32 + lane);
+    float m[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it)
+      m[it] = fmaxf(fmaxf(fabsf(w[it].x), fabsf(w[it].y)), fmaxf(fabsf(w[it].z), fabsf(w[it].w)));
+    butterfly_max<8, 2>(m, lane);                 // m[0]: amax of block it_own over the warp
+    float Mj = m[0];
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 1));
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 2));
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 4));
+
+    uint32_t sb; float D;
+    block_scale(m[0], Mj, sb, D);
+    const float r = __frcp_rn(D);
+    const float x_sc = __fmul_rn(e8m0_to_f32(sb), Mj);       // the dequantizer's multiplier: raw amax, no floor
+
+    typename Out4<OutT>::vec* dst = out + g * (kGroupElems / 4);
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int srcl = bitrev<3>(it);
+      const float Di = __shfl_sync(0xffffffffu, D, srcl);
+      const float ri = __shfl_sync(0xffffffffu, r, srcl);
+      const float si = __shfl_sync(0xffffffffu, x_sc, srcl);
+      const uint32_t p0 = pack_bf16x2(div_hoisted(w[it].x, Di, ri), div_hoisted(w[it].y, Di, ri));
+      const uint32_t p1 = pack_bf16x2(div_hoisted(w[it].z, Di, ri), div_hoisted(w[it].w, Di, ri));
+      const float2 a = fp8x2_to_f32x2<FMT>((uint16_t)bf16x2_to_fp8x2<FMT>(p0));
+      const float2 b = fp8x2_to_f32x2<FMT>((uint16_t)bf16x2_to_fp8x2<FMT>(p1));
+      const float k128 = 0.0078125f;
+      __stcs(dst + it * 32 + lane, Out4<OutT>::make(__fmul_rn(__fmul_rn(a.x, si), k128), __fmul_rn(__fmul_rn(a.y, si), k128),
+                                                    __fmul_rn(__fmul_rn(b.x, si), k128), __fmul_rn(__fmul_rn(b.y, si), k128)));
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------
 // Generic path.  Scratch layout: uint32 amax_bits[batch*Nb] | float divisor[batch*Nb].
 struct GenericDims {
@@ -418,6 +477,33 @@ extern "C" int pb_quantize_for_gemm(const void* x, int x_dtype, int64_t rows, in
   a_op.grid_a = 1; a_op.grid_b = 128; a_op.format = out_format; a_op.transposed_blocks = 0;
   if (int s = pb::gemm_a_prep_location(&a_op, b, gemm_workspace, gemm_workspace_bytes, &prep.sf, &prep.f, &prep.tiles, &prep.Mpad, stream)) return s;
   return quantize_entry(x, x_dtype, 1, rows, cols, 1, 128, out_format, q, sc8, sc32, nullptr, 0, stream, prep);
+}
+
+extern "C" int pb_fake_quantize(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols, int a, int b,
+                                int out_format, void* out, int out_dtype, void* stream) {
+  if (!x || !out) return fail(PB_ERR_NULL_POINTER, "pb_fake_quantize: x and out must be non-null");
+  if (batch <= 0) return fail(PB_ERR_BAD_SHAPE, "pb_fake_quantize: batch=%lld must be positive", (long long)batch);
+  if (out_format != PB_E4M3 && out_format != PB_E5M2) return fail(PB_ERR_BAD_DTYPE, "pb_fake_quantize: out_format %d is neither PB_E4M3 nor PB_E5M2", out_format);
+  if (out_dtype != PB_F32 && out_dtype != PB_BF16) return fail(PB_ERR_BAD_DTYPE, "pb_fake_quantize: out_dtype %d is neither PB_F32 nor PB_BF16", out_dtype);
+  Geometry g;
+  if (int s = make_geometry(rows, cols, a, b, &g)) return s;
+  if (x_dtype != PB_F32 || !row128_eligible(g))
+    return fail(PB_ERR_UNSUPPORTED, "pb_fake_quantize: only f32 input on the (1,128) grid with 8-block super-groups; use pb_quantize + pb_dequantize");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return fail(PB_ERR_MISALIGNED, "pb_fake_quantize: x and out must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t n_groups = batch * g.M;
+  const int grid = grid_for(n_groups * 32, kRowThreads, 8);
+  const bool e4 = out_format == PB_E4M3;
+  if (out_dtype == PB_F32) {
+    if (e4) fake_quantize_row128_f32_kernel<PB_E4M3, float><<<grid, kRowThreads, 0, st>>>((const float4*)x, (float4*)out, n_groups);
+    else    fake_quantize_row128_f32_kernel<PB_E5M2, float><<<grid, kRowThreads, 0, st>>>((const float4*)x, (float4*)out, n_groups);
+  } else {
+    if (e4) fake_quantize_row128_f32_kernel<PB_E4M3, __nv_bfloat16><<<grid, kRowThreads, 0, st>>>((const float4*)x, (uint2*)out, n_groups);
+    else    fake_quantize_row128_f32_kernel<PB_E5M2, __nv_bfloat16><<<grid, kRowThreads, 0, st>>>((const float4*)x, (uint2*)out, n_groups);
+  }
+  PB_LAUNCH_CHECK("fake_quantize_row128_f32_kernel");
+  return PB_OK;
 }
 
 // ---------------------------------------------------------------------------------------------

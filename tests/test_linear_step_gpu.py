@@ -103,3 +103,48 @@ def test_rejections(built_lib):
     assert list(lin._steps.values()) == [None]
     kq = lin.kernel
     assert torch.equal(y, matmul_impl(*quantize_impl(x, (1, 128)), kq.get_value(), kq.sc_fp8, kq.sc_fp32, (1, 128), (128, 128)))
+
+
+@pytest.mark.parametrize("shape,out_dtype", [((256, 1024), torch.float32), ((3, 64, 2048), torch.bfloat16), ((1000, 8192), torch.bfloat16),
+                                             ((8, 1024), torch.float32)])
+def test_fake_quantize_has_the_bits_of_quantize_then_dequantize(built_lib, shape, out_dtype):
+    from pratchya_b200._qualia import dequantize_impl, fake_quantize_impl
+    x = synth(shape, seed=sum(shape), outliers=0.01)
+    x.reshape(-1)[:2048] = 0.0            # an all-zero super-group and a half-zero one
+    x.reshape(-1)[5000] = -0.0
+    xt = to_torch(x)
+    got = fake_quantize_impl(xt, (1, 128), out_dtype)
+    want = dequantize_impl(*quantize_impl(xt, (1, 128)), out_dtype, (1, 128))
+    assert got.dtype == out_dtype and got.shape == want.shape
+    assert torch.equal(got.view(torch.int32 if out_dtype == torch.float32 else torch.int16),
+                       want.view(torch.int32 if out_dtype == torch.float32 else torch.int16))
+    oq = oracle.quantize_nd(np.asarray(x), (1, 128)) if len(shape) == 3 else oracle.quantize_impl(np.asarray(x), (1, 128))
+    ref = (oracle.dequantize_nd if len(shape) == 3 else oracle.dequantize_impl)(*oq, np.float32, (1, 128))
+    if out_dtype == torch.float32:
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), np.asarray(ref, dtype=np.float32).view(np.uint32))
+
+
+def test_fake_quantize_falls_back_on_other_grids_and_inputs(built_lib):
+    from pratchya_b200._qualia import dequantize_impl, fake_quantize_impl
+    x = to_torch(synth((256, 256), seed=3))
+    for grid in ((128, 128), (1, 16), (16, 16)):
+        got = fake_quantize_impl(x, grid, torch.float32)
+        assert torch.equal(got, dequantize_impl(*quantize_impl(x, grid), torch.float32, grid))
+    xb = to_torch(synth((128, 1024), seed=4).astype(BF16))           # bf16 input: the two-call path
+    assert torch.equal(fake_quantize_impl(xb, (1, 128), torch.bfloat16),
+                       dequantize_impl(*quantize_impl(xb, (1, 128)), torch.bfloat16, (1, 128)))
+    # the C entry point itself refuses what it has no kernel for
+    out = torch.empty_like(x)
+    st = built_lib.pb_fake_quantize(x.data_ptr(), 0, 1, 256, 256, 128, 128, 0, out.data_ptr(), 0, None)
+    assert st == _lib.PB_ERR_UNSUPPORTED
+
+
+def test_linear_call_equals_the_three_reference_steps(built_lib):
+    from pratchya_b200 import QArrayImpl
+    k, n = 1024, 2048
+    lin = Linear(k, n, (128, 128), generator=torch.Generator(device="cuda").manual_seed(11))
+    for x in (to_torch(synth((4, 64, k), seed=1)), to_torch(synth((200, k), seed=2).astype(BF16))):
+        got = lin(x)
+        want = (QArrayImpl(x, (1, 128)) @ lin.kernel).astype(x.dtype)
+        assert got.dtype == x.dtype and got.shape == want.shape
+        assert torch.equal(got, want)
