@@ -484,6 +484,11 @@ def run_triple():
         parts["quantize_dy_1x128_e5m2"] = {"ms": ms, "gbs": tokens * n_out * QUANT_BYTES_PER_ELEM / ms / 1e6}
         ms = timed(lambda: _ops.quantize_transposed_impl(dy, 128))
         parts["quantize_dyT_1x128"] = {"ms": ms, "gbs": tokens * n_out * QUANT_BYTES_PER_ELEM / ms / 1e6}
+        dual_bytes = 2 + 2 * (1 + 1 / 128 + 4 / 1024)      # one read, two quantized forms written
+        ms = timed(lambda: _ops.quantize_dual_impl(x))
+        parts["quantize_x_both_forms"] = {"ms": ms, "gbs": tokens * k_in * dual_bytes / ms / 1e6}
+        ms = timed(lambda: _ops.quantize_dual_impl(dy))
+        parts["quantize_dy_both_forms"] = {"ms": ms, "gbs": tokens * n_out * dual_bytes / ms / 1e6}
         ms = timed(lambda: _ops.quantize_impl(w, (128, 128)))
         parts["quantize_w_128x128"] = {"ms": ms, "gbs": k_in * n_out * QUANT_BYTES_PER_ELEM / ms / 1e6}
         out["layers"][name] = parts

@@ -173,6 +173,26 @@ PB_API int pb_fake_quantize(const void* x, int x_dtype, int64_t batch, int64_t r
  * device; synchronises `stream`.  PB_OK or PB_ERR_DEVICE_TIMEOUT. */
 PB_API int pb_gemm_check(void* stream);
 
+/* The middle of ChannelMix (pratchya/_nnx_impl/_module.py:246-251) on the f32 product y[rows, cols] of
+ * its first Linear, in one pass: k = dq(q(y, (1,128))) as Linear.__call__ returns it for an f32
+ * input (:46-50), k = relu(k)^2 (:249), then quantize_impl(k, (1,128)) for the second Linear (:46-47).
+ * Outputs the triple of k; the bits are those of pb_fake_quantize (f32 out), an f32 relu and square
+ * and pb_quantize.  With a non-null `b` it also writes k's scales for pb_gemm_tn_ex(...,
+ * PB_GEMM_A_PREPARED ...) against b into gemm_workspace, as pb_quantize_for_gemm does.
+ * cols must be a multiple of 1024, otherwise PB_ERR_UNSUPPORTED. */
+PB_API int pb_relu2_requantize(const void* y, int64_t rows, int64_t cols, int out_format,
+                        void* q, uint8_t* sc8, float* sc32,
+                        const pb_operand* b, void* gemm_workspace, size_t gemm_workspace_bytes, void* stream);
+/* Both quantized forms of an activation (or gradient) that a training step needs, from one
+ * call: Q(x, (1,128)) for the forward / dgrad product and Q(x^T, (1,128)) for wgrad (the
+ * operands of fp8_matmul_bwd, pratchya/_qualia/_qarr.py:784-789).  The same bits as pb_quantize
+ * on (1,128) and pb_quantize_transposed with b = 128; x is read twice instead of three times
+ * (the row quantizer's pass also takes the column-block maxima).  bf16 x with rows % 128 == 0 and
+ * cols % 1024 == 0, otherwise PB_ERR_UNSUPPORTED (use the two calls).  Workspace:
+ * pb_quantize_transposed_workspace_size(batch, rows, cols, 128). */
+PB_API int pb_quantize_dual(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols, int out_format,
+                     void* q, uint8_t* sc8, float* sc32, void* q_t, uint8_t* sc8_t, float* sc32_t,
+                     void* workspace, size_t workspace_bytes, void* stream);
 /* byte transpose [rows, cols] -> [cols, rows] of an fp8 matrix (weight prepared for the forward GEMM) */
 PB_API int pb_transpose_bytes(const void* src, int64_t rows, int64_t cols, void* dst, void* stream);
 

@@ -1,1 +1,1 @@
-from ._module import Linear, LowRankFFN, lecun_normal, linear_fp8
+from ._module import ChannelMixFFN, Linear, LowRankFFN, lecun_normal, linear_fp8

@@ -84,6 +84,40 @@ class Linear:
         return self._steps[key]
 
 
+class ChannelMixFFN:
+    """The two Linears of ChannelMix with relu^2 between them (pratchya/_nnx_impl/_module.py:231-233,
+    246-250): `w_v(relu(w_k(x).astype(f32)) ** 2)`.  The token shift and lerp in front of it (:240-245)
+    are the model's glue and stay with the caller.  Where the fused step applies (f32 x, (128,128)
+    kernels, widths that are multiples of 1024) the middle -- fake-quantize of the first product,
+    relu^2, quantize for the second product -- is one pass; the result has the bits of the literal
+    sequence, which is what runs otherwise."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, blksize: int = 128, *, generator=None,
+                 device="cuda", dtype=torch.float32):
+        grid = (blksize, blksize)
+        self.w_k = Linear(hidden_size, intermediate_size, grid, generator=generator, device=device, dtype=dtype)
+        self.w_v = Linear(intermediate_size, hidden_size, grid, generator=generator, device=device, dtype=dtype)
+
+    def literal(self, x: torch.Tensor) -> torch.Tensor:
+        k = self.w_k(x).to(torch.float32)
+        k = torch.relu(k) ** 2
+        return self.w_v(k)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if x.dtype != torch.float32 or x.dim() < 2:
+            return self.literal(x)
+        rows = x.numel() // x.shape[-1]
+        step_k = self.w_k._fused_step(x, torch.float32)
+        probe = torch.empty((rows, self.w_v.kernel.shape[0]), dtype=torch.float32, device=x.device) if step_k is not None else None
+        step_v = self.w_v._fused_step(probe, torch.float32) if probe is not None else None
+        if step_k is None or step_v is None:
+            return self.literal(x)
+        y1, _ = step_k(x)                                             # f32 product of the first Linear
+        y2, _ = step_v(y1, relu2_of_fake_quantized=True)               # middle + second product
+        out = _ops.fake_quantize_impl(y2, (1, self.w_v.kernel.tgrid[1]), x.dtype)
+        return out.reshape(*x.shape[:-1], out.shape[-1])
+
+
 class LowRankFFN:
     """down (a,1) -> tanh -> up (b,1), _module.py:74-89."""
 
@@ -113,15 +147,19 @@ class _LinearFn(torch.autograd.Function):
         a, b = grid
         x2 = x.reshape(-1, x.shape[-1])
         wq = _ops.quantize_impl(weight, grid)
-        xq = _ops.quantize_impl(x2, (1, a))
+        want_xt = recipe == "fp8" and a == 128 and x2.shape[0] % 1024 == 0
+        if want_xt:       # both forms of x in one call (x itself is not kept for the backward pass)
+            xq, xt = _ops.quantize_dual_impl(x2)
+        else:
+            xq, xt = _ops.quantize_impl(x2, (1, a)), None
         eligible = _ops._tensor_core_eligible(xq[0], wq[0], (1, a), grid)
         w_t = _ops.transpose_bytes(wq[0]) if eligible else None
         y = _ops.matmul_impl(*xq, *wq, (1, a), grid, y_fp8_t=w_t, out_dtype=torch.float32)
         ctx.grid, ctx.recipe, ctx.grad_format, ctx.fake = grid, recipe, grad_format, fake_quant_output
         ctx.x_shape, ctx.x_dtype, ctx.w_dtype = x.shape, x.dtype, weight.dtype
         saved = [*xq, *wq]
-        if recipe == "fp8" and eligible and x2.shape[0] % 1024 == 0:
-            saved += list(_ops.quantize_transposed_impl(x2, 128))      # X^T on (1,128) for wgrad; x itself is not kept
+        if want_xt and eligible:
+            saved += list(xt)                                           # X^T on (1,128) for wgrad
             ctx.have_xt = True
         else:
             ctx.have_xt = False
@@ -149,8 +187,7 @@ class _LinearFn(torch.autograd.Function):
         m, k = xq[0].shape
         n = wq[0].shape[1]
         if xt is not None:
-            gq = _ops.quantize_impl(g, (1, 128), out_format=ctx.grad_format)
-            gt = _ops.quantize_transposed_impl(g, 128, out_format=ctx.grad_format)
+            gq, gt = _ops.quantize_dual_impl(g, out_format=ctx.grad_format)
             op = _ops._operand
             gx = _ops.gemm_tn(op(gq[0], gq[1], gq[2], m, n, (1, 128)), op(wq[0], wq[1], wq[2], k, n, (128, 128)), torch.float32, g.device)
             gw = _ops.gemm_tn(op(xt[0], xt[1], xt[2], k, m, (1, 128)), op(gt[0], gt[1], gt[2], n, m, (1, 128)), torch.float32, g.device)
@@ -160,7 +197,7 @@ class _LinearFn(torch.autograd.Function):
             g32 = g.to(torch.float32)
             gx = _ops._matmul_f32(g32, w_hat.t())
             gw = _ops._matmul_f32(x_hat.t(), g32)
-        gx = _ops.dequantize_impl(*_ops.quantize_impl(gx, (1, a)), torch.float32, (1, a))        # :637 then :522-526
+        gx = _ops.fake_quantize_impl(gx, (1, a), torch.float32)                                  # :637 then :522-526
         gw = _ops.dequantize_impl(*_ops.quantize_impl(gw, ctx.grid), torch.float32, ctx.grid)    # :638; the optimizer dequantizes it
         return gx.reshape(ctx.x_shape).to(ctx.x_dtype), gw.to(ctx.w_dtype), None, None, None, None
 

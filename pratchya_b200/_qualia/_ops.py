@@ -115,6 +115,39 @@ def quantize_transposed_impl(x: torch.Tensor, b: int = 128, out_format: str = "e
     return q, sc8, sc32
 
 
+def quantize_dual_impl(x: torch.Tensor, out_format: str = "e4m3"):
+    """(quantize_impl(x, (1,128)), quantize_transposed_impl(x, 128)) for a 2-D or batched x: the two
+    forms a training step needs of an activation or a gradient (_qarr.py:784-789).  One call that
+    reads x twice where it applies (bf16, rows % 128 == 0, cols % 1024 == 0), else the two calls."""
+    _require_cuda(x, "quantize_dual_impl input")
+    if x.dim() < 2:
+        raise ValueError("quantize_dual_impl needs at least 2 dims")
+    rows, cols = x.shape[-2], x.shape[-1]
+    if not (x.dtype == torch.bfloat16 and rows % 128 == 0 and cols % 1024 == 0 and x.numel() > 0):
+        return quantize_impl(x, (1, 128), out_format), quantize_transposed_impl(x, 128, out_format)
+    lib = _lib.load()
+    lead = tuple(x.shape[:-2])
+    batch = math.prod(lead)
+    m, k = group_geometry(rows, cols, (1, 128))
+    mt, kt = group_geometry(cols, rows, (1, 128))
+    x = x.contiguous()
+    dev = x.device
+    with torch.cuda.device(dev):
+        fmt = _FMT_DTYPE[out_format]
+        q = torch.empty(tuple(x.shape), dtype=fmt, device=dev)
+        sc8 = torch.empty((*lead, m, k), dtype=E8M0, device=dev)
+        sc32 = torch.empty((*lead, m, 1, 1), dtype=torch.float32, device=dev)
+        q_t = torch.empty((*lead, cols, rows), dtype=fmt, device=dev)
+        sc8_t = torch.empty((*lead, mt, kt), dtype=E8M0, device=dev)
+        sc32_t = torch.empty((*lead, mt, 1, 1), dtype=torch.float32, device=dev)
+        ws_bytes = lib.pb_quantize_transposed_workspace_size(batch, rows, cols, 128)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        check(lib.pb_quantize_dual(x.data_ptr(), _DENSE_CODE[x.dtype], batch, rows, cols, _FMT_CODE[out_format],
+                                   q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(), q_t.data_ptr(), sc8_t.data_ptr(), sc32_t.data_ptr(),
+                                   ws.data_ptr(), ws_bytes, _stream(x)))
+    return (q, sc8, sc32), (q_t, sc8_t, sc32_t)
+
+
 def dequantize_impl(x_fp8: torch.Tensor, sc_fp8: torch.Tensor, sc_fp32: torch.Tensor, dtype, tgrid):
     """_qarr.py:541-569.  (M, K) come from sc_fp8's last two dims, as in the reference (:550)."""
     _require_cuda(x_fp8, "dequantize_impl input")
@@ -259,9 +292,14 @@ class LinearStep:
         """The weight's scales changed (an optimizer step re-quantized it): prepare them again next call."""
         self._b_ready = False
 
-    def __call__(self, x: torch.Tensor, out=None, triple=None):
+    def __call__(self, x: torch.Tensor, out=None, triple=None, relu2_of_fake_quantized: bool = False):
+        """`relu2_of_fake_quantized`: x is the f32 product of a previous Linear, and this layer's input
+        is relu(dq(q(x, (1,128))))**2 (the middle of ChannelMix, _module.py:246-251), computed and
+        quantized in the same pass."""
         lib = _lib.load()
         x = _dense_input(x)
+        if relu2_of_fake_quantized and x.dtype != torch.float32:
+            raise ValueError("relu2_of_fake_quantized needs the f32 product of the previous layer")
         if x.numel() != self.rows * self.k or x.shape[-1] != self.k:
             raise ValueError(f"LinearStep was planned for [{self.rows}, {self.k}], got {tuple(x.shape)}")
         dev = x.device
@@ -274,9 +312,14 @@ class LinearStep:
                 q, sc8, sc32 = triple
             d = out if out is not None else torch.empty((self.rows, self.n), dtype=self.out_dtype, device=dev)
             st = torch.cuda.current_stream(dev).cuda_stream
-            check(lib.pb_quantize_for_gemm(x.data_ptr(), _DENSE_CODE[x.dtype], self.rows, self.k, _FMT_CODE[self.out_format],
-                                           q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(), self.b,
-                                           self.ws.data_ptr(), self.ws_bytes, st))
+            if relu2_of_fake_quantized:
+                check(lib.pb_relu2_requantize(x.data_ptr(), self.rows, self.k, _FMT_CODE[self.out_format],
+                                              q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(), self.b,
+                                              self.ws.data_ptr(), self.ws_bytes, st))
+            else:
+                check(lib.pb_quantize_for_gemm(x.data_ptr(), _DENSE_CODE[x.dtype], self.rows, self.k, _FMT_CODE[self.out_format],
+                                               q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(), self.b,
+                                               self.ws.data_ptr(), self.ws_bytes, st))
             a = _operand(q, sc8, sc32, self.rows, self.k, (1, 128))
             flags = GEMM_A_PREPARED | (GEMM_B_PREPARED if self._b_ready else 0)
             check(lib.pb_gemm_tn_ex(a, self.b, d.data_ptr(), _DENSE_CODE[self.out_dtype], self.n,

@@ -174,6 +174,99 @@ quantize_row128_f32_kernel(const float4* __restrict__ x, uint32_t* __restrict__ 
   }
 }
 
+// The row quantizer (bf16 input) on 128-row x 1024-column tiles that also leaves the amax of every
+// 128-row column block, for the transposed quantizer's second pass: Q(x,(1,128)) and the first
+// half of Q(x^T,(1,128)) from one read of x.  A warp owns 16 rows of the tile; per row it is the
+// kernel above, plus a running per-column maximum kept as packed bf16 pairs.
+template <int FMT>
+__global__ void __launch_bounds__(kRowThreads, 2)
+quantize_row128_bf16_colmax_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, uint8_t* __restrict__ sc8,
+                                   float* __restrict__ sc32, uint32_t* __restrict__ col_amax_bits, int rows, int cols) {
+  __shared__ uint32_t red[kRowThreads / 32][512];          // per warp: 1024 column maxima as bf16 pairs
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int segs = cols >> 10;                              // super-groups per row
+  const int seg = blockIdx.x, rb = blockIdx.y;
+  const int64_t row0 = (int64_t)blockIdx.z * rows + (int64_t)rb * 128 + warp * 16;
+  uint32_t cmax[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) cmax[i] = 0u;
+  uint4 w[4], wn[4];
+  {
+    const uint4* src = x + (row0 * segs + seg) * (kGroupElems / 8);
+#pragma unroll
+    for (int it = 0; it < 4; ++it) wn[it] = __ldcs(src + it * 32 + lane);
+  }
+  for (int r = 0; r < 16; ++r) {
+    const int64_t g = (row0 + r) * segs + seg;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) w[it] = wn[it];
+    if (r + 1 < 16) {
+      const uint4* src = x + (g + segs) * (kGroupElems / 8);
+#pragma unroll
+      for (int it = 0; it < 4; ++it) wn[it] = __ldcs(src + it * 32 + lane);
+    }
+    float m[4];
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const uint32_t a[4] = {w[it].x & 0x7fff7fffu, w[it].y & 0x7fff7fffu, w[it].z & 0x7fff7fffu, w[it].w & 0x7fff7fffu};
+      __nv_bfloat162 h[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        h[j] = *reinterpret_cast<const __nv_bfloat162*>(&a[j]);
+        const __nv_bfloat162 c = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&cmax[it * 4 + j]), h[j]);
+        cmax[it * 4 + j] = *reinterpret_cast<const uint32_t*>(&c);
+      }
+      const __nv_bfloat162 hm = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+      const uint32_t hb = *reinterpret_cast<const uint32_t*>(&hm);
+      m[it] = fmaxf(__uint_as_float(hb << 16), __uint_as_float(hb & 0xffff0000u));
+    }
+    butterfly_max<4, 2>(m, lane);
+    const int it_own = bitrev<2>(lane & 3);
+    float Mj = m[0];
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 1));
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 2));
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 16));
+    uint32_t sb; float D;
+    block_scale(m[0], Mj, sb, D);
+    const float rc = __frcp_rn(D);
+    if ((lane & 12) == 0) sc8[g * 8 + 2 * it_own + (lane >> 4)] = (uint8_t)sb;
+    if (lane == 0) sc32[g] = Mj;
+    uint2* dst = q + g * (kGroupElems / 8);
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int srcl = (lane & 16) | bitrev<2>(it);
+      const float Di = __shfl_sync(0xffffffffu, D, srcl);
+      const float ri = __shfl_sync(0xffffffffu, rc, srcl);
+      const uint32_t in[4] = {w[it].x, w[it].y, w[it].z, w[it].w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = div_hoisted_unsigned(__uint_as_float(in[j] << 16), Di, ri);
+        const float hi = div_hoisted_unsigned(__uint_as_float(in[j] & 0xffff0000u), Di, ri);
+        const uint32_t pk = (pack_bf16x2(lo, hi) & 0x7fff7fffu) | (in[j] & 0x80008000u);
+        o[j] = bf16x2_to_fp8x2<FMT>(pk);
+      }
+      __stcs(dst + it * 32 + lane, make_uint2(o[0] | (o[1] << 16), o[2] | (o[3] << 16)));
+    }
+  }
+  // column maxima of the 8 warps (16 rows each) -> one amax per column for this block row
+#pragma unroll
+  for (int it = 0; it < 4; ++it)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) red[warp][(it * 32 + lane) * 4 + j] = cmax[it * 4 + j];
+  __syncthreads();
+  const int nrb = rows >> 7;
+  for (int cp = threadIdx.x; cp < 512; cp += kRowThreads) {
+    __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&red[0][cp]);
+#pragma unroll
+    for (int k = 1; k < kRowThreads / 32; ++k) v = __hmax2(v, *reinterpret_cast<const __nv_bfloat162*>(&red[k][cp]));
+    const uint32_t vb = *reinterpret_cast<const uint32_t*>(&v);
+    const size_t col = (size_t)blockIdx.z * cols + (size_t)seg * 1024 + 2 * cp;
+    col_amax_bits[col * nrb + rb] = vb << 16;                    // f32 bits of the even column's amax
+    col_amax_bits[(col + 1) * nrb + rb] = vb & 0xffff0000u;      // and of the odd one
+  }
+}
+
 // Quantize and dequantize in one pass (f32 input, grid (1,128), 8-block super-groups): what
 // `(x_q @ kernel).astype(dtype)` does to the f32 product in Linear.__call__
 // (pratchya/_nnx_impl/_module.py:46-50 through QArrayImpl.__matmul__, _qarr.py:104-105, and
@@ -229,6 +322,81 @@ fake_quantize_row128_f32_kernel(const float4* __restrict__ x, typename Out4<OutT
       const float k128 = 0.0078125f;
       __stcs(dst + it * 32 + lane, Out4<OutT>::make(__fmul_rn(__fmul_rn(a.x, si), k128), __fmul_rn(__fmul_rn(a.y, si), k128),
                                                     __fmul_rn(__fmul_rn(b.x, si), k128), __fmul_rn(__fmul_rn(b.y, si), k128)));
+    }
+  }
+}
+
+// The middle of ChannelMix (pratchya/_nnx_impl/_module.py:246-251) in one pass over the f32 product
+// y of its first Linear:  k = dq(q(y, (1,128))) in f32 (what Linear.__call__ returns for an f32 input,
+// :46-50), k = relu(k)^2 (:249), then the second Linear's own quantize_impl(k, (1,128)) (:46-47).  Both
+// quantizations partition a row into the same 1024-element super-groups, so a warp keeps its
+// super-group in registers across the three steps.  The bits are those of pb_fake_quantize, an f32
+// relu and square, and pb_quantize.
+template <int FMT, bool PREP>
+__global__ void __launch_bounds__(kRowThreads)
+relu2_requantize_row128_f32_kernel(const float4* __restrict__ y, uint32_t* __restrict__ q, uint8_t* __restrict__ sc8,
+                                   float* __restrict__ sc32, int64_t n_groups, const GemmPrepOut prep) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (int64_t)gridDim.x * (kRowThreads / 32);
+  for (int64_t g = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); g < n_groups; g += warps_total) {
+    const float4* src = y + g * (kGroupElems / 4);
+    float4 w[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) w[it] = __ldcs(src + it * 32 + lane);
+    float m[8];
+    {   // ---- k = relu(dq(q(y)))^2, in place
+#pragma unroll
+      for (int it = 0; it < 8; ++it)
+        m[it] = fmaxf(fmaxf(fabsf(w[it].x), fabsf(w[it].y)), fmaxf(fabsf(w[it].z), fabsf(w[it].w)));
+      butterfly_max<8, 2>(m, lane);
+      float Mj = m[0];
+      Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 1));
+      Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 2));
+      Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 4));
+      uint32_t sb; float D;
+      block_scale(m[0], Mj, sb, D);
+      const float r = __frcp_rn(D);
+      const float x_sc = __fmul_rn(e8m0_to_f32(sb), Mj);
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int srcl = bitrev<3>(it);
+        const float Di = __shfl_sync(0xffffffffu, D, srcl);
+        const float ri = __shfl_sync(0xffffffffu, r, srcl);
+        const float si = __shfl_sync(0xffffffffu, x_sc, srcl);
+        const uint32_t p0 = pack_bf16x2(div_hoisted(w[it].x, Di, ri), div_hoisted(w[it].y, Di, ri));
+        const uint32_t p1 = pack_bf16x2(div_hoisted(w[it].z, Di, ri), div_hoisted(w[it].w, Di, ri));
+        const float2 a = fp8x2_to_f32x2<FMT>((uint16_t)bf16x2_to_fp8x2<FMT>(p0));
+        const float2 b = fp8x2_to_f32x2<FMT>((uint16_t)bf16x2_to_fp8x2<FMT>(p1));
+        const float k128 = 0.0078125f;
+        const float t0 = fmaxf(__fmul_rn(__fmul_rn(a.x, si), k128), 0.0f), t1 = fmaxf(__fmul_rn(__fmul_rn(a.y, si), k128), 0.0f);
+        const float t2 = fmaxf(__fmul_rn(__fmul_rn(b.x, si), k128), 0.0f), t3 = fmaxf(__fmul_rn(__fmul_rn(b.y, si), k128), 0.0f);
+        w[it] = make_float4(__fmul_rn(t0, t0), __fmul_rn(t1, t1), __fmul_rn(t2, t2), __fmul_rn(t3, t3));
+      }
+    }
+    // ---- quantize_impl(k, (1,128)): the f32 row kernel on the values now in registers (all >= 0)
+#pragma unroll
+    for (int it = 0; it < 8; ++it) m[it] = fmaxf(fmaxf(w[it].x, w[it].y), fmaxf(w[it].z, w[it].w));
+    butterfly_max<8, 2>(m, lane);
+    const int it_own = bitrev<3>(lane & 7);
+    float Mj = m[0];
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 1));
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 2));
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 4));
+    uint32_t sb; float D;
+    block_scale(m[0], Mj, sb, D);
+    const float r = __frcp_rn(D);
+    if (lane < 8) sc8[g * 8 + it_own] = (uint8_t)sb;
+    if (lane == 0) sc32[g] = Mj;
+    if (PREP) write_gemm_prep(prep, g, it_own, sb, Mj, lane < 8, lane == 0);
+    uint32_t* dst = q + g * (kGroupElems / 4);
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int srcl = bitrev<3>(it);
+      const float Di = __shfl_sync(0xffffffffu, D, srcl);
+      const float ri = __shfl_sync(0xffffffffu, r, srcl);
+      const uint32_t p0 = pack_bf16x2(div_hoisted(w[it].x, Di, ri), div_hoisted(w[it].y, Di, ri));
+      const uint32_t p1 = pack_bf16x2(div_hoisted(w[it].z, Di, ri), div_hoisted(w[it].w, Di, ri));
+      __stcs(dst + it * 32 + lane, bf16x2_to_fp8x2<FMT>(p0) | (bf16x2_to_fp8x2<FMT>(p1) << 16));
     }
   }
 }
@@ -385,6 +553,18 @@ int launch_generic(const InT* x, const Geometry& g, int64_t batch, int fmt, uint
 bool row128_eligible(const Geometry& g) { return g.a == 1 && g.b == 128 && g.K == 8; }
 
 }  // namespace
+
+// First pass of pb_quantize_dual (transpose_quantize.cu): bf16 x[batch, rows, cols], rows % 128 == 0, cols % 1024 == 0.
+int launch_row128_colmax(const void* x, int out_format, void* q, uint8_t* sc8, float* sc32, uint32_t* col_amax_bits,
+                         int64_t batch, int64_t rows, int64_t cols, cudaStream_t st) {
+  const dim3 grid((unsigned)(cols / 1024), (unsigned)(rows / 128), (unsigned)batch);
+  if (out_format == PB_E4M3)
+    quantize_row128_bf16_colmax_kernel<PB_E4M3><<<grid, kRowThreads, 0, st>>>((const uint4*)x, (uint2*)q, sc8, sc32, col_amax_bits, (int)rows, (int)cols);
+  else
+    quantize_row128_bf16_colmax_kernel<PB_E5M2><<<grid, kRowThreads, 0, st>>>((const uint4*)x, (uint2*)q, sc8, sc32, col_amax_bits, (int)rows, (int)cols);
+  PB_LAUNCH_CHECK("quantize_row128_bf16_colmax_kernel");
+  return PB_OK;
+}
 }  // namespace pb
 
 using namespace pb;
@@ -477,6 +657,37 @@ extern "C" int pb_quantize_for_gemm(const void* x, int x_dtype, int64_t rows, in
   a_op.grid_a = 1; a_op.grid_b = 128; a_op.format = out_format; a_op.transposed_blocks = 0;
   if (int s = pb::gemm_a_prep_location(&a_op, b, gemm_workspace, gemm_workspace_bytes, &prep.sf, &prep.f, &prep.tiles, &prep.Mpad, stream)) return s;
   return quantize_entry(x, x_dtype, 1, rows, cols, 1, 128, out_format, q, sc8, sc32, nullptr, 0, stream, prep);
+}
+
+extern "C" int pb_relu2_requantize(const void* y, int64_t rows, int64_t cols, int out_format, void* q, uint8_t* sc8, float* sc32,
+                                   const pb_operand* b, void* gemm_workspace, size_t gemm_workspace_bytes, void* stream) {
+  if (!y || !q || !sc8 || !sc32) return fail(PB_ERR_NULL_POINTER, "pb_relu2_requantize: y, q, sc8 and sc32 must be non-null");
+  if (out_format != PB_E4M3 && out_format != PB_E5M2) return fail(PB_ERR_BAD_DTYPE, "pb_relu2_requantize: out_format %d is neither PB_E4M3 nor PB_E5M2", out_format);
+  if (rows <= 0 || cols <= 0 || cols % 1024 != 0)
+    return fail(PB_ERR_UNSUPPORTED, "pb_relu2_requantize: [%lld, %lld]: cols must be a positive multiple of 1024 (whole super-groups per row)", (long long)rows, (long long)cols);
+  if (rows * (cols / 128) > kMaxIndexed) return fail(PB_ERR_UNSUPPORTED, "pb_relu2_requantize: too many blocks");
+  if ((reinterpret_cast<uintptr_t>(y) & 15) || (reinterpret_cast<uintptr_t>(q) & 3))
+    return fail(PB_ERR_MISALIGNED, "pb_relu2_requantize: y must be 16-byte and q 4-byte aligned");
+  GemmPrepOut prep{nullptr, nullptr, (uint32_t)(cols / 128), 0, 0};
+  if (b) {      // also lay the scales out for the GEMM against b, as pb_quantize_for_gemm does
+    pb_operand a_op;
+    a_op.q = q; a_op.sc8 = sc8; a_op.sc32 = sc32; a_op.rows = rows; a_op.depth = cols;
+    a_op.grid_a = 1; a_op.grid_b = 128; a_op.format = out_format; a_op.transposed_blocks = 0;
+    if (int s = pb::gemm_a_prep_location(&a_op, b, gemm_workspace, gemm_workspace_bytes, &prep.sf, &prep.f, &prep.tiles, &prep.Mpad, stream)) return s;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t n_groups = rows * (cols / 1024);
+  const int grid = grid_for(n_groups * 32, kRowThreads, 8);
+  const bool e4 = out_format == PB_E4M3;
+  if (prep.sf) {
+    if (e4) relu2_requantize_row128_f32_kernel<PB_E4M3, true><<<grid, kRowThreads, 0, st>>>((const float4*)y, (uint32_t*)q, sc8, sc32, n_groups, prep);
+    else    relu2_requantize_row128_f32_kernel<PB_E5M2, true><<<grid, kRowThreads, 0, st>>>((const float4*)y, (uint32_t*)q, sc8, sc32, n_groups, prep);
+  } else {
+    if (e4) relu2_requantize_row128_f32_kernel<PB_E4M3, false><<<grid, kRowThreads, 0, st>>>((const float4*)y, (uint32_t*)q, sc8, sc32, n_groups, prep);
+    else    relu2_requantize_row128_f32_kernel<PB_E5M2, false><<<grid, kRowThreads, 0, st>>>((const float4*)y, (uint32_t*)q, sc8, sc32, n_groups, prep);
+  }
+  PB_LAUNCH_CHECK("relu2_requantize_row128_f32_kernel");
+  return PB_OK;
 }
 
 extern "C" int pb_fake_quantize(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols, int a, int b,

@@ -12,6 +12,8 @@ namespace pb {
 
 // defined in quantize.cu
 int launch_group_scales(const uint32_t* amax_bits, float* divisor, uint8_t* sc8, float* sc32, int64_t n_groups, int64_t K, cudaStream_t st);
+int launch_row128_colmax(const void* x, int out_format, void* q, uint8_t* sc8, float* sc32, uint32_t* col_amax_bits,
+                         int64_t batch, int64_t rows, int64_t cols, cudaStream_t st);
 
 namespace {
 
@@ -269,6 +271,38 @@ extern "C" int pb_quantize_transposed(const void* x, int x_dtype, int64_t batch,
     else                       transpose_apply_kernel<float, PB_E5M2><<<grid3, 256, 0, st>>>((const float*)x, divisor, out, (int)rows, (int)cols, b);
   }
   PB_LAUNCH_CHECK("transpose_apply_kernel");
+  return PB_OK;
+}
+
+extern "C" int pb_quantize_dual(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols, int out_format,
+                                void* q, uint8_t* sc8, float* sc32, void* q_t, uint8_t* sc8_t, float* sc32_t,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !q || !sc8 || !sc32 || !q_t || !sc8_t || !sc32_t) return fail(PB_ERR_NULL_POINTER, "pb_quantize_dual: x and the six outputs must be non-null");
+  if (batch <= 0) return fail(PB_ERR_BAD_SHAPE, "pb_quantize_dual: batch=%lld must be positive", (long long)batch);
+  if (out_format != PB_E4M3 && out_format != PB_E5M2) return fail(PB_ERR_BAD_DTYPE, "pb_quantize_dual: out_format %d is neither PB_E4M3 nor PB_E5M2", out_format);
+  if (x_dtype != PB_BF16 && x_dtype != PB_F32) return fail(PB_ERR_BAD_DTYPE, "pb_quantize_dual: x_dtype %d is neither PB_F32 nor PB_BF16", x_dtype);
+  Geometry gr, gt;      // x on (1,128) and x^T on (1,128)
+  if (int s = make_geometry(rows, cols, 1, 128, &gr)) return s;
+  if (int s = make_geometry(cols, rows, 1, 128, &gt)) return s;
+  if (x_dtype != PB_BF16 || cols % 1024 != 0 || rows % 128 != 0 || gr.K != 8 || batch > 65535 || rows / 128 > 65535 ||
+      rows > kMaxIndexed || cols > kMaxIndexed)
+    return fail(PB_ERR_UNSUPPORTED, "pb_quantize_dual: needs bf16 x with rows %% 128 == 0 and cols %% 1024 == 0; use pb_quantize and pb_quantize_transposed");
+  const size_t need = (size_t)(batch * gt.Nb) * 8;
+  if (!workspace || workspace_bytes < need)
+    return fail(PB_ERR_WORKSPACE_TOO_SMALL, "pb_quantize_dual: needs %zu bytes of workspace, got %zu", need, workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 3) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7) ||
+      (reinterpret_cast<uintptr_t>(q_t) & 31))
+    return fail(PB_ERR_MISALIGNED, "pb_quantize_dual: x must be 16-byte, q 8-byte, q_t 32-byte and the workspace 4-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t* amax_bits = static_cast<uint32_t*>(workspace);
+  float* divisor = reinterpret_cast<float*>(amax_bits + batch * gt.Nb);
+  if (int s = launch_row128_colmax(x, out_format, q, sc8, sc32, amax_bits, batch, rows, cols, st)) return s;
+  if (int s = launch_group_scales(amax_bits, divisor, sc8_t, sc32_t, batch * gt.M, gt.K, st)) return s;
+  const dim3 gc((unsigned)(cols / 64), (unsigned)(rows / 128), (unsigned)batch);
+  uint8_t* out = static_cast<uint8_t*>(q_t);
+  if (out_format == PB_E4M3) transpose_apply128_kernel<__nv_bfloat16, PB_E4M3><<<gc, 256, 0, st>>>((const __nv_bfloat16*)x, divisor, out, (int)rows, (int)cols);
+  else                       transpose_apply128_kernel<__nv_bfloat16, PB_E5M2><<<gc, 256, 0, st>>>((const __nv_bfloat16*)x, divisor, out, (int)rows, (int)cols);
+  PB_LAUNCH_CHECK("transpose_apply128_kernel");
   return PB_OK;
 }
 

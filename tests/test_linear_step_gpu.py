@@ -148,3 +148,67 @@ def test_linear_call_equals_the_three_reference_steps(built_lib):
         want = (QArrayImpl(x, (1, 128)) @ lin.kernel).astype(x.dtype)
         assert got.dtype == x.dtype and got.shape == want.shape
         assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("shape,fmt", [((128, 1024), "e4m3"), ((1024, 2048), "e4m3"), ((2, 256, 1024), "e4m3"), ((384, 3072), "e5m2")])
+def test_dual_quantizer_equals_the_two_calls(built_lib, shape, fmt):
+    from pratchya_b200._qualia import quantize_dual_impl, quantize_transposed_impl
+    x = synth(shape, seed=sum(shape), outliers=0.01).astype(BF16)
+    x.reshape(-1)[:1024] = 0
+    xt = to_torch(x)
+    (row, tr) = quantize_dual_impl(xt, out_format=fmt)
+    assert_triple_equal(np_triple(row), np_triple(quantize_impl(xt, (1, 128), out_format=fmt)), "row triple")
+    assert_triple_equal(np_triple(tr), np_triple(quantize_transposed_impl(xt, 128, out_format=fmt)), "transposed triple")
+    if fmt == "e4m3" and len(shape) == 2:
+        oq = oracle.quantize_impl(np.ascontiguousarray(np.asarray(x).astype(np.float32).T), (1, 128))
+        assert_triple_equal(np_triple(tr), (oq[0].view(np.uint8), oq[1].view(np.uint8), oq[2]), "transposed triple vs oracle on x^T")
+
+
+def test_dual_quantizer_falls_back(built_lib):
+    from pratchya_b200._qualia import quantize_dual_impl, quantize_transposed_impl
+    for x in (to_torch(synth((128, 1024), seed=1)),                       # f32 input
+              to_torch(synth((128, 512), seed=2).astype(BF16))):          # cols not a multiple of 1024
+        row, tr = quantize_dual_impl(x)
+        assert_triple_equal(np_triple(row), np_triple(quantize_impl(x, (1, 128))), "row")
+        assert_triple_equal(np_triple(tr), np_triple(quantize_transposed_impl(x, 128)), "transposed")
+    x = to_torch(synth((128, 512), seed=2).astype(BF16))
+    outs = [torch.empty(128 * 512, dtype=torch.uint8, device="cuda") for _ in range(6)]
+    st = built_lib.pb_quantize_dual(x.data_ptr(), 1, 1, 128, 512, 0, *[o.data_ptr() for o in outs], outs[0].data_ptr(), 1 << 16, None)
+    assert st == _lib.PB_ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("rows,cols", [(128, 1024), (200, 4096), (1000, 2048)])
+def test_relu2_requantize_has_the_bits_of_the_three_steps(built_lib, rows, cols):
+    from pratchya_b200._qualia import fake_quantize_impl
+    y = synth((rows, cols), seed=rows + cols, outliers=0.01)
+    y.reshape(-1)[:1024] = 0.0
+    y.reshape(-1)[1024:2048] = -np.abs(y.reshape(-1)[1024:2048])          # a super-group that relu wipes out
+    yt = to_torch(y)
+    k = torch.relu(fake_quantize_impl(yt, (1, 128), torch.float32)) ** 2
+    want = quantize_impl(k, (1, 128))
+    q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device="cuda")
+    sc8 = torch.empty_like(want[1])
+    sc32 = torch.empty_like(want[2])
+    _lib.check(built_lib.pb_relu2_requantize(yt.data_ptr(), rows, cols, 0, q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(),
+                                             None, None, 0, torch.cuda.current_stream().cuda_stream))
+    assert_triple_equal(np_triple((q, sc8, sc32)), np_triple(want), "fused middle vs fake-quantize, relu^2, quantize")
+    # and against the oracle's three steps
+    oq = oracle.quantize_impl(np.asarray(y), (1, 128))
+    kk = np.maximum(oracle.dequantize_impl(*oq, np.float32, (1, 128)), 0).astype(np.float32) ** 2
+    ok = oracle.quantize_impl(kk.astype(np.float32), (1, 128))
+    assert_triple_equal(np_triple((q, sc8, sc32)), (ok[0].view(np.uint8), ok[1].view(np.uint8), ok[2]), "fused middle vs oracle")
+    st = built_lib.pb_relu2_requantize(yt.data_ptr(), rows, 512, 0, q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(), None, None, 0, None)
+    assert st == _lib.PB_ERR_UNSUPPORTED
+
+
+def test_channel_mix_ffn_fused_equals_literal(built_lib):
+    from pratchya_b200._nnx_impl import ChannelMixFFN
+    ffn = ChannelMixFFN(1024, 4096, generator=torch.Generator(device="cuda").manual_seed(21))
+    for x in (to_torch(synth((2, 96, 1024), seed=5)), to_torch(synth((256, 1024), seed=6))):
+        got = ffn(x)
+        assert ffn.w_k._steps and ffn.w_v._steps and all(v is not None for v in ffn.w_v._steps.values())
+        want = ffn.literal(x)
+        assert got.shape == want.shape and got.dtype == want.dtype
+        assert torch.equal(got, want)
+    xb = to_torch(synth((256, 1024), seed=7).astype(BF16))          # bf16 input: the literal sequence
+    assert torch.equal(ffn(xb), ffn.literal(xb))
