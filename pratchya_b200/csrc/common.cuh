@@ -128,6 +128,24 @@ __device__ __forceinline__ float div_hoisted_unsigned(float x, float D, float r)
   q = __fmaf_rn(e, r, q);
   return q;
 }
+// The same five operations on two elements at a time (packed f32x2 arithmetic of sm_100): r2 holds
+// the reciprocal twice and nD2 the negated divisor twice; fma(q, -D, x) has the bits of fma(-q, D, x).
+__device__ __forceinline__ float2 div_hoisted_unsigned2(float2 x, float2 nD2, float2 r2) {
+  float2 q = __fmul2_rn(x, r2);
+  float2 e = __ffma2_rn(q, nD2, x);
+  q = __ffma2_rn(e, r2, q);
+  e = __ffma2_rn(q, nD2, x);
+  q = __ffma2_rn(e, r2, q);
+  return q;
+}
+// (x0, x1) / D for f32 inputs, packed to bf16x2 with the inputs' signs (the quotient's own sign is
+// lost only for x = -0): the bits of pack_bf16x2(div_hoisted(x0, D, r), div_hoisted(x1, D, r)).
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi);
+__device__ __forceinline__ uint32_t div_hoisted_pack2(float x0, float x1, float2 nD2, float2 r2) {
+  const float2 q = div_hoisted_unsigned2(make_float2(x0, x1), nD2, r2);
+  const uint32_t sign = ((__float_as_uint(x0) >> 16) & 0x8000u) | (__float_as_uint(x1) & 0x80000000u);
+  return (pack_bf16x2(q.x, q.y) & 0x7fff7fffu) | sign;
+}
 __device__ __forceinline__ float div_hoisted(float x, float D, float r) {
   const float q = div_hoisted_unsigned(x, D, r);
   return __uint_as_float((__float_as_uint(q) & 0x7fffffffu) | (__float_as_uint(x) & 0x80000000u));

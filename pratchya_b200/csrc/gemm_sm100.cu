@@ -182,20 +182,26 @@ __device__ __forceinline__ void tc_ld32f(uint32_t taddr, float (&a)[128]) {
         "=f"(a[OFF + 24]), "=f"(a[OFF + 25]), "=f"(a[OFF + 26]), "=f"(a[OFF + 27]), "=f"(a[OFF + 28]), "=f"(a[OFF + 29]), "=f"(a[OFF + 30]), "=f"(a[OFF + 31])
       : "r"(taddr) : "memory");
 }
-// acc[OFF .. OFF+31] += r * fa * fb[column]
+// acc[OFF .. OFF+31] += r * fa * fb[column], two columns per instruction (packed f32x2 arithmetic of sm_100)
 template <int OFF>
 __device__ __forceinline__ void promote(float (&acc)[128], const uint32_t (&r)[32], float fa, float s_uni, const float* fbp, int uniform) {
   if (uniform) {
+    const float2 s2 = make_float2(s_uni, s_uni);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) acc[OFF + j] = fmaf(__uint_as_float(r[j]), s_uni, acc[OFF + j]);
+    for (int j = 0; j < 32; j += 2) {
+      const float2 v = __ffma2_rn(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), s2, make_float2(acc[OFF + j], acc[OFF + j + 1]));
+      acc[OFF + j] = v.x; acc[OFF + j + 1] = v.y;
+    }
   } else {
+    const float2 fa2 = make_float2(fa, fa);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float4 fb = __ldg(reinterpret_cast<const float4*>(fbp + OFF) + j);
-      acc[OFF + 4 * j + 0] = fmaf(__uint_as_float(r[4 * j + 0]) * fa, fb.x, acc[OFF + 4 * j + 0]);
-      acc[OFF + 4 * j + 1] = fmaf(__uint_as_float(r[4 * j + 1]) * fa, fb.y, acc[OFF + 4 * j + 1]);
-      acc[OFF + 4 * j + 2] = fmaf(__uint_as_float(r[4 * j + 2]) * fa, fb.z, acc[OFF + 4 * j + 2]);
-      acc[OFF + 4 * j + 3] = fmaf(__uint_as_float(r[4 * j + 3]) * fa, fb.w, acc[OFF + 4 * j + 3]);
+      const float2 t0 = __fmul2_rn(make_float2(__uint_as_float(r[4 * j + 0]), __uint_as_float(r[4 * j + 1])), fa2);
+      const float2 t1 = __fmul2_rn(make_float2(__uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])), fa2);
+      const float2 v0 = __ffma2_rn(t0, make_float2(fb.x, fb.y), make_float2(acc[OFF + 4 * j + 0], acc[OFF + 4 * j + 1]));
+      const float2 v1 = __ffma2_rn(t1, make_float2(fb.z, fb.w), make_float2(acc[OFF + 4 * j + 2], acc[OFF + 4 * j + 3]));
+      acc[OFF + 4 * j + 0] = v0.x; acc[OFF + 4 * j + 1] = v0.y; acc[OFF + 4 * j + 2] = v1.x; acc[OFF + 4 * j + 3] = v1.y;
     }
   }
 }

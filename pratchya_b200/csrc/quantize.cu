@@ -118,12 +118,12 @@ quantize_row128_bf16_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
       const float ri = __shfl_sync(0xffffffffu, r, srcl);
       const uint32_t in[4] = {w[it].x, w[it].y, w[it].z, w[it].w};
       uint32_t o[4];
+      const float2 nD2 = make_float2(-Di, -Di), r2 = make_float2(ri, ri);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float lo = div_hoisted_unsigned(__uint_as_float(in[j] << 16), Di, ri);
-        const float hi = div_hoisted_unsigned(__uint_as_float(in[j] & 0xffff0000u), Di, ri);
+        const float2 v = div_hoisted_unsigned2(make_float2(__uint_as_float(in[j] << 16), __uint_as_float(in[j] & 0xffff0000u)), nD2, r2);
         // sign of the input (also for -0) re-applied on the packed bf16 pair
-        const uint32_t p = (pack_bf16x2(lo, hi) & 0x7fff7fffu) | (in[j] & 0x80008000u);
+        const uint32_t p = (pack_bf16x2(v.x, v.y) & 0x7fff7fffu) | (in[j] & 0x80008000u);
         o[j] = bf16x2_to_fp8x2<FMT>(p);
       }
       __stcs(dst + it * 32 + lane, make_uint2(o[0] | (o[1] << 16), o[2] | (o[3] << 16)));
@@ -167,8 +167,9 @@ quantize_row128_f32_kernel(const float4* __restrict__ x, uint32_t* __restrict__ 
       const int srcl = bitrev<3>(it);
       const float Di = __shfl_sync(0xffffffffu, D, srcl);
       const float ri = __shfl_sync(0xffffffffu, r, srcl);
-      const uint32_t p0 = pack_bf16x2(div_hoisted(w[it].x, Di, ri), div_hoisted(w[it].y, Di, ri));
-      const uint32_t p1 = pack_bf16x2(div_hoisted(w[it].z, Di, ri), div_hoisted(w[it].w, Di, ri));
+      const float2 nD2 = make_float2(-Di, -Di), r2 = make_float2(ri, ri);
+      const uint32_t p0 = div_hoisted_pack2(w[it].x, w[it].y, nD2, r2);
+      const uint32_t p1 = div_hoisted_pack2(w[it].z, w[it].w, nD2, r2);
       __stcs(dst + it * 32 + lane, bf16x2_to_fp8x2<FMT>(p0) | (bf16x2_to_fp8x2<FMT>(p1) << 16));
     }
   }
@@ -239,11 +240,11 @@ quantize_row128_bf16_colmax_kernel(const uint4* __restrict__ x, uint2* __restric
       const float ri = __shfl_sync(0xffffffffu, rc, srcl);
       const uint32_t in[4] = {w[it].x, w[it].y, w[it].z, w[it].w};
       uint32_t o[4];
+      const float2 nD2 = make_float2(-Di, -Di), r2 = make_float2(ri, ri);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float lo = div_hoisted_unsigned(__uint_as_float(in[j] << 16), Di, ri);
-        const float hi = div_hoisted_unsigned(__uint_as_float(in[j] & 0xffff0000u), Di, ri);
-        const uint32_t pk = (pack_bf16x2(lo, hi) & 0x7fff7fffu) | (in[j] & 0x80008000u);
+        const float2 v = div_hoisted_unsigned2(make_float2(__uint_as_float(in[j] << 16), __uint_as_float(in[j] & 0xffff0000u)), nD2, r2);
+        const uint32_t pk = (pack_bf16x2(v.x, v.y) & 0x7fff7fffu) | (in[j] & 0x80008000u);
         o[j] = bf16x2_to_fp8x2<FMT>(pk);
       }
       __stcs(dst + it * 32 + lane, make_uint2(o[0] | (o[1] << 16), o[2] | (o[3] << 16)));
@@ -315,8 +316,9 @@ fake_quantize_row128_f32_kernel(const float4* __restrict__ x, typename Out4<OutT
       const float Di = __shfl_sync(0xffffffffu, D, srcl);
       const float ri = __shfl_sync(0xffffffffu, r, srcl);
       const float si = __shfl_sync(0xffffffffu, x_sc, srcl);
-      const uint32_t p0 = pack_bf16x2(div_hoisted(w[it].x, Di, ri), div_hoisted(w[it].y, Di, ri));
-      const uint32_t p1 = pack_bf16x2(div_hoisted(w[it].z, Di, ri), div_hoisted(w[it].w, Di, ri));
+      const float2 nD2 = make_float2(-Di, -Di), r2 = make_float2(ri, ri);
+      const uint32_t p0 = div_hoisted_pack2(w[it].x, w[it].y, nD2, r2);
+      const uint32_t p1 = div_hoisted_pack2(w[it].z, w[it].w, nD2, r2);
       const float2 a = fp8x2_to_f32x2<FMT>((uint16_t)bf16x2_to_fp8x2<FMT>(p0));
       const float2 b = fp8x2_to_f32x2<FMT>((uint16_t)bf16x2_to_fp8x2<FMT>(p1));
       const float k128 = 0.0078125f;
@@ -363,8 +365,9 @@ relu2_requantize_row128_f32_kernel(const float4* __restrict__ y, uint32_t* __res
         const float Di = __shfl_sync(0xffffffffu, D, srcl);
         const float ri = __shfl_sync(0xffffffffu, r, srcl);
         const float si = __shfl_sync(0xffffffffu, x_sc, srcl);
-        const uint32_t p0 = pack_bf16x2(div_hoisted(w[it].x, Di, ri), div_hoisted(w[it].y, Di, ri));
-        const uint32_t p1 = pack_bf16x2(div_hoisted(w[it].z, Di, ri), div_hoisted(w[it].w, Di, ri));
+        const float2 nD2 = make_float2(-Di, -Di), r2 = make_float2(ri, ri);
+        const uint32_t p0 = div_hoisted_pack2(w[it].x, w[it].y, nD2, r2);
+        const uint32_t p1 = div_hoisted_pack2(w[it].z, w[it].w, nD2, r2);
         const float2 a = fp8x2_to_f32x2<FMT>((uint16_t)bf16x2_to_fp8x2<FMT>(p0));
         const float2 b = fp8x2_to_f32x2<FMT>((uint16_t)bf16x2_to_fp8x2<FMT>(p1));
         const float k128 = 0.0078125f;
@@ -394,8 +397,9 @@ relu2_requantize_row128_f32_kernel(const float4* __restrict__ y, uint32_t* __res
       const int srcl = bitrev<3>(it);
       const float Di = __shfl_sync(0xffffffffu, D, srcl);
       const float ri = __shfl_sync(0xffffffffu, r, srcl);
-      const uint32_t p0 = pack_bf16x2(div_hoisted(w[it].x, Di, ri), div_hoisted(w[it].y, Di, ri));
-      const uint32_t p1 = pack_bf16x2(div_hoisted(w[it].z, Di, ri), div_hoisted(w[it].w, Di, ri));
+      const float2 nD2 = make_float2(-Di, -Di), r2 = make_float2(ri, ri);
+      const uint32_t p0 = div_hoisted_pack2(w[it].x, w[it].y, nD2, r2);
+      const uint32_t p1 = div_hoisted_pack2(w[it].z, w[it].w, nD2, r2);
       __stcs(dst + it * 32 + lane, bf16x2_to_fp8x2<FMT>(p0) | (bf16x2_to_fp8x2<FMT>(p1) << 16));
     }
   }
@@ -597,7 +601,11 @@ static int quantize_entry(const void* x, int x_dtype, int64_t batch, int64_t row
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7))
       return fail(PB_ERR_MISALIGNED, "pb_quantize: x must be 16-byte and q 8-byte aligned");
     const int64_t n_groups = batch * g.M;
-    const int grid = grid_for(n_groups * 32, kRowThreads, 8);
+    // 8 CTAs per SM, 16 once every warp then still gets three super-groups or more (measured: X[8192,2048] is
+    // best at 8, X[32768,2048] and larger at 16); PB_QUANT_CTAS_PER_SM overrides
+    static const int forced_ctas = [] { const char* e = getenv("PB_QUANT_CTAS_PER_SM"); const int v = e ? atoi(e) : 0; return v > 0 ? v : 0; }();
+    const int ctas_per_sm = forced_ctas ? forced_ctas : (n_groups >= (int64_t)sm_count() * 16 * (kRowThreads / 32) * 3 ? 16 : 8);
+    const int grid = grid_for(n_groups * 32, kRowThreads, ctas_per_sm);
     // 40 registers per thread (6 CTAs of 256 threads per SM) measures the same as the compiler's
     // unconstrained 49; an unconstrained single CTA per SM (96 registers) is 15 % slower.
     const bool e4 = out_format == PB_E4M3;

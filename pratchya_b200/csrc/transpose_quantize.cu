@@ -176,12 +176,13 @@ transpose_apply128_kernel(const InT* __restrict__ x, const float* __restrict__ d
   const float D = divisor[((size_t)blockIdx.z * cols + c0 + c) * nrb + blockIdx.y];
   const float rcp = __frcp_rn(D);
   uint32_t out[8];
+  const float2 nD2 = make_float2(-D, -D), r2 = make_float2(rcp, rcp);
 #pragma unroll
   for (int w = 0; w < 8; ++w) {
     float v[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = div_hoisted(Elem<InT>::to_f32(tile[(seg * 32 + w * 4 + j) * kPitch + c]), D, rcp);
-    out[w] = bf16x2_to_fp8x2<FMT>(pack_bf16x2(v[0], v[1])) | (bf16x2_to_fp8x2<FMT>(pack_bf16x2(v[2], v[3])) << 16);
+    for (int j = 0; j < 4; ++j) v[j] = Elem<InT>::to_f32(tile[(seg * 32 + w * 4 + j) * kPitch + c]);
+    out[w] = bf16x2_to_fp8x2<FMT>(div_hoisted_pack2(v[0], v[1], nD2, r2)) | (bf16x2_to_fp8x2<FMT>(div_hoisted_pack2(v[2], v[3], nD2, r2)) << 16);
   }
   uint8_t* o = q_t + (size_t)blockIdx.z * rows * cols + (size_t)(c0 + c) * rows + r0 + seg * 32;
   asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
