@@ -94,6 +94,40 @@ dequantize_bwd_kernel(const T* __restrict__ g, const uint8_t* __restrict__ sc8, 
   }
 }
 
+// Grid (1,128) with 8-block super-groups: a super-group is 1024 consecutive bytes with eight e8m0
+// bytes and one fp32 amax, so a warp takes a super-group per step (two in flight): lanes 0-7 form the
+// eight block multipliers, every lane converts two 16-byte vectors and no index arithmetic is left.
+template <typename OutT, int FMT>
+__global__ void __launch_bounds__(256)
+dequantize_row128_kernel(const uint4* __restrict__ q, const uint8_t* __restrict__ sc8, const float* __restrict__ sc32,
+                         OutT* __restrict__ out, int64_t n_groups) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (int64_t)gridDim.x * 8;
+  int64_t g = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  for (; g + warps_total < n_groups; g += 2 * warps_total) {
+    const int64_t g2 = g + warps_total;
+    const uint4 a0 = __ldcs(q + g * 64 + lane), a1 = __ldcs(q + g * 64 + 32 + lane);
+    const uint4 b0 = __ldcs(q + g2 * 64 + lane), b1 = __ldcs(q + g2 * 64 + 32 + lane);
+    float sa = 0.0f, sb = 0.0f;
+    if (lane < 8) {
+      sa = __fmul_rn(e8m0_to_f32(__ldg(sc8 + g * 8 + lane)), __ldg(sc32 + g));
+      sb = __fmul_rn(e8m0_to_f32(__ldg(sc8 + g2 * 8 + lane)), __ldg(sc32 + g2));
+    }
+    // vector (it*32 + lane) holds elements of block it*4 + lane/8
+    dequantize16<OutT, FMT>(a0, __shfl_sync(0xffffffffu, sa, lane >> 3), out + (g * 64 + lane) * 16);
+    dequantize16<OutT, FMT>(a1, __shfl_sync(0xffffffffu, sa, 4 + (lane >> 3)), out + (g * 64 + 32 + lane) * 16);
+    dequantize16<OutT, FMT>(b0, __shfl_sync(0xffffffffu, sb, lane >> 3), out + (g2 * 64 + lane) * 16);
+    dequantize16<OutT, FMT>(b1, __shfl_sync(0xffffffffu, sb, 4 + (lane >> 3)), out + (g2 * 64 + 32 + lane) * 16);
+  }
+  if (g < n_groups) {
+    const uint4 a0 = __ldcs(q + g * 64 + lane), a1 = __ldcs(q + g * 64 + 32 + lane);
+    float sa = 0.0f;
+    if (lane < 8) sa = __fmul_rn(e8m0_to_f32(__ldg(sc8 + g * 8 + lane)), __ldg(sc32 + g));
+    dequantize16<OutT, FMT>(a0, __shfl_sync(0xffffffffu, sa, lane >> 3), out + (g * 64 + lane) * 16);
+    dequantize16<OutT, FMT>(a1, __shfl_sync(0xffffffffu, sa, 4 + (lane >> 3)), out + (g * 64 + 32 + lane) * 16);
+  }
+}
+
 int dq_grid(int64_t vecs) {
   const int64_t need = (vecs + 255) / 256;
   const int64_t cap = (int64_t)sm_count() * 8;
@@ -104,6 +138,13 @@ template <typename OutT, int FMT>
 int launch_dq(const uint8_t* q, const uint8_t* sc8, const float* sc32, OutT* out, const Geometry& g, int64_t batch, cudaStream_t st) {
   const int64_t total = batch * g.rows * g.cols;
   const bool vec16 = (g.b % 16 == 0) && (reinterpret_cast<uintptr_t>(q) % 16 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0);
+  if (vec16 && g.a == 1 && g.b == 128 && g.K == 8) {
+    const int64_t n_groups = batch * g.M;
+    const int64_t need = (n_groups + 7) / 8, cap = (int64_t)sm_count() * 16;
+    dequantize_row128_kernel<OutT, FMT><<<(int)(need < cap ? need : cap), 256, 0, st>>>((const uint4*)q, sc8, sc32, out, n_groups);
+    PB_LAUNCH_CHECK("dequantize_row128_kernel");
+    return PB_OK;
+  }
   const int vec = vec16 ? 16 : 1;
   if (total / vec > kMaxIndexed || batch * g.rows > kMaxIndexed)
     return fail(PB_ERR_UNSUPPORTED, "pb_dequantize: %lld elements exceed the 31-bit index range of this kernel", (long long)total);
