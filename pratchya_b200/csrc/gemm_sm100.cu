@@ -258,6 +258,7 @@ struct GemmParams {
   int a_fmt, b_fmt;
   int d_dtype;
   int diag;         // timing experiments in the profiling build of the pair kernel: 1 skips the loads of B, 2 those of A, 4 those of the scale factors
+  int splitk;       // pair kernel: 1, or 2 = each tile's chunks are shared by two work units that add into a zeroed f32 D
   int band;         // pair kernel: tile rows per band; a band's tiles are visited column by column before the next band
   int fb_uniform;   // B's fp32 factor is the same for all rows of B within a chunk
   int tma_store;    // D is written through shared memory and TMA stores (needs 16-byte aligned rows)
@@ -268,6 +269,12 @@ struct GemmParams {
 // TMA store of a [32 rows x 32 columns] box from shared memory, tracked by this thread's bulk group
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// the same box added to what global memory holds (f32 only)
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -283,7 +290,7 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 // lanes on distinct banks.  bf16 alternates between two 2 KB halves; f32 uses the whole 4 KB.
 template <int OFF>
 __device__ __forceinline__ void stage_and_store(const CUtensorMap* map, const float (&acc)[128], uint32_t stage, int lane,
-                                                int d_dtype, int col0, int row0, uint32_t& stores) {
+                                                int d_dtype, int col0, int row0, uint32_t& stores, bool add = false) {
   if (d_dtype == PB_BF16) {
     const uint32_t buf = stage + (stores++ & 1u) * 2048;     // halves alternate over the warp's whole run of stores
     if (lane == 0) tma_store_wait_read<1>();      // the store that last read this half has finished reading
@@ -307,7 +314,10 @@ __device__ __forceinline__ void stage_and_store(const CUtensorMap* map, const fl
                    __float_as_uint(acc[OFF + 4 * c + 2]), __float_as_uint(acc[OFF + 4 * c + 3]));
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
-    if (lane == 0) tma_store_2d(map, stage, col0 + OFF, row0);
+    if (lane == 0) {
+      if (add) tma_reduce_add_2d(map, stage, col0 + OFF, row0);
+      else tma_store_2d(map, stage, col0 + OFF, row0);
+    }
   }
 }
 
@@ -735,6 +745,18 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   const int num_tiles = p.tiles_m * p.tiles_n;          // 256 x 224 tiles
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  // Work units: a tile, or with p.splitk == 2 one half of a tile's chunks (units 2t and 2t+1 of tile t).
+  const int num_units = num_tiles * p.splitk;
+  auto unit_chunks = [&](int unit, int& tile, int& c_begin, int& c_end) {
+    if (p.splitk == 2) {
+      tile = unit >> 1;
+      const int half = (p.nchunks + 1) >> 1;
+      c_begin = (unit & 1) ? half : 0;
+      c_end = (unit & 1) ? p.nchunks : half;
+    } else {
+      tile = unit; c_begin = 0; c_end = p.nchunks;
+    }
+  };
   long long life_c0 = 0; unsigned long long life_n0 = 0;
   if (PROF && threadIdx.x == 96) { life_c0 = clock64(); asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(life_n0)); }
 
@@ -749,12 +771,13 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       bool ok = true;
       long long prod_wait = 0;
       const long long prod_begin = PROF ? clock64() : 0;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        int tm, tn;
+      for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters) {
+        int tile, c_begin, c_end, tm, tn;
+        unit_chunks(unit, tile, c_begin, c_end);
         tile_coords(p, tile, tm, tn);
         const int m0 = tm * 256 + (int)rank * 128;          // this CTA's rows of A and D
         const int nb0 = tn * BN + (int)rank * (BN / 2);     // this CTA's half of the tile's B rows
-        for (int c = 0; c < p.nchunks && ok; ++c) {
+        for (int c = c_begin; c < c_end && ok; ++c) {
           const int kb_end = min(p.KB, (c + 1) * p.P);
           for (int kb = c * p.P; kb < kb_end; kb += 2, ++it) {
             const int q = it % C::kSlots;
@@ -807,8 +830,10 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       long long wait_full = 0, wait_acc = 0;
       const long long t_begin = PROF ? clock64() : 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        for (int c = 0; c < nchunks && ok; ++c, ++g) {
+      for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters) {
+        int tile, c_begin, c_end;
+        unit_chunks(unit, tile, c_begin, c_end);
+        for (int c = c_begin; c < c_end && ok; ++c, ++g) {
           const int buf = g % C::kAccBufs;
           long long t0 = PROF ? clock64() : 0;
           if (!mbar_wait(bar_acc_empty(buf), ((g / C::kAccBufs) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
@@ -872,12 +897,14 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int row_in_tile = quarter * 32 + lane;
     uint32_t g = 0, stores = 0;
     bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-      int tm, tn;
+    const bool add = p.splitk == 2;
+    for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters) {
+      int tile, c_begin, c_end, tm, tn;
+      unit_chunks(unit, tile, c_begin, c_end);
       tile_coords(p, tile, tm, tn);
       const int m0 = tm * 256 + (int)rank * 128, n0 = tn * BN + col_half * 128;
       float acc[128];
-      for (int c = 0; c < p.nchunks; ++c, ++g) {
+      for (int c = c_begin; c < c_end; ++c, ++g) {
         const int buf = g % C::kAccBufs;
         const float fa = __ldg(p.fa + (size_t)c * p.Mpad + m0 + row_in_tile);
         const float* fbp = p.fb + (size_t)c * p.Npad + n0;
@@ -892,7 +919,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         };
         if (p.profile == 3) { release(); continue; }     // diagnostic knobs, see the single-CTA kernel
-        if (c == 0) {
+        if (c == c_begin) {
           tc_ld32f<0>(t_addr, acc); tc_ld32f<32>(t_addr + 32, acc); tc_ld32f<64>(t_addr + 64, acc);
           if (four_parts) tc_ld32f<96>(t_addr + 96, acc);
           tc_wait_ld();
@@ -928,10 +955,10 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (p.tma_store) {
         const uint32_t stage = s_base + C::kOffStore + ew * 4096;
         const int row0 = m0 + quarter * 32;
-        stage_and_store<0>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores);
-        stage_and_store<32>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores);
-        stage_and_store<64>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores);
-        if (four_parts) stage_and_store<96>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores);
+        stage_and_store<0>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores, add);
+        stage_and_store<32>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores, add);
+        stage_and_store<64>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores, add);
+        if (four_parts) stage_and_store<96>(&map_d, acc, stage, lane, p.d_dtype, n0, row0, stores, add);
       } else {
         store_row_segment(p, acc, m0 + row_in_tile, n0, ncols);
       }
@@ -1218,7 +1245,7 @@ int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
       configured[dev] = true;
     }
   }
-  const int tiles = p.tiles_m * p.tiles_n;
+  const int tiles = p.tiles_m * p.tiles_n * p.splitk;
   const int pairs = sm_count() / 2;
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
   gemm_tn_pair_kernel<PROF><<<grid, Cfg2::kThreads, Cfg2::kSmemBytes, st>>>(ma, mb, msfa, msfb, md, p);
@@ -1312,6 +1339,7 @@ extern "C" int pb_gemm_tn_ex(const pb_operand* a, const pb_operand* b, void* d, 
     p.band = band;
   }
   p.tma_store = 0;
+  p.splitk = 1;
   p.profile = profile_level();
   p.diag = [] { const char* e = getenv("PB_GEMM_DIAG"); return e ? atoi(e) : 0; }();
   // D goes out through TMA stores when its rows are 16-byte aligned; otherwise by direct stores
@@ -1322,6 +1350,19 @@ extern "C" int pb_gemm_tn_ex(const pb_operand* a, const pb_operand* b, void* d, 
     if (int s = make_store_map(&md, d, d_dtype, a->rows, b->rows, ldd)) return s;
   }
   if (gp.pair) {
+    // Few tiles for the 74 CTA pairs (a 2048 x 2048 weight gradient is 80): give each tile's chunks to
+    // two work units that add their halves into D.  Needs f32 output through TMA (the reduction is
+    // an f32 TMA add into zeros, so the two orders give the same bits) and at least two chunks a half.
+    static const int split_env = [] { const char* e = getenv("PB_GEMM_SPLITK"); return e ? atoi(e) : 0; }();
+    const int pairs = sm_count() / 2, tiles = p.tiles_m * p.tiles_n;
+    auto efficiency = [&](int units) { return (double)units / (double)(((units + pairs - 1) / pairs) * pairs); };
+    bool split = d_dtype == PB_F32 && p.tma_store && gp.nchunks >= 4 && efficiency(tiles) < 0.8 && efficiency(2 * tiles) > efficiency(tiles) + 0.1;
+    if (split_env == 1) split = false;
+    if (split_env == 2) split = d_dtype == PB_F32 && p.tma_store && gp.nchunks >= 2;
+    if (split) {
+      p.splitk = 2;
+      PB_CUDA_TRY(cudaMemset2DAsync(d, (size_t)ldd * 4, 0, (size_t)b->rows * 4, (size_t)a->rows, st));
+    }
     CUtensorMap msfa, msfb;
     if (int s = make_sf_map(&msfa, ws + gp.off_sfa, (int64_t)gp.KG * gp.tiles_m, 1)) return s;
     if (int s = make_sf_map(&msfb, ws + gp.off_sfb, (int64_t)gp.KG * gp.tiles_n * 2, 2)) return s;

@@ -125,3 +125,26 @@ def test_transposed_quantizer_bit_exact(built_lib):
         want = oracle.quantize_impl(np.ascontiguousarray(x.T), (1, 128))
         assert np.array_equal(bytes_of(got[0]), bytes_of(want[0])), shape
         assert np.array_equal(bytes_of(got[1]), want[1]) and np.array_equal(from_torch(got[2]), want[2])
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 512, 4096), (2048, 2048, 8192), (300, 700, 5120)])
+def test_few_tiles_split_over_k(built_lib, m, n, k):
+    """f32 outputs with few tiles and a long K run as two half-K work units per tile that add into a
+    zeroed D: same tolerance against the oracle, bit-identical from run to run, and equal within
+    rounding of the output type to the bf16 result (which is never split)."""
+    if n % 128:
+        n = (n // 128 + 1) * 128
+    x = synth((m, k), seed=m + k, outliers=0.01)
+    w = synth((k, n), seed=n, scale=0.02, outliers=0)
+    xq, wq = gpu_triple(x, (1, 128)), gpu_triple(w, (128, 128))
+    if oracle.group_geometry(m, k, (1, 128))[1] != 8:
+        pytest.skip("activation super-group is not 8 blocks")
+    got = matmul_impl(*xq, *wq, (1, 128), (128, 128))
+    again = matmul_impl(*xq, *wq, (1, 128), (128, 128))
+    _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+    assert torch.equal(got, again)
+    ref = oracle.matmul_impl(*np_triple(xq), *np_triple(wq), (1, 128), (128, 128), acc=np.float64)
+    check_close(got.cpu().numpy(), ref, f"split {m}x{n}x{k}")
+    as_bf16 = matmul_impl(*xq, *wq, (1, 128), (128, 128), out_dtype=torch.bfloat16)
+    scale = float(np.abs(ref).max())
+    assert (got - as_bf16.float()).abs().max().item() <= 2.0 ** -7 * scale
