@@ -8,6 +8,8 @@
 //   3. tile transpose through shared memory, dividing on the way, coalesced byte rows out.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace pb {
 
 // defined in quantize.cu
@@ -189,6 +191,97 @@ transpose_apply128_kernel(const InT* __restrict__ x, const float* __restrict__ d
                ::"l"(o), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7]) : "memory");
 }
 
+// Single pass for b = 128 when rows % 1024 == 0: then a super-group of x^T (eight blocks of 128) is
+// 1024 consecutive rows of one column of x, so a CTA that holds a 1024-row x kCols-column tile of x
+// in shared memory (64 KB) has everything its part of the output needs: x is read once and nothing
+// goes through scratch.  Thread (column c, block blk): amax of its 128 rows, the column's amax over the
+// eight blocks, the block's scale, then its 128 output bytes as four 32-byte stores along x^T's row.
+template <typename InT> struct OnePass {
+  static constexpr int kCols = 64 / (int)sizeof(InT);        // 32 (bf16) or 16 (f32): 64-byte row segments
+  static constexpr int kThreads = kCols * 8;
+  static constexpr int kSmem = 1024 * 64;
+};
+
+template <typename InT, int FMT>
+__global__ void __launch_bounds__(OnePass<InT>::kThreads)
+transpose_quantize1024_kernel(const InT* __restrict__ x, uint8_t* __restrict__ q_t, uint8_t* __restrict__ sc8,
+                              float* __restrict__ sc32, int rows, int cols) {
+  constexpr int kCols = OnePass<InT>::kCols, kThreads = OnePass<InT>::kThreads;
+  extern __shared__ __align__(16) uint8_t tile_raw[];
+  InT* tile = reinterpret_cast<InT*>(tile_raw);                // [1024][kCols]
+  __shared__ float col_amax[8][kCols];
+  const int c0 = blockIdx.x * kCols, r0 = blockIdx.y * 1024;
+  const InT* src = x + ((size_t)blockIdx.z * rows + r0) * cols + c0;
+  // load: 4 threads per 64-byte row segment
+  // sixteen loads in flight per thread before the first one is stored
+#pragma unroll 1
+  for (int base = 0; base < 1024 * 4; base += 16 * kThreads) {
+    uint4 w[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int v = base + k * kThreads + threadIdx.x, r = v >> 2, part = v & 3;
+      w[k] = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(src + (size_t)r * cols) + part * 16));
+    }
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int v = base + k * kThreads + threadIdx.x;
+      *reinterpret_cast<uint4*>(tile_raw + (v >> 2) * 64 + (v & 3) * 16) = w[k];
+    }
+  }
+  __syncthreads();
+  const int c = threadIdx.x % kCols, blk = threadIdx.x / kCols;
+  const InT* colp = tile + (blk * 128) * kCols + c;
+  float m = 0.0f;
+#pragma unroll 16
+  for (int i = 0; i < 128; ++i) m = fmaxf(m, fabsf(Elem<InT>::to_f32(colp[i * kCols])));
+  col_amax[blk][c] = m;
+  __syncthreads();
+  float Mj = col_amax[0][c];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) Mj = fmaxf(Mj, col_amax[k][c]);
+  uint32_t sb; float D;
+  block_scale(m, Mj, sb, D);
+  const int nsg = rows >> 10;                                  // super-groups per column of x
+  const size_t grp = ((size_t)blockIdx.z * cols + c0 + c) * nsg + blockIdx.y;
+  sc8[grp * 8 + blk] = (uint8_t)sb;
+  if (blk == 0) sc32[grp] = Mj;
+  const float rcp = __frcp_rn(D);
+  const float2 nD2 = make_float2(-D, -D), r2 = make_float2(rcp, rcp);
+  uint8_t* o = q_t + ((size_t)blockIdx.z * cols + c0 + c) * rows + r0 + blk * 128;
+#pragma unroll
+  for (int seg = 0; seg < 4; ++seg) {
+    uint32_t out[8];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = Elem<InT>::to_f32(colp[(seg * 32 + w * 4 + j) * kCols]);
+      out[w] = bf16x2_to_fp8x2<FMT>(div_hoisted_pack2(v[0], v[1], nD2, r2)) | (bf16x2_to_fp8x2<FMT>(div_hoisted_pack2(v[2], v[3], nD2, r2)) << 16);
+    }
+    asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(o + seg * 32), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7]) : "memory");
+  }
+}
+
+template <typename InT, int FMT>
+int launch_one_pass(const void* x, uint8_t* q_t, uint8_t* sc8, float* sc32, int64_t batch, int64_t rows, int64_t cols, cudaStream_t st) {
+  static std::mutex mu;
+  static bool configured[64] = {false};
+  int dev = 0;
+  PB_CUDA_TRY(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      PB_CUDA_TRY(cudaFuncSetAttribute(transpose_quantize1024_kernel<InT, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, OnePass<InT>::kSmem));
+      configured[dev] = true;
+    }
+  }
+  const dim3 grid((unsigned)(cols / OnePass<InT>::kCols), (unsigned)(rows / 1024), (unsigned)batch);
+  transpose_quantize1024_kernel<InT, FMT><<<grid, OnePass<InT>::kThreads, OnePass<InT>::kSmem, st>>>((const InT*)x, q_t, sc8, sc32, (int)rows, (int)cols);
+  PB_LAUNCH_CHECK("transpose_quantize1024_kernel");
+  return PB_OK;
+}
+
 __global__ void __launch_bounds__(256)
 transpose_bytes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int rows, int cols) {
   __shared__ uint8_t tile[kTile][kTile + 4];
@@ -226,12 +319,25 @@ extern "C" int pb_quantize_transposed(const void* x, int x_dtype, int64_t batch,
   if (int s = make_geometry(cols, rows, 1, b, &g)) return s;
   if (rows > kMaxIndexed || cols > kMaxIndexed || batch > 65535 || rows / b > 65535 || (rows + kTile - 1) / kTile > 65535)
     return fail(PB_ERR_UNSUPPORTED, "pb_quantize_transposed: shape [%lld, %lld, %lld] exceeds the launch limits", (long long)batch, (long long)rows, (long long)cols);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  {   // one read of x, no scratch: whole super-groups of x^T inside 1024-row tiles
+    const int esz = x_dtype == PB_BF16 ? 2 : 4;
+    const int tile_cols = 64 / esz;
+    if (b == 128 && rows % 1024 == 0 && cols % tile_cols == 0 && g.K == 8 && rows / 1024 <= 65535 &&
+        (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (cols * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(q_t) & 31) == 0) {
+      uint8_t* o = static_cast<uint8_t*>(q_t);
+      if (x_dtype == PB_BF16)
+        return out_format == PB_E4M3 ? launch_one_pass<__nv_bfloat16, PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
+                                     : launch_one_pass<__nv_bfloat16, PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
+      return out_format == PB_E4M3 ? launch_one_pass<float, PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
+                                   : launch_one_pass<float, PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
+    }
+  }
   const size_t need = (size_t)(batch * g.Nb) * 8;
   if (!workspace || workspace_bytes < need)
     return fail(PB_ERR_WORKSPACE_TOO_SMALL, "pb_quantize_transposed: needs %zu bytes of workspace, got %zu", need, workspace_bytes);
   if (reinterpret_cast<uintptr_t>(workspace) & 3) return fail(PB_ERR_MISALIGNED, "pb_quantize_transposed: workspace must be 4-byte aligned");
   if (reinterpret_cast<uintptr_t>(x) & 7) return fail(PB_ERR_MISALIGNED, "pb_quantize_transposed: x must be 8-byte aligned");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint32_t* amax_bits = static_cast<uint32_t*>(workspace);
   float* divisor = reinterpret_cast<float*>(amax_bits + batch * g.Nb);
 
