@@ -263,6 +263,112 @@ transpose_quantize1024_kernel(const InT* __restrict__ x, uint8_t* __restrict__ q
   }
 }
 
+// bf16 version of the single pass: 512 threads, thread (column pair, block, quarter) keeps its 32 rows x
+// 2 columns (32 words) in registers between the amax and the quantization, works on packed bf16 pairs
+// like the row quantizer (a byte permute regroups two rows of a column pair into one pair per
+// column), and writes one 32-byte store per column.  Rows of odd blocks are stored with their
+// 64-byte halves swapped in pairs (row ^ 1 ... as a bank-half swizzle), so that the two rows a warp
+// reads at once, 128 rows apart, fall into different halves of the banks.
+template <int FMT>
+__global__ void __launch_bounds__(512, 2)
+transpose_quantize1024_bf16_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q_t, uint8_t* __restrict__ sc8,
+                                   float* __restrict__ sc32, int rows, int cols) {
+  extern __shared__ __align__(16) uint8_t tile_raw[];              // [1024 rows][64 bytes]
+  __shared__ uint32_t part_amax[32][16];                            // [block*4 + quarter][column pair], bf16 pairs
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 1024;
+  const __nv_bfloat16* src = x + ((size_t)blockIdx.z * rows + r0) * cols + c0;
+  auto row_offset = [](int r) { return (uint32_t)(r * 64) ^ (uint32_t)(((r >> 7) & 1) << 6); };
+  {
+    uint4 w[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int v = k * 512 + threadIdx.x, r = v >> 2, part = v & 3;
+      w[k] = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(src + (size_t)r * cols) + part * 16));
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int v = k * 512 + threadIdx.x;
+      *reinterpret_cast<uint4*>(tile_raw + row_offset(v >> 2) + (v & 3) * 16) = w[k];
+    }
+  }
+  __syncthreads();
+  const int cp = threadIdx.x & 15, blk = (threadIdx.x >> 4) & 7, quarter = threadIdx.x >> 7;
+  const int row_first = blk * 128 + quarter * 32;
+  uint32_t w[32];
+  uint32_t cm = 0u;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    w[i] = *reinterpret_cast<const uint32_t*>(tile_raw + row_offset(row_first + i) + cp * 4);
+    const uint32_t a = w[i] & 0x7fff7fffu;
+    const __nv_bfloat162 h = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&cm), *reinterpret_cast<const __nv_bfloat162*>(&a));
+    cm = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  part_amax[blk * 4 + quarter][cp] = cm;
+  __syncthreads();
+  uint32_t mb = 0u, mg = 0u;           // block amax and super-group amax of the two columns, packed
+#pragma unroll
+  for (int k = 0; k < 32; ++k) {
+    const uint32_t v = part_amax[k][cp];
+    const __nv_bfloat162 g = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&mg), *reinterpret_cast<const __nv_bfloat162*>(&v));
+    mg = *reinterpret_cast<const uint32_t*>(&g);
+    if ((k >> 2) == blk) {
+      const __nv_bfloat162 b2 = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&mb), *reinterpret_cast<const __nv_bfloat162*>(&v));
+      mb = *reinterpret_cast<const uint32_t*>(&b2);
+    }
+  }
+  const int nsg = rows >> 10;
+  uint32_t sbv[2]; float D[2];
+  block_scale(__uint_as_float(mb << 16), __uint_as_float(mg << 16), sbv[0], D[0]);
+  block_scale(__uint_as_float(mb & 0xffff0000u), __uint_as_float(mg & 0xffff0000u), sbv[1], D[1]);
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const size_t col = (size_t)blockIdx.z * cols + c0 + 2 * cp + j;
+    const size_t grp = col * nsg + blockIdx.y;
+    if (quarter == 0) {
+      sc8[grp * 8 + blk] = (uint8_t)sbv[j];
+      if (blk == 0) sc32[grp] = j == 0 ? __uint_as_float(mg << 16) : __uint_as_float(mg & 0xffff0000u);
+    }
+    const float rcp = __frcp_rn(D[j]);
+    const float2 nD2 = make_float2(-D[j], -D[j]), r2 = make_float2(rcp, rcp);
+    uint32_t out[8];
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      uint32_t o2[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        // rows i+2h and i+2h+1 of column j as one packed bf16 pair
+        const uint32_t pr = __byte_perm(w[i + 2 * h], w[i + 2 * h + 1], j == 0 ? 0x5410 : 0x7632);
+        const float2 v = div_hoisted_unsigned2(make_float2(__uint_as_float(pr << 16), __uint_as_float(pr & 0xffff0000u)), nD2, r2);
+        const uint32_t pk = (pack_bf16x2(v.x, v.y) & 0x7fff7fffu) | (pr & 0x80008000u);
+        o2[h] = bf16x2_to_fp8x2<FMT>(pk);
+      }
+      out[i >> 2] = o2[0] | (o2[1] << 16);
+    }
+    uint8_t* o = q_t + col * rows + r0 + row_first;
+    asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(o), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7]) : "memory");
+  }
+}
+
+template <int FMT>
+int launch_one_pass_bf16(const void* x, uint8_t* q_t, uint8_t* sc8, float* sc32, int64_t batch, int64_t rows, int64_t cols, cudaStream_t st) {
+  static std::mutex mu;
+  static bool configured[64] = {false};
+  int dev = 0;
+  PB_CUDA_TRY(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      PB_CUDA_TRY(cudaFuncSetAttribute(transpose_quantize1024_bf16_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 * 64));
+      configured[dev] = true;
+    }
+  }
+  const dim3 grid((unsigned)(cols / 32), (unsigned)(rows / 1024), (unsigned)batch);
+  transpose_quantize1024_bf16_kernel<FMT><<<grid, 512, 1024 * 64, st>>>((const __nv_bfloat16*)x, q_t, sc8, sc32, (int)rows, (int)cols);
+  PB_LAUNCH_CHECK("transpose_quantize1024_bf16_kernel");
+  return PB_OK;
+}
+
 template <typename InT, int FMT>
 int launch_one_pass(const void* x, uint8_t* q_t, uint8_t* sc8, float* sc32, int64_t batch, int64_t rows, int64_t cols, cudaStream_t st) {
   static std::mutex mu;
@@ -327,8 +433,8 @@ extern "C" int pb_quantize_transposed(const void* x, int x_dtype, int64_t batch,
         (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (cols * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(q_t) & 31) == 0) {
       uint8_t* o = static_cast<uint8_t*>(q_t);
       if (x_dtype == PB_BF16)
-        return out_format == PB_E4M3 ? launch_one_pass<__nv_bfloat16, PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
-                                     : launch_one_pass<__nv_bfloat16, PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
+        return out_format == PB_E4M3 ? launch_one_pass_bf16<PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
+                                     : launch_one_pass_bf16<PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
       return out_format == PB_E4M3 ? launch_one_pass<float, PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
                                    : launch_one_pass<float, PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
     }
@@ -394,6 +500,12 @@ extern "C" int pb_quantize_dual(const void* x, int x_dtype, int64_t batch, int64
   if (x_dtype != PB_BF16 || cols % 1024 != 0 || rows % 128 != 0 || gr.K != 8 || batch > 65535 || rows / 128 > 65535 ||
       rows > kMaxIndexed || cols > kMaxIndexed)
     return fail(PB_ERR_UNSUPPORTED, "pb_quantize_dual: needs bf16 x with rows %% 128 == 0 and cols %% 1024 == 0; use pb_quantize and pb_quantize_transposed");
+  if (rows % 1024 == 0 && gt.K == 8) {
+    // whole super-groups of x^T inside 1024-row tiles: the transposed side is a single pass of its own
+    // (measured a little faster than sharing the row quantizer's pass), and the row side is the plain row quantizer
+    if (int s = pb_quantize(x, x_dtype, batch, rows, cols, 1, 128, out_format, q, sc8, sc32, nullptr, 0, stream)) return s;
+    return pb_quantize_transposed(x, x_dtype, batch, rows, cols, 128, out_format, q_t, sc8_t, sc32_t, workspace, workspace_bytes, stream);
+  }
   const size_t need = (size_t)(batch * gt.Nb) * 8;
   if (!workspace || workspace_bytes < need)
     return fail(PB_ERR_WORKSPACE_TOO_SMALL, "pb_quantize_dual: needs %zu bytes of workspace, got %zu", need, workspace_bytes);
