@@ -909,6 +909,9 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const float fa = __ldg(p.fa + (size_t)c * p.Mpad + m0 + row_in_tile);
         const float* fbp = p.fb + (size_t)c * p.Npad + n0;
         const float s_uni = fa * __ldg(fbp);
+        // per-column factors of this chunk: new lines every chunk, so ask for them now; the chunk's MMAs
+        // are still running and an L2 round trip per 32 columns would otherwise sit inside the drain
+        if (!p.fb_uniform && lane * 32 < ncols) asm volatile("prefetch.global.L1 [%0];" ::"l"(fbp + lane * 32));
         if (!mbar_wait(bar_acc_full(buf), (g / C::kAccBufs) & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + col_half * 128;
