@@ -109,6 +109,18 @@ PB_API int pb_dequantize_bwd(const void* g, int dtype, const uint8_t* sc8, const
                       int64_t batch, int64_t rows, int64_t cols, int a, int b,
                       void* out, void* stream);
 
+/* out = op(dq(x), dq(y)) in f32 for two quantized arrays of the same shape on the same grid: the
+ * forward of make_elementwise_impl (pratchya/_qualia/_qarr.py:715-720; add_impl, sub_impl, mul_impl,
+ * truediv_impl :757-760) in one pass instead of two dequantizations and an op.  IEEE f32 arithmetic,
+ * so the bits are those of the three steps.  floordiv, mod and pow (:761-763) are not offered here. */
+#define PB_OP_ADD 0
+#define PB_OP_SUB 1
+#define PB_OP_MUL 2
+#define PB_OP_DIV 3
+PB_API int pb_elementwise(int op, const void* xq, int x_format, const uint8_t* x_sc8, const float* x_sc32,
+                   const void* yq, int y_format, const uint8_t* y_sc8, const float* y_sc32,
+                   int64_t batch, int64_t rows, int64_t cols, int a, int b, float* out, void* stream);
+
 /* ---- block-scaled FP8 matmul.
  * A GEMM operand is a K-major quantized matrix: bytes [rows, depth] (depth = the
  * contraction length, contiguous), one e8m0 byte per (row-block, 128-deep block)

@@ -376,9 +376,28 @@ def rmatmul_mixed_impl(x_f32, y_fp8, y_sc8, y_sc32, block_grid_y):
     return _matmul_f32(x_f32.to(torch.float32), y)
 
 
+_FUSED_OPS = {torch.add: 0, torch.sub: 1, torch.mul: 2, torch.div: 3}
+
+
 def make_elementwise_impl(op):
-    """_qarr.py:715-720: dequantize both operands on the same grid, apply `op`, f32 out."""
+    """_qarr.py:715-720: dequantize both operands on the same grid, apply `op`, f32 out.
+    add, sub, mul and div of same-shape operands run as one kernel (pb_elementwise, same bits);
+    floor_divide, remainder and pow, and broadcasting operands, take the literal three steps."""
     def impl(x_fp8, x_sc8, x_sc32, y_fp8, y_sc8, y_sc32, tgrid):
+        code = _FUSED_OPS.get(op)
+        if (code is not None and tuple(x_fp8.shape) == tuple(y_fp8.shape) and x_fp8.numel() > 0
+                and tuple(x_sc8.shape) == tuple(y_sc8.shape) and x_fp8.dtype in _DTYPE_FMT and y_fp8.dtype in _DTYPE_FMT):
+            _require_cuda(x_fp8, "elementwise input")
+            lib = _lib.load()
+            shape = _as_2d(tuple(x_fp8.shape))
+            a, b = int(tgrid[0]), int(tgrid[1])
+            xs = [t.contiguous() for t in (x_fp8, x_sc8, x_sc32, y_fp8, y_sc8, y_sc32)]
+            with torch.cuda.device(x_fp8.device):
+                out = torch.empty(tuple(x_fp8.shape), dtype=torch.float32, device=x_fp8.device)
+                check(lib.pb_elementwise(code, xs[0].data_ptr(), _DTYPE_FMT[x_fp8.dtype], xs[1].data_ptr(), xs[2].data_ptr(),
+                                         xs[3].data_ptr(), _DTYPE_FMT[y_fp8.dtype], xs[4].data_ptr(), xs[5].data_ptr(),
+                                         math.prod(shape[:-2]), shape[-2], shape[-1], a, b, out.data_ptr(), _stream(x_fp8)))
+            return out
         x = dequantize_impl(x_fp8, x_sc8, x_sc32, torch.float32, tgrid)
         y = dequantize_impl(y_fp8, y_sc8, y_sc32, torch.float32, tgrid)
         return op(x, y)

@@ -128,6 +128,47 @@ dequantize_row128_kernel(const uint4* __restrict__ q, const uint8_t* __restrict_
   }
 }
 
+// Both operands of an elementwise op dequantized and combined in one pass (same shape, same grid):
+// out = op(dq(x), dq(y)) in f32, the forward of make_elementwise_impl (_qarr.py:715-720).
+enum { kOpAdd = 0, kOpSub = 1, kOpMul = 2, kOpDiv = 3 };
+
+template <int OP> __device__ __forceinline__ float combine(float a, float b) {
+  if (OP == kOpAdd) return __fadd_rn(a, b);
+  if (OP == kOpSub) return __fsub_rn(a, b);
+  if (OP == kOpMul) return __fmul_rn(a, b);
+  return __fdiv_rn(a, b);
+}
+
+template <int OP, int FX, int FY, int VEC>
+__global__ void __launch_bounds__(256)
+elementwise_kernel(const uint8_t* __restrict__ xq, const uint8_t* __restrict__ xs8, const float* __restrict__ xs32,
+                   const uint8_t* __restrict__ yq, const uint8_t* __restrict__ ys8, const float* __restrict__ ys32,
+                   float* __restrict__ out, DqDims d) {
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < d.total_vecs; i += stride) {
+    const float sx = block_multiplier(d, xs8, xs32, i), sy = block_multiplier(d, ys8, ys32, i);
+    if constexpr (VEC == 16) {
+      const uint4 wx = __ldcs(reinterpret_cast<const uint4*>(xq) + i), wy = __ldcs(reinterpret_cast<const uint4*>(yq) + i);
+      const uint32_t ax[4] = {wx.x, wx.y, wx.z, wx.w}, ay[4] = {wy.x, wy.y, wy.z, wy.w};
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 xl = fp8x2_to_f32x2<FX>((uint16_t)(ax[j] & 0xffffu)), xh = fp8x2_to_f32x2<FX>((uint16_t)(ax[j] >> 16));
+        const float2 yl = fp8x2_to_f32x2<FY>((uint16_t)(ay[j] & 0xffffu)), yh = fp8x2_to_f32x2<FY>((uint16_t)(ay[j] >> 16));
+        v[4 * j + 0] = combine<OP>(apply_scale(xl.x, sx), apply_scale(yl.x, sy));
+        v[4 * j + 1] = combine<OP>(apply_scale(xl.y, sx), apply_scale(yl.y, sy));
+        v[4 * j + 2] = combine<OP>(apply_scale(xh.x, sx), apply_scale(yh.x, sy));
+        v[4 * j + 3] = combine<OP>(apply_scale(xh.y, sx), apply_scale(yh.y, sy));
+      }
+      store16<float>(out + (size_t)i * 16, v);
+    } else {
+      const float a = apply_scale(fp8x2_to_f32x2<FX>((uint16_t)xq[i]).x, sx);
+      const float b = apply_scale(fp8x2_to_f32x2<FY>((uint16_t)yq[i]).x, sy);
+      out[i] = combine<OP>(a, b);
+    }
+  }
+}
+
 int dq_grid(int64_t vecs) {
   const int64_t need = (vecs + 255) / 256;
   const int64_t cap = (int64_t)sm_count() * 8;
@@ -155,10 +196,55 @@ int launch_dq(const uint8_t* q, const uint8_t* sc8, const float* sc32, OutT* out
   return PB_OK;
 }
 
+template <int OP, int FX, int FY>
+int launch_elementwise(const uint8_t* xq, const uint8_t* xs8, const float* xs32, const uint8_t* yq, const uint8_t* ys8, const float* ys32,
+                       float* out, const Geometry& g, int64_t batch, cudaStream_t st) {
+  const int64_t total = batch * g.rows * g.cols;
+  const bool vec16 = (g.b % 16 == 0) && ((reinterpret_cast<uintptr_t>(xq) | reinterpret_cast<uintptr_t>(yq) | reinterpret_cast<uintptr_t>(out)) % 16 == 0);
+  const int vec = vec16 ? 16 : 1;
+  if (total / vec > kMaxIndexed || batch * g.rows > kMaxIndexed)
+    return fail(PB_ERR_UNSUPPORTED, "pb_elementwise: %lld elements exceed the 31-bit index range of this kernel", (long long)total);
+  DqDims d{VecIndexer(g.cols, g.a, g.b, vec), FastDiv((uint32_t)g.K), (uint32_t)(total / vec)};
+  if (vec16) elementwise_kernel<OP, FX, FY, 16><<<dq_grid(d.total_vecs), 256, 0, st>>>(xq, xs8, xs32, yq, ys8, ys32, out, d);
+  else       elementwise_kernel<OP, FX, FY, 1><<<dq_grid(d.total_vecs), 256, 0, st>>>(xq, xs8, xs32, yq, ys8, ys32, out, d);
+  PB_LAUNCH_CHECK("elementwise_kernel");
+  return PB_OK;
+}
+
+template <int OP>
+int launch_elementwise_fmt(int fx, int fy, const uint8_t* xq, const uint8_t* xs8, const float* xs32, const uint8_t* yq, const uint8_t* ys8,
+                           const float* ys32, float* out, const Geometry& g, int64_t batch, cudaStream_t st) {
+  if (fx == PB_E4M3 && fy == PB_E4M3) return launch_elementwise<OP, PB_E4M3, PB_E4M3>(xq, xs8, xs32, yq, ys8, ys32, out, g, batch, st);
+  if (fx == PB_E4M3) return launch_elementwise<OP, PB_E4M3, PB_E5M2>(xq, xs8, xs32, yq, ys8, ys32, out, g, batch, st);
+  if (fy == PB_E4M3) return launch_elementwise<OP, PB_E5M2, PB_E4M3>(xq, xs8, xs32, yq, ys8, ys32, out, g, batch, st);
+  return launch_elementwise<OP, PB_E5M2, PB_E5M2>(xq, xs8, xs32, yq, ys8, ys32, out, g, batch, st);
+}
+
 }  // namespace
 }  // namespace pb
 
 using namespace pb;
+
+extern "C" int pb_elementwise(int op, const void* xq, int x_format, const uint8_t* xs8, const float* xs32,
+                              const void* yq, int y_format, const uint8_t* ys8, const float* ys32,
+                              int64_t batch, int64_t rows, int64_t cols, int a, int b, float* out, void* stream) {
+  if (!xq || !xs8 || !xs32 || !yq || !ys8 || !ys32 || !out) return fail(PB_ERR_NULL_POINTER, "pb_elementwise: operands and out must be non-null");
+  if (batch <= 0) return fail(PB_ERR_BAD_SHAPE, "pb_elementwise: batch=%lld must be positive", (long long)batch);
+  if ((x_format != PB_E4M3 && x_format != PB_E5M2) || (y_format != PB_E4M3 && y_format != PB_E5M2))
+    return fail(PB_ERR_BAD_DTYPE, "pb_elementwise: formats %d, %d", x_format, y_format);
+  Geometry g;
+  if (int s = make_geometry(rows, cols, a, b, &g)) return s;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint8_t* x8 = static_cast<const uint8_t*>(xq);
+  const uint8_t* y8 = static_cast<const uint8_t*>(yq);
+  switch (op) {
+    case PB_OP_ADD: return launch_elementwise_fmt<kOpAdd>(x_format, y_format, x8, xs8, xs32, y8, ys8, ys32, out, g, batch, st);
+    case PB_OP_SUB: return launch_elementwise_fmt<kOpSub>(x_format, y_format, x8, xs8, xs32, y8, ys8, ys32, out, g, batch, st);
+    case PB_OP_MUL: return launch_elementwise_fmt<kOpMul>(x_format, y_format, x8, xs8, xs32, y8, ys8, ys32, out, g, batch, st);
+    case PB_OP_DIV: return launch_elementwise_fmt<kOpDiv>(x_format, y_format, x8, xs8, xs32, y8, ys8, ys32, out, g, batch, st);
+    default: return fail(PB_ERR_UNSUPPORTED, "pb_elementwise: op %d (add, sub, mul and div only; floor_divide, mod and pow go through pb_dequantize)", op);
+  }
+}
 
 extern "C" int pb_dequantize(const void* q, int q_format, const uint8_t* sc8, const float* sc32,
                              int64_t batch, int64_t rows, int64_t cols, int a, int b,

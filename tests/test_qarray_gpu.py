@@ -180,3 +180,23 @@ def test_linear_layers(built_lib):
     out = ffn(to_torch(synth((8, 256), 18)))
     assert out.shape == (8, 256) and torch.isfinite(out).all()
     assert ffn.down.kernel.tgrid == (16, 1) and ffn.up.kernel.tgrid == (16, 1)
+
+
+@pytest.mark.parametrize("grid,shape", [((1, 128), (64, 1024)), ((128, 128), (256, 384)), ((16, 16), (48, 80)), ((1, 16), (3, 8, 64)),
+                                        ((4, 4), (12, 20))])
+def test_fused_elementwise_has_the_bits_of_the_three_steps(built_lib, grid, shape):
+    """add / sub / mul / div of two quantized arrays in one kernel against dequantize, dequantize, op."""
+    from helpers import synth, to_torch
+    from pratchya_b200._qualia import _ops, dequantize_impl, quantize_impl
+    x = synth(shape, seed=1, outliers=0.02)
+    y = synth(shape, seed=2, outliers=0.02)
+    y.reshape(-1)[:7] = 0.0                     # division by zero and 0/0
+    x.reshape(-1)[:3] = 0.0
+    xq, yq = quantize_impl(to_torch(x), grid), quantize_impl(to_torch(y), grid)
+    xd, yd = dequantize_impl(*xq, torch.float32, grid), dequantize_impl(*yq, torch.float32, grid)
+    for impl, op in ((_ops.add_impl, torch.add), (_ops.sub_impl, torch.sub), (_ops.mul_impl, torch.mul), (_ops.truediv_impl, torch.div)):
+        got = impl(*xq, *yq, grid)
+        want = op(xd, yd)
+        assert got.shape == want.shape and got.dtype == torch.float32
+        same = (got.view(torch.int32) == want.view(torch.int32)) | (torch.isnan(got) & torch.isnan(want))
+        assert bool(same.all()), f"{op.__name__} on grid {grid}: {(~same).sum().item()} elements differ"
