@@ -46,3 +46,31 @@ def test_argument_errors_are_reported_without_a_device(built_lib):
     assert built_lib.pb_dequantize(None, 0, None, None, 1, 8, 8, 1, 8, 0, None, None) == 1
     assert built_lib.pb_quantize_workspace_size(1, 2048, 2048, 1, 128) == 0
     assert built_lib.pb_quantize_workspace_size(1, 2048, 2048, 128, 128) == 256 * 8
+
+
+def test_argument_errors_of_the_fused_entry_points(built_lib):
+    """The fused calls validate before launching: the status codes say why a caller must take the plain calls."""
+    one = C.c_void_p(4096)
+    op = _lib.Operand(4096, 4096, 4096, 1024, 1024, 128, 128, 0, 1)
+    # pb_quantize_for_gemm / pb_relu2_requantize: whole super-groups per row only
+    assert built_lib.pb_quantize_for_gemm(one, 1, 128, 512, 0, one, one, one, op, one, 1 << 20, None) == 2
+    assert built_lib.pb_quantize_for_gemm(None, 1, 128, 1024, 0, one, one, one, op, one, 1 << 20, None) == 1
+    assert built_lib.pb_quantize_for_gemm(one, 1, 128, 1024, 0, one, one, one, op, one, 16, None) == 5          # workspace too small
+    assert built_lib.pb_relu2_requantize(one, 128, 512, 0, one, one, one, None, None, 0, None) == _lib.PB_ERR_UNSUPPORTED
+    assert built_lib.pb_relu2_requantize(one, 128, 1024, 3, one, one, one, None, None, 0, None) == 4
+    # pb_fake_quantize: f32 on (1,128) with 8-block super-groups, nothing else
+    assert built_lib.pb_fake_quantize(one, 1, 1, 128, 1024, 1, 128, 0, one, 0, None) == _lib.PB_ERR_UNSUPPORTED   # bf16 input
+    assert built_lib.pb_fake_quantize(one, 0, 1, 128, 1024, 128, 128, 0, one, 0, None) == _lib.PB_ERR_UNSUPPORTED
+    assert built_lib.pb_fake_quantize(one, 0, 1, 128, 1000, 1, 128, 0, one, 0, None) == 2
+    # pb_quantize_dual: bf16, rows % 128 == 0, cols % 1024 == 0
+    assert built_lib.pb_quantize_dual(one, 0, 1, 128, 1024, 0, one, one, one, one, one, one, one, 1 << 20, None) == _lib.PB_ERR_UNSUPPORTED
+    assert built_lib.pb_quantize_dual(one, 1, 1, 128, 512, 0, one, one, one, one, one, one, one, 1 << 20, None) == _lib.PB_ERR_UNSUPPORTED
+    assert built_lib.pb_quantize_dual(one, 1, 1, 128, 1024, 0, one, one, one, one, one, one, None, 0, None) == 5
+    # pb_elementwise: four ops
+    assert built_lib.pb_elementwise(7, one, 0, one, one, one, 0, one, one, 1, 16, 16, 16, 16, one, None) == _lib.PB_ERR_UNSUPPORTED
+    assert built_lib.pb_elementwise(0, one, 0, one, one, one, 0, one, one, 1, 16, 17, 16, 16, one, None) == 2
+    assert built_lib.pb_elementwise(0, None, 0, one, one, one, 0, one, one, 1, 16, 16, 16, 16, one, None) == 1
+    # pb_gemm_tn_ex: unknown flag bits
+    a = _lib.Operand(4096, 4096, 4096, 256, 1024, 1, 128, 0, 0)
+    assert built_lib.pb_gemm_tn_ex(a, op, one, 0, 1024, one, 1 << 20, 8, None) == _lib.PB_ERR_UNSUPPORTED
+    assert b"flag" in built_lib.pb_last_error()
