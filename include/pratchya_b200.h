@@ -121,6 +121,23 @@ PB_API int pb_elementwise(int op, const void* xq, int x_format, const uint8_t* x
                    const void* yq, int y_format, const uint8_t* y_sc8, const float* y_sc32,
                    int64_t batch, int64_t rows, int64_t cols, int a, int b, float* out, void* stream);
 
+/* Momentum step of the reference's optimizer for a quantized parameter
+ * (pratchya/_nnx_impl/_optimizer.py:171-205): with g and m the gradient and momentum triples on the
+ * parameter's grid (a,b),
+ *     c     = beta1 * dq(m) + (1 - beta1) * dq(g)     f32, written to c_out (input of sign() / Newton-Schulz)
+ *     new_m = beta2 * dq(m) + (1 - beta2) * dq(g)     written as the triple quantize_impl(new_m, (a,b))
+ * in two passes over the bytes of g and m instead of two dequantizations, four scaled temporaries
+ * and a quantization.  The four scalars are passed as the f32 values JAX would use (beta and
+ * 1 - beta, each computed in double and rounded once).  e4m3 triples; workspace:
+ * pb_momentum_workspace_size (8 bytes per block). */
+PB_API size_t pb_momentum_workspace_size(int64_t batch, int64_t rows, int64_t cols, int a, int b);
+PB_API int pb_momentum_update(const void* gq, const uint8_t* g_sc8, const float* g_sc32,
+                       const void* mq, const uint8_t* m_sc8, const float* m_sc32,
+                       int64_t batch, int64_t rows, int64_t cols, int a, int b,
+                       float beta1, float one_minus_beta1, float beta2, float one_minus_beta2,
+                       float* c_out, void* new_mq, uint8_t* new_m_sc8, float* new_m_sc32,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- block-scaled FP8 matmul.
  * A GEMM operand is a K-major quantized matrix: bytes [rows, depth] (depth = the
  * contraction length, contiguous), one e8m0 byte per (row-block, 128-deep block)

@@ -285,3 +285,20 @@ def effective_scale(sc_fp8, sc_fp32):
     sc8 = np.asarray(sc_fp8).view(np.uint8)
     sc32 = np.asarray(sc_fp32, dtype=np.float32).reshape(*sc8.shape[:-1], 1)
     return (_e8m0_to_f32(sc8) * sc32 / np.float32(128.0)).astype(np.float32)
+
+
+def momentum_update(g_triple, m_triple, tgrid, beta1, beta2):
+    """The momentum step of the optimizer for a quantized parameter,
+    pratchya/_nnx_impl/_optimizer.py:171-205 (the branch where param is a 2-D QArrayImpl):
+    g and m are dequantized to f32 (:178-179); c = beta1*m + (1-beta1)*g (:191),
+    new_m = beta2*m + (1-beta2)*g (:192) re-quantized on the parameter's grid (:204-205).
+    The Python scalars enter as f32 (JAX weak typing): beta and 1.0 - beta, each rounded once.
+    Returns (c f32, new_m triple)."""
+    g = dequantize_impl(*g_triple, np.float32, tgrid).astype(np.float32)
+    m = dequantize_impl(*m_triple, np.float32, tgrid).astype(np.float32)
+    b1, c1 = np.float32(beta1), np.float32(1.0 - beta1)
+    b2, c2 = np.float32(beta2), np.float32(1.0 - beta2)
+    c = (b1 * m + c1 * g).astype(np.float32)
+    new_m = (b2 * m + c2 * g).astype(np.float32)
+    return c, quantize_impl(new_m, tgrid)
+

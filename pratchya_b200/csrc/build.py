@@ -15,7 +15,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 INCLUDE = HERE.parent.parent / "include"
 LIB = HERE / "libpratchya_b200.so"
-SOURCES = ["api.cu", "quantize.cu", "dequantize.cu", "transpose_quantize.cu", "gemm_sm100.cu", "selftest.cu"]
+SOURCES = ["api.cu", "quantize.cu", "dequantize.cu", "transpose_quantize.cu", "optimizer.cu", "gemm_sm100.cu", "selftest.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--cudart", "static",

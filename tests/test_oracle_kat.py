@@ -187,3 +187,26 @@ def test_matmul_and_linear_shapes():
     assert gx[0].shape == (16, 256) and gw[0].shape == (256, 128)
     fx, fy = o.fp8_matmul_bwd(x, w, np.ones((16, 128), np.float32), (1, 16))
     assert fx.shape == x.shape and fy.shape == w.shape
+
+
+def test_momentum_update_known_answers():
+    """_optimizer.py:171-205 restated: constant g and m on one (4,4) block dequantize exactly, so c and
+    new_m are the scalar blends, and new_m re-quantizes to the byte of 128 with its own value as sc32."""
+    import numpy as np
+    from oracle import qarr_oracle as o
+    g = np.full((4, 4), 2.0, np.float32)
+    m = np.full((4, 4), -1.0, np.float32)
+    gq, mq = o.quantize_impl(g, (4, 4)), o.quantize_impl(m, (4, 4))
+    c, nm = o.momentum_update(gq, mq, (4, 4), 0.9, 0.99)
+    b1, c1, b2, c2 = np.float32(0.9), np.float32(1.0 - 0.9), np.float32(0.99), np.float32(1.0 - 0.99)
+    assert np.all(c == b1 * np.float32(-1.0) + c1 * np.float32(2.0))
+    want = np.float32(b2 * np.float32(-1.0) + c2 * np.float32(2.0))
+    assert nm[2].reshape(-1)[0] == abs(want)
+    assert np.all(nm[0].view(np.uint8) == 0xF0)            # -128 in e4m3
+    assert np.all(nm[1].view(np.uint8) == 127)
+    # a zero gradient leaves beta2 * m; a zero momentum starts at (1 - beta2) * g
+    z = o.quantize_impl(np.zeros((4, 4), np.float32), (4, 4))
+    _, nm0 = o.momentum_update(z, mq, (4, 4), 0.9, 0.99)
+    assert nm0[2].reshape(-1)[0] == np.float32(b2 * np.float32(1.0))
+    _, nm1 = o.momentum_update(gq, z, (4, 4), 0.9, 0.99)
+    assert nm1[2].reshape(-1)[0] == np.float32(c2 * np.float32(2.0))
