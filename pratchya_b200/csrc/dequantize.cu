@@ -25,14 +25,28 @@ __device__ __forceinline__ float apply_scale(float v, float x_sc) { return __fmu
 
 template <typename OutT> __device__ __forceinline__ void store16(OutT* p, const float (&v)[16]);
 template <> __device__ __forceinline__ void store16<float>(float* p, const float (&v)[16]) {
+  if ((reinterpret_cast<uintptr_t>(p) & 31) == 0) {      // whole 32-byte sectors per store
 #pragma unroll
-  for (int j = 0; j < 4; ++j) __stcs(reinterpret_cast<float4*>(p) + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+    for (int j = 0; j < 2; ++j)
+      asm volatile("st.global.cs.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                   ::"l"(p + 8 * j), "f"(v[8 * j]), "f"(v[8 * j + 1]), "f"(v[8 * j + 2]), "f"(v[8 * j + 3]),
+                     "f"(v[8 * j + 4]), "f"(v[8 * j + 5]), "f"(v[8 * j + 6]), "f"(v[8 * j + 7]) : "memory");
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) __stcs(reinterpret_cast<float4*>(p) + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+  }
 }
 template <> __device__ __forceinline__ void store16<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[16]) {
+  uint32_t w[8];
 #pragma unroll
-  for (int j = 0; j < 2; ++j)
-    __stcs(reinterpret_cast<uint4*>(p) + j, make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
-                                                        pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7])));
+  for (int j = 0; j < 8; ++j) w[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+  if ((reinterpret_cast<uintptr_t>(p) & 31) == 0) {      // one whole 32-byte sector per store
+    asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+  } else {
+    __stcs(reinterpret_cast<uint4*>(p), make_uint4(w[0], w[1], w[2], w[3]));
+    __stcs(reinterpret_cast<uint4*>(p) + 1, make_uint4(w[4], w[5], w[6], w[7]));
+  }
 }
 
 template <typename OutT, int FMT>

@@ -70,6 +70,71 @@ __device__ __forceinline__ void write_gemm_prep(const GemmPrepOut& o, int64_t g,
 }
 
 // ---------------------------------------------------------------------------------
+// bf16 input, 32-byte accesses: lane l, load j (0, 1) -> 16 elements at (j*32 + l)*16, which lie in
+// block 4j + (l >> 3).  Two 256-bit loads and two 128-bit stores per lane and super-group (whole
+// sectors per lane), eight lanes per block, and every lane forms the scales of its own two blocks,
+// so nothing has to be handed round after the reductions.
+__device__ __forceinline__ void ld_global_256(const void* p, uint32_t (&w)[8]) {
+  asm volatile("ld.global.cs.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "l"(p));
+}
+
+template <int FMT, int MINB, bool PREP>
+__global__ void __launch_bounds__(kRowThreads, MINB)
+quantize_row128_bf16_wide_kernel(const uint8_t* __restrict__ x, uint4* __restrict__ q,
+                                 uint8_t* __restrict__ sc8, float* __restrict__ sc32, int64_t n_groups, const GemmPrepOut prep) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (int64_t)gridDim.x * (kRowThreads / 32);
+  for (int64_t g = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); g < n_groups; g += warps_total) {
+    const uint8_t* src = x + g * (kGroupElems * 2);
+    uint32_t w[2][8];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) ld_global_256(src + (j * 32 + lane) * 32, w[j]);
+
+    float m[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      uint32_t a = w[j][0] & 0x7fff7fffu;
+      __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+      for (int k = 1; k < 8; ++k) {
+        a = w[j][k] & 0x7fff7fffu;
+        h = __hmax2(h, *reinterpret_cast<const __nv_bfloat162*>(&a));
+      }
+      const uint32_t hb = *reinterpret_cast<const uint32_t*>(&h);
+      m[j] = fmaxf(__uint_as_float(hb << 16), __uint_as_float(hb & 0xffff0000u));
+#pragma unroll
+      for (int sft = 1; sft < 8; sft <<= 1) m[j] = fmaxf(m[j], __shfl_xor_sync(0xffffffffu, m[j], sft));      // the block's eight lanes
+    }
+    float Mj = fmaxf(m[0], m[1]);
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 8));
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 16));
+    if (lane == 0) sc32[g] = Mj;
+
+    uint4* dst = q + g * (kGroupElems / 16);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      uint32_t sb; float D;
+      block_scale(m[j], Mj, sb, D);
+      const int blk = 4 * j + (lane >> 3);
+      if ((lane & 7) == 0) sc8[g * 8 + blk] = (uint8_t)sb;
+      if (PREP) write_gemm_prep(prep, g, blk, sb, Mj, (lane & 7) == 0, lane == 0 && j == 0);
+      const float r = __frcp_rn(D);
+      const float2 nD2 = make_float2(-D, -D), r2 = make_float2(r, r);
+      uint32_t o[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const uint32_t in = w[j][k];
+        const float2 v = div_hoisted_unsigned2(make_float2(__uint_as_float(in << 16), __uint_as_float(in & 0xffff0000u)), nD2, r2);
+        const uint32_t p = (pack_bf16x2(v.x, v.y) & 0x7fff7fffu) | (in & 0x80008000u);      // the input's signs, also for -0
+        o[k] = bf16x2_to_fp8x2<FMT>(p);
+      }
+      __stcs(dst + j * 32 + lane, make_uint4(o[0] | (o[1] << 16), o[2] | (o[3] << 16), o[4] | (o[5] << 16), o[6] | (o[7] << 16)));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
 // bf16 input: lane l, load it -> 8 elements at (it*32 + l)*8; block = 2*it + (l >> 4).
 template <int FMT, int MINB, bool PREP>
 __global__ void __launch_bounds__(kRowThreads, MINB)
@@ -610,7 +675,16 @@ static int quantize_entry(const void* x, int x_dtype, int64_t batch, int64_t row
     // unconstrained 49; an unconstrained single CTA per SM (96 registers) is 15 % slower.
     const bool e4 = out_format == PB_E4M3;
 #define PB_ROW128_LAUNCH(KERNEL, XT, QT) KERNEL<<<grid, kRowThreads, 0, st>>>((const XT*)x, (QT*)q, sc8, sc32, n_groups, prep)
-    if (x_dtype == PB_BF16) {
+    static const bool wide = [] { const char* e = getenv("PB_QUANT_WIDE"); return !(e && e[0] == '0'); }();
+    if (x_dtype == PB_BF16 && wide && (reinterpret_cast<uintptr_t>(x) & 31) == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0) {
+      if (prep.sf) {
+        if (e4) PB_ROW128_LAUNCH((quantize_row128_bf16_wide_kernel<PB_E4M3, 6, true>), uint8_t, uint4);
+        else    PB_ROW128_LAUNCH((quantize_row128_bf16_wide_kernel<PB_E5M2, 6, true>), uint8_t, uint4);
+      } else {
+        if (e4) PB_ROW128_LAUNCH((quantize_row128_bf16_wide_kernel<PB_E4M3, 6, false>), uint8_t, uint4);
+        else    PB_ROW128_LAUNCH((quantize_row128_bf16_wide_kernel<PB_E5M2, 6, false>), uint8_t, uint4);
+      }
+    } else if (x_dtype == PB_BF16) {
       if (prep.sf) {
         if (e4) PB_ROW128_LAUNCH((quantize_row128_bf16_kernel<PB_E4M3, 6, true>), uint4, uint2);
         else    PB_ROW128_LAUNCH((quantize_row128_bf16_kernel<PB_E5M2, 6, true>), uint4, uint2);
