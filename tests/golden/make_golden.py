@@ -51,6 +51,34 @@ def main():
         out[f"{name}.dq_bf16"] = o.dequantize_impl(q, s8, s32, ml_dtypes.bfloat16, grid).view(np.uint16)
     np.savez_compressed(Path(__file__).with_name("quant_golden.npz"), **out)
     print("wrote", len(CASES), "cases")
+    write_derived()
+
+
+def relu2_middle(y, grid=(1, 128)):
+    """ChannelMix between its two Linears: dq(q(y)) in f32, relu, square, quantize (the oracle's steps)."""
+    k = o.dequantize_impl(*o.quantize_impl(y, grid), np.float32, grid).astype(np.float32)
+    k = (np.maximum(k, 0) ** 2).astype(np.float32)
+    return o.quantize_impl(k, grid)
+
+
+def write_derived():
+    """derived_golden.npz: the optimizer's momentum step and the ChannelMix middle, from the oracle."""
+    out = {}
+    for i, (name, shape, grid) in enumerate([("mom_tensor_wide", (64, 64), (16, 16)), ("mom_rows", (2, 1024), (1, 128))]):
+        rng = np.random.default_rng(2000 + i)
+        g = (rng.standard_normal(shape) * 1e-3).astype(np.float32)
+        m = (rng.standard_normal(shape) * 5e-4).astype(np.float32)
+        gq, mq = o.quantize_impl(g, grid), o.quantize_impl(m, grid)
+        c, nm = o.momentum_update(gq, mq, grid, 0.9, 0.99)
+        out[f"{name}.g"], out[f"{name}.m"], out[f"{name}.grid"] = g, m, np.array(grid)
+        out[f"{name}.c"] = c
+        out[f"{name}.q"], out[f"{name}.sc8"], out[f"{name}.sc32"] = nm[0].view(np.uint8), nm[1], nm[2]
+    y = make_input((2, 1024), "outliers", 3000)
+    kq = relu2_middle(y)
+    out["relu2.y"] = y
+    out["relu2.q"], out["relu2.sc8"], out["relu2.sc32"] = kq[0].view(np.uint8), kq[1], kq[2]
+    np.savez_compressed(Path(__file__).with_name("derived_golden.npz"), **out)
+    print("wrote derived cases")
 
 
 if __name__ == "__main__":
