@@ -148,3 +148,31 @@ def test_few_tiles_split_over_k(built_lib, m, n, k):
     as_bf16 = matmul_impl(*xq, *wq, (1, 128), (128, 128), out_dtype=torch.bfloat16)
     scale = float(np.abs(ref).max())
     assert (got - as_bf16.float()).abs().max().item() <= 2.0 ** -7 * scale
+
+
+def test_random_shapes_against_f64_product(built_lib):
+    """Seeded sweep over row counts, widths and depths that exercise partial tiles, both kernels (operands of
+    at most 128 rows use the single-CTA one), bands, the split over K and both output types; the check is
+    the f64 product of the dequantized operands (the dequantizer itself is bit-exact against the oracle)."""
+    import random
+    from pratchya_b200._qualia import dequantize_impl
+    rnd = random.Random(7)
+    done = 0
+    while done < 14:
+        m = rnd.choice([8, 64, 128, 136, 264, 520, 1024, 2048, 4096])
+        n = 128 * rnd.choice([1, 2, 3, 5, 8, 17, 32, 64])
+        k = 128 * rnd.choice([1, 2, 4, 8, 16, 24, 32, 64])
+        if (m * k // 128) % 8:
+            continue
+        done += 1
+        out = rnd.choice([torch.float32, torch.bfloat16])
+        x = torch.randn(m, k, device="cuda", generator=torch.Generator(device="cuda").manual_seed(done)) * rnd.choice([1e-3, 1.0, 30.0])
+        w = torch.randn(k, n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(100 + done)) * 0.02
+        xq, wq = quantize_impl(x, (1, 128)), quantize_impl(w, (128, 128))
+        got = matmul_impl(*xq, *wq, (1, 128), (128, 128), out_dtype=out)
+        _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+        ref = dequantize_impl(*xq, torch.float32, (1, 128)).double() @ dequantize_impl(*wq, torch.float32, (128, 128)).double()
+        scale = ref.abs().max().item()
+        err = (got.double() - ref).abs().max().item()
+        tol = 1e-5 if out == torch.float32 else 2.0 ** -7
+        assert err <= tol * scale, f"{m}x{n}x{k} {out}: max abs err {err:.3e} vs scale {scale:.3e}"
