@@ -74,8 +74,17 @@ momentum_first_pass_kernel(MomentumParams p, float* __restrict__ c_out, uint32_t
         mx = fmaxf(mx, fabsf(blend(p.b2, m[j], p.c2, g[j])));
       }
       if constexpr (VEC == 16) {
+        float* dst = c_out + (size_t)i * 16;
+        if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {      // whole 32-byte sectors per store
 #pragma unroll
-        for (int j = 0; j < 4; ++j) __stcs(reinterpret_cast<float4*>(c_out + (size_t)i * 16) + j, make_float4(c[4 * j], c[4 * j + 1], c[4 * j + 2], c[4 * j + 3]));
+          for (int j = 0; j < 2; ++j)
+            asm volatile("st.global.cs.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                         ::"l"(dst + 8 * j), "f"(c[8 * j]), "f"(c[8 * j + 1]), "f"(c[8 * j + 2]), "f"(c[8 * j + 3]),
+                           "f"(c[8 * j + 4]), "f"(c[8 * j + 5]), "f"(c[8 * j + 6]), "f"(c[8 * j + 7]) : "memory");
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) __stcs(reinterpret_cast<float4*>(dst) + j, make_float4(c[4 * j], c[4 * j + 1], c[4 * j + 2], c[4 * j + 3]));
+        }
       } else {
         c_out[i] = c[0];
       }
