@@ -481,6 +481,20 @@ template <typename InT, int VEC>
 __device__ __forceinline__ void load_vec(const InT* p, float (&v)[VEC]) {
   if constexpr (VEC == 1) {
     v[0] = Elem<InT>::to_f32(p[0]);
+  } else if constexpr (VEC == 16 && sizeof(InT) == 4) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 t = __ldcs(reinterpret_cast<const float4*>(p) + j);
+      v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+    }
+  } else if constexpr (VEC == 16) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint4 t = __ldcs(reinterpret_cast<const uint4*>(p) + j);
+      const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { v[8 * j + 2 * k] = __uint_as_float(w[k] << 16); v[8 * j + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
+    }
   } else if constexpr (sizeof(InT) == 4) {
     const float4 t = *reinterpret_cast<const float4*>(p);
     v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
@@ -584,6 +598,14 @@ generic_apply_kernel(const InT* __restrict__ x, const float* __restrict__ diviso
     if constexpr (VEC == 1) {
       const uint32_t p = pack_bf16x2(div_hoisted(v[0], D, r), 0.0f);
       q[i] = (uint8_t)(bf16x2_to_fp8x2<FMT>(p) & 0xffu);
+    } else if constexpr (VEC == 16) {
+      const float2 nD2 = make_float2(-D, -D), r2 = make_float2(r, r);
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o[j] = bf16x2_to_fp8x2<FMT>(div_hoisted_pack2(v[4 * j], v[4 * j + 1], nD2, r2)) |
+               (bf16x2_to_fp8x2<FMT>(div_hoisted_pack2(v[4 * j + 2], v[4 * j + 3], nD2, r2)) << 16);
+      __stcs(reinterpret_cast<uint4*>(q) + i, make_uint4(o[0], o[1], o[2], o[3]));
     } else {
       const uint32_t p0 = pack_bf16x2(div_hoisted(v[0], D, r), div_hoisted(v[1], D, r));
       const uint32_t p1 = pack_bf16x2(div_hoisted(v[2], D, r), div_hoisted(v[3], D, r));
@@ -711,6 +733,11 @@ static int quantize_entry(const void* x, int x_dtype, int64_t batch, int64_t row
     return fail(PB_ERR_WORKSPACE_TOO_SMALL, "pb_quantize: grid (%d,%d) needs %zu bytes of workspace, got %zu", a, b, need, workspace_bytes);
   if (reinterpret_cast<uintptr_t>(workspace) & 3) return fail(PB_ERR_MISALIGNED, "pb_quantize: workspace must be 4-byte aligned");
   const bool vec4 = (b % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(q) % 4 == 0);
+  const bool vec16 = (b % 16 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(q) % 16 == 0);
+  if (vec16) {      // 16 elements per thread: whole sectors in, one 16-byte store out
+    if (x_dtype == PB_BF16) return launch_generic<__nv_bfloat16, 16>((const __nv_bfloat16*)x, g, batch, out_format, (uint8_t*)q, sc8, sc32, workspace, st);
+    return launch_generic<float, 16>((const float*)x, g, batch, out_format, (uint8_t*)q, sc8, sc32, workspace, st);
+  }
   if (x_dtype == PB_BF16) {
     return vec4 ? launch_generic<__nv_bfloat16, 4>((const __nv_bfloat16*)x, g, batch, out_format, (uint8_t*)q, sc8, sc32, workspace, st)
                 : launch_generic<__nv_bfloat16, 1>((const __nv_bfloat16*)x, g, batch, out_format, (uint8_t*)q, sc8, sc32, workspace, st);
