@@ -212,3 +212,40 @@ def test_channel_mix_ffn_fused_equals_literal(built_lib):
         assert torch.equal(got, want)
     xb = to_torch(synth((256, 1024), seed=7).astype(BF16))          # bf16 input: the literal sequence
     assert torch.equal(ffn(xb), ffn.literal(xb))
+
+
+def test_step_captures_into_a_cuda_graph(built_lib):
+    """The calls are stream-ordered and allocate nothing, so a quantize + GEMM step records into a CUDA
+    graph as it is; replaying the graph on new input gives the bits of the eager calls."""
+    m, n, k = 512, 1024, 2048
+    wq, w_t = weight(k, n, seed=8)
+    x = to_torch(synth((m, k), seed=1).astype(BF16))
+    q = torch.empty((m, k), dtype=torch.uint8, device="cuda")
+    s8 = torch.empty(m * k // 128, dtype=torch.uint8, device="cuda")
+    s32 = torch.empty(m * k // 1024, dtype=torch.float32, device="cuda")
+    y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    a = _lib.Operand(q.data_ptr(), s8.data_ptr(), s32.data_ptr(), m, k, 1, 128, 0, 0)
+    b = _ops._operand(w_t, wq[1], wq[2], n, k, (128, 128), 1)
+    ws_bytes = built_lib.pb_gemm_workspace_size(a, b)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+
+    def step(stream, flags):
+        _lib.check(built_lib.pb_quantize_for_gemm(x.data_ptr(), 1, m, k, 0, q.data_ptr(), s8.data_ptr(), s32.data_ptr(), b, ws.data_ptr(), ws_bytes, stream))
+        _lib.check(built_lib.pb_gemm_tn_ex(a, b, y.data_ptr(), 1, n, ws.data_ptr(), ws_bytes, flags, stream))
+
+    step(torch.cuda.current_stream().cuda_stream, _ops.GEMM_A_PREPARED)          # also prepares the weight's scales
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            step(side.cuda_stream, _ops.GEMM_A_PREPARED | _ops.GEMM_B_PREPARED)
+    torch.cuda.current_stream().wait_stream(side)
+    x.copy_(to_torch(synth((m, k), seed=2, scale=7.0).astype(BF16)))             # new input in the same buffer
+    y.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+    want = matmul_impl(*quantize_impl(x, (1, 128)), *wq, (1, 128), (128, 128), y_fp8_t=w_t, out_dtype=torch.bfloat16)
+    assert torch.equal(y, want)
