@@ -9,7 +9,9 @@ import ctypes as C
 from pathlib import Path
 
 _LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libpratchya_b200.so"
+_DIAG_LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libpratchya_b200_diag.so"
 _lib = None
+_diag_lib = None
 
 PB_F32, PB_BF16 = 0, 1
 PB_E4M3, PB_E5M2 = 0, 1
@@ -59,34 +61,51 @@ _SIGNATURES = {
     "pb_fake_quantize": (_int, [_ptr, _int, _i64, _i64, _i64, _int, _int, _int, _ptr, _int, _ptr]),
     "pb_gemm_check": (_int, [_ptr]),
     "pb_transpose_bytes": (_int, [_ptr, _i64, _i64, _ptr, _ptr]),
+}
+# extra exports of the diagnostics build (libpratchya_b200_diag.so): test hooks, not part of the C ABI
+_DIAG_SIGNATURES = {
     "pb_debug_division_check": (_int, [C.c_uint64, C.c_uint64, _ptr, _ptr]),
     "pb_debug_gemm_profile": (_int, [C.POINTER(C.c_uint64), _ptr]),
+    "pb_debug_gemm_control": (_int, [C.c_uint, _int]),
 }
 
 # every symbol include/pratchya_b200.h declares (checked by the CPU test-suite)
-DECLARED_SYMBOLS = tuple(k for k in _SIGNATURES if not k.startswith("pb_debug"))
+DECLARED_SYMBOLS = tuple(_SIGNATURES)
 
 
 def lib_path() -> Path:
     return _LIB_PATH
 
 
+def _open(path: Path, signatures):
+    if not path.exists():
+        raise RuntimeError(
+            f"{path} is missing: build it with `python -m pratchya_b200.csrc.build` "
+            "(there is no CPU fallback for the pratchya_b200 ops)")
+    lib = C.CDLL(str(path))
+    for name, (res, args) in signatures.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue          # reported by the symbol test; calling it raises AttributeError
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
 def load():
     """Loads the shared library once; raises if it has not been built."""
     global _lib
     if _lib is None:
-        if not _LIB_PATH.exists():
-            raise RuntimeError(
-                f"{_LIB_PATH} is missing: build it with `python -m pratchya_b200.csrc.build` "
-                "(there is no CPU fallback for the pratchya_b200 ops)")
-        lib = C.CDLL(str(_LIB_PATH))
-        for name, (res, args) in _SIGNATURES.items():
-            fn = getattr(lib, name, None)
-            if fn is None:
-                continue          # reported by the symbol test; calling it raises AttributeError
-            fn.restype, fn.argtypes = res, args
-        _lib = lib
+        _lib = _open(_LIB_PATH, _SIGNATURES)
     return _lib
+
+
+def load_diagnostics():
+    """The diagnostics build of the same sources (cycle counters, fault injection, device self-checks).
+    A separate library with its own device state; the ops of this package never use it."""
+    global _diag_lib
+    if _diag_lib is None:
+        _diag_lib = _open(_DIAG_LIB_PATH, {**_SIGNATURES, **_DIAG_SIGNATURES})
+    return _diag_lib
 
 
 def check(status: int):

@@ -1,8 +1,11 @@
-"""Builds libpratchya_b200.so in this directory with nvcc for sm_100a.
+"""Builds the shared libraries in this directory with nvcc for sm_100a.
 
-    python -m pratchya_b200.csrc.build [--force]
+    python -m pratchya_b200.csrc.build [--force] [-v]
 
-The library is kept in-tree next to its sources; it is not installed anywhere.
+libpratchya_b200.so is the product.  libpratchya_b200_diag.so is the same sources compiled with
+-DPB_DIAGNOSTICS plus selftest.cu: cycle counters, timing experiments, environment switches, the
+fault injection of the abort-path test and the device self-checks live there only, and only the
+tests load it.  Both are kept in-tree next to their sources; nothing is installed anywhere.
 """
 from __future__ import annotations
 
@@ -15,7 +18,9 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 INCLUDE = HERE.parent.parent / "include"
 LIB = HERE / "libpratchya_b200.so"
-SOURCES = ["api.cu", "quantize.cu", "dequantize.cu", "transpose_quantize.cu", "optimizer.cu", "gemm_sm100.cu", "selftest.cu"]
+DIAG_LIB = HERE / "libpratchya_b200_diag.so"
+SOURCES = ["api.cu", "quantize.cu", "dequantize.cu", "transpose_quantize.cu", "optimizer.cu", "gemm_sm100.cu", "wkv7.cu"]
+DIAG_SOURCES = SOURCES + ["selftest.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--cudart", "static",
@@ -36,10 +41,14 @@ def _stale(target: Path, deps) -> bool:
     return any(Path(d).stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    srcs = [HERE / s for s in SOURCES if (HERE / s).exists()]
+def build(force: bool = False, verbose: bool = False, diagnostics: bool = False) -> Path:
+    """Compiles what is stale and links the product library (or, with `diagnostics`, the diagnostics one)."""
+    names = DIAG_SOURCES if diagnostics else SOURCES
+    lib = DIAG_LIB if diagnostics else LIB
+    extra = ["-DPB_DIAGNOSTICS"] if diagnostics else []
+    srcs = [HERE / s for s in names if (HERE / s).exists()]
     headers = list(HERE.glob("*.cuh")) + list(INCLUDE.glob("*.h"))
-    objdir = HERE / "build"
+    objdir = HERE / ("build_diag" if diagnostics else "build")
     objdir.mkdir(exist_ok=True)
     nvcc = _nvcc()
     objs = []
@@ -48,7 +57,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         obj = objdir / (src.stem + ".o")
         objs.append(obj)
         if force or _stale(obj, [src, *headers]):
-            cmd = [nvcc, *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{HERE}", "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc, *NVCC_FLAGS, *extra, f"-I{INCLUDE}", f"-I{HERE}", "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
                 print(" ".join(cmd), flush=True)
@@ -59,14 +68,18 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             print(out)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src.name}:\n{out}")
-    if force or procs or _stale(LIB, objs):
+    if force or procs or _stale(lib, objs):
         cmd = [nvcc, "-shared", "--cudart", "static", "-gencode", "arch=compute_100a,code=sm_100a",
-               "-o", str(LIB), *map(str, objs), "-ldl", "-lpthread"]
+               "-o", str(lib), *map(str, objs), "-ldl", "-lpthread"]
         r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}")
-    return LIB
+    return lib
+
+
+def build_all(force: bool = False, verbose: bool = False):
+    return build(force, verbose), build(force, verbose, diagnostics=True)
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(*build_all(force="--force" in sys.argv, verbose="-v" in sys.argv))

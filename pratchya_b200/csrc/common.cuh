@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <numeric>
 
 #include "pratchya_b200.h"
@@ -58,6 +59,18 @@ inline int make_geometry(int64_t rows, int64_t cols, int a, int b, Geometry* g) 
 }
 
 int sm_count();   // SMs of the current device (cached per device)
+
+// Tuning and diagnostic switches are read from the environment by the diagnostics build only
+// (-DPB_DIAGNOSTICS); the product build always runs the defaults.
+inline int env_switch(const char* name, int fallback) {
+#ifdef PB_DIAGNOSTICS
+  const char* e = getenv(name);
+  return e ? atoi(e) : fallback;
+#else
+  (void)name;
+  return fallback;
+#endif
+}
 
 // Division of a 31-bit index by a run-time constant as multiply-high + shift
 // (Granlund-Montgomery with N = 31: m = ceil(2^(31+l) / d), l = ceil(log2 d)).

@@ -20,10 +20,23 @@
 // a device status word, all roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
+
+// The cycle counters, the timing experiments that skip loads or stores, and the fault injection
+// of the abort-path test exist only in the diagnostics build (-DPB_DIAGNOSTICS, a second library
+// that the tests load by name).  The product library has none of them and reads no switch that
+// could change its results.
+#ifdef PB_DIAGNOSTICS
+#define PB_EPI_SKIP_DRAIN (PROF && p.profile == 3)
+#define PB_EPI_SKIP_STORE (PROF && p.profile >= 2)
+#else
+#define PB_EPI_SKIP_DRAIN false
+#define PB_EPI_SKIP_STORE false
+#endif
 
 namespace pb {
 namespace {
@@ -102,13 +115,14 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
       : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and raises the abort flag) when the poll budget ran out or
-// another role already aborted.  The budget is a poll count, not a clock: 2^24 polls take at
-// least half a second even if the hardware never parks the warp (and ~30 s if every poll parks
-// for its full 2 us), while a healthy wait in this kernel lasts microseconds.  Counting keeps the
-// slow path to a handful of registers, which matters in the MMA-issuing thread.
-constexpr uint32_t kWaitPolls = 1u << 24;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+// Bounded wait.  Returns false (and raises the abort flag) when the poll budget ran out.  The
+// budget (GemmParams::wait_polls) is a poll count, not a clock: a poll parks the warp for up to
+// 2 us, so the default of 2^21 polls gives up after about four seconds at most (tens of
+// milliseconds if the hardware never parks the warp), while a healthy wait in this kernel lasts
+// microseconds.  Counting keeps the slow path to a handful of registers, which matters in the
+// MMA-issuing thread.
+constexpr uint32_t kDefaultWaitPolls = 1u << 21;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t polls) {
   // The whole poll loop is one PTX block: the compiler sees a single opaque instruction, so the
   // loops that wait (the MMA issue loop above all) keep their state in registers.
   uint32_t ok;
@@ -124,7 +138,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       "setp.ne.u32 p, n, n;\n"          // budget exhausted: p = false
       "DONE_%=:\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity), "r"(kWaitPolls) : "memory");
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(polls) : "memory");
   if (ok) return true;
   *abort_flag = 1;
   atomicExch(&g_gemm_status, (unsigned int)PB_ERR_DEVICE_TIMEOUT);
@@ -158,17 +172,6 @@ __device__ __forceinline__ void tc_mma_block_scaled(uint32_t d_tmem, uint64_t a_
       "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
 }
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
 // the same load, written straight into 32 consecutive floats of an accumulator array
 template <int OFF>
 __device__ __forceinline__ void tc_ld32f(uint32_t taddr, float (&a)[128]) {
@@ -182,30 +185,66 @@ __device__ __forceinline__ void tc_ld32f(uint32_t taddr, float (&a)[128]) {
         "=f"(a[OFF + 24]), "=f"(a[OFF + 25]), "=f"(a[OFF + 26]), "=f"(a[OFF + 27]), "=f"(a[OFF + 28]), "=f"(a[OFF + 29]), "=f"(a[OFF + 30]), "=f"(a[OFF + 31])
       : "r"(taddr) : "memory");
 }
-// acc[OFF .. OFF+31] += r * fa * fb[column], two columns per instruction (packed f32x2 arithmetic of sm_100)
-template <int OFF>
-__device__ __forceinline__ void promote(float (&acc)[128], const uint32_t (&r)[32], float fa, float s_uni, const float* fbp, int uniform) {
+// Four per-column factors through the read-only path, as a volatile instruction: the compiler keeps it
+// where it is written.  As a plain load it hoisted every factor of a chunk (up to 128 registers) to the
+// top of the drain, on top of the 128 accumulators, and the epilogue spilled.
+__device__ __forceinline__ float4 ld_factors(const float* p) {
+  float4 v;
+  asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+// acc[off .. off+15] += r * fa * fb[column]; `off` is a constant after unrolling
+__device__ __forceinline__ void promote16(float (&acc)[128], int off, const uint32_t (&r)[16], float fa, float s_uni, const float* fbp, int uniform) {
   if (uniform) {
     const float2 s2 = make_float2(s_uni, s_uni);
 #pragma unroll
-    for (int j = 0; j < 32; j += 2) {
-      const float2 v = __ffma2_rn(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), s2, make_float2(acc[OFF + j], acc[OFF + j + 1]));
-      acc[OFF + j] = v.x; acc[OFF + j + 1] = v.y;
+    for (int j = 0; j < 16; j += 2) {
+      const float2 v = __ffma2_rn(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), s2, make_float2(acc[off + j], acc[off + j + 1]));
+      acc[off + j] = v.x; acc[off + j + 1] = v.y;
     }
   } else {
     const float2 fa2 = make_float2(fa, fa);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float4 fb = __ldg(reinterpret_cast<const float4*>(fbp + OFF) + j);
+    for (int j = 0; j < 4; ++j) {
+      const float4 fb = ld_factors(fbp + off + 4 * j);
       const float2 t0 = __fmul2_rn(make_float2(__uint_as_float(r[4 * j + 0]), __uint_as_float(r[4 * j + 1])), fa2);
       const float2 t1 = __fmul2_rn(make_float2(__uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])), fa2);
-      const float2 v0 = __ffma2_rn(t0, make_float2(fb.x, fb.y), make_float2(acc[OFF + 4 * j + 0], acc[OFF + 4 * j + 1]));
-      const float2 v1 = __ffma2_rn(t1, make_float2(fb.z, fb.w), make_float2(acc[OFF + 4 * j + 2], acc[OFF + 4 * j + 3]));
-      acc[OFF + 4 * j + 0] = v0.x; acc[OFF + 4 * j + 1] = v0.y; acc[OFF + 4 * j + 2] = v1.x; acc[OFF + 4 * j + 3] = v1.y;
+      const float2 v0 = __ffma2_rn(t0, make_float2(fb.x, fb.y), make_float2(acc[off + 4 * j + 0], acc[off + 4 * j + 1]));
+      const float2 v1 = __ffma2_rn(t1, make_float2(fb.z, fb.w), make_float2(acc[off + 4 * j + 2], acc[off + 4 * j + 3]));
+      acc[off + 4 * j + 0] = v0.x; acc[off + 4 * j + 1] = v0.y; acc[off + 4 * j + 2] = v1.x; acc[off + 4 * j + 3] = v1.y;
     }
   }
 }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// A later chunk of a tile: 16-column parts through two alternating 16-register buffers, the load of
+// part i+1 in flight under the arithmetic of part i.  128 accumulators + 32 staging registers leave the
+// epilogue's 216-register budget with room to spare (with two 32-register buffers the kernel spilled).
+// `release` hands the TMEM buffer back as soon as the last load has landed.
+template <typename Release>
+__device__ __forceinline__ void drain_later_chunk(float (&acc)[128], uint32_t t_addr, bool four_parts, float fa, float s_uni,
+                                                  const float* fbp, int uniform, Release&& release) {
+  uint32_t r[2][16];
+  tc_ld16(t_addr, r[0]);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (j < 6 || four_parts) {
+      tc_wait_ld();
+      const bool more = j + 1 < 6 || (four_parts && j + 1 < 8);
+      if (more) tc_ld16(t_addr + 16 * (j + 1), r[(j + 1) & 1]);
+      else release();
+      promote16(acc, 16 * j, r[j & 1], fa, s_uni, fbp, uniform);
+    }
+  }
+}
 
 // K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row groups
 // 1024 bytes apart.  Fields: start >> 4 at [0,14), LBO >> 4 at [16,30) (unused for swizzled
@@ -257,12 +296,15 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int a_fmt, b_fmt;
   int d_dtype;
-  int diag;         // timing experiments in the profiling build of the pair kernel: 1 skips the loads of B, 2 those of A, 4 those of the scale factors
+  int diag;         // diagnostics build only (PB_DIAGNOSTICS), pair kernel: 1 skips the loads of B, 2 those of A, 4 those of the scale
+                    // factors (timing experiments); 8 leaves the first pipeline slot unfilled and unarmed, so that every bounded
+                    // wait of the launch runs out (the test of the abort path).  Always 0 in the product build.
   int splitk;       // pair kernel: 1, or 2 = each tile's chunks are shared by two work units that add into a zeroed f32 D
   int band;         // pair kernel: tile rows per band; a band's tiles are visited column by column before the next band
-  int fb_uniform;   // B's fp32 factor is the same for all rows of B within a chunk
+  int fb_uniform;   // B's fp32 factor is the same for all rows of B within a chunk (selects the kernel instantiation)
   int tma_store;    // D is written through shared memory and TMA stores (needs 16-byte aligned rows)
-  int profile;
+  int profile;      // diagnostics build only: 1 per-role cycle counters, 2 also no stores of D, 3 also no TMEM reads.  0 in the product build.
+  uint32_t wait_polls;   // poll budget of every bounded mbarrier wait
 };
 
 
@@ -368,7 +410,7 @@ __device__ __forceinline__ void store_row_segment(const GemmParams& p, const flo
   }
 }
 
-template <int BN, bool PROF>
+template <int BN, bool PROF, bool UNI>
 __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_d, const __grid_constant__ GemmParams p) {
@@ -418,7 +460,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int kb = 0; kb < p.KB; ++kb, ++it) {
           const int s = it % C::kStages;
           const long long t0 = PROF ? clock64() : 0;
-          if (!mbar_wait(bar_empty(s), ((it / C::kStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar_empty(s), ((it / C::kStages) & 1u) ^ 1u, abort_flag, p.wait_polls)) { ok = false; break; }
           if (PROF) waited += clock64() - t0;
           // the scale-factor atom of a stage covers 4 k-blocks: only the first of them carries it
           const bool with_sf = (kb & 3) == 0;
@@ -441,7 +483,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // kStages fills are the ones that can still be in flight.
       const uint32_t issued = it;
       for (uint32_t j = (issued > (uint32_t)C::kStages ? issued - C::kStages : 0); j < issued; ++j)
-        (void)mbar_wait(bar_full(j % C::kStages), (j / C::kStages) & 1u, abort_flag);
+        (void)mbar_wait(bar_full(j % C::kStages), (j / C::kStages) & 1u, abort_flag, p.wait_polls);
       if (PROF) atomicAdd(&g_gemm_prof[0], (unsigned long long)waited);
     } else if (warp == 1 && lane == 0) {
       // ------------------------------------------------------------- MMA issuer
@@ -465,7 +507,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int c = 0; c < nchunks && ok; ++c, ++g) {
           const int buf = g % C::kAccBufs;
           long long t0 = PROF ? clock64() : 0;
-          if (!mbar_wait(bar_acc_empty(buf), ((g / C::kAccBufs) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar_acc_empty(buf), ((g / C::kAccBufs) & 1u) ^ 1u, abort_flag, p.wait_polls)) { ok = false; break; }
           if (PROF) wait_acc += clock64() - t0;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
@@ -473,7 +515,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           uint32_t accumulate = 0;
           for (int kb = c * P; kb < kb_end; ++kb) {
             if (PROF) t0 = clock64();
-            if (!mbar_wait(full, phase, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(full, phase, abort_flag, p.wait_polls)) { ok = false; break; }
             if (PROF) wait_full += clock64() - t0;
             // scale factors of k-blocks 4j..4j+3 live in TMEM set j & 1; the MMAs of set j-2 were
             // issued (and are ordered) before this copy
@@ -530,7 +572,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const float* fbp = p.fb + (size_t)c * p.Npad + n0;
         const float s_uni = fa * __ldg(fbp);      // the whole factor when B's fp32 factor does not vary over the tile
         const long long t0 = PROF ? clock64() : 0;
-        if (!mbar_wait(bar_acc_full(buf), (g / C::kAccBufs) & 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(bar_acc_full(buf), (g / C::kAccBufs) & 1u, abort_flag, p.wait_polls)) { ok = false; break; }
         if (PROF) wait_chunk += clock64() - t0;
         tc_fence_after();
         const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + col_half * 128;
@@ -540,11 +582,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_acc_empty(buf));
         };
-        // Diagnostic knobs (PB_GEMM_PROFILE=3: handshake only; >=2: no stores of D, below).  They are
-        // tested in every build on purpose: with these two branches in the loop the compiler keeps
-        // the accumulators of a tile apart from the next tile's prologue, and the kernel measures
-        // 132 us instead of 151 us on the 8192 x 8192 x 2048 case.
-        if (p.profile == 3) { release(); continue; }
+        if (PB_EPI_SKIP_DRAIN) { release(); continue; }      // diagnostics build: handshake only
         if (c == 0) {
           // First chunk of a tile: straight into the accumulator registers, so the buffer goes
           // back to the MMA warp before any arithmetic.
@@ -552,35 +590,25 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (four_parts) tc_ld32f<96>(t_addr + 96, acc);
           tc_wait_ld();
           release();
-          if (p.fb_uniform) {
+          if (UNI) {
 #pragma unroll
             for (int j = 0; j < 128; ++j) acc[j] *= s_uni;
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               if (j < 24 || four_parts) {
-                const float4 fb = __ldg(reinterpret_cast<const float4*>(fbp) + j);
+                const float4 fb = ld_factors(fbp + 4 * j);
                 acc[4 * j + 0] = acc[4 * j + 0] * fa * fb.x; acc[4 * j + 1] = acc[4 * j + 1] * fa * fb.y;
                 acc[4 * j + 2] = acc[4 * j + 2] * fa * fb.z; acc[4 * j + 3] = acc[4 * j + 3] * fa * fb.w;
               }
             }
           }
         } else {
-          // Later chunks: 32-column parts, the load of part i+1 in flight under the arithmetic of part i.
-          uint32_t r0[32], r1[32];
-          tc_ld32(t_addr, r0);
-          tc_wait_ld(); tc_ld32(t_addr + 32, r1); promote<0>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
-          tc_wait_ld(); tc_ld32(t_addr + 64, r0); promote<32>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
-          if (four_parts) {
-            tc_wait_ld(); tc_ld32(t_addr + 96, r1); promote<64>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
-            tc_wait_ld(); release();                promote<96>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
-          } else {
-            tc_wait_ld(); release();                promote<64>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
-          }
+          drain_later_chunk(acc, t_addr, four_parts, fa, s_uni, fbp, UNI, release);
         }
       }
       if (!ok) break;
-      if (p.profile >= 2) continue;       // 2, 3: diagnostics without the stores of D
+      if (PB_EPI_SKIP_STORE) continue;       // diagnostics build: no stores of D
       if (p.tma_store) {
         const uint32_t stage = s_base + C::kOffStore + ew * 4096;
         const int row0 = m0 + quarter * 32;
@@ -705,7 +733,7 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
   tm = b * p.band + (within - tn * rows);
 }
 
-template <bool PROF>
+template <bool PROF, bool UNI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg2::kThreads, 1)
 gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
@@ -782,13 +810,16 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           for (int kb = c * p.P; kb < kb_end; kb += 2, ++it) {
             const int q = it % C::kSlots;
             const long long tw = PROF ? clock64() : 0;
-            if (!mbar_wait(bar_empty(q), ((it / C::kSlots) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(bar_empty(q), ((it / C::kSlots) & 1u) ^ 1u, abort_flag, p.wait_polls)) { ok = false; break; }
             if (PROF) prod_wait += clock64() - tw;
             const bool two = kb + 1 < kb_end;
             const bool with_sf = (kb & 3) == 0;             // a step of two starts at an even k-block: only its first can open a group of four
             const uint32_t full = map_to_cta(bar_full(q), 0);
-            const bool ld_a = !(PROF && (p.diag & 2)), ld_b = !(PROF && (p.diag & 1)), ld_sf = !(PROF && (p.diag & 4));
-            if (leader) mbar_arrive_expect_tx(bar_full(q), 2 * ((two ? 2 : 1) * ((ld_a ? C::kABytes : 0) + (ld_b ? C::kBBytes : 0)) + (with_sf && ld_sf ? C::kSfSlot : 0)));
+            // diagnostics build: the very first slot of the launch is neither armed nor filled, so its barrier
+            // never completes, nothing is in flight for it, and every role's bounded wait runs out
+            const bool unarmed = PROF && (p.diag & 8) && it == 0;
+            const bool ld_a = !(PROF && (p.diag & 2)) && !unarmed, ld_b = !(PROF && (p.diag & 1)) && !unarmed, ld_sf = !(PROF && (p.diag & 4)) && !unarmed;
+            if (leader && !unarmed) mbar_arrive_expect_tx(bar_full(q), 2 * ((two ? 2 : 1) * ((ld_a ? C::kABytes : 0) + (ld_b ? C::kBBytes : 0)) + (with_sf && ld_sf ? C::kSfSlot : 0)));
             const int s = 2 * q;
             if (ld_a) tma_load_2d_pair(s_a + s * C::kABytes, &map_a, kb * BK, m0, full);
             if (ld_b) tma_load_2d_pair(s_b + s * C::kBBytes, &map_b, kb * BK, nb0, full);
@@ -836,7 +867,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int c = c_begin; c < c_end && ok; ++c, ++g) {
           const int buf = g % C::kAccBufs;
           long long t0 = PROF ? clock64() : 0;
-          if (!mbar_wait(bar_acc_empty(buf), ((g / C::kAccBufs) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar_acc_empty(buf), ((g / C::kAccBufs) & 1u) ^ 1u, abort_flag, p.wait_polls)) { ok = false; break; }
           if (PROF) wait_acc += clock64() - t0;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
@@ -844,7 +875,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           uint32_t accumulate = 0;
           for (int kb = c * P; kb < kb_end; kb += 2) {
             if (PROF) t0 = clock64();
-            if (!mbar_wait(full, phase, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(full, phase, abort_flag, p.wait_polls)) { ok = false; break; }
             if (PROF) wait_full += clock64() - t0;
             const uint32_t sf_col = sf_tmem0 + ((uint32_t)(kb >> 2) & 1u) * C::kSfCols;
             if ((kb & 3) == 0) {
@@ -911,8 +942,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const float s_uni = fa * __ldg(fbp);
         // per-column factors of this chunk: new lines every chunk, so ask for them now; the chunk's MMAs
         // are still running and an L2 round trip per 32 columns would otherwise sit inside the drain
-        if (!p.fb_uniform && lane * 32 < ncols) asm volatile("prefetch.global.L1 [%0];" ::"l"(fbp + lane * 32));
-        if (!mbar_wait(bar_acc_full(buf), (g / C::kAccBufs) & 1u, abort_flag)) { ok = false; break; }
+        if (!UNI && lane * 32 < ncols) asm volatile("prefetch.global.L1 [%0];" ::"l"(fbp + lane * 32));
+        if (!mbar_wait(bar_acc_full(buf), (g / C::kAccBufs) & 1u, abort_flag, p.wait_polls)) { ok = false; break; }
         tc_fence_after();
         const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + col_half * 128;
         const uint32_t acc_empty_leader = map_to_cta(bar_acc_empty(buf), 0);
@@ -921,40 +952,31 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         };
-        if (p.profile == 3) { release(); continue; }     // diagnostic knobs, see the single-CTA kernel
+        if (PB_EPI_SKIP_DRAIN) { release(); continue; }      // diagnostics build: handshake only
         if (c == c_begin) {
           tc_ld32f<0>(t_addr, acc); tc_ld32f<32>(t_addr + 32, acc); tc_ld32f<64>(t_addr + 64, acc);
           if (four_parts) tc_ld32f<96>(t_addr + 96, acc);
           tc_wait_ld();
           release();
-          if (p.fb_uniform) {
+          if (UNI) {
 #pragma unroll
             for (int j = 0; j < 128; ++j) acc[j] *= s_uni;
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               if (j < 24 || four_parts) {
-                const float4 fb = __ldg(reinterpret_cast<const float4*>(fbp) + j);
+                const float4 fb = ld_factors(fbp + 4 * j);
                 acc[4 * j + 0] = acc[4 * j + 0] * fa * fb.x; acc[4 * j + 1] = acc[4 * j + 1] * fa * fb.y;
                 acc[4 * j + 2] = acc[4 * j + 2] * fa * fb.z; acc[4 * j + 3] = acc[4 * j + 3] * fa * fb.w;
               }
             }
           }
         } else {
-          uint32_t r0[32], r1[32];
-          tc_ld32(t_addr, r0);
-          tc_wait_ld(); tc_ld32(t_addr + 32, r1); promote<0>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
-          tc_wait_ld(); tc_ld32(t_addr + 64, r0); promote<32>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
-          if (four_parts) {
-            tc_wait_ld(); tc_ld32(t_addr + 96, r1); promote<64>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
-            tc_wait_ld(); release();                promote<96>(acc, r1, fa, s_uni, fbp, p.fb_uniform);
-          } else {
-            tc_wait_ld(); release();                promote<64>(acc, r0, fa, s_uni, fbp, p.fb_uniform);
-          }
+          drain_later_chunk(acc, t_addr, four_parts, fa, s_uni, fbp, UNI, release);
         }
       }
       if (!ok) break;
-      if (p.profile >= 2) continue;
+      if (PB_EPI_SKIP_STORE) continue;       // diagnostics build: no stores of D
       if (p.tma_store) {
         const uint32_t stage = s_base + C::kOffStore + ew * 4096;
         const int row0 = m0 + quarter * 32;
@@ -1042,16 +1064,14 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn encode_tiled() {
-  static std::mutex mu;
-  static EncodeTiledFn fn = nullptr;
-  std::lock_guard<std::mutex> lock(mu);
-  if (!fn) {
+  static const EncodeTiledFn fn = [] {      // looked up once per process (thread-safe static initialisation)
     void* p = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
         qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
+      return reinterpret_cast<EncodeTiledFn>(p);
+    return static_cast<EncodeTiledFn>(nullptr);
+  }();
   return fn;
 }
 
@@ -1155,24 +1175,35 @@ struct GemmPlan {
   size_t off_sfa, off_sfb, off_fa, off_fb, total;
 };
 
-bool pick_pair() {      // the CTA-pair kernel is the default; PB_GEMM_MODE=single selects the single-CTA one
-  static const bool pair = [] { const char* e = getenv("PB_GEMM_MODE"); return !(e && e[0] == 's'); }();
+bool pick_pair() {      // the CTA-pair kernel is the default; PB_GEMM_SINGLE=1 selects the single-CTA one
+  static const bool pair = env_switch("PB_GEMM_SINGLE", 0) == 0;
   return pair;
 }
 
-int pick_bn() {      // PB_GEMM_BN=128|224|256 overrides the default tile width
-  static int bn = [] {
-    const char* e = getenv("PB_GEMM_BN");
-    const int v = e ? atoi(e) : 224;
-    return (v == 128 || v == 256) ? v : 224;
-  }();
+int pick_bn() {      // PB_GEMM_BN=128|224|256: tile width of the single-CTA kernel
+  static const int bn = [] { const int v = env_switch("PB_GEMM_BN", 224); return (v == 128 || v == 256) ? v : 224; }();
   return bn;
 }
 
+#ifdef PB_DIAGNOSTICS
+std::atomic<int> g_diag_bits{-1};                       // -1: take PB_GEMM_DIAG from the environment
+std::atomic<uint32_t> g_wait_polls{kDefaultWaitPolls};
 int profile_level() {   // 0 off, 1 per-role cycle counters; 2 also skips the stores of D, 3 also the TMEM reads (timing only)
-  static const int level = [] { const char* e = getenv("PB_GEMM_PROFILE"); return e ? atoi(e) : 0; }();
+  static const int level = env_switch("PB_GEMM_PROFILE", 0);
   return level;
 }
+int diag_bits() {
+  const int forced = g_diag_bits.load();
+  if (forced >= 0) return forced;
+  static const int env = env_switch("PB_GEMM_DIAG", 0);
+  return env;
+}
+uint32_t wait_polls() { return g_wait_polls.load(); }
+#else
+constexpr int profile_level() { return 0; }
+constexpr int diag_bits() { return 0; }
+constexpr uint32_t wait_polls() { return kDefaultWaitPolls; }
+#endif
 
 int make_plan(const pb_operand* a, const pb_operand* b, GemmPlan* gp) {
   if (!a || !b) return fail(PB_ERR_NULL_POINTER, "pb_gemm_tn: operands must be non-null");
@@ -1214,7 +1245,7 @@ int launch_prep(const pb_operand* o, const OperandPlan& op, const GemmPlan& gp, 
   return PB_OK;
 }
 
-template <int BN, bool PROF>
+template <int BN, bool PROF, bool UNI>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const GemmParams& p, cudaStream_t st) {
   static std::mutex mu;
   static bool configured[64] = {false};
@@ -1223,18 +1254,22 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
   {
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-      PB_CUDA_TRY(cudaFuncSetAttribute(gemm_tn_kernel<BN, PROF>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes));
+      PB_CUDA_TRY(cudaFuncSetAttribute(gemm_tn_kernel<BN, PROF, UNI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes));
       configured[dev] = true;
     }
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_tn_kernel<BN, PROF><<<grid, Cfg<BN>::kThreads, Cfg<BN>::kSmemBytes, st>>>(ma, mb, md, p);
+  gemm_tn_kernel<BN, PROF, UNI><<<grid, Cfg<BN>::kThreads, Cfg<BN>::kSmemBytes, st>>>(ma, mb, md, p);
   PB_LAUNCH_CHECK("gemm_tn_kernel");
   return PB_OK;
 }
+template <int BN, bool PROF>
+int launch_gemm_uni(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const GemmParams& p, cudaStream_t st) {
+  return p.fb_uniform ? launch_gemm<BN, PROF, true>(ma, mb, md, p, st) : launch_gemm<BN, PROF, false>(ma, mb, md, p, st);
+}
 
-template <bool PROF>
+template <bool PROF, bool UNI>
 int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msfa, const CUtensorMap& msfb,
                      const CUtensorMap& md, const GemmParams& p, cudaStream_t st) {
   static std::mutex mu;
@@ -1244,16 +1279,21 @@ int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   {
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-      PB_CUDA_TRY(cudaFuncSetAttribute(gemm_tn_pair_kernel<PROF>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::kSmemBytes));
+      PB_CUDA_TRY(cudaFuncSetAttribute(gemm_tn_pair_kernel<PROF, UNI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::kSmemBytes));
       configured[dev] = true;
     }
   }
   const int tiles = p.tiles_m * p.tiles_n * p.splitk;
   const int pairs = sm_count() / 2;
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  gemm_tn_pair_kernel<PROF><<<grid, Cfg2::kThreads, Cfg2::kSmemBytes, st>>>(ma, mb, msfa, msfb, md, p);
+  gemm_tn_pair_kernel<PROF, UNI><<<grid, Cfg2::kThreads, Cfg2::kSmemBytes, st>>>(ma, mb, msfa, msfb, md, p);
   PB_LAUNCH_CHECK("gemm_tn_pair_kernel");
   return PB_OK;
+}
+template <bool PROF>
+int launch_gemm_pair_uni(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msfa, const CUtensorMap& msfb,
+                         const CUtensorMap& md, const GemmParams& p, cudaStream_t st) {
+  return p.fb_uniform ? launch_gemm_pair<PROF, true>(ma, mb, msfa, msfb, md, p, st) : launch_gemm_pair<PROF, false>(ma, mb, msfa, msfb, md, p, st);
 }
 
 }  // namespace
@@ -1334,7 +1374,7 @@ extern "C" int pb_gemm_tn_ex(const pb_operand* a, const pb_operand* b, void* d, 
   p.fb_uniform = gp.pb.row_uniform ? 1 : 0;
   {
     // band height: about 16 MB of A rows (they and B, at most a few tens of MB, then share the 126 MB L2 with the stream of D)
-    static const int forced = [] { const char* e = getenv("PB_GEMM_BAND"); return e ? atoi(e) : 0; }();
+    static const int forced = env_switch("PB_GEMM_BAND", 0);
     int band = (int)((16ll << 20) / (256 * a->depth));
     if (forced > 0) band = forced;
     if (band < 4) band = 4;
@@ -1344,7 +1384,8 @@ extern "C" int pb_gemm_tn_ex(const pb_operand* a, const pb_operand* b, void* d, 
   p.tma_store = 0;
   p.splitk = 1;
   p.profile = profile_level();
-  p.diag = [] { const char* e = getenv("PB_GEMM_DIAG"); return e ? atoi(e) : 0; }();
+  p.diag = diag_bits();
+  p.wait_polls = wait_polls();
   // D goes out through TMA stores when its rows are 16-byte aligned; otherwise by direct stores
   CUtensorMap md = ma;
   const int es = d_dtype == PB_BF16 ? 2 : 4;
@@ -1356,7 +1397,7 @@ extern "C" int pb_gemm_tn_ex(const pb_operand* a, const pb_operand* b, void* d, 
     // Few tiles for the 74 CTA pairs (a 2048 x 2048 weight gradient is 80): give each tile's chunks to
     // two work units that add their halves into D.  Needs f32 output through TMA (the reduction is
     // an f32 TMA add into zeros, so the two orders give the same bits) and at least two chunks a half.
-    static const int split_env = [] { const char* e = getenv("PB_GEMM_SPLITK"); return e ? atoi(e) : 0; }();
+    static const int split_env = env_switch("PB_GEMM_SPLITK", 0);
     const int pairs = sm_count() / 2, tiles = p.tiles_m * p.tiles_n;
     auto efficiency = [&](int units) { return (double)units / (double)(((units + pairs - 1) / pairs) * pairs); };
     bool split = d_dtype == PB_F32 && p.tma_store && gp.nchunks >= 4 && efficiency(tiles) < 0.8 && efficiency(2 * tiles) > efficiency(tiles) + 0.1;
@@ -1369,14 +1410,20 @@ extern "C" int pb_gemm_tn_ex(const pb_operand* a, const pb_operand* b, void* d, 
     CUtensorMap msfa, msfb;
     if (int s = make_sf_map(&msfa, ws + gp.off_sfa, (int64_t)gp.KG * gp.tiles_m, 1)) return s;
     if (int s = make_sf_map(&msfb, ws + gp.off_sfb, (int64_t)gp.KG * gp.tiles_n * 2, 2)) return s;
-    return p.profile ? launch_gemm_pair<true>(ma, mb, msfa, msfb, md, p, st) : launch_gemm_pair<false>(ma, mb, msfa, msfb, md, p, st);
+#ifdef PB_DIAGNOSTICS
+    if (p.profile || p.diag) return launch_gemm_pair_uni<true>(ma, mb, msfa, msfb, md, p, st);
+#endif
+    return launch_gemm_pair_uni<false>(ma, mb, msfa, msfb, md, p, st);
   }
+#ifdef PB_DIAGNOSTICS
   if (p.profile) {
-    if (gp.BN == 224) return launch_gemm<224, true>(ma, mb, md, p, st);
-    return gp.BN == 256 ? launch_gemm<256, true>(ma, mb, md, p, st) : launch_gemm<128, true>(ma, mb, md, p, st);
+    if (gp.BN == 224) return launch_gemm_uni<224, true>(ma, mb, md, p, st);
+    return gp.BN == 256 ? launch_gemm_uni<256, true>(ma, mb, md, p, st) : launch_gemm_uni<128, true>(ma, mb, md, p, st);
   }
-  if (gp.BN == 224) return launch_gemm<224, false>(ma, mb, md, p, st);
-  return gp.BN == 256 ? launch_gemm<256, false>(ma, mb, md, p, st) : launch_gemm<128, false>(ma, mb, md, p, st);
+  if (gp.BN == 256) return launch_gemm_uni<256, false>(ma, mb, md, p, st);
+  if (gp.BN == 128) return launch_gemm_uni<128, false>(ma, mb, md, p, st);
+#endif
+  return launch_gemm_uni<224, false>(ma, mb, md, p, st);
 }
 
 extern "C" int pb_gemm_check(void* stream) {
@@ -1390,14 +1437,22 @@ extern "C" int pb_gemm_check(void* stream) {
   return PB_OK;
 }
 
-// Not part of the reference's surface: diagnostics.  Copies (and clears) the eight cycle
-// counters the GEMM kernel accumulates when the environment sets PB_GEMM_PROFILE=1.
+#ifdef PB_DIAGNOSTICS
+// Diagnostics build only (not part of the reference's surface, not in the product library).
+// Copies (and clears) the sixteen cycle counters the GEMM kernels accumulate under PB_GEMM_PROFILE=1.
 extern "C" PB_API int pb_debug_gemm_profile(unsigned long long* out16, void* stream) {
-  unsigned long long* out8 = out16;
-  if (!out8) return fail(PB_ERR_NULL_POINTER, "pb_debug_gemm_profile: out16 must be non-null");
+  if (!out16) return fail(PB_ERR_NULL_POINTER, "pb_debug_gemm_profile: out16 must be non-null");
   PB_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   unsigned long long zero[16] = {0};
-  PB_CUDA_TRY(cudaMemcpyFromSymbol(out8, g_gemm_prof, sizeof(zero)));
+  PB_CUDA_TRY(cudaMemcpyFromSymbol(out16, g_gemm_prof, sizeof(zero)));
   PB_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_prof, zero, sizeof(zero)));
   return PB_OK;
 }
+// Sets the poll budget of the bounded waits (0 restores the default) and the diagnostic bits of
+// GemmParams::diag (-1 hands them back to the environment) for the launches that follow.
+extern "C" PB_API int pb_debug_gemm_control(unsigned int polls, int diag) {
+  g_wait_polls.store(polls ? polls : kDefaultWaitPolls);
+  g_diag_bits.store(diag);
+  return PB_OK;
+}
+#endif

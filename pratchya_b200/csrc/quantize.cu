@@ -690,14 +690,14 @@ static int quantize_entry(const void* x, int x_dtype, int64_t batch, int64_t row
     const int64_t n_groups = batch * g.M;
     // 8 CTAs per SM, 16 once every warp then still gets three super-groups or more (measured: X[8192,2048] is
     // best at 8, X[32768,2048] and larger at 16); PB_QUANT_CTAS_PER_SM overrides
-    static const int forced_ctas = [] { const char* e = getenv("PB_QUANT_CTAS_PER_SM"); const int v = e ? atoi(e) : 0; return v > 0 ? v : 0; }();
+    static const int forced_ctas = [] { const int v = env_switch("PB_QUANT_CTAS_PER_SM", 0); return v > 0 ? v : 0; }();
     const int ctas_per_sm = forced_ctas ? forced_ctas : (n_groups >= (int64_t)sm_count() * 16 * (kRowThreads / 32) * 3 ? 16 : 8);
     const int grid = grid_for(n_groups * 32, kRowThreads, ctas_per_sm);
     // 40 registers per thread (6 CTAs of 256 threads per SM) measures the same as the compiler's
     // unconstrained 49; an unconstrained single CTA per SM (96 registers) is 15 % slower.
     const bool e4 = out_format == PB_E4M3;
 #define PB_ROW128_LAUNCH(KERNEL, XT, QT) KERNEL<<<grid, kRowThreads, 0, st>>>((const XT*)x, (QT*)q, sc8, sc32, n_groups, prep)
-    static const bool wide = [] { const char* e = getenv("PB_QUANT_WIDE"); return !(e && e[0] == '0'); }();
+    static const bool wide = env_switch("PB_QUANT_WIDE", 1) != 0;
     if (x_dtype == PB_BF16 && wide && (reinterpret_cast<uintptr_t>(x) & 31) == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0) {
       if (prep.sf) {
         if (e4) PB_ROW128_LAUNCH((quantize_row128_bf16_wide_kernel<PB_E4M3, 6, true>), uint8_t, uint4);

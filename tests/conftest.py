@@ -37,3 +37,12 @@ def built_lib():
     build()
     from pratchya_b200 import _lib
     return _lib.load()
+
+
+@pytest.fixture(scope="session")
+def diag_lib():
+    """Builds (if stale) and loads the diagnostics build of the library (test hooks, fault injection)."""
+    from pratchya_b200.csrc.build import build
+    build(diagnostics=True)
+    from pratchya_b200 import _lib
+    return _lib.load_diagnostics()

@@ -56,3 +56,20 @@ def assert_triple_equal(got, want, what=""):
     g32 = from_torch(g32) if not isinstance(g32, np.ndarray) else g32
     assert g32.shape == w32.shape, f"{what}: sc32 shape {g32.shape} vs {w32.shape}"
     assert np.array_equal(g32.view(np.uint32), w32.view(np.uint32)), f"{what}: fp32 scales differ"
+
+
+REL_TOL = 1e-2
+
+
+def check_close(got, ref, what):
+    ref = np.asarray(ref, dtype=np.float64)
+    got = np.asarray(got, dtype=np.float64)
+    assert got.shape == ref.shape, f"{what}: shape {got.shape} vs {ref.shape}"
+    scale = np.abs(ref).max()
+    err = np.abs(got - ref)
+    assert err.max() <= REL_TOL * scale, f"{what}: max abs err {err.max():.3e} vs scale {scale:.3e}"
+    big = np.abs(ref) > 0.05 * scale
+    if big.any():
+        rel = (err[big] / np.abs(ref[big])).max()
+        assert rel <= REL_TOL, f"{what}: max rel err {rel:.3e}"
+    return err.max() / scale

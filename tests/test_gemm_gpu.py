@@ -6,29 +6,12 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import BF16, bytes_of, from_torch, oracle, synth, to_torch
+from helpers import BF16, bytes_of, check_close, from_torch, oracle, synth, to_torch
 from pratchya_b200 import _lib
 from pratchya_b200._qualia import matmul_impl, quantize_impl, quantize_transposed_impl
 from pratchya_b200._qualia import _ops
 
 pytestmark = pytest.mark.gpu
-
-REL_TOL = 1e-2
-
-
-def check_close(got, ref, what):
-    ref = np.asarray(ref, dtype=np.float64)
-    got = np.asarray(got, dtype=np.float64)
-    assert got.shape == ref.shape, f"{what}: shape {got.shape} vs {ref.shape}"
-    scale = np.abs(ref).max()
-    err = np.abs(got - ref)
-    assert err.max() <= REL_TOL * scale, f"{what}: max abs err {err.max():.3e} vs scale {scale:.3e}"
-    big = np.abs(ref) > 0.05 * scale
-    if big.any():
-        rel = (err[big] / np.abs(ref[big])).max()
-        assert rel <= REL_TOL, f"{what}: max rel err {rel:.3e}"
-    return err.max() / scale
-
 
 def gpu_triple(x, grid):
     return quantize_impl(to_torch(x), grid)
