@@ -138,6 +138,19 @@ PB_API int pb_momentum_update(const void* gq, const uint8_t* g_sc8, const float*
                        float* c_out, void* new_mq, uint8_t* new_m_sc8, float* new_m_sc32,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same step for a stacked parameter [layers, rows, cols], the scanned branch of the reference's optimizer
+ * (pratchya/_nnx_impl/_optimizer.py:108-160), which every parameter of the model's scanned blocks takes: per layer
+ * g and m are dequantized to bfloat16 (:113-114), c and new_m are blended in bfloat16 (:123-124; the scalars
+ * become bfloat16, every product and sum rounds to bfloat16) and new_m is quantized again on (a,b) (:134).
+ * c_out_bf16 is bfloat16 [layers, rows, cols].  The four scalars are passed as f32 holding the bfloat16 values of
+ * beta and 1 - beta.  Super-groups never cross a layer.  Workspace: pb_momentum_workspace_size(layers, ...). */
+PB_API int pb_momentum_update_stacked(const void* gq, const uint8_t* g_sc8, const float* g_sc32,
+                               const void* mq, const uint8_t* m_sc8, const float* m_sc32,
+                               int64_t layers, int64_t rows, int64_t cols, int a, int b,
+                               float beta1, float one_minus_beta1, float beta2, float one_minus_beta2,
+                               void* c_out_bf16, void* new_mq, uint8_t* new_m_sc8, float* new_m_sc32,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- block-scaled FP8 matmul.
  * A GEMM operand is a K-major quantized matrix: bytes [rows, depth] (depth = the
  * contraction length, contiguous), one e8m0 byte per (row-block, 128-deep block)

@@ -302,3 +302,92 @@ def momentum_update(g_triple, m_triple, tgrid, beta1, beta2):
     new_m = (b2 * m + c2 * g).astype(np.float32)
     return c, quantize_impl(new_m, tgrid)
 
+
+
+def matmul_mixed_impl_bwd(res, g_out, grid_x):
+    """_qarr.py:654-675: gradients of Q @ dense; only the quantized side's is quantized."""
+    x_fp8, x_sc8, x_sc32, y_f32 = res
+    x = dequantize_impl(x_fp8, x_sc8, x_sc32, np.float32, grid_x)
+    g = np.asarray(g_out, dtype=np.float32)
+    gx = _reduce_broadcast(g @ np.swapaxes(np.asarray(y_f32, dtype=np.float32), -1, -2), x_fp8.shape)
+    gy = np.swapaxes(x, -1, -2) @ g
+    return quantize_impl(gx, grid_x), gy
+
+
+def rmatmul_mixed_impl_bwd(res, g_out, grid_y):
+    """_qarr.py:689-710: gradients of dense @ Q."""
+    x_f32, y_fp8, y_sc8, y_sc32 = res
+    y = dequantize_impl(y_fp8, y_sc8, y_sc32, np.float32, grid_y)
+    g = np.asarray(g_out, dtype=np.float32)
+    gx = g @ np.swapaxes(y, -1, -2)
+    gy = _reduce_broadcast(np.swapaxes(np.asarray(x_f32, dtype=np.float32), -1, -2) @ g, y_fp8.shape)
+    return gx, quantize_impl(gy, grid_y)
+
+
+def _elementwise_vjp(op: str, x, y, g):
+    """jax.vjp(op, x, y) applied to g (_qarr.py:732-733), restated from JAX's differentiation rules of the
+    lax primitives jnp.add / subtract / multiply / divide / floor_divide / mod / power lower to:
+    div -> (g / y, (-g * x) * y**-2); floor_divide ends in a rounding (no gradient); mod = rem(x, y)
+    (+ y where the signs differ), rem -> (g, -g * sign(x/y) * floor|x/y|); pow -> (g * y * x**(y-1)
+    with 0 at y == 0, g * log(x or 1) * x**y)."""
+    f = np.float32
+    with np.errstate(all="ignore"):
+        if op == "add":
+            return g, g
+        if op == "sub":
+            return g, -g
+        if op == "mul":
+            return (g * y).astype(f), (x * g).astype(f)
+        if op == "truediv":
+            return (g / y).astype(f), (((-g) * x).astype(f) * (f(1.0) / (y * y).astype(f)).astype(f)).astype(f)
+        if op == "floordiv":
+            return np.zeros_like(g), np.zeros_like(g)
+        if op == "mod":
+            q = (x / y).astype(f)
+            rem = np.fmod(x, y).astype(f)
+            plus = ((rem < 0) != (y < 0)) & (rem != 0)
+            gy = ((-g) * (np.sign(q) * np.floor(np.abs(q))).astype(f)).astype(f)
+            return g, np.where(plus, (gy + g).astype(f), gy).astype(f)
+        if op == "pow":
+            ans = np.power(x, y).astype(f)
+            jac = np.where(y == 0, f(0.0), (y * np.power(x, (y - f(1.0)).astype(f)).astype(f)).astype(f)).astype(f)
+            safe_x = np.where(x == 0, f(1.0), x).astype(f)
+            return (g * jac).astype(f), (g * (np.log(safe_x).astype(f) * ans).astype(f)).astype(f)
+    raise ValueError(op)
+
+
+def elementwise_impl_bwd(op: str, res, g_out, tgrid):
+    """_qarr.py:727-752: the backward half of an elementwise impl: both gradients as fp8 triples."""
+    x_fp8, x_sc8, x_sc32, y_fp8, y_sc8, y_sc32 = res
+    x = dequantize_impl(x_fp8, x_sc8, x_sc32, np.float32, tgrid)
+    y = dequantize_impl(y_fp8, y_sc8, y_sc32, np.float32, tgrid)
+    g = np.asarray(g_out, dtype=np.float32)
+    gx, gy = _elementwise_vjp(op, x, y, g)
+    full = np.broadcast_shapes(g.shape, x.shape, y.shape)
+    gx = _reduce_broadcast(np.broadcast_to(gx, full), x_fp8.shape)
+    gy = _reduce_broadcast(np.broadcast_to(gy, full), y_fp8.shape)
+    return quantize_impl(np.ascontiguousarray(gx, dtype=np.float32), tgrid), quantize_impl(np.ascontiguousarray(gy, dtype=np.float32), tgrid)
+
+
+def momentum_update_stacked(g_triple, m_triple, tgrid, beta1, beta2):
+    """The momentum step for a stacked (3-D) quantized parameter, pratchya/_nnx_impl/_optimizer.py:108-160:
+    per leading index (lax.scan, :144) gradient and momentum are dequantized to bfloat16 (:113-114), blended in
+    bfloat16, c = beta1*m + (1-beta1)*g (:123) and new_m = beta2*m + (1-beta2)*g (:124), and new_m is quantized again
+    on the parameter's grid (:134; QArrayImpl casts it to f32 first, _qarr.py:29).
+    Arithmetic as jax.numpy defines it for bfloat16 arrays and weakly typed Python scalars: the scalars beta and
+    1.0 - beta (computed in double) become bfloat16, and every multiply and add rounds its result to bfloat16.
+    UNPINNED: XLA is free to keep such intermediates in f32 (xla_allow_excess_precision); the reference ships
+    no output that says which.  Returns (c bf16 [L, R, C], new_m triple with leading dim L)."""
+    gq, g8, g32 = g_triple
+    mq, m8, m32 = m_triple
+    cs, parts = [], []
+    b1, c1 = BF16(beta1), BF16(1.0 - beta1)
+    b2, c2 = BF16(beta2), BF16(1.0 - beta2)
+    for i in range(np.asarray(gq).shape[0]):
+        g = dequantize_impl(gq[i], g8[i], g32[i], BF16, tgrid)
+        m = dequantize_impl(mq[i], m8[i], m32[i], BF16, tgrid)
+        c = ((b1 * m).astype(BF16) + (c1 * g).astype(BF16)).astype(BF16)
+        new_m = ((b2 * m).astype(BF16) + (c2 * g).astype(BF16)).astype(BF16)
+        cs.append(c)
+        parts.append(quantize_impl(new_m.astype(np.float32), tgrid))
+    return np.stack(cs), tuple(np.stack([p[j] for p in parts]) for j in range(3))

@@ -58,6 +58,8 @@ _SIGNATURES = {
     "pb_momentum_workspace_size": (_sz, [_i64, _i64, _i64, _int, _int]),
     "pb_momentum_update": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _int,
                                   C.c_float, C.c_float, C.c_float, C.c_float, _ptr, _ptr, _ptr, _ptr, _ptr, _sz, _ptr]),
+    "pb_momentum_update_stacked": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _int,
+                                          C.c_float, C.c_float, C.c_float, C.c_float, _ptr, _ptr, _ptr, _ptr, _ptr, _sz, _ptr]),
     "pb_fake_quantize": (_int, [_ptr, _int, _i64, _i64, _i64, _int, _int, _int, _ptr, _int, _ptr]),
     "pb_gemm_check": (_int, [_ptr]),
     "pb_transpose_bytes": (_int, [_ptr, _i64, _i64, _ptr, _ptr]),

@@ -210,6 +210,22 @@ def dequantize_impl_bwd(sc_fp8: torch.Tensor, sc_fp32: torch.Tensor, g_out: torc
     return out.to(g_out.dtype)
 
 
+def quantize_impl_bwd(g_out, tgrid):
+    """Cotangent rule of quantize_impl, _qarr.py:514-526.  `g_out` is the cotangent of the quantized
+    triple: a dense array (any dtype but e4m3) passes through unchanged (:519-520); an e4m3 triple
+    (value, sc_fp8, sc_fp32) is dequantized to f32 after the NaN bytes (0xFF) of its e8m0 scales have
+    been replaced by 1.0 (byte 127) (:522-526)."""
+    if not isinstance(g_out, (tuple, list)):
+        return g_out
+    g_fp8, g_sc8, g_sc32 = g_out
+    if g_fp8.dtype != E4M3:
+        return g_fp8
+    _require_cuda(g_fp8, "quantize_impl_bwd cotangent")
+    b8 = g_sc8.contiguous().view(torch.uint8)
+    b8 = torch.where(b8 == 0xFF, torch.full_like(b8, 127), b8).view(E8M0)      # one byte per block: 1/128 of the data
+    return dequantize_impl(g_fp8, b8, g_sc32, torch.float32, tgrid)
+
+
 # ---- matmuls ---------------------------------------------------------------------------
 
 def _tensor_core_eligible(x_fp8, y_fp8, grid_x, grid_y) -> bool:
@@ -376,6 +392,96 @@ def rmatmul_mixed_impl(x_f32, y_fp8, y_sc8, y_sc32, block_grid_y):
     return _matmul_f32(x_f32.to(torch.float32), y)
 
 
+def reduce_broadcast(g: torch.Tensor, target_shape) -> torch.Tensor:
+    """_qarr.py:624-632: sums the leading dims `g` has on top of `target_shape`, and the dims where the
+    target has extent 1, then reshapes to the target."""
+    target_shape = tuple(target_shape)
+    if tuple(g.shape) == target_shape:
+        return g
+    lead = g.dim() - len(target_shape)
+    axes = list(range(lead))
+    for i, (gs, ts) in enumerate(zip(g.shape[lead:], target_shape)):
+        if ts == 1 and gs > 1:
+            axes.append(lead + i)
+    return g.sum(dim=tuple(axes)).reshape(target_shape) if axes else g.reshape(target_shape)
+
+
+def matmul_impl_bwd(block_grid_x, block_grid_y, res, g_out):
+    """_qarr.py:616-640: with the saved triples dequantized, g_x = g @ y^T and g_y = x^T @ g as f32
+    dots (the cotangent `g_out` is dense here, so this is the reference's literal recipe on a library
+    f32 matmul; the tensor-core recipe that quantizes g is `linear_fp8` / `fp8_matmul_bwd`), leading
+    dims reduced, both results returned as fp8 triples on their operand's grid."""
+    x_fp8, x_sc8, x_sc32, y_fp8, y_sc8, y_sc32 = res
+    x = dequantize_impl(x_fp8, x_sc8, x_sc32, torch.float32, block_grid_x)
+    y = dequantize_impl(y_fp8, y_sc8, y_sc32, torch.float32, block_grid_y)
+    g = g_out.to(torch.float32)
+    g_x = reduce_broadcast(_matmul_f32(g, y.transpose(-1, -2)), x_fp8.shape)
+    g_y = reduce_broadcast(_matmul_f32(x.transpose(-1, -2), g), y_fp8.shape)
+    return (*quantize_impl(g_x, block_grid_x), *quantize_impl(g_y, block_grid_y))
+
+
+def matmul_mixed_impl_bwd(block_grid_x, res, g_out):
+    """_qarr.py:654-675: only the quantized side's gradient is quantized."""
+    x_fp8, x_sc8, x_sc32, y_f32 = res
+    x = dequantize_impl(x_fp8, x_sc8, x_sc32, torch.float32, block_grid_x)
+    g = g_out.to(torch.float32)
+    g_x = reduce_broadcast(_matmul_f32(g, y_f32.to(torch.float32).transpose(-1, -2)), x_fp8.shape)
+    g_y = _matmul_f32(x.transpose(-1, -2), g)
+    return (*quantize_impl(g_x, block_grid_x), g_y)
+
+
+def rmatmul_mixed_impl_bwd(block_grid_y, res, g_out):
+    """_qarr.py:689-710."""
+    x_f32, y_fp8, y_sc8, y_sc32 = res
+    y = dequantize_impl(y_fp8, y_sc8, y_sc32, torch.float32, block_grid_y)
+    g = g_out.to(torch.float32)
+    g_x = _matmul_f32(g, y.transpose(-1, -2))
+    g_y = reduce_broadcast(_matmul_f32(x_f32.to(torch.float32).transpose(-1, -2), g), y_fp8.shape)
+    return (g_x, *quantize_impl(g_y, block_grid_y))
+
+
+def _elementwise_vjp(op, x, y, g):
+    """(g_x, g_y) of op(x, y) under JAX's differentiation rules for the lax primitives the
+    reference's jnp functions lower to (jax.vjp(op, x, y) at _qarr.py:732-733), in f32."""
+    if op is torch.add:
+        return g, g
+    if op is torch.sub:
+        return g, -g
+    if op is torch.mul:
+        return g * y, x * g
+    if op is torch.div:                   # div: g / y and (-g * x) * y**-2
+        return g / y, ((-g) * x) * (1.0 / (y * y))
+    if op is torch.floor_divide:          # ends in a rounding: no gradient flows
+        return torch.zeros_like(g), torch.zeros_like(g)
+    if op is torch.remainder:             # rem(x, y), plus y where the signs differ
+        q = x / y
+        rem = torch.fmod(x, y)
+        plus = ((rem < 0) != (y < 0)) & (rem != 0)
+        g_y = (-g) * (torch.sign(q) * torch.floor(torch.abs(q)))
+        return g, torch.where(plus, g_y + g, g_y)
+    if op is torch.pow:
+        ans = torch.pow(x, y)
+        jac = torch.where(y == 0, torch.zeros_like(y), y * torch.pow(x, y - 1.0))
+        safe_x = torch.where(x == 0, torch.ones_like(x), x)
+        return g * jac, g * (torch.log(safe_x) * ans)
+    raise ValueError(f"no differentiation rule for {op}")
+
+
+def make_elementwise_impl_bwd(op):
+    """The backward half of make_elementwise_impl, _qarr.py:727-752: dequantize the saved operands,
+    pull the cotangent back through `op`, reduce broadcast dims, and return both gradients as fp8
+    triples on `tgrid`."""
+    def impl_bwd(tgrid, res, g_out):
+        x_fp8, x_sc8, x_sc32, y_fp8, y_sc8, y_sc32 = res
+        x = dequantize_impl(x_fp8, x_sc8, x_sc32, torch.float32, tgrid)
+        y = dequantize_impl(y_fp8, y_sc8, y_sc32, torch.float32, tgrid)
+        g_x, g_y = _elementwise_vjp(op, x, y, g_out.to(torch.float32))
+        g_x = reduce_broadcast(g_x.expand(torch.broadcast_shapes(g_x.shape, x.shape, y.shape)), x_fp8.shape)
+        g_y = reduce_broadcast(g_y.expand(torch.broadcast_shapes(g_y.shape, x.shape, y.shape)), y_fp8.shape)
+        return (*quantize_impl(g_x.contiguous(), tgrid), *quantize_impl(g_y.contiguous(), tgrid))
+    return impl_bwd
+
+
 _FUSED_OPS = {torch.add: 0, torch.sub: 1, torch.mul: 2, torch.div: 3}
 
 
@@ -411,3 +517,12 @@ truediv_impl = make_elementwise_impl(torch.div)
 floordiv_impl = make_elementwise_impl(torch.floor_divide)
 mod_impl = make_elementwise_impl(torch.remainder)
 pow_impl = make_elementwise_impl(torch.pow)
+
+
+add_impl_bwd = make_elementwise_impl_bwd(torch.add)
+mul_impl_bwd = make_elementwise_impl_bwd(torch.mul)
+sub_impl_bwd = make_elementwise_impl_bwd(torch.sub)
+truediv_impl_bwd = make_elementwise_impl_bwd(torch.div)
+floordiv_impl_bwd = make_elementwise_impl_bwd(torch.floor_divide)
+mod_impl_bwd = make_elementwise_impl_bwd(torch.remainder)
+pow_impl_bwd = make_elementwise_impl_bwd(torch.pow)

@@ -270,7 +270,34 @@ class QArrayImpl:
         return cls(out, _adapt_grid(grid, tuple(out.shape)))
 
 
-def fp8_matmul(x_f32, y_f32, tgrid=(1, 16)):
-    """_qarr.py:766-771 (forward value; the differentiable form is pratchya_b200.autograd.fp8_matmul)."""
+def _fp8_matmul_value(x_f32, y_f32, tgrid):
     out = QArrayImpl(x_f32, tgrid) @ QArrayImpl(y_f32, tgrid)
     return out.dequantize(torch.float32)
+
+
+def fp8_matmul_bwd(tgrid, res, g_out):
+    """_qarr.py:780-791: both gradients by the same quantized product, on the transposed dense inputs:
+    g_x = fp8_matmul(g, y^T), g_y = fp8_matmul(x^T, g)."""
+    x_f32, y_f32 = res
+    y_t = y_f32.transpose(-1, -2).contiguous()
+    x_t = x_f32.transpose(-1, -2).contiguous()
+    return _fp8_matmul_value(g_out, y_t, tgrid), _fp8_matmul_value(x_t, g_out, tgrid)
+
+
+class _Fp8MatmulFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_f32, y_f32, tgrid):
+        ctx.save_for_backward(x_f32, y_f32)         # the dense inputs are the residuals (:775-777)
+        ctx.tgrid = tgrid
+        return _fp8_matmul_value(x_f32, y_f32, tgrid)
+
+    @staticmethod
+    def backward(ctx, g_out):
+        g_x, g_y = fp8_matmul_bwd(ctx.tgrid, ctx.saved_tensors, g_out.contiguous())
+        return g_x, g_y, None
+
+
+def fp8_matmul(x_f32, y_f32, tgrid=(1, 16)):
+    """_qarr.py:766-793: dq(Q(x, t) @ Q(y, t)), differentiable in x and y with the reference's
+    custom VJP (fp8_matmul_bwd) instead of the derivative of the forward graph."""
+    return _Fp8MatmulFn.apply(x_f32, y_f32, (int(tgrid[0]), int(tgrid[1])))

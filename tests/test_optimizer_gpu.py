@@ -59,3 +59,33 @@ def test_lion_update_and_rejections(built_lib):
     b = QArrayImpl(p, (1, 128))
     with pytest.raises(ValueError):
         momentum_update(a, b, 0.9, 0.99)
+
+
+@pytest.mark.parametrize("shape,grid", [((24, 2048, 2048), (128, 128)), ((4, 256, 384), (128, 128)), ((3, 64, 256), (1, 128)), ((5, 48, 80), (16, 16)),
+                                        ((2, 128, 8), (128, 1))])
+def test_stacked_momentum_step_is_the_bf16_scan_of_the_reference(built_lib, shape, grid):
+    """pb_momentum_update_stacked against the oracle's restatement of the scanned branch for stacked parameters
+    (pratchya/_nnx_impl/_optimizer.py:108-160): bf16 dequantization, bf16 blend, re-quantization per layer.  Bit-exact:
+    c as bf16 bits, the new momentum as its triple."""
+    from pratchya_b200._nnx_impl import momentum_update_stacked
+    beta1, beta2 = 0.9, 0.99
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    g = torch.randn(shape, device="cuda", generator=gen) * 1e-3
+    m = torch.randn(shape, device="cuda", generator=gen) * 5e-4
+    m[0, : shape[1] // 2] = 0.0                       # a young momentum: zero blocks
+    gq, mq = QArrayImpl(g, grid), QArrayImpl(m, grid)
+    assert gq.sc_fp32.shape[0] == shape[0]            # quantized per layer
+    c, new_m = momentum_update_stacked(gq, mq, beta1, beta2)
+    assert c.dtype == torch.bfloat16 and tuple(c.shape) == shape
+    og = tuple(np.asarray(t) for t in np_triple(gq))
+    om = tuple(np.asarray(t) for t in np_triple(mq))
+    og = (og[0].view(oracle.E4M3), og[1], og[2])
+    om = (om[0].view(oracle.E4M3), om[1], om[2])
+    layers = range(shape[0]) if shape[0] <= 6 else (0, 7, 23)       # the large stack: three of its layers on the CPU
+    for i in layers:
+        oc, onm = oracle.momentum_update_stacked(tuple(t[i:i + 1] for t in og), tuple(t[i:i + 1] for t in om), grid, beta1, beta2)
+        assert np.array_equal(from_torch(c[i]).view(np.uint16), oc[0].view(np.uint16)), f"layer {i}: c differs from the oracle"
+        got = (bytes_of(new_m.get_value()[i]), bytes_of(new_m.sc_fp8[i]), from_torch(new_m.sc_fp32[i]))
+        assert_triple_equal(got, (onm[0][0].view(np.uint8), onm[1][0].view(np.uint8), onm[2][0]), f"layer {i}: new momentum vs oracle")
+    with pytest.raises(ValueError):
+        momentum_update_stacked(QArrayImpl(g[0], grid), QArrayImpl(m[0], grid), beta1, beta2)
