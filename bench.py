@@ -1,13 +1,20 @@
 #!/usr/bin/env python
 """Benchmark of the FP8 block-quantization hot path (one JSON line on stdout).
 
-Workload (per GPU, weak scaling): the block-scaled FP8 GEMM forward of BASELINE.json configs[1]
+Headline workload (per GPU, weak scaling): the block-scaled FP8 GEMM forward of BASELINE.json configs[1]
     X bf16 [8192, 2048] ~ N(0,1)  --(1,128) e4m3-->  Xq      (timed, every step)
     W bf16 [2048, 8192] ~ N(0,0.02), quantized (128,128) once (the layer holds it quantized)
     Y = dq(Xq) . dq(Wq), fp32 accumulation, bf16 [8192, 8192]    (timed, every step)
 A step is quantize(X) + GEMM; `value` is 2*M*N*K per step time, summed over ranks.
 Synthetic seeded inputs; the step rotates over several input/output buffer sets so that every
 step's data (201 MB per set, 800+ MB in rotation) comes from HBM, not from the 126 MB L2.
+
+Beside the headline the line carries
+    triple    (1 GPU)   configs[2]: forward + dgrad + wgrad with their quantizers at M = 32768, d_model 2048
+    scaleout  (every N) configs[3]: the same triple at d_model 4096, FFN 16384, M = 65536 rows SPLIT over the
+                        N GPUs (strong scaling, Student-t(3) activations, weights replicated, no collective)
+    roofline_quantize / roofline_transposed / roofline_dequantize   the HBM-bound kernels on X[32768,2048]
+    e2e       Linear.product with host buffers (X up, the quantized product down), with its copy-only ceiling
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 """
@@ -16,6 +23,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -61,7 +69,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -90,13 +98,7 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU reference arm
-def _use_all_host_threads():
-    """torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core."""
-    try:
-        from threadpoolctl import threadpool_limits
-        threadpool_limits(limits=os.cpu_count())
-    except Exception:
-        pass
+CPU_SAMPLE_ROWS = 2048      # a quarter of the workload's rows; W is the full [2048, 8192]
 
 
 def cpu_sample(rows: int, seed: int = 0):
@@ -115,49 +117,166 @@ def cpu_sample(rows: int, seed: int = 0):
     return dt, float(np.abs(y).max())
 
 
-CPU_SAMPLE_ROWS = 2048      # a quarter of the workload's rows; W is the full [2048, 8192]
+def _blas_threads():
+    try:
+        from threadpoolctl import threadpool_info
+        return max([int(p.get("num_threads", 1)) for p in threadpool_info()] or [1])
+    except Exception:
+        return None
 
 
-def cpu_baseline(budget_s: float = 12.0):
-    _use_all_host_threads()
+def run_cpu_child(args):
+    """The CPU pass proper, in a process whose BLAS thread count was set before numpy was imported (a
+    launcher such as torchrun exports OMP_NUM_THREADS=1 to its ranks, which numpy's BLAS reads at import).
+    `--steps K --warmup W`: W untimed passes, K timed ones; budget mode (--steps 0): passes for about 12 s."""
     rows = CPU_SAMPLE_ROWS
-    dt, _ = cpu_sample(rows)                      # warm-up / calibration
-    reps, total = 0, 0.0
-    while total < budget_s and reps < 50:
-        dt, _ = cpu_sample(rows, seed=reps + 1)
-        total += dt
-        reps += 1
-    per = total / reps
-    return {"value": 2 * rows * N * K / per / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+    for i in range(max(args.warmup, 1)):
+        cpu_sample(rows, seed=100 + i)
+    total, reps = 0.0, 0
+    if args.steps > 0:
+        for i in range(args.steps):
+            total += cpu_sample(rows, seed=i)[0]       # the pass itself: inputs are generated and the weight quantized outside the clock, as on the GPU arm
+        reps = args.steps
+    else:
+        while total < 12.0 and reps < 50:
+            total += cpu_sample(rows, seed=reps + 1)[0]
+            reps += 1
+    print(json.dumps({"seconds": total, "passes": reps, "rows": rows, "threads": _blas_threads(), "cores": os.cpu_count()}))
+    return 0
+
+
+def cpu_pass(steps: int, warmup: int):
+    env = dict(os.environ)
+    for v in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        env[v] = str(os.cpu_count() or 1)
+    r = subprocess.run([sys.executable, str(Path(__file__).resolve()), "--cpu-child", "--steps", str(steps), "--warmup", str(warmup)],
+                       env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900)
+    if r.returncode != 0:
+        raise RuntimeError(f"CPU pass failed: {r.stderr[-500:]}")
+    return json.loads(r.stdout.strip().splitlines()[-1])
+
+
+def cpu_baseline():
+    c = cpu_pass(0, 1)
+    per = c["seconds"] / c["passes"]
+    return {"value": 2 * c["rows"] * N * K / per / 1e12, "unit": "TFLOP/s", "cores": c["cores"], "threads": c["threads"], "kind": "port",
             "sample": f"oracle (numpy+ml_dtypes restatement; jax is not installed, so the reference's own JAX CPU path cannot run): "
-                      f"quantize X[{rows},{K}] + dequantize both operands + f32 matmul to [{rows},{N}], mean of {reps} passes, "
-                      f"numpy BLAS threads = all cores, elementwise part single-threaded"}
+                      f"quantize X[{c['rows']},{K}] + dequantize both operands + f32 matmul to [{c['rows']},{N}], mean of {c['passes']} passes, "
+                      f"numpy BLAS threads = {c['threads']}, elementwise part single-threaded"}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    _use_all_host_threads()
-    rows = CPU_SAMPLE_ROWS
-    for i in range(args.warmup):
-        cpu_sample(rows, seed=100 + i)
-    dt = 0.0
-    for i in range(args.steps):
-        dt += cpu_sample(rows, seed=i)[0]       # the pass itself: inputs are generated and the weight quantized outside the clock, as on the GPU arm
-    val = 2 * rows * N * K * args.steps / dt / 1e12
-    cb = {"value": val, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
-          "sample": f"each step = oracle pass over a {rows}-row sample of X (quantize + dequantize + f32 matmul against the full W[{K},{N}])"}
+    c = cpu_pass(max(args.steps, 1), args.warmup)
+    rows, dt = c["rows"], c["seconds"]
+    val = 2 * rows * N * K * c["passes"] / dt / 1e12
+    cb = {"value": val, "unit": "TFLOP/s", "cores": c["cores"], "threads": c["threads"], "kind": "port",
+          "sample": f"each step = oracle pass over a {rows}-row sample of X (quantize + dequantize + f32 matmul against the full W[{K},{N}]); "
+                    f"run in a child process with the BLAS thread count set to all cores before numpy is imported"}
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": dt / c["passes"] * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "sample_rows": rows},
         "cpu_baseline": cb, "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
     return 0
 
 
+# --------------------------------------------------------------------------- the training triple (configs[2], configs[3])
+def student_t3(shape, gen, device):
+    """Student-t with 3 degrees of freedom from seeded normals: z / sqrt(chi2_3 / 3)."""
+    import torch
+    z = torch.randn(shape, device=device, generator=gen)
+    chi = torch.zeros(shape, device=device)
+    for _ in range(3):
+        chi += torch.randn(shape, device=device, generator=gen) ** 2
+    return z / (chi / 3.0).sqrt()
+
+
+def time_triple(tokens: int, d_model: int, ffn: int, dist: str, seed: int, reps: int, sync):
+    """forward + dgrad + wgrad of the six projections of one block (4 x [d,d], [d,ffn], [ffn,d]) on `tokens` rows with
+    their quantizers: per projection quantize_dual(x) -> fwd GEMM (bf16 Y), quantize_dual(dY) -> dgrad GEMM (bf16 dX)
+    and wgrad GEMM (f32 dW, contraction over the tokens).  Weights are held quantized (quantized once, outside the
+    clock, as the layer holds them).  Returns milliseconds per triple (all six projections) with and without the
+    quantizers, timed with CUDA events after warm-up; `sync` is called on both sides of each timed region."""
+    import torch
+    from pratchya_b200 import _lib
+    from pratchya_b200._qualia import _ops
+    lib = _lib.load()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    stream = torch.cuda.current_stream().cuda_stream
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    op = _ops._operand
+    shapes = [(d_model, d_model), (d_model, ffn), (ffn, d_model)]
+    counts = [4, 1, 1]
+    total_ms, gemm_ms, per_shape = 0.0, 0.0, {}
+    for (k_in, n_out), count in zip(shapes, counts):
+        x = (student_t3((tokens, k_in), gen, dev) if dist == "student_t" else torch.randn(tokens, k_in, device=dev, generator=gen)).to(torch.bfloat16)
+        dy = (torch.randn(tokens, n_out, device=dev, generator=gen) * 1e-3).to(torch.bfloat16)
+        w = (torch.randn(k_in, n_out, device=dev, generator=torch.Generator(device=dev).manual_seed(7 + k_in + n_out)) * 0.02).to(torch.bfloat16)
+        wq = _ops.quantize_impl(w, (128, 128))
+        wt = _ops.transpose_bytes(wq[0])
+
+        def gemms(xq, xt, gq, gt):
+            y = _ops.gemm_tn(op(xq[0], xq[1], xq[2], tokens, k_in, (1, 128)), op(wt, wq[1], wq[2], n_out, k_in, (128, 128), 1), torch.bfloat16, dev)
+            dx = _ops.gemm_tn(op(gq[0], gq[1], gq[2], tokens, n_out, (1, 128)), op(wq[0], wq[1], wq[2], k_in, n_out, (128, 128)), torch.bfloat16, dev)
+            dw = _ops.gemm_tn(op(xt[0], xt[1], xt[2], k_in, tokens, (1, 128)), op(gt[0], gt[1], gt[2], n_out, tokens, (1, 128)), torch.float32, dev)
+            return y, dx, dw
+
+        def full():
+            xq, xt = _ops.quantize_dual_impl(x)
+            gq, gt = _ops.quantize_dual_impl(dy)
+            return gemms(xq, xt, gq, gt)
+
+        def timed(fn):
+            for _ in range(2):
+                fn()
+            sync()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            sync()
+            _lib.check(lib.pb_gemm_check(stream))
+            return a.elapsed_time(b) / reps
+
+        t_full = timed(full)
+        xq, xt = _ops.quantize_dual_impl(x)
+        gq, gt = _ops.quantize_dual_impl(dy)
+        t_gemm = timed(lambda: gemms(xq, xt, gq, gt))
+        per_shape[f"{k_in}->{n_out}"] = {"ms": t_full, "gemm_ms": t_gemm, "tflops": 6.0 * tokens * k_in * n_out / t_full / 1e9,
+                                         "gemm_tflops": 6.0 * tokens * k_in * n_out / t_gemm / 1e9}
+        total_ms += count * t_full
+        gemm_ms += count * t_gemm
+        del x, dy, w, wq, wt, xq, xt, gq, gt
+        torch.cuda.empty_cache()
+    flop = 6.0 * tokens * (4 * d_model * d_model + 2 * d_model * ffn)
+    return {"ms": total_ms, "gemm_ms": gemm_ms, "flop": flop, "per_projection": per_shape}
+
+
 # --------------------------------------------------------------------------- GPU arm
+def gpu_cpu_affinity(index: int):
+    """The CPU set `nvidia-smi topo -m` lists for this GPU (read only), or None."""
+    try:
+        out = subprocess.run(["nvidia-smi", "topo", "-m"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, timeout=20).stdout
+    except (OSError, subprocess.TimeoutExpired):
+        return None
+    for line in out.splitlines():
+        if re.match(rf"\s*GPU{index}\s", line):
+            m = re.search(r"\s(\d+(?:-\d+)?(?:,\d+(?:-\d+)?)*)\s+(\d+|N/A)\s", line + " ")
+            if not m:
+                return None
+            cpus = set()
+            for part in m.group(1).split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+            return cpus
+    return None
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -172,6 +291,13 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device: the pratchya_b200 ops have no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # pinned host buffers are allocated by a process that sits on the CPUs next to its GPU
+    affinity = gpu_cpu_affinity(local)
+    if affinity:
+        try:
+            os.sched_setaffinity(0, affinity & os.sched_getaffinity(0) or os.sched_getaffinity(0))
+        except OSError:
+            affinity = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
@@ -262,95 +388,140 @@ def run_ours(args):
 
     # the same K steps once more with an event after every launch, for the per-kernel durations
     # (an event between two launches costs the step ~6 %, so it stays out of the timed region)
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
+    n_parts = min(args.steps, 200)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * n_parts + 1)]
     ev[0].record()
-    for i in range(args.steps):
+    for i in range(n_parts):
         quantize(i % NBUF)
         ev[2 * i + 1].record()
         gemm(i % NBUF)
         ev[2 * i + 2].record()
     barrier()
-    q_ms = statistics.mean(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(args.steps))
-    g_ms = statistics.mean(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps))
+    q_ms = statistics.mean(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(n_parts))
+    g_ms = statistics.mean(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(n_parts))
     _lib.check(lib.pb_gemm_check(stream))
 
-    # ---- quantizer alone on the largest activation of the training configs (HBM-bound, 202 MB per launch)
+    # ---- the HBM-bound kernels alone on the largest activation of the training configs (202 MB per launch)
     qm, qk = 32768, 2048
     big = [torch.randn(qm, qk, device=dev, dtype=torch.bfloat16) for _ in range(2)]
     bq = torch.empty(qm, qk, device=dev, dtype=torch.uint8)
     b8 = torch.empty(qm * qk // 128, device=dev, dtype=torch.uint8)
     b32 = torch.empty(qm * qk // 1024, device=dev, dtype=torch.float32)
+    bqt = torch.empty(qk, qm, device=dev, dtype=torch.uint8)
+    back = [torch.empty(qm, qk, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    tws_bytes = lib.pb_quantize_transposed_workspace_size(1, qm, qk, 128)
+    tws = torch.empty(max(tws_bytes, 16), device=dev, dtype=torch.uint8)
 
     def big_quant(i):
         _lib.check(lib.pb_quantize(big[i % 2].data_ptr(), _lib.PB_BF16, 1, qm, qk, 1, 128, _lib.PB_E4M3,
                                    bq.data_ptr(), b8.data_ptr(), b32.data_ptr(), None, 0, stream))
-    for i in range(3):
-        big_quant(i)
-    torch.cuda.synchronize()
-    qe = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    reps = 20
-    qe[0].record()
-    for i in range(reps):
-        big_quant(i)
-    qe[1].record()
-    torch.cuda.synchronize()
-    big_q_ms = qe[0].elapsed_time(qe[1]) / reps
-    quant_bytes = qm * qk * QUANT_BYTES_PER_ELEM
 
-    # ---- end to end through the public API with host buffers: every step copies its X from pinned
-    # host memory and its Y back to pinned host memory.  Copies run on their own streams, so step
-    # i+1's upload and step i-1's download overlap step i's kernels (two buffer sets).
+    def big_quant_t(i):
+        _lib.check(lib.pb_quantize_transposed(big[i % 2].data_ptr(), _lib.PB_BF16, 1, qm, qk, 128, _lib.PB_E4M3,
+                                              bqt.data_ptr(), b8.data_ptr(), b32.data_ptr(), tws.data_ptr(), tws_bytes, stream))
+
+    def big_dequant(i):
+        _lib.check(lib.pb_dequantize(bq.data_ptr(), _lib.PB_E4M3, b8.data_ptr(), b32.data_ptr(), 1, qm, qk, 1, 128,
+                                     _lib.PB_BF16, back[i % 2].data_ptr(), stream))
+
+    def time_alone(fn, reps=20):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        e[0].record()
+        for i in range(reps):
+            fn(i)
+        e[1].record()
+        torch.cuda.synchronize()
+        return e[0].elapsed_time(e[1]) / reps
+
+    big_qt_ms = time_alone(big_quant_t)
+    big_q_ms = time_alone(big_quant)          # leaves the row form's triple in (bq, b8, b32) for the dequantizer
+    big_dq_ms = time_alone(big_dequant)
+    quant_bytes = qm * qk * QUANT_BYTES_PER_ELEM
+    del big, bq, bqt, back, tws
+
+    # ---- end to end through the public API with host buffers: every step copies its X from pinned host
+    # memory, runs Linear.product (quantize, GEMM, and the (1,128) re-quantization of the product that the
+    # reference's `x_q @ kernel` returns), and copies that quantized product -- bytes and both scale arrays --
+    # back to pinned host memory.  Copies run on their own streams over two buffer sets, so step i+1's
+    # upload and step i-1's download overlap step i's kernels; the same copies without any kernel give
+    # the ceiling the host side allows.
     x_host = [x.cpu().pin_memory() for x in xs[:2]]
-    y_host = [torch.empty(M, N, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    yq_host = [torch.empty(M, N, dtype=torch.uint8).pin_memory() for _ in range(2)]
+    y8_host = [torch.empty(M * N // 128, dtype=torch.uint8).pin_memory() for _ in range(2)]
+    y32_host = [torch.empty(M * N // 1024, dtype=torch.float32).pin_memory() for _ in range(2)]
     x_dev = [torch.empty(M, K, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    d2h_bytes = M * N + M * N // 128 + 4 * (M * N // 1024)
     cur = torch.cuda.current_stream()
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     in_ready = [torch.cuda.Event() for _ in range(2)]
     cmp_done = [torch.cuda.Event() for _ in range(2)]
     out_done = [torch.cuda.Event() for _ in range(2)]
+    last = [None, None]
 
-    def e2e_step(i, overlap):
+    def download(b, yq):
+        yq_host[b].copy_(yq.get_value().view(torch.uint8), non_blocking=True)
+        y8_host[b].copy_(yq.sc_fp8.view(torch.uint8).reshape(-1), non_blocking=True)
+        y32_host[b].copy_(yq.sc_fp32.reshape(-1), non_blocking=True)
+
+    def e2e_step(i, compute=True):
         b = i % 2
-        if not overlap:
-            x_dev[b].copy_(x_host[b], non_blocking=True)
-            y = layer.matmul(x_dev[b], out_dtype=torch.bfloat16)
-            y_host[b].copy_(y, non_blocking=True)
-            return
         with torch.cuda.stream(s_in):
             s_in.wait_event(cmp_done[b])            # the kernels of step i-2 have read x_dev[b]
             x_dev[b].copy_(x_host[b], non_blocking=True)
             in_ready[b].record(s_in)
         cur.wait_event(in_ready[b])
-        y = layer.matmul(x_dev[b], out_dtype=torch.bfloat16)
+        if compute:
+            last[b] = layer.product(x_dev[b])
+        yq = last[b]
         cmp_done[b].record(cur)
         with torch.cuda.stream(s_out):
             s_out.wait_event(cmp_done[b])
-            s_out.wait_event(out_done[b])           # y_host[b] of step i-2 has been written
-            y_host[b].copy_(y, non_blocking=True)
+            s_out.wait_event(out_done[b])           # the host buffers of step i-2 have been written
+            download(b, yq)
             out_done[b].record(s_out)
-        y.record_stream(s_out)
+        for t in (yq.get_value(), yq.sc_fp8, yq.sc_fp32):
+            t.record_stream(s_out)
 
     e2e_steps = max(4, min(args.steps, 10))
 
-    def e2e_time(overlap):
+    def e2e_time(compute):
         for i in range(2):
-            e2e_step(i, overlap)
+            e2e_step(i, compute)
         cur.wait_stream(s_out)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(e2e_steps):
-            e2e_step(i, overlap)
+            e2e_step(i, compute)
         cur.wait_stream(s_in)
         cur.wait_stream(s_out)
         e1.record()
         barrier()
         return e0.elapsed_time(e1) / e2e_steps
 
-    # best of three passes per mode: the host side of these copies (shared PCIe switch, other tenants) is noisy
-    e2e_serial_ms = min(e2e_time(False) for _ in range(3))
-    e2e_overlap_ms = min(e2e_time(True) for _ in range(3))
-    e2e_ms = min(e2e_serial_ms, e2e_overlap_ms)
+    # median of five passes: the host side of these copies (shared PCIe switch, other tenants) is noisy
+    e2e_runs = [e2e_time(True) for _ in range(5)]
+    e2e_ms = statistics.median(e2e_runs)
+    copy_only_ms = statistics.median(e2e_time(False) for _ in range(3))
+    _lib.check(lib.pb_gemm_check(stream))
+
+    # ---- the training triple: configs[2] on one GPU, and configs[3] split by rows over all the ranks
+    def local_sync():
+        torch.cuda.synchronize()
+
+    triple = time_triple(32768, 2048, 8192, "normal", 99, reps=5, sync=local_sync) if world == 1 else None
+    so_tokens, so_d, so_ffn = 65536, 4096, 16384
+    scale = time_triple(so_tokens // world, so_d, so_ffn, "student_t", 500 + rank, reps=3, sync=barrier)
+    one_gpu = scale if world == 1 else None
+    if world > 1:
+        # rank 0 alone repeats the whole 65536-row job, so that the line carries its own 1-GPU time
+        barrier()
+        if rank == 0:
+            one_gpu = time_triple(so_tokens, so_d, so_ffn, "student_t", 500, reps=2, sync=local_sync)
+        barrier()
 
     # ---- last, because it leaves the GPU at its power cap: the same step back to back for about a second
     sustained = None
@@ -363,7 +534,7 @@ def run_ours(args):
         if rank == 0:
             s_sampler.start()
         se = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        n_sus = int(1.2 / (total_ms / args.steps * 1e-3))
+        n_sus = int(1.2 / 0.000135)
         se[0].record()
         for i in range(n_sus // 3):
             step(i)
@@ -378,16 +549,25 @@ def run_ours(args):
                      "steps": n_sus - n_sus // 3, "clocks": s_clocks}
         _lib.check(lib.pb_gemm_check(stream))
 
-    times = torch.tensor([total_ms, e2e_ms, g_ms, q_ms, big_q_ms], device=dev, dtype=torch.float64)
+    times = torch.tensor([total_ms, e2e_ms, g_ms, q_ms, big_q_ms, big_qt_ms, big_dq_ms, copy_only_ms, scale["ms"], scale["gemm_ms"]],
+                         device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, g_ms, q_ms, big_q_ms = times.tolist()
+    total_ms, e2e_ms, g_ms, q_ms, big_q_ms, big_qt_ms, big_dq_ms, copy_only_ms, scale_ms, scale_gemm_ms = times.tolist()
 
     if rank == 0:
         peaks = load_peaks()
         ms_per_step = total_ms / args.steps
         fp8_peak = 2.0 * peaks["bf16_tflops"]
         gemm_tflops = FLOP_PER_STEP / (g_ms * 1e-3) / 1e12
+
+        def hbm(kernel, ms, traffic=None):
+            gbs = quant_bytes / (ms * 1e-3) / 1e9
+            return {"bound": "hbm", "kernel": kernel, "workload": f"X[{qm},{qk}] bf16", "achieved": gbs, "peak": peaks["hbm_gbs"],
+                    "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": traffic, "us": ms * 1e3,
+                    "peak_source": f"hbm_gbs of {peaks['source']}"}
+
+        so_flop = 6.0 * so_tokens * (4 * so_d * so_d + 2 * so_d * so_ffn)
         out = {
             "metric": METRIC, "value": world * FLOP_PER_STEP / (ms_per_step * 1e-3) / 1e12, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
@@ -406,17 +586,34 @@ def run_ours(args):
                          "frac": gemm_tflops / fp8_peak, "traffic": GEMM_DRAM_TRAFFIC_BYTES,
                          "peak_source": f"2 x bf16_tflops burst of {peaks['source']} (no FP8 figure is measured); nominal dense FP8 is 4500",
                          "frac_of_nominal_4500": gemm_tflops / 4500.0},
-            "roofline_quantize": {"bound": "hbm", "kernel": "quantize_row128_bf16_kernel", "workload": f"X[{qm},{qk}] bf16",
-                                  "achieved": quant_bytes / (big_q_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                  "frac": quant_bytes / (big_q_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": QUANT_DRAM_TRAFFIC_BYTES,
-                                  "peak_source": f"hbm_gbs of {peaks['source']}"},
+            "roofline_quantize": hbm("quantize_row128_bf16_kernel", big_q_ms, QUANT_DRAM_TRAFFIC_BYTES),
+            "roofline_transposed": hbm("transpose_quantize1024_bf16_kernel", big_qt_ms),
+            "roofline_dequantize": hbm("dequantize_row128_kernel", big_dq_ms),
             "e2e": {"value": world * FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
-                    "api": "pratchya_b200._nnx_impl.Linear.matmul on a device copy of pinned host X; Y copied back to pinned host memory; "
-                           "uploads and downloads on their own streams, two buffer sets",
-                    "ms_per_step_without_overlap": e2e_serial_ms, "ms_per_step_with_overlap": e2e_overlap_ms},
+                    "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": d2h_bytes,
+                    "api": "pratchya_b200._nnx_impl.Linear.product (= QArrayImpl(x,(1,128)) @ kernel, the (1,128)-quantized product the "
+                           "reference's __matmul__ returns) on a device copy of pinned host X; the product's fp8 bytes and both scale arrays "
+                           "copied back to pinned host memory; uploads and downloads on their own streams, two buffer sets",
+                    "ms_per_step_runs": e2e_runs, "statistic": "median of 5 passes",
+                    "copy_only_ms": copy_only_ms, "frac_of_copy_only": copy_only_ms / e2e_ms,
+                    "cpu_affinity": (f"{min(affinity)}-{max(affinity)} ({len(affinity)} CPUs, from nvidia-smi topo -m)" if affinity else None)},
+            "scaleout": {"workload": "configs[3]: training triple (fwd+dgrad+wgrad with quantizers) at d_model 4096, FFN 16384, "
+                                     f"M = {so_tokens} tokens split by rows over {world} GPU(s), X ~ Student-t(3), weights replicated, no collective",
+                         "scaling": "strong", "rows_per_gpu": so_tokens // world, "ms": scale_ms, "gemm_only_ms": scale_gemm_ms,
+                         "tflops_aggregate": so_flop / scale_ms / 1e9, "tflops_per_gpu": so_flop / scale_ms / 1e9 / world,
+                         "gemm_only_tflops_per_gpu": so_flop / scale_gemm_ms / 1e9 / world,
+                         "one_gpu_ms": one_gpu["ms"] if one_gpu else None,
+                         "speedup_vs_one_gpu": (one_gpu["ms"] / scale_ms) if one_gpu else None,
+                         "timing": "CUDA events, max over ranks; the 1-GPU time is rank 0 running all rows alone in the same process",
+                         "per_projection_rank0": scale["per_projection"]},
             "clocks": clocks,
+            "clock_note": "the timed region of K steps is shorter than one sampling period unless K is large: the samples bracket it; "
+                          "`sustained` carries the clocks seen inside a second-long run of the same step",
         }
+        if triple is not None:
+            out["triple"] = {"workload": "configs[2]: fwd+dgrad+wgrad of 4x[2048->2048], [2048->8192], [8192->2048] at M = 32768 tokens, dY e4m3",
+                             "ms": triple["ms"], "gemm_only_ms": triple["gemm_ms"], "tflops": triple["flop"] / triple["ms"] / 1e9,
+                             "gemm_only_tflops": triple["flop"] / triple["gemm_ms"] / 1e9, "per_projection": triple["per_projection"]}
         if sustained is not None:
             out["sustained"] = dict(sustained, peak=2.0 * peaks["bf16_tflops_sustained"],
                                     peak_source="2 x bf16_tflops_sustained of " + peaks["source"],
@@ -433,12 +630,16 @@ def run_profile_case(name: str):
     """A few launches of one kernel on a reduced case, for `ncu --set full` captures
     (not a benchmark: prints nothing that is a result)."""
     import torch
-    from pratchya_b200._qualia import _ops, quantize_impl
+    from pratchya_b200._qualia import _ops, quantize_impl, quantize_transposed_impl
     torch.cuda.set_device(0)
     if name == "quantize":
         x = torch.randn(16384, 4096, device="cuda", dtype=torch.bfloat16)      # 134 MB in: larger than L2
         for _ in range(4):
             quantize_impl(x, (1, 128))
+    elif name == "transposed":
+        x = torch.randn(16384, 4096, device="cuda", dtype=torch.bfloat16)
+        for _ in range(4):
+            quantize_transposed_impl(x, 128)
     elif name == "dequantize":
         x = torch.randn(16384, 4096, device="cuda", dtype=torch.bfloat16)
         t = quantize_impl(x, (1, 128))
@@ -463,89 +664,18 @@ def run_profile_case(name: str):
     return 0
 
 
-def run_triple():
-    """BASELINE.json configs[2] on one GPU, one projection at a time: forward, dgrad and wgrad of a
-    d_model=2048 layer at M = 32768 tokens with their quantizers.  Prints one JSON object (not
-    the benchmark line): device times per part, CUDA events, inputs seeded and resident in HBM."""
-    import torch
-    from pratchya_b200 import _lib
-    from pratchya_b200._qualia import _ops
-    torch.cuda.set_device(0)
-    lib = _lib.load()
-    stream = torch.cuda.current_stream().cuda_stream
-    tokens = 32768
-    gen = torch.Generator(device="cuda").manual_seed(3)
-    out = {"config": "configs[2]: M=32768 tokens, d_model=2048, W~N(0,0.02), X~N(0,1), dY~N(0,1e-3); dY in e4m3 (reference dtype) unless noted",
-           "layers": {}}
-
-    def timed(fn, reps=10):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(reps):
-            fn()
-        b.record()
-        torch.cuda.synchronize()
-        _lib.check(lib.pb_gemm_check(stream))
-        return a.elapsed_time(b) / reps
-
-    for name, (k_in, n_out) in {"attn 2048->2048": (2048, 2048), "ffn up 2048->8192": (2048, 8192), "ffn down 8192->2048": (8192, 2048)}.items():
-        x = torch.randn(tokens, k_in, device="cuda", generator=gen).to(torch.bfloat16)
-        w = (torch.randn(k_in, n_out, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
-        dy = (torch.randn(tokens, n_out, device="cuda", generator=gen) * 1e-3).to(torch.bfloat16)
-        wq = _ops.quantize_impl(w, (128, 128))
-        wt = _ops.transpose_bytes(wq[0])
-        xq = _ops.quantize_impl(x, (1, 128))
-        gq = _ops.quantize_impl(dy, (1, 128))
-        xt = _ops.quantize_transposed_impl(x, 128)
-        gt = _ops.quantize_transposed_impl(dy, 128)
-        dev = x.device
-        op = _ops._operand
-        parts = {}
-        flop = 2.0 * tokens * k_in * n_out
-        ms = timed(lambda: _ops.gemm_tn(op(xq[0], xq[1], xq[2], tokens, k_in, (1, 128)), op(wt, wq[1], wq[2], n_out, k_in, (128, 128), 1), torch.bfloat16, dev))
-        parts["fwd_gemm"] = {"ms": ms, "tflops": flop / ms / 1e9}
-        ms = timed(lambda: _ops.gemm_tn(op(gq[0], gq[1], gq[2], tokens, n_out, (1, 128)), op(wq[0], wq[1], wq[2], k_in, n_out, (128, 128)), torch.bfloat16, dev))
-        parts["dgrad_gemm"] = {"ms": ms, "tflops": flop / ms / 1e9}
-        ms = timed(lambda: _ops.gemm_tn(op(xt[0], xt[1], xt[2], k_in, tokens, (1, 128)), op(gt[0], gt[1], gt[2], n_out, tokens, (1, 128)), torch.float32, dev))
-        parts["wgrad_gemm"] = {"ms": ms, "tflops": flop / ms / 1e9}
-        ms = timed(lambda: _ops.quantize_impl(x, (1, 128)))
-        parts["quantize_x_1x128"] = {"ms": ms, "gbs": tokens * k_in * QUANT_BYTES_PER_ELEM / ms / 1e6}
-        ms = timed(lambda: _ops.quantize_transposed_impl(x, 128))
-        parts["quantize_xT_1x128"] = {"ms": ms, "gbs": tokens * k_in * QUANT_BYTES_PER_ELEM / ms / 1e6}
-        ms = timed(lambda: _ops.quantize_impl(dy, (1, 128)))
-        parts["quantize_dy_1x128"] = {"ms": ms, "gbs": tokens * n_out * QUANT_BYTES_PER_ELEM / ms / 1e6}
-        ms = timed(lambda: _ops.quantize_impl(dy, (1, 128), out_format="e5m2"))
-        parts["quantize_dy_1x128_e5m2"] = {"ms": ms, "gbs": tokens * n_out * QUANT_BYTES_PER_ELEM / ms / 1e6}
-        ms = timed(lambda: _ops.quantize_transposed_impl(dy, 128))
-        parts["quantize_dyT_1x128"] = {"ms": ms, "gbs": tokens * n_out * QUANT_BYTES_PER_ELEM / ms / 1e6}
-        dual_bytes = 2 + 2 * (1 + 1 / 128 + 4 / 1024)      # one read, two quantized forms written
-        ms = timed(lambda: _ops.quantize_dual_impl(x))
-        parts["quantize_x_both_forms"] = {"ms": ms, "gbs": tokens * k_in * dual_bytes / ms / 1e6}
-        ms = timed(lambda: _ops.quantize_dual_impl(dy))
-        parts["quantize_dy_both_forms"] = {"ms": ms, "gbs": tokens * n_out * dual_bytes / ms / 1e6}
-        ms = timed(lambda: _ops.quantize_impl(w, (128, 128)))
-        parts["quantize_w_128x128"] = {"ms": ms, "gbs": k_in * n_out * QUANT_BYTES_PER_ELEM / ms / 1e6}
-        out["layers"][name] = parts
-        del x, w, dy, xq, gq, xt, gt
-    print(json.dumps(out))
-    return 0
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "dequantize"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "transposed", "dequantize"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
-    ap.add_argument("--triple", action="store_true", help="time the forward/dgrad/wgrad parts of BASELINE configs[2] and exit")
+    ap.add_argument("--cpu-child", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
-    if args.triple:
-        return run_triple()
+    if args.cpu_child:
+        return run_cpu_child(args)
     if args.profile_case:
         return run_profile_case(args.profile_case)
     if args.impl == "reference":

@@ -51,13 +51,21 @@ class Linear:
         k = self.kernel
         step = self._fused_step(x, out_dtype or x.dtype)
         if step is not None:
-            d, _ = step(x)
-            return d.reshape(*x.shape[:-1], d.shape[-1])
+            out = self._run_step(step, x)
+            if out is not None:
+                return out[0].reshape(*x.shape[:-1], out[0].shape[-1])
         xq = _ops.quantize_impl(x, (1, a))
         y_t = k.transposed_value() if _ops._tensor_core_eligible(xq[0], k.get_value(), (1, a), k.tgrid) else None
         return _ops.matmul_impl(*xq, k.get_value(), k.sc_fp8, k.sc_fp32, (1, a), k.tgrid, y_fp8_t=y_t,
                                 out_dtype=out_dtype or x.dtype)
 
+
+    def product(self, x: torch.Tensor) -> QArrayImpl:
+        """`QArrayImpl(x, (1, a)) @ kernel` as the reference returns it (_qarr.py:99-105): the product
+        re-quantized on (1, b), as a QArrayImpl (1 byte per element plus scales instead of a dense array)."""
+        a, b = self.kernel.tgrid
+        y = self.matmul(x, out_dtype=torch.float32)
+        return QArrayImpl(y, (1, b))
 
     def _fused_step(self, x, out_dtype):
         """The two-launch path (quantizer that also lays out the GEMM's scales, weight prepared once)
@@ -73,15 +81,21 @@ class Linear:
         rows = x.numel() // kk
         key = (rows, out_dtype)
         if key not in self._steps:
-            try:
-                step = _ops.LinearStep(k.transposed_value(), k.sc_fp8, k.sc_fp32, rows, out_dtype)
-                step(torch.zeros((rows, kk), dtype=torch.bfloat16, device=x.device))     # plan check + weight preparation
-                self._steps[key] = step
-            except _lib.PbError as e:
-                if e.status != _lib.PB_ERR_UNSUPPORTED:
-                    raise
-                self._steps[key] = None
+            self._steps[key] = _ops.LinearStep(k.transposed_value(), k.sc_fp8, k.sc_fp32, rows, out_dtype)
         return self._steps[key]
+
+    def _run_step(self, step, x, **kwargs):
+        """Runs the fused step; None (and the step is dropped for good) when the library says that this weight's
+        scales do not allow it.  That answer comes from the argument checks, before anything is launched."""
+        try:
+            return step(x, **kwargs)
+        except _lib.PbError as e:
+            if e.status != _lib.PB_ERR_UNSUPPORTED:
+                raise
+            for key, value in list(self._steps.items()):
+                if value is step:
+                    self._steps[key] = None
+            return None
 
 
 class ChannelMixFFN:
@@ -112,9 +126,11 @@ class ChannelMixFFN:
         step_v = self.w_v._fused_step(probe, torch.float32) if probe is not None else None
         if step_k is None or step_v is None:
             return self.literal(x)
-        y1, _ = step_k(x)                                             # f32 product of the first Linear
-        y2, _ = step_v(y1, relu2_of_fake_quantized=True)               # middle + second product
-        out = _ops.fake_quantize_impl(y2, (1, self.w_v.kernel.tgrid[1]), x.dtype)
+        r1 = self.w_k._run_step(step_k, x)                             # f32 product of the first Linear
+        r2 = self.w_v._run_step(step_v, r1[0], relu2_of_fake_quantized=True) if r1 is not None else None     # middle + second product
+        if r2 is None:
+            return self.literal(x)
+        out = _ops.fake_quantize_impl(r2[0], (1, self.w_v.kernel.tgrid[1]), x.dtype)
         return out.reshape(*x.shape[:-1], out.shape[-1])
 
 
