@@ -235,6 +235,16 @@ PB_API int pb_relu2_requantize(const void* y, int64_t rows, int64_t cols, int ou
 PB_API int pb_quantize_dual(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols, int out_format,
                      void* q, uint8_t* sc8, float* sc32, void* q_t, uint8_t* sc8_t, float* sc32_t,
                      void* workspace, size_t workspace_bytes, void* stream);
+/* ---- WKV-7 state scan of the TimeMix block: replaces the per-timestep nnx.scan `wkv_state_scan`,
+ *      pratchya/_nnx_impl/_module.py:187-207.  The six inputs (decay, iclr, removal_k, replacement_k, v, r)
+ *      are f32 [batch, steps, heads*head_dim]; state_in / state_out are f32 [batch, heads, head_dim, head_dim]
+ *      (state_in may be null for a zero state, state_out may be null); y is f32 [batch, steps, heads*head_dim],
+ *      the order the reference has after its transpose (:210).  head_dim must be 64.  16-byte aligned arrays. */
+PB_API int pb_wkv7_forward(const float* decay, const float* iclr, const float* removal_k, const float* replacement_k,
+                    const float* v, const float* r, const float* state_in,
+                    int64_t batch, int64_t steps, int64_t heads, int head_dim,
+                    float* y, float* state_out, void* stream);
+
 /* byte transpose [rows, cols] -> [cols, rows] of an fp8 matrix (weight prepared for the forward GEMM) */
 PB_API int pb_transpose_bytes(const void* src, int64_t rows, int64_t cols, void* dst, void* stream);
 
