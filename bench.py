@@ -523,6 +523,25 @@ def run_ours(args):
             one_gpu = time_triple(so_tokens, so_d, so_ffn, "student_t", 500, reps=2, sync=local_sync)
         barrier()
 
+    # ---- the one collective of the end-to-end step (configs[4]): the data-parallel all-reduce of the gradients,
+    # plain NCCL over NVLink.  The quantize / GEMM path above has no collective; this times the exchange that a
+    # 24-layer d_model-2048 model (1.48 G parameters, bf16 gradients) adds per step.
+    allreduce = None
+    if world > 1:
+        n_params = 24 * (4 * 2048 * 2048 + 2 * 2048 * 8192) + 2 * 65536 * 2048
+        grads = torch.zeros(n_params, device=dev, dtype=torch.bfloat16)
+        for _ in range(2):
+            dist.all_reduce(grads)
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(5):
+            dist.all_reduce(grads)
+        a1.record()
+        barrier()
+        allreduce = {"ms": a0.elapsed_time(a1) / 5, "bytes": n_params * 2}
+        del grads
+
     # ---- last, because it leaves the GPU at its power cap: the same step back to back for about a second
     sustained = None
     if args.steps >= 10:        # skipped in short runs (launch lists under a profiler)
@@ -549,11 +568,11 @@ def run_ours(args):
                      "steps": n_sus - n_sus // 3, "clocks": s_clocks}
         _lib.check(lib.pb_gemm_check(stream))
 
-    times = torch.tensor([total_ms, e2e_ms, g_ms, q_ms, big_q_ms, big_qt_ms, big_dq_ms, copy_only_ms, scale["ms"], scale["gemm_ms"]],
-                         device=dev, dtype=torch.float64)
+    times = torch.tensor([total_ms, e2e_ms, g_ms, q_ms, big_q_ms, big_qt_ms, big_dq_ms, copy_only_ms, scale["ms"], scale["gemm_ms"],
+                          allreduce["ms"] if allreduce else 0.0], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, g_ms, q_ms, big_q_ms, big_qt_ms, big_dq_ms, copy_only_ms, scale_ms, scale_gemm_ms = times.tolist()
+    total_ms, e2e_ms, g_ms, q_ms, big_q_ms, big_qt_ms, big_dq_ms, copy_only_ms, scale_ms, scale_gemm_ms, ar_ms = times.tolist()
 
     if rank == 0:
         peaks = load_peaks()
@@ -610,6 +629,12 @@ def run_ours(args):
             "clock_note": "the timed region of K steps is shorter than one sampling period unless K is large: the samples bracket it; "
                           "`sustained` carries the clocks seen inside a second-long run of the same step",
         }
+        if allreduce is not None:
+            bus = allreduce["bytes"] * 2 * (world - 1) / world / (ar_ms * 1e-3) / 1e9
+            out["grad_allreduce"] = {"what": "dist.all_reduce (NCCL, sum) of the bf16 gradients of a 24-layer d_model-2048 model with a 65536-token "
+                                             "vocabulary: the end-to-end step's only collective (configs[4]); the quantize/GEMM path has none",
+                                     "bytes": allreduce["bytes"], "ms": ar_ms, "bus_gbs": bus,
+                                     "frac_of_measured_allreduce_725_gbs": bus / 725.0, "timing": "CUDA events, max over ranks, mean of 5"}
         if triple is not None:
             out["triple"] = {"workload": "configs[2]: fwd+dgrad+wgrad of 4x[2048->2048], [2048->8192], [8192->2048] at M = 32768 tokens, dY e4m3",
                              "ms": triple["ms"], "gemm_only_ms": triple["gemm_ms"], "tflops": triple["flop"] / triple["ms"] / 1e9,

@@ -172,8 +172,10 @@ typedef struct pb_operand {
   int64_t depth;          /* contraction length, multiple of 128 */
   int grid_a, grid_b;     /* (1,128) or (128,128); blocks are counted on the [rows, depth] view */
   int format;             /* PB_E4M3 | PB_E5M2 */
-  int transposed_blocks;  /* 1: sc8/sc32 were produced on the [depth, rows] view of the same bytes' transpose
-                             (a (128,128) weight used without re-quantizing); 0 otherwise */
+  int transposed_blocks;  /* 1: sc8/sc32 were produced on the [depth, rows] view of the same bytes' transpose, where the
+                             blocks are (128, grid_a): a weight stored [K, N] and quantized on (128,128) (grid_a = 128)
+                             or on (128,1) (grid_a = 1: the reference's gate, lm_head and LoRA weights,
+                             pratchya/_nnx_impl/_module.py:82-84, 326), used without re-quantizing; 0 otherwise */
 } pb_operand;
 
 PB_API size_t pb_gemm_workspace_size(const pb_operand* a, const pb_operand* b);

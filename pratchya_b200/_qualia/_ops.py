@@ -229,15 +229,19 @@ def quantize_impl_bwd(g_out, tgrid):
 # ---- matmuls ---------------------------------------------------------------------------
 
 def _tensor_core_eligible(x_fp8, y_fp8, grid_x, grid_y) -> bool:
-    """(1,128) activations (any leading dims, 8-block super-groups inside every slice)
-    times a 2-D (128,128) weight."""
+    """(1,128) activations (any leading dims, 8-block super-groups inside every slice) times a 2-D
+    weight on (128,128), or on (128,1) -- the reference's gate, lm_head and LoRA weights
+    (pratchya/_nnx_impl/_module.py:82-84, 326): their scales are one e8m0 byte per column and 128-deep
+    block, which is a K-major operand with per-row block scales."""
     if x_fp8.dim() < 2 or y_fp8.dim() != 2:
         return False
     mm, kk = x_fp8.shape[-2:]
     k2, nn = y_fp8.shape
-    return (tuple(grid_x) == (1, 128) and tuple(grid_y) == (128, 128) and kk == k2
-            and kk % 128 == 0 and nn % 128 == 0 and mm >= 1
-            and group_geometry(mm, kk, grid_x)[1] == 8)
+    gy = tuple(grid_y)
+    if not (tuple(grid_x) == (1, 128) and gy in ((128, 128), (128, 1)) and kk == k2 and kk % 128 == 0 and mm >= 1
+            and group_geometry(mm, kk, grid_x)[1] == 8):
+        return False
+    return nn % 128 == 0 if gy == (128, 128) else nn % 16 == 0
 
 
 def transpose_bytes(q: torch.Tensor) -> torch.Tensor:
@@ -363,7 +367,8 @@ def matmul_impl(x_fp8, x_sc8, x_sc32, y_fp8, y_sc8, y_sc32, block_grid_x, block_
         x_fp8, x_sc8, x_sc32 = x_fp8.contiguous(), x_sc8.contiguous(), x_sc32.contiguous()
         y_sc8, y_sc32 = y_sc8.contiguous(), y_sc32.contiguous()
         a = _operand(x_fp8, x_sc8, x_sc32, mm, kk, (1, 128))
-        b = _operand(y_fp8_t, y_sc8, y_sc32, nn, kk, (128, 128), transposed_blocks=1)
+        # the weight's scales were produced on its stored [K, N] view: blocks (128, 128) or (128, 1) there
+        b = _operand(y_fp8_t, y_sc8, y_sc32, nn, kk, (block_grid_y[1], 128), transposed_blocks=1)
         d = gemm_tn(a, b, out_dtype, x_fp8.device)
         return d.reshape(*lead, x_fp8.shape[-2], nn) if lead else d
     x = dequantize_impl(x_fp8, x_sc8, x_sc32, torch.float32, block_grid_x)

@@ -1027,7 +1027,7 @@ struct PrepParams {
 };
 
 __device__ __forceinline__ int64_t flat_block(const PrepParams& q, int r, int kb) {
-  return q.transposed ? (int64_t)kb * (q.rows / 128) + r / 128 : (int64_t)(r / q.grid_a) * q.KB + kb;
+  return q.transposed ? (int64_t)kb * (q.rows / q.grid_a) + r / q.grid_a : (int64_t)(r / q.grid_a) * q.KB + kb;
 }
 
 __global__ void __launch_bounds__(256) gemm_prep_kernel(PrepParams q) {
@@ -1138,13 +1138,12 @@ int plan_operand(const pb_operand* o, const char* name, OperandPlan* plan) {
   if (o->format != PB_E4M3 && o->format != PB_E5M2) return fail(PB_ERR_BAD_DTYPE, "pb_gemm_tn: operand %s format %d", name, o->format);
   if (o->grid_a == 128 && o->rows % 128 != 0)
     return fail(PB_ERR_BAD_SHAPE, "pb_gemm_tn: operand %s rows=%lld not divisible by its 128-row blocks", name, (long long)o->rows);
-  if (o->transposed_blocks && o->grid_a != 128)
-    return fail(PB_ERR_BAD_GRID, "pb_gemm_tn: operand %s: transposed_blocks needs a (128,128) grid", name);
   if (reinterpret_cast<uintptr_t>(o->q) & 15) return fail(PB_ERR_MISALIGNED, "pb_gemm_tn: operand %s bytes must be 16-byte aligned", name);
   if (o->rows > (1ll << 30) || o->depth > (1ll << 30)) return fail(PB_ERR_UNSUPPORTED, "pb_gemm_tn: operand %s is too large", name);
   Geometry g;
-  // the scales were produced on the [rows, depth] view, or on its transpose
-  const int s = o->transposed_blocks ? make_geometry(o->depth, o->rows, 128, 128, &g) : make_geometry(o->rows, o->depth, o->grid_a, 128, &g);
+  // the scales were produced on the [rows, depth] view, or on its transpose [depth, rows], where the same blocks
+  // are (128, grid_a): a (128,128) weight, or a (128,1) weight (one scale per column and 128-deep block)
+  const int s = o->transposed_blocks ? make_geometry(o->depth, o->rows, 128, o->grid_a, &g) : make_geometry(o->rows, o->depth, o->grid_a, 128, &g);
   if (s) return s;
   plan->Ksg = g.K;
   plan->Mgroups = g.M;
@@ -1154,16 +1153,16 @@ int plan_operand(const pb_operand* o, const char* name, OperandPlan* plan) {
     if (!o->transposed_blocks) {
       P = (int)std::gcd((int64_t)kMaxChunk, std::gcd(g.K, KB));
     } else {
-      const int64_t nbc = o->rows / 128;
+      const int64_t nbc = o->rows / o->grid_a;
       P = 1;
       for (int c = kMaxChunk; c > 1; c >>= 1)
         if (g.K % (c * nbc) == 0) { P = c; break; }
     }
   }
   plan->P = P;
-  // one super-group in all, or (128,128) blocks numbered along the rows first with whole
-  // block-rows per super-group: every row then sees the same fp32 amax in a given k-block
-  plan->row_uniform = (g.M == 1) || (o->transposed_blocks && g.K % (o->rows / 128) == 0);
+  // one super-group in all, or blocks numbered along the rows first with whole block-rows per
+  // super-group: every row then sees the same fp32 amax in a given k-block
+  plan->row_uniform = (g.M == 1) || (o->transposed_blocks && g.K % (o->rows / o->grid_a) == 0);
   return PB_OK;
 }
 

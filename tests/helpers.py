@@ -73,3 +73,20 @@ def check_close(got, ref, what):
         rel = (err[big] / np.abs(ref[big])).max()
         assert rel <= REL_TOL, f"{what}: max rel err {rel:.3e}"
     return err.max() / scale
+
+
+def assert_fake_quantized_close(got, want, what, boundary_fraction=0.01, bf16=False):
+    """Two arrays that are both the fp8 (fake-)quantization of almost the same f32 matrix (their sources agree to
+    ~1e-6): equal to 1e-5 (one bf16 ulp if `bf16`) on all but `boundary_fraction` of the elements -- those whose
+    source sits on a rounding boundary of the cast -- and within one fp8 step of each other everywhere
+    (2^-3 of the value; 2^-6 of the array's maximum covers the small values of a block with a large scale)."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape, f"{what}: shape {got.shape} vs {want.shape}"
+    scale = np.abs(want).max()
+    diff = np.abs(got - want)
+    eps = 2.0 ** -7 if bf16 else 1e-5
+    off = diff > eps * np.abs(want) + 1e-9 * scale
+    assert off.mean() <= boundary_fraction, f"{what}: {off.mean():.4f} of the elements differ (allowed {boundary_fraction})"
+    worst = (diff - 2.0 ** -3 * np.abs(want)).max()
+    assert worst <= 2.0 ** -6 * scale, f"{what}: a difference exceeds one fp8 step by {worst / scale:.2e} of the maximum"

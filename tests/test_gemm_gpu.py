@@ -159,3 +159,45 @@ def test_random_shapes_against_f64_product(built_lib):
         err = (got.double() - ref).abs().max().item()
         tol = 1e-5 if out == torch.float32 else 2.0 ** -7
         assert err <= tol * scale, f"{m}x{n}x{k} {out}: max abs err {err:.3e} vs scale {scale:.3e}"
+
+
+@pytest.mark.parametrize("m,k,n", [(256, 2048, 64), (512, 128, 2048), (384, 1024, 4096), (128, 2048, 48)])
+def test_column_scaled_weights_run_on_the_tensor_cores(built_lib, m, k, n):
+    """Weights on the (128,1) grid -- the reference's LoRA down/up, gate and lm_head kernels
+    (pratchya/_nnx_impl/_module.py:82-84, 326; _model.py:77): one e8m0 byte per column and 128-deep block, an
+    fp32 amax per eight adjacent columns of a 128-row band.  Same check as the (128,128) weights: the oracle's
+    f64 product of the same quantized operands."""
+    x = synth((m, k), seed=m + k, outliers=0.01)
+    w = synth((k, n), seed=n, scale=0.05, outliers=0.02)          # outliers make neighbouring column groups differ
+    xq, wq = gpu_triple(x, (1, 128)), gpu_triple(w, (128, 1))
+    assert _ops._tensor_core_eligible(xq[0], wq[0], (1, 128), (128, 1))
+    for out in (torch.float32, torch.bfloat16):
+        got = matmul_impl(*xq, *wq, (1, 128), (128, 1), out_dtype=out)
+        _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+        ref = oracle.matmul_impl(*np_triple(xq), *np_triple(wq), (1, 128), (128, 1), acc=np.float64)
+        err = check_close(got.float().cpu().numpy(), ref, f"(128,1) weight {m}x{n}x{k} {out}")
+    # the literal route (dequantize both, f32 library matmul) agrees with it
+    lit = _ops._matmul_f32(_ops.dequantize_impl(*xq, torch.float32, (1, 128)), _ops.dequantize_impl(*wq, torch.float32, (128, 1)))
+    assert (lit - matmul_impl(*xq, *wq, (1, 128), (128, 1))).abs().max().item() <= 1e-4 * np.abs(ref).max()
+
+
+def test_low_rank_ffn_matches_the_oracle_chain(built_lib):
+    """LowRankFFN (pratchya/_nnx_impl/_module.py:74-89): up(tanh(down(x))) with both kernels on (blk,1) grids, each
+    Linear returning dq(q(product, (1,1))) -- on the (1,1) grid every element is its own block, so the fake
+    quantization is exact up to the f32 -> bf16 -> fp8 cast of +-128 and a scale of |y|: the layer's value is
+    the plain product to f32 rounding.  Checked against the oracle's chain on the layer's own quantized kernels."""
+    from pratchya_b200._nnx_impl import LowRankFFN
+    hidden, rank, rows = 1024, 128, 256
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    layer = LowRankFFN(hidden, rank, (128, 128), generator=gen)
+    assert layer.down.kernel.tgrid == (128, 1) and layer.up.kernel.tgrid == (128, 1)
+    x = synth((rows, hidden), seed=5, outliers=0.01)
+    got = layer(to_torch(x)).cpu().numpy()
+    kd, ku = layer.down.kernel, layer.up.kernel
+    down = oracle.linear_forward(x, np_triple((kd.get_value(), kd.sc_fp8, kd.sc_fp32)), (128, 1))
+    want = oracle.linear_forward(np.tanh(down).astype(np.float32), np_triple((ku.get_value(), ku.sc_fp8, ku.sc_fp32)), (128, 1))
+    assert got.shape == want.shape == (rows, hidden)
+    scale = np.abs(want).max()
+    # tanh differs in the last bit between numpy and the device, which can move an element of the second
+    # quantization across an fp8 rounding boundary: 5e-3 of the maximum leaves room for a few of those
+    assert np.abs(got - want).max() <= 5e-3 * scale, f"LowRankFFN differs from the oracle chain by {np.abs(got - want).max() / scale:.2e} of its maximum"

@@ -1,13 +1,19 @@
 """The differentiable FP8 linear layer against the oracle's restatement of the reference's VJP chain
-(_qarr.py:575-601, 616-640, 514-526).  With recipe="reference" the chain is the reference's own and
-is checked closely; with recipe="fp8" (dY and the token-direction operands quantized for the tensor
-cores) the result is checked against the oracle run on the same quantized operands, and its
-deviation from the reference recipe is only reported."""
+(_qarr.py:575-601, 616-640, 514-526).  With recipe="reference" the chain is the reference's own; with
+recipe="fp8" (dY and the token-direction operands quantized for the tensor cores) the result is checked
+against the oracle run on the same quantized operands, and its deviation from the reference recipe is
+only reported.
+
+Every compared quantity has gone through a final fp8 (fake-)quantization of a matmul result.  The
+matmuls agree with the oracle's to ~1e-6 (tests/test_gemm_gpu.py), so after that quantization the two
+sides are equal to 1e-5 on all but the few elements whose pre-quantization value sits on a rounding
+boundary of the cast (or whose block's scale does), and those differ by one fp8 step: the checks below
+say exactly that, instead of a blanket 2^-3."""
 import numpy as np
 import pytest
 import torch
 
-from helpers import from_torch, oracle, synth, to_torch
+from helpers import assert_fake_quantized_close, from_torch, oracle, synth, to_torch
 from pratchya_b200._nnx_impl import linear_fp8
 
 pytestmark = pytest.mark.gpu
@@ -40,39 +46,66 @@ def test_reference_recipe_matches_the_oracle_chain(built_lib, fake):
     y = linear_fp8(xt, wt, (128, 128), fake_quant_output=fake, recipe="reference")
     y.backward(to_torch(g_y))
     y_ref, gx_ref, gw_ref, _ = reference_chain(x, w, g_y, (128, 128), fake)
-    # forward: tensor-core product, then (optionally) an fp8 re-quantization step (2^-4 relative)
-    assert rel(from_torch(y.detach()), y_ref) <= (2 ** -3 if fake else 1e-2)
-    assert rel(from_torch(xt.grad), gx_ref) <= 2 ** -3
-    assert rel(from_torch(wt.grad), gw_ref) <= 2 ** -3
+    if fake:
+        assert_fake_quantized_close(from_torch(y.detach()), y_ref, "forward")
+    else:        # the tensor-core product itself: the GEMM tolerance
+        assert rel(from_torch(y.detach()), y_ref) <= 1e-2
+    # the cotangent that enters the matmuls is scaled by the output's block scales (:575-601): where the forward's
+    # scale bytes differ on a boundary, a whole block of g differs by a factor of two -- rare, and counted below
+    assert_fake_quantized_close(from_torch(xt.grad), gx_ref, "dX", boundary_fraction=0.03)
+    assert_fake_quantized_close(from_torch(wt.grad), gw_ref, "dW", boundary_fraction=0.03)
 
 
-def test_fp8_recipe_matches_the_oracle_on_the_same_operands(built_lib):
+@pytest.mark.parametrize("grad_format", ["e4m3", "e5m2"])
+def test_fp8_recipe_matches_the_oracle_on_the_same_operands(built_lib, grad_format):
+    """dY quantized on (1,128) for dgrad and along the tokens for wgrad, in e4m3 (the reference's dtype) or e5m2
+    (the extension): the oracle builds the same operands and multiplies them in f64."""
     m, k, n = 2048, 512, 256
     x, w = synth((m, k), 4), synth((k, n), 5, scale=0.02, outliers=0)
     g_y = synth((m, n), 6, scale=1e-3, outliers=0)
     xt = to_torch(x).requires_grad_(True)
     wt = to_torch(w).requires_grad_(True)
-    y = linear_fp8(xt, wt, (128, 128), fake_quant_output=False, recipe="fp8")
+    y = linear_fp8(xt, wt, (128, 128), fake_quant_output=False, recipe="fp8", grad_format=grad_format)
     y.backward(to_torch(g_y))
     wq = oracle.quantize_impl(w, (128, 128))
     w_hat = oracle.dequantize_impl(*wq, np.float64, (128, 128))
-    g_hat = oracle.dequantize_impl(*oracle.quantize_impl(g_y, (1, 128)), np.float64, (1, 128))
+    g_hat = oracle.dequantize_impl(*oracle.quantize_impl(g_y, (1, 128), grad_format), np.float64, (1, 128))
     gx = oracle.dequantize_impl(*oracle.quantize_impl((g_hat @ w_hat.T).astype(np.float32), (1, 128)), np.float32, (1, 128))
     xT_hat = oracle.dequantize_impl(*oracle.quantize_impl(np.ascontiguousarray(x.T), (1, 128)), np.float64, (1, 128))
-    gT_hat = oracle.dequantize_impl(*oracle.quantize_impl(np.ascontiguousarray(g_y.T), (1, 128)), np.float64, (1, 128))
+    gT_hat = oracle.dequantize_impl(*oracle.quantize_impl(np.ascontiguousarray(g_y.T), (1, 128), grad_format), np.float64, (1, 128))
     gw = oracle.dequantize_impl(*oracle.quantize_impl((xT_hat @ gT_hat.T).astype(np.float32), (128, 128)), np.float32, (128, 128))
-    assert rel(from_torch(xt.grad), gx) <= 2 ** -3          # one fp8 rounding step of slack: a GEMM value on a rounding boundary
-    assert rel(from_torch(wt.grad), gw) <= 2 ** -3
+    assert_fake_quantized_close(from_torch(xt.grad), gx, f"dX, dY {grad_format}")
+    assert_fake_quantized_close(from_torch(wt.grad), gw, f"dW, dY {grad_format}")
     # deviation of the fp8 recipe from the reference's f32-dY recipe: reported, not bounded
     _, gx_ref, gw_ref, _ = reference_chain(x, w, g_y, (128, 128), False)
-    print(f"recipe deviation: dX {rel(from_torch(xt.grad), gx_ref):.3e}, dW {rel(from_torch(wt.grad), gw_ref):.3e}")
+    print(f"recipe deviation ({grad_format} dY): dX {rel(from_torch(xt.grad), gx_ref):.3e}, dW {rel(from_torch(wt.grad), gw_ref):.3e}")
 
 
-def test_batched_input_and_e5m2_gradients(built_lib):
-    x = to_torch(synth((2, 512, 256), 7)).to(torch.bfloat16).requires_grad_(True)
-    w = to_torch(synth((256, 384), 8, scale=0.02, outliers=0)).requires_grad_(True)
-    y = linear_fp8(x, w, (128, 128), grad_format="e5m2")
+def test_batched_bf16_input_with_e5m2_gradients_matches_the_oracle(built_lib):
+    """A [2, 512, 256] bf16 activation: leading dims stack into rows, the output is fake-quantized (the layer's
+    default), the loss gradient goes back through the output's scales, dY is stored in e5m2."""
+    x = synth((2, 512, 256), 7).astype(oracle.BF16)
+    w = synth((256, 384), 8, scale=0.02, outliers=0)
+    g_y = synth((2, 512, 384), 9, scale=1e-3, outliers=0).astype(oracle.BF16)
+    xt = to_torch(x).requires_grad_(True)
+    wt = to_torch(w).requires_grad_(True)
+    y = linear_fp8(xt, wt, (128, 128), grad_format="e5m2")
     assert y.shape == (2, 512, 384) and y.dtype == torch.bfloat16
-    y.float().square().mean().backward()
-    assert x.grad.shape == x.shape and x.grad.dtype == torch.bfloat16 and w.grad.shape == w.shape
-    assert torch.isfinite(x.grad.float()).all() and torch.isfinite(w.grad).all() and w.grad.abs().max() > 0
+    y.backward(to_torch(g_y))
+    assert xt.grad.shape == xt.shape and xt.grad.dtype == torch.bfloat16 and wt.grad.shape == wt.shape
+    # the oracle on the stacked rows
+    x2 = x.astype(np.float32).reshape(1024, 256)
+    xq, wq = oracle.quantize_impl(x2, (1, 128)), oracle.quantize_impl(w, (128, 128))
+    prod = oracle.matmul_impl(*xq, *wq, (1, 128), (128, 128))
+    yq = oracle.quantize_impl(prod, (1, 128))
+    y_ref = oracle.dequantize_impl(*yq, oracle.BF16, (1, 128)).reshape(2, 512, 384)
+    assert_fake_quantized_close(from_torch(y.detach()).astype(np.float32), y_ref.astype(np.float32), "forward", bf16=True)
+    g = oracle.dequantize_impl_bwd(yq[1], yq[2], g_y.reshape(1024, 384), (1, 128)).astype(np.float32)     # stays bf16-valued, as the cotangent's dtype (:599)
+    w_hat = oracle.dequantize_impl(*wq, np.float64, (128, 128))
+    g_hat = oracle.dequantize_impl(*oracle.quantize_impl(g, (1, 128), "e5m2"), np.float64, (1, 128))
+    gx = oracle.dequantize_impl(*oracle.quantize_impl((g_hat @ w_hat.T).astype(np.float32), (1, 128)), np.float32, (1, 128))
+    xT_hat = oracle.dequantize_impl(*oracle.quantize_impl(np.ascontiguousarray(x2.T), (1, 128)), np.float64, (1, 128))
+    gT_hat = oracle.dequantize_impl(*oracle.quantize_impl(np.ascontiguousarray(g.T), (1, 128), "e5m2"), np.float64, (1, 128))
+    gw = oracle.dequantize_impl(*oracle.quantize_impl((xT_hat @ gT_hat.T).astype(np.float32), (128, 128)), np.float32, (128, 128))
+    assert_fake_quantized_close(from_torch(xt.grad).astype(np.float32).reshape(1024, 256), gx.astype(oracle.BF16).astype(np.float32), "dX", boundary_fraction=0.03, bf16=True)
+    assert_fake_quantized_close(from_torch(wt.grad), gw, "dW", boundary_fraction=0.03)
