@@ -442,6 +442,16 @@ def run_ours(args):
     quant_bytes = qm * qk * QUANT_BYTES_PER_ELEM
     del big, bq, bqt, back, tws
 
+    if args.headline_only:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": world * FLOP_PER_STEP / (total_ms / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+                              "n_gpus": world, "steps": args.steps, "ms_per_step": total_ms / args.steps, "gemm_ms": g_ms, "quantize_ms": q_ms,
+                              "quantize_alone_us": big_q_ms * 1e3, "transposed_alone_us": big_qt_ms * 1e3, "dequantize_alone_us": big_dq_ms * 1e3,
+                              "note": "--headline-only: a reduced line for profiler runs, not the benchmark line"}))
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
     # ---- end to end through the public API with host buffers: every step copies its X from pinned host
     # memory, runs Linear.product (quantize, GEMM, and the (1,128) re-quantization of the product that the
     # reference's `x_q @ kernel` returns), and copies that quantized product -- bytes and both scale arrays --
@@ -670,6 +680,18 @@ def run_profile_case(name: str):
         t = quantize_impl(x, (1, 128))
         for _ in range(4):
             _ops.dequantize_impl(*t, torch.bfloat16, (1, 128))
+    elif name == "wkv7":
+        from pratchya_b200._nnx_impl import wkv_state_scan
+        bsz, steps, heads = 8, 512, 32                      # 6 x 33.5 MB in, 33.5 MB out: larger than L2
+        g = torch.Generator(device="cuda").manual_seed(0)
+        shape = (bsz, steps, heads * 64)
+        decay = torch.exp(-torch.exp(torch.randn(shape, device="cuda", generator=g) * 0.5 - 1.0))
+        iclr = torch.sigmoid(torch.randn(shape, device="cuda", generator=g))
+        k = torch.randn(shape, device="cuda", generator=g)
+        rk = torch.nn.functional.normalize(k.view(bsz, steps, heads, 64), dim=-1).reshape(shape)
+        v, r = torch.randn(shape, device="cuda", generator=g), torch.randn(shape, device="cuda", generator=g)
+        for _ in range(3):
+            wkv_state_scan(None, decay, iclr, rk, k * iclr, v, r, heads)
     elif name == "gemm_full":
         m, n, k = M, N, K                                   # the benchmark's own launch, for DRAM-byte counters only
         x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
@@ -695,7 +717,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "transposed", "dequantize"],
+    ap.add_argument("--headline-only", action="store_true",
+                    help="only the headline step and its per-kernel pass (for launch lists under a profiler): no e2e, triple, scaleout or CPU leg")
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "transposed", "dequantize", "wkv7"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
     ap.add_argument("--cpu-child", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()

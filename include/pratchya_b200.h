@@ -67,7 +67,12 @@ PB_API int pb_group_geometry(int64_t rows, int64_t cols, int a, int b, int64_t* 
 
 /* ---- quantize: replaces quantize_impl(x, tgrid), _qarr.py:458-506 (and the
  *      per-leading-index scan of QArrayImpl.__quantize, :34-44, via `batch`).
- *      x is [batch, rows, cols] of x_dtype (PB_F32 | PB_BF16), row-major, 16-byte aligned. */
+ *      x is [batch, rows, cols] of x_dtype (PB_F32 | PB_BF16), row-major, 16-byte aligned.
+ *      Non-finite inputs are where this library knowingly departs from the reference: jnp.max propagates a
+ *      NaN, so one NaN makes the reference's whole super-group (its fp32 amax, every scale and byte) NaN; the
+ *      amax reductions here drop NaNs (fmaxf / __hmax2 / integer max on the bits), so only the NaN element
+ *      itself becomes the fp8 NaN byte and its neighbours keep finite scales.  An Inf input gives an Inf amax
+ *      in both.  Finite inputs are bit-exact. */
 PB_API size_t pb_quantize_workspace_size(int64_t batch, int64_t rows, int64_t cols, int a, int b);
 PB_API int pb_quantize(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols,
                 int a, int b, int out_format,
@@ -213,8 +218,10 @@ PB_API int pb_quantize_for_gemm(const void* x, int x_dtype, int64_t rows, int64_
  * super-groups of eight blocks only; anything else returns PB_ERR_UNSUPPORTED (use the two calls). */
 PB_API int pb_fake_quantize(const void* x, int x_dtype, int64_t batch, int64_t rows, int64_t cols, int a, int b,
                      int out_format, void* out, int out_dtype, void* stream);
-/* Reads (and clears) the device status word of the last GEMMs launched on this
- * device; synchronises `stream`.  PB_OK or PB_ERR_DEVICE_TIMEOUT. */
+/* Reads (and clears) the device status words of the kernels that wait on mbarriers (the GEMM kernels and the
+ * persistent transposed quantizer) launched on this device; synchronises `stream`.  Every such wait is bounded
+ * (a few seconds at most); a wait that runs out makes its kernel return early and is reported here:
+ * PB_OK or PB_ERR_DEVICE_TIMEOUT. */
 PB_API int pb_gemm_check(void* stream);
 
 /* The middle of ChannelMix (pratchya/_nnx_impl/_module.py:246-251) on the f32 product y[rows, cols] of

@@ -32,6 +32,18 @@ int sm_count() {
   return cached[dev];
 }
 
+void* tensor_map_encoder() {
+  static void* const fn = [] {      // thread-safe static initialisation
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      return p;
+    return static_cast<void*>(nullptr);
+  }();
+  return fn;
+}
+
 }  // namespace pb
 
 extern "C" int pb_version(void) { return 100; }

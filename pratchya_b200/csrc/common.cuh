@@ -59,6 +59,7 @@ inline int make_geometry(int64_t rows, int64_t cols, int a, int b, Geometry* g) 
 }
 
 int sm_count();   // SMs of the current device (cached per device)
+void* tensor_map_encoder();   // cuTensorMapEncodeTiled from the driver (looked up once per process), or nullptr
 
 // Tuning and diagnostic switches are read from the environment by the diagnostics build only
 // (-DPB_DIAGNOSTICS); the product build always runs the defaults.

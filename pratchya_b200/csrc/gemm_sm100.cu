@@ -1063,17 +1063,7 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-EncodeTiledFn encode_tiled() {
-  static const EncodeTiledFn fn = [] {      // looked up once per process (thread-safe static initialisation)
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      return reinterpret_cast<EncodeTiledFn>(p);
-    return static_cast<EncodeTiledFn>(nullptr);
-  }();
-  return fn;
-}
+EncodeTiledFn encode_tiled() { return reinterpret_cast<EncodeTiledFn>(tensor_map_encoder()); }
 
 int make_operand_map(CUtensorMap* map, const void* q, int64_t rows, int64_t depth, int box_rows) {
   EncodeTiledFn fn = encode_tiled();
@@ -1425,6 +1415,8 @@ extern "C" int pb_gemm_tn_ex(const pb_operand* a, const pb_operand* b, void* d, 
   return launch_gemm_uni<224, false>(ma, mb, md, p, st);
 }
 
+namespace pb { int transposed_status_fetch(unsigned int* out); }   // transpose_quantize.cu
+
 extern "C" int pb_gemm_check(void* stream) {
   PB_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   unsigned int v = 0, zero = 0;
@@ -1433,6 +1425,8 @@ extern "C" int pb_gemm_check(void* stream) {
     PB_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(zero)));
     return fail((int)v, "a bounded device-side wait in the GEMM kernel ran out");
   }
+  if (int s = transposed_status_fetch(&v)) return s;
+  if (v != 0) return fail((int)v, "a bounded device-side wait in the transposed quantizer ran out");
   return PB_OK;
 }
 

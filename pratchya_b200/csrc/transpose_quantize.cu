@@ -6,6 +6,8 @@
 //   1. column-block amax: m[c][rb] = max |x[rb*b .. rb*b+b-1, c]|   (scratch, the block order of x^T)
 //   2. the shared per-super-group scale kernel (divisors into scratch, sc8 / sc32 out)
 //   3. tile transpose through shared memory, dividing on the way, coalesced byte rows out.
+#include <cuda.h>
+
 #include "common.cuh"
 
 #include <mutex>
@@ -369,6 +371,186 @@ int launch_one_pass_bf16(const void* x, uint8_t* q_t, uint8_t* sc8, float* sc32,
   return PB_OK;
 }
 
+// ---- persistent form of the bf16 single pass: TMA-staged tiles, copy and arithmetic overlapped ----------
+// The kernel above holds one tile per CTA and alternates between filling it and working on it, so with two
+// CTAs per SM the memory system idles while both compute (58 us for X[32768,2048]: the sum of the two phases,
+// not their maximum).  Here one CTA per SM stays resident and walks over its tiles: three 64 KB tile buffers
+// are filled by TMA (four boxes of 256 rows x 64 bytes per tile, one mbarrier per buffer), two groups of 512
+// threads take the tiles in turn with the arithmetic of the kernel above, and the group that has just moved a
+// tile into its registers refills that buffer with the tile three ahead.  A tile buffer is plain row-major
+// (64-byte rows): the two half-warps of a warp read rows 128 apart, which would share banks, so the upper
+// half-warp walks its rows in swapped pairs (row i ^ 1) and swaps them back in the byte permute that pairs rows.
+constexpr int kRingBufs = 3;
+constexpr int kRingTileBytes = 1024 * 64;
+constexpr int kRingSmem = kRingBufs * kRingTileBytes + 2 * 2 * 32 * 16 * 4 + 64 + 1024;   // tiles, part_amax[group][parity], barriers, alignment slack
+constexpr uint32_t kRingWaitPolls = 1u << 21;      // bounded wait: at most ~4 s of 2 us polls, then the kernel gives up
+
+__device__ unsigned int g_tq_status;               // 0, or PB_ERR_DEVICE_TIMEOUT once a bounded wait ran out
+
+__device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .u32 n;\n\t"
+      "mov.u32 n, 0;\n"
+      "WAIT_%=:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 2000;\n\t"
+      "@p bra DONE_%=;\n\t"
+      "add.u32 n, n, 1;\n\t"
+      "setp.lt.u32 p, n, %3;\n\t"
+      "@p bra WAIT_%=;\n\t"
+      "setp.ne.u32 p, n, n;\n"
+      "DONE_%=:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(kRingWaitPolls) : "memory");
+  return ok != 0;
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(1024, 1)
+transpose_quantize1024_bf16_ring_kernel(const __grid_constant__ CUtensorMap map_x, uint8_t* __restrict__ q_t, uint8_t* __restrict__ sc8,
+                                        float* __restrict__ sc32, int rows, int cols, int tiles_x, int tiles_y, int n_tiles) {
+  extern __shared__ uint8_t ring_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ring_raw) + 1023) & ~(uintptr_t)1023);
+  uint32_t (*part_amax)[32][16] = reinterpret_cast<uint32_t (*)[32][16]>(smem + kRingBufs * kRingTileBytes);   // [group * 2 + parity]
+  const uint32_t s_tiles = (uint32_t)__cvta_generic_to_shared(smem);
+  const uint32_t s_bar = s_tiles + kRingBufs * kRingTileBytes + 2 * 2 * 32 * 16 * 4;
+  const int tid = threadIdx.x, grp = tid >> 9, gt = tid & 511;
+
+  if (tid == 0) {
+    for (int b = 0; b < kRingBufs; ++b) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_bar + 8u * b));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  // tile `seq` of this CTA: global tile blockIdx.x + seq * gridDim.x, column tiles fastest (neighbouring CTAs read
+  // neighbouring 64-byte segments of the same rows)
+  auto issue = [&](int seq) {
+    const int tl = blockIdx.x + seq * gridDim.x;
+    if (tl >= n_tiles) return;
+    const int cx = tl % tiles_x, rest = tl / tiles_x, ry = rest % tiles_y, z = rest / tiles_y;
+    const uint32_t bar = s_bar + 8u * (seq % kRingBufs), dst = s_tiles + (uint32_t)(seq % kRingBufs) * kRingTileBytes;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)kRingTileBytes) : "memory");
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                   ::"r"(dst + j * 16384u), "l"(&map_x), "r"(cx * 32), "r"(z * rows + ry * 1024 + j * 256), "r"(bar) : "memory");
+  };
+  if (tid == 0) { issue(0); issue(1); issue(2); }
+
+  const int cp = gt & 15, blk = (gt >> 4) & 7, quarter = gt >> 7;
+  const int row_first = blk * 128 + quarter * 32;
+  const int swap = (gt >> 4) & 1;                 // upper half-warp: rows in swapped pairs
+  const uint32_t sel0 = swap ? 0x1054u : 0x5410u, sel1 = swap ? 0x3276u : 0x7632u;
+  const int nsg = rows >> 10;
+  int local = 0;
+  for (int seq = grp; blockIdx.x + seq * (int)gridDim.x < n_tiles; seq += 2, ++local) {
+    const int tl = blockIdx.x + seq * gridDim.x;
+    const int cx = tl % tiles_x, rest = tl / tiles_x, ry = rest % tiles_y, z = rest / tiles_y;
+    const int c0 = cx * 32, r0 = ry * 1024;
+    const bool landed = ring_wait(s_bar + 8u * (seq % kRingBufs), (uint32_t)(seq / kRingBufs) & 1u);
+    if (!landed) atomicExch(&g_tq_status, (unsigned int)PB_ERR_DEVICE_TIMEOUT);
+    const uint8_t* tile = smem + (size_t)(seq % kRingBufs) * kRingTileBytes;
+    uint32_t w[32];
+    uint32_t cm = 0u;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      w[i] = *reinterpret_cast<const uint32_t*>(tile + (row_first + (i ^ swap)) * 64 + cp * 4);
+      const uint32_t a = w[i] & 0x7fff7fffu;
+      const __nv_bfloat162 h = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&cm), *reinterpret_cast<const __nv_bfloat162*>(&a));
+      cm = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    uint32_t (*pa)[16] = part_amax[grp * 2 + (local & 1)];
+    pa[blk * 4 + quarter][cp] = cm;
+    // every thread of the group has moved its part of the tile into registers and published its maxima; the vote
+    // makes the whole group leave together if any of its threads gave up waiting
+    int give_up;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbarrier.cta.red.or.pred q, %2, 512, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(give_up) : "r"(landed ? 0 : 1), "r"(grp + 1) : "memory");
+    if (give_up) break;
+    if (gt == 0) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the group's reads of the buffer come before the copy that refills it
+      issue(seq + kRingBufs);
+    }
+    uint32_t mb = 0u, mg = 0u;           // block amax and super-group amax of the two columns, packed
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      const uint32_t v = pa[k][cp];
+      const __nv_bfloat162 g = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&mg), *reinterpret_cast<const __nv_bfloat162*>(&v));
+      mg = *reinterpret_cast<const uint32_t*>(&g);
+      if ((k >> 2) == blk) {
+        const __nv_bfloat162 b2 = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&mb), *reinterpret_cast<const __nv_bfloat162*>(&v));
+        mb = *reinterpret_cast<const uint32_t*>(&b2);
+      }
+    }
+    uint32_t sbv[2]; float D[2];
+    block_scale(__uint_as_float(mb << 16), __uint_as_float(mg << 16), sbv[0], D[0]);
+    block_scale(__uint_as_float(mb & 0xffff0000u), __uint_as_float(mg & 0xffff0000u), sbv[1], D[1]);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const size_t col = (size_t)z * cols + c0 + 2 * cp + j;
+      const size_t grpi = col * nsg + ry;
+      if (quarter == 0) {
+        sc8[grpi * 8 + blk] = (uint8_t)sbv[j];
+        if (blk == 0) sc32[grpi] = j == 0 ? __uint_as_float(mg << 16) : __uint_as_float(mg & 0xffff0000u);
+      }
+      const float rcp = __frcp_rn(D[j]);
+      const float2 nD2 = make_float2(-D[j], -D[j]), r2 = make_float2(rcp, rcp);
+      uint32_t out[8];
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        uint32_t o2[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          // rows i+2h and i+2h+1 of column j as one packed bf16 pair (the registers of the upper half-warp hold them swapped)
+          const uint32_t pr = __byte_perm(w[i + 2 * h], w[i + 2 * h + 1], j == 0 ? sel0 : sel1);
+          const float2 v = div_hoisted_unsigned2(make_float2(__uint_as_float(pr << 16), __uint_as_float(pr & 0xffff0000u)), nD2, r2);
+          const uint32_t pk = (pack_bf16x2(v.x, v.y) & 0x7fff7fffu) | (pr & 0x80008000u);
+          o2[h] = bf16x2_to_fp8x2<FMT>(pk);
+        }
+        out[i >> 2] = o2[0] | (o2[1] << 16);
+      }
+      uint8_t* o = q_t + col * rows + r0 + row_first;
+      asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                   ::"l"(o), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7]) : "memory");
+    }
+  }
+}
+
+template <int FMT>
+int launch_one_pass_bf16_ring(const void* x, uint8_t* q_t, uint8_t* sc8, float* sc32, int64_t batch, int64_t rows, int64_t cols, cudaStream_t st) {
+  using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  EncodeFn encode = reinterpret_cast<EncodeFn>(tensor_map_encoder());
+  if (!encode) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)(batch * rows)};
+  const cuuint64_t strides[1] = {(cuuint64_t)(cols * 2)};
+  const cuuint32_t box[2] = {32, 256};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled (transposed quantizer) failed with CUresult %d", (int)r);
+  static std::mutex mu;
+  static bool configured[64] = {false};
+  int dev = 0;
+  PB_CUDA_TRY(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      PB_CUDA_TRY(cudaFuncSetAttribute(transpose_quantize1024_bf16_ring_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem));
+      configured[dev] = true;
+    }
+  }
+  const int tiles_x = (int)(cols / 32), tiles_y = (int)(rows / 1024);
+  const int64_t n_tiles = (int64_t)tiles_x * tiles_y * batch;
+  const int grid = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
+  transpose_quantize1024_bf16_ring_kernel<FMT><<<grid, 1024, kRingSmem, st>>>(map, q_t, sc8, sc32, (int)rows, (int)cols, tiles_x, tiles_y, (int)n_tiles);
+  PB_LAUNCH_CHECK("transpose_quantize1024_bf16_ring_kernel");
+  return PB_OK;
+}
+
 template <typename InT, int FMT>
 int launch_one_pass(const void* x, uint8_t* q_t, uint8_t* sc8, float* sc32, int64_t batch, int64_t rows, int64_t cols, cudaStream_t st) {
   static std::mutex mu;
@@ -404,6 +586,14 @@ transpose_bytes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ ds
 }
 
 }  // namespace
+
+// Reads and clears the transposed quantizer's device status word (see pb_gemm_check).
+int transposed_status_fetch(unsigned int* out) {
+  unsigned int zero = 0;
+  PB_CUDA_TRY(cudaMemcpyFromSymbol(out, g_tq_status, sizeof(*out)));
+  if (*out != 0) PB_CUDA_TRY(cudaMemcpyToSymbol(g_tq_status, &zero, sizeof(zero)));
+  return PB_OK;
+}
 }  // namespace pb
 
 using namespace pb;
@@ -432,9 +622,15 @@ extern "C" int pb_quantize_transposed(const void* x, int x_dtype, int64_t batch,
     if (b == 128 && rows % 1024 == 0 && cols % tile_cols == 0 && g.K == 8 && rows / 1024 <= 65535 &&
         (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (cols * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(q_t) & 31) == 0) {
       uint8_t* o = static_cast<uint8_t*>(q_t);
-      if (x_dtype == PB_BF16)
+      if (x_dtype == PB_BF16) {
+        // the persistent TMA-staged form needs every tile's rows inside one slice's 2^31 row range and enough tiles to fill the SMs
+        const bool ring = batch * rows < (1ll << 31) && (cols / 32) * (rows / 1024) * batch >= 2 * sm_count() && env_switch("PB_TQ_RING", 1) != 0;
+        if (ring)
+          return out_format == PB_E4M3 ? launch_one_pass_bf16_ring<PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
+                                       : launch_one_pass_bf16_ring<PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
         return out_format == PB_E4M3 ? launch_one_pass_bf16<PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
                                      : launch_one_pass_bf16<PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
+      }
       return out_format == PB_E4M3 ? launch_one_pass<float, PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
                                    : launch_one_pass<float, PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
     }

@@ -89,6 +89,18 @@ ffi::Error MatmulImpl(cudaStream_t stream, ffi::AnyBuffer xq, ffi::AnyBuffer x_s
   if (wd.size() != 2 || wd[1] != depth) return ffi::Error(ffi::ErrorCode::kInvalidArgument, "pb_gemm_tn: w_t must be [N, K] with K = x's last dim");
   const int fa = fp8_code(xq.element_type()), fb = fp8_code(w_t.element_type()), dt = dense_code(y->element_type());
   if (fa < 0 || fb < 0 || dt < 0) return ffi::Error(ffi::ErrorCode::kInvalidArgument, "pb_gemm_tn: operands must be fp8 and y f32 or bf16");
+  // The stacked rows are declared as one (1,128) operand, which is only the layout the scales were written with
+  // when every slice's super-groups are eight blocks of one row: check the scale arrays against that.
+  const auto sd = x_sc8.dimensions();
+  if (sd.empty() || sd.back() != 8 || (rows * depth / 128) % 8 != 0)
+    return ffi::Error(ffi::ErrorCode::kInvalidArgument, "pb_gemm_tn: x's super-groups must be eight 128-wide blocks (x_sc8[..., M, 8])");
+  int64_t wm = 0, wk = 0;
+  if (pb_group_geometry(depth, wd[0], 128, 128, &wm, &wk) != PB_OK) return ffi::Error(ffi::ErrorCode::kInvalidArgument, pb_last_error());
+  if ((int64_t)x_sc8.element_count() != batch * rows * depth / 128 || (int64_t)x_sc32.element_count() != batch * rows * depth / 1024 ||
+      (int64_t)w_sc8.element_count() != wm * wk || (int64_t)w_sc32.element_count() != wm)
+    return ffi::Error(ffi::ErrorCode::kInvalidArgument, "pb_gemm_tn: scale arrays do not match the operands' block geometry");
+  // A bounded device-side wait that runs out is recorded in a device status word, not returned here (the call is
+  // asynchronous): the host polls pb_gemm_check between steps.
   pb_operand a, b;
   a.q = xq.untyped_data(); a.sc8 = static_cast<const uint8_t*>(x_sc8.untyped_data()); a.sc32 = static_cast<const float*>(x_sc32.untyped_data());
   a.rows = batch * rows; a.depth = depth; a.grid_a = 1; a.grid_b = 128; a.format = fa; a.transposed_blocks = 0;

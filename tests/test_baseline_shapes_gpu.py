@@ -132,6 +132,27 @@ def test_config3_quantizers_at_full_size(built_lib):
     assert_token_band_bits((q2, s2, t2), x, 5120)
 
 
+@pytest.mark.parametrize("shape,fmt", [((4096, 4096), "e4m3"), ((3, 2048, 2048), "e5m2"), ((1024, 16384), "e4m3")])
+def test_persistent_transposed_quantizer_against_the_full_oracle(built_lib, shape, fmt):
+    """Shapes with enough 1024-row x 32-column tiles to run the persistent TMA-staged form of the single-pass
+    transposed quantizer, compared with the oracle over the whole array (not bands), twice in a row (the second
+    call reuses the kernel's barriers and buffers from a fresh launch)."""
+    x = seeded(shape, 61, scale=3.0)
+    x.view(-1)[::4097] *= 64.0                      # outliers
+    x[..., :1024, 5] = 0.0                         # an all-zero super-group
+    xn = to_np(x)
+    lead = shape[:-2]
+    for _ in range(2):
+        got = quantize_transposed_impl(x, 128, out_format=fmt)
+        torch.cuda.synchronize()
+        _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+        for idx in np.ndindex(*lead) if lead else [()]:
+            want = oracle.quantize_impl(np.ascontiguousarray(xn[idx].T), (1, 128), fmt)
+            assert np.array_equal(bytes_of(got[0][idx]), bytes_of(want[0])), f"fp8 bytes differ in slice {idx}"
+            assert np.array_equal(bytes_of(got[1][idx]), want[1]), f"e8m0 bytes differ in slice {idx}"
+            assert np.array_equal(from_torch(got[2][idx]).view(np.uint32), want[2].view(np.uint32)), f"fp32 scales differ in slice {idx}"
+
+
 @pytest.mark.parametrize("k_in,n_out", [(2048, 2048), (2048, 8192), (8192, 2048)])
 @pytest.mark.parametrize("grad_format", ["e4m3", "e5m2"])
 def test_config3_triple_at_full_size(built_lib, k_in, n_out, grad_format):

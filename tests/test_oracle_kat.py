@@ -210,3 +210,23 @@ def test_momentum_update_known_answers():
     assert nm0[2].reshape(-1)[0] == np.float32(b2 * np.float32(1.0))
     _, nm1 = o.momentum_update(gq, z, (4, 4), 0.9, 0.99)
     assert nm1[2].reshape(-1)[0] == np.float32(c2 * np.float32(2.0))
+
+
+def test_non_finite_inputs_follow_the_rule_s_arithmetic():
+    """What the reference's arithmetic gives for non-finite inputs (numpy and jax.numpy agree on these steps: max and
+    maximum propagate NaN).  The CUDA kernels depart from it knowingly (their amax reductions drop NaNs; the header
+    says so at pb_quantize), so these are answers of the oracle only."""
+    x = np.ones((1, 2048), dtype=np.float32)
+    x[0, 5] = np.nan                     # first super-group (columns 0..1023)
+    x[0, 1500] = np.inf                  # second super-group
+    q, s8, s32 = o.quantize_impl(x, (1, 128))
+    qb = q.view(np.uint8)
+    # a NaN reaches the block amax, the super-group amax and, through S_eff, every element of the super-group
+    assert np.isnan(s32[0, 0, 0]) and (qb[0, :1024] & 0x7F == 0x7F).all()
+    # an Inf amax: the block holding it has the ratio inf/inf = NaN (scale byte 255, which decodes to Inf: its finite
+    # elements become 0 and the Inf itself NaN); the other blocks have the ratio 1/inf = 0, and 0 * inf = NaN in S_eff
+    assert np.isinf(s32[1, 0, 0])
+    assert s8[0].tolist() == [255] * 8 and s8[1].tolist() == [0, 0, 0, 255, 0, 0, 0, 0]
+    blk = qb[0, 1024:].reshape(8, 128)
+    assert (blk[[0, 1, 2, 4, 5, 6, 7]] & 0x7F == 0x7F).all()
+    assert blk[3, 1500 - 1024 - 384] & 0x7F == 0x7F and np.delete(blk[3], 1500 - 1024 - 384).max() == 0
