@@ -10,10 +10,14 @@
 //     y_i   = sum_j S[i][j] * r_j                           (:199)
 // All arithmetic is fp32, as in the reference (its inputs are cast to f32 before the scan).
 //
-// One CTA of 256 threads per (b, n), H = 64: thread (i, q) keeps columns 16q .. 16q+15 of row i in
-// registers for the whole sequence; the two dot products are 16 FMAs per thread and two shuffles
-// across the four threads of a row.  The six input vectors of a timestep (1.5 KB) are brought into a
-// ring of shared-memory buffers by cp.async several steps ahead: the only serial dependence is S.
+// One CTA of 64 threads per (b, n), H = 64: thread i keeps row i of S (64 floats, as 32 float2) in
+// registers for the whole sequence, so both dot products run inside a thread (packed f32x2 FMAs, four
+// independent partial sums) and need no shuffle, and every shared-memory read of an input vector is a
+// 16-byte broadcast (all lanes read the same address: one pass, where distinct 16-byte reads take four).
+// A first form with four threads per row was bound by exactly that shared-memory traffic.  The six
+// input vectors of a timestep (1.5 KB) are brought into a ring of shared-memory buffers by cp.async
+// eight steps ahead, two timesteps per block-wide barrier; a * kap is formed once per step by the
+// block (one element per thread).  The only serial dependence is S.
 // HBM traffic is the algorithmic minimum: every input read once (6 x 4 B per channel and step), y
 // written once (4 B), the state read and written once per sequence.
 #include "common.cuh"
@@ -22,7 +26,7 @@ namespace pb {
 namespace {
 
 constexpr int kH = 64;            // head size
-constexpr int kDepth = 8;         // timesteps of input in flight
+constexpr int kPairs = 4;         // ring depth in pairs of timesteps: eight timesteps of input in flight
 constexpr int kVecs = 6;          // decay, iclr, removal_k, replacement_k, v, r
 
 struct WkvParams {
@@ -39,86 +43,96 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-__global__ void __launch_bounds__(256)
+// One timestep for row i of S.  `buf` holds the step's decay, iclr, removal_k, replacement_k, v, r; `bk` = iclr * removal_k.
+__device__ __forceinline__ float wkv_step(float2 (&S)[32], const float (*buf)[kH], const float* bk, int i) {
+  // sa_i = sum_j S[i][j] * kap_j, four partial sums
+  float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float4 k4 = *reinterpret_cast<const float4*>(&buf[2][4 * j]);
+    acc[(2 * j) & 3] = __ffma2_rn(S[2 * j], make_float2(k4.x, k4.y), acc[(2 * j) & 3]);
+    acc[(2 * j + 1) & 3] = __ffma2_rn(S[2 * j + 1], make_float2(k4.z, k4.w), acc[(2 * j + 1) & 3]);
+  }
+  const float sa = ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
+  const float vi = buf[4][i];
+  const float2 nsa2 = make_float2(-sa, -sa), vi2 = make_float2(vi, vi);
+  float2 y[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float4 w4 = *reinterpret_cast<const float4*>(&buf[0][4 * j]);
+    const float4 b4 = *reinterpret_cast<const float4*>(&bk[4 * j]);
+    const float4 kt4 = *reinterpret_cast<const float4*>(&buf[3][4 * j]);
+    const float4 r4 = *reinterpret_cast<const float4*>(&buf[5][4 * j]);
+    float2 s0 = __ffma2_rn(nsa2, make_float2(b4.x, b4.y), __fmul2_rn(S[2 * j], make_float2(w4.x, w4.y)));
+    float2 s1 = __ffma2_rn(nsa2, make_float2(b4.z, b4.w), __fmul2_rn(S[2 * j + 1], make_float2(w4.z, w4.w)));
+    s0 = __ffma2_rn(vi2, make_float2(kt4.x, kt4.y), s0);
+    s1 = __ffma2_rn(vi2, make_float2(kt4.z, kt4.w), s1);
+    S[2 * j] = s0; S[2 * j + 1] = s1;
+    y[(2 * j) & 3] = __ffma2_rn(s0, make_float2(r4.x, r4.y), y[(2 * j) & 3]);
+    y[(2 * j + 1) & 3] = __ffma2_rn(s1, make_float2(r4.z, r4.w), y[(2 * j + 1) & 3]);
+  }
+  return ((y[0].x + y[0].y) + (y[1].x + y[1].y)) + ((y[2].x + y[2].y) + (y[3].x + y[3].y));
+}
+
+constexpr int kThreads = kH;      // one thread per state row
+
+__global__ void __launch_bounds__(kThreads)
 wkv7_forward_kernel(const __grid_constant__ WkvParams p) {
-  __shared__ __align__(16) float ring[kDepth][kVecs][kH];
+  __shared__ __align__(16) float ring[kPairs][2][kVecs][kH];      // [pair slot][step of the pair][vector][channel]
+  __shared__ __align__(16) float bk[2][kH];                       // iclr * removal_k of the two steps of the current pair
   const int n = blockIdx.x % p.N, b = blockIdx.x / p.N;
   const int C = p.N * kH;
-  const int tid = threadIdx.x, i = tid >> 2, q = tid & 3;
+  const int i = threadIdx.x;
   const size_t head_base = (size_t)b * p.T * C + (size_t)n * kH;      // element (b, t = 0, channel n*H)
 
-  // threads 0..95 each own one 16-byte chunk of one input vector
-  const bool loader = tid < kVecs * (kH / 4);
-  const int lvec = tid / (kH / 4), lchunk = tid % (kH / 4);
-  const float* lsrc = loader ? p.in[lvec] + head_base + lchunk * 4 : nullptr;
-  const uint32_t ldst = (uint32_t)__cvta_generic_to_shared(&ring[0][loader ? lvec : 0][loader ? lchunk * 4 : 0]);
-  auto issue = [&](int t) {
-    if (loader && t < p.T) cp_async16(ldst + (uint32_t)(t % kDepth) * (kVecs * kH * 4), lsrc + (size_t)t * C);
-    cp_async_commit();            // every thread commits a (possibly empty) group per step: the counts stay aligned
+  // a pair of timesteps is 2 x 6 vectors x 16 chunks of 16 bytes = 192 chunks: three per thread
+  auto issue = [&](int pair) {
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+      const int id = c * kThreads + i;                         // 0 .. 191
+      const int step = id / (kVecs * (kH / 4)), vec = (id / (kH / 4)) % kVecs, chunk = id % (kH / 4);
+      const int t = 2 * pair + step;
+      if (t < p.T)
+        cp_async16((uint32_t)__cvta_generic_to_shared(&ring[pair % kPairs][step][vec][chunk * 4]),
+                   p.in[vec] + head_base + (size_t)t * C + chunk * 4);
+    }
+    cp_async_commit();            // every thread commits a (possibly empty) group per pair: the counts stay aligned
   };
 
-  float S[16];
-  const size_t srow = (((size_t)b * p.N + n) * kH + i) * kH + q * 16;
+  float2 S[32];                   // row i of this head's state
+  const size_t srow = (((size_t)b * p.N + n) * kH + i) * kH;
   if (p.state_in) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 16; ++j) {
       const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.state_in + srow) + j);
-      S[4 * j] = s4.x; S[4 * j + 1] = s4.y; S[4 * j + 2] = s4.z; S[4 * j + 3] = s4.w;
+      S[2 * j] = make_float2(s4.x, s4.y); S[2 * j + 1] = make_float2(s4.z, s4.w);
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) S[j] = 0.0f;
+    for (int j = 0; j < 32; ++j) S[j] = make_float2(0.0f, 0.0f);
   }
 
-  for (int t = 0; t < kDepth - 1; ++t) issue(t);
+  const int n_pairs = (p.T + 1) >> 1;
+  for (int pr = 0; pr < kPairs - 1; ++pr) issue(pr);
   float* yp = p.y + head_base + i;
-  for (int t = 0; t < p.T; ++t) {
-    cp_async_wait<kDepth - 2>();      // this thread's copies for step t have landed
-    __syncthreads();                  // ... and everyone's; every thread is also done with step t-1
-    issue(t + kDepth - 1);            // into the buffer step t-1 used
-    const float(*buf)[kH] = ring[t % kDepth];
-    float w[16], kap[16], bk[16];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float4 w4 = *reinterpret_cast<const float4*>(&buf[0][q * 16 + 4 * j]);
-      const float4 a4 = *reinterpret_cast<const float4*>(&buf[1][q * 16 + 4 * j]);
-      const float4 k4 = *reinterpret_cast<const float4*>(&buf[2][q * 16 + 4 * j]);
-      w[4 * j] = w4.x; w[4 * j + 1] = w4.y; w[4 * j + 2] = w4.z; w[4 * j + 3] = w4.w;
-      kap[4 * j] = k4.x; kap[4 * j + 1] = k4.y; kap[4 * j + 2] = k4.z; kap[4 * j + 3] = k4.w;
-      bk[4 * j] = a4.x * k4.x; bk[4 * j + 1] = a4.y * k4.y; bk[4 * j + 2] = a4.z * k4.z; bk[4 * j + 3] = a4.w * k4.w;
-    }
-    float sa0 = 0.0f, sa1 = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 16; j += 2) { sa0 = fmaf(S[j], kap[j], sa0); sa1 = fmaf(S[j + 1], kap[j + 1], sa1); }
-    float sa = sa0 + sa1;
-    sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-    sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-    const float vi = buf[4][i];
-    float y0 = 0.0f, y1 = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float4 kt4 = *reinterpret_cast<const float4*>(&buf[3][q * 16 + 4 * j]);
-      const float4 r4 = *reinterpret_cast<const float4*>(&buf[5][q * 16 + 4 * j]);
-      const float kt[4] = {kt4.x, kt4.y, kt4.z, kt4.w}, rr[4] = {r4.x, r4.y, r4.z, r4.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int c = 4 * j + e;
-        float s = fmaf(-sa, bk[c], S[c] * w[c]);
-        s = fmaf(vi, kt[e], s);
-        S[c] = s;
-        if (e & 1) y1 = fmaf(s, rr[e], y1); else y0 = fmaf(s, rr[e], y0);
-      }
-    }
-    float y = y0 + y1;
-    y += __shfl_xor_sync(0xffffffffu, y, 1);
-    y += __shfl_xor_sync(0xffffffffu, y, 2);
-    if (q == 0) yp[(size_t)t * C] = y;
+  for (int pr = 0; pr < n_pairs; ++pr) {
+    cp_async_wait<kPairs - 2>();      // this thread's copies for this pair have landed
+    __syncthreads();                  // ... and everyone's; every thread is also done with the previous pair (ring slot and bk)
+    issue(pr + kPairs - 1);           // into the slot the previous pair used
+    const float (*step0)[kH] = ring[pr % kPairs][0];
+    const float (*step1)[kH] = ring[pr % kPairs][1];
+    bk[0][i] = step0[1][i] * step0[2][i];
+    bk[1][i] = step1[1][i] * step1[2][i];
+    __syncthreads();
+    const int t = 2 * pr;
+    yp[(size_t)t * C] = wkv_step(S, step0, bk[0], i);
+    if (t + 1 < p.T) yp[(size_t)(t + 1) * C] = wkv_step(S, step1, bk[1], i);
   }
   cp_async_wait<0>();
   if (p.state_out) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      reinterpret_cast<float4*>(p.state_out + srow)[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+    for (int j = 0; j < 16; ++j)
+      reinterpret_cast<float4*>(p.state_out + srow)[j] = make_float4(S[2 * j].x, S[2 * j].y, S[2 * j + 1].x, S[2 * j + 1].y);
   }
 }
 
@@ -140,7 +154,7 @@ extern "C" int pb_wkv7_forward(const float* decay, const float* iclr, const floa
   for (const void* ptr : ptrs)
     if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(PB_ERR_MISALIGNED, "pb_wkv7_forward: every array must be 16-byte aligned");
   WkvParams p{{decay, iclr, removal_k, replacement_k, v, r}, state_in, y, state_out, (int)steps, (int)heads};
-  wkv7_forward_kernel<<<(unsigned)(batch * heads), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  wkv7_forward_kernel<<<(unsigned)(batch * heads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   PB_LAUNCH_CHECK("wkv7_forward_kernel");
   return PB_OK;
 }
