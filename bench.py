@@ -257,6 +257,76 @@ def time_triple(tokens: int, d_model: int, ffn: int, dist: str, seed: int, reps:
     return {"ms": total_ms, "gemm_ms": gemm_ms, "flop": flop, "per_projection": per_shape}
 
 
+# --------------------------------------------------------------------------- the end-to-end training step (configs[4])
+def time_model_step(world: int, rank: int, dev, barrier, steps: int = 2):
+    """One data-parallel training step of the modified RWKV-7 model with every linear layer on the FP8 path: 24 layers,
+    d_model 2048, head size 64, vocabulary 65536, context 4096, 8 sequences per GPU (the configuration's global batch of
+    64 at 8 GPUs) of random token ids, random-init f32 master weights.  A step = forward + backward (blocks recomputed in
+    the backward pass) + all-reduce of the gradients in bf16 over NCCL + a sign-momentum update of the masters.
+    CUDA events around each step, barrier on both sides, mean of `steps` after one warm-up."""
+    import torch
+    import torch.distributed as dist
+    from pratchya_b200._nnx_impl._model import PratchyaCausalLM, PratchyaConfig
+    cfg = PratchyaConfig()
+    seqs, ctx = 8, 4096
+    model = PratchyaCausalLM(cfg, seed=11, device=dev, remat=True)
+    params = [p for p in model.parameters()]
+    momentum = [torch.zeros_like(p) for p in params]
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    ids = torch.randint(0, cfg.vocab_size, (seqs, ctx), device=dev, generator=gen)
+    n_params = sum(p.numel() for p in params)
+    losses = []
+
+    def step(exchange=True):
+        for p in params:
+            p.grad = None
+        _, loss = model(ids, ids)
+        loss.backward()
+        if world > 1 and exchange:
+            flat = torch.cat([p.grad.reshape(-1) for p in params]).to(torch.bfloat16)
+            dist.all_reduce(flat)
+            flat = flat.to(torch.float32) / world
+            off = 0
+            for p in params:
+                p.grad.copy_(flat[off:off + p.numel()].view_as(p))
+                off += p.numel()
+            del flat
+        grads = [p.grad for p in params]
+        with torch.no_grad():
+            torch._foreach_mul_(momentum, 0.9)
+            torch._foreach_add_(momentum, grads, alpha=0.1)
+            torch._foreach_add_(params, [m.sign() for m in momentum], alpha=-1e-4)
+        losses.append(loss.detach())
+
+    # warm-up without the exchange first, so that a rank that cannot run the step says so before any collective waits on it
+    ok = torch.ones(1, device=dev)
+    failure = None
+    try:
+        step(exchange=False)
+        torch.cuda.synchronize()
+    except Exception as e:      # noqa: BLE001 - reported in the record
+        failure = f"{type(e).__name__}: {e}"[:300]
+        ok.zero_()
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if ok.item() == 0:
+        return {"error": failure or "another rank failed in the warm-up step"}
+    step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / steps
+    out = {"ms_per_step": ms, "tokens_per_gpu": seqs * ctx, "parameters": n_params, "losses": [float(l) for l in losses],
+           "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9}
+    del model, params, momentum
+    torch.cuda.empty_cache()
+    return out
+
+
 # --------------------------------------------------------------------------- GPU arm
 def gpu_cpu_affinity(index: int):
     """The CPU set `nvidia-smi topo -m` lists for this GPU (read only), or None."""
@@ -578,6 +648,17 @@ def run_ours(args):
                      "steps": n_sus - n_sus // 3, "clocks": s_clocks}
         _lib.check(lib.pb_gemm_check(stream))
 
+    # ---- the end-to-end training step (configs[4]); its own record, not the headline
+    model_step = None
+    if not args.skip_model_step:
+        torch.cuda.empty_cache()
+        model_step = time_model_step(world, rank, dev, barrier)
+        if "ms_per_step" in model_step:
+            ms_t = torch.tensor([model_step["ms_per_step"]], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+            model_step["ms_per_step"] = ms_t.item()
+
     times = torch.tensor([total_ms, e2e_ms, g_ms, q_ms, big_q_ms, big_qt_ms, big_dq_ms, copy_only_ms, scale["ms"], scale["gemm_ms"],
                           allreduce["ms"] if allreduce else 0.0], device=dev, dtype=torch.float64)
     if world > 1:
@@ -649,6 +730,15 @@ def run_ours(args):
             out["triple"] = {"workload": "configs[2]: fwd+dgrad+wgrad of 4x[2048->2048], [2048->8192], [8192->2048] at M = 32768 tokens, dY e4m3",
                              "ms": triple["ms"], "gemm_only_ms": triple["gemm_ms"], "tflops": triple["flop"] / triple["ms"] / 1e9,
                              "gemm_only_tflops": triple["flop"] / triple["gemm_ms"] / 1e9, "per_projection": triple["per_projection"]}
+        if model_step is not None:
+            if "ms_per_step" in model_step:
+                model_step["tokens_per_s"] = world * model_step["tokens_per_gpu"] / (model_step["ms_per_step"] * 1e-3)
+            out["model_step"] = dict(model_step, workload=(
+                "configs[4]: modified RWKV-7, 24 layers, d_model 2048, head size 64, vocabulary 65536, context 4096, 8 sequences per GPU "
+                f"({8 * world} global; the configuration's 64 at 8 GPUs), random token ids, random-init f32 masters; forward + backward with "
+                "block recomputation + bf16 gradient all-reduce (NCCL) + sign-momentum update; every linear layer through linear_fp8, "
+                "the WKV-7 scan and its backward pass through the package's kernels, the remaining elementwise work in torch"),
+                scaling="weak", timing="CUDA events around 2 steps after 2 warm-up steps, max over ranks")
         if sustained is not None:
             out["sustained"] = dict(sustained, peak=2.0 * peaks["bf16_tflops_sustained"],
                                     peak_source="2 x bf16_tflops_sustained of " + peaks["source"],
@@ -721,6 +811,7 @@ def main():
                     help="only the headline step and its per-kernel pass (for launch lists under a profiler): no e2e, triple, scaleout or CPU leg")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "transposed", "dequantize", "wkv7"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
+    ap.add_argument("--skip-model-step", action="store_true", help="leave out the end-to-end training-step record (about half a minute)")
     ap.add_argument("--cpu-child", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.cpu_child:

@@ -163,7 +163,10 @@ class _LinearFn(torch.autograd.Function):
         a, b = grid
         x2 = x.reshape(-1, x.shape[-1])
         wq = _ops.quantize_impl(weight, grid)
-        want_xt = recipe == "fp8" and a == 128 and x2.shape[0] % 1024 == 0
+        # the tensor-core backward needs the weight as a K-major operand in both directions: (128,128) blocks only.
+        # A (128,1) weight (LoRA, gate, lm_head) has one scale per column and 128 rows, which no 128-deep block
+        # along its columns can carry: its forward runs on the tensor cores, its backward on the literal recipe.
+        want_xt = recipe == "fp8" and (a, b) == (128, 128) and x2.shape[0] % 1024 == 0
         if want_xt:       # both forms of x in one call (x itself is not kept for the backward pass)
             xq, xt = _ops.quantize_dual_impl(x2)
         else:

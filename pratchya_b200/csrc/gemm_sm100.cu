@@ -1065,16 +1065,39 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 
 EncodeTiledFn encode_tiled() { return reinterpret_cast<EncodeTiledFn>(tensor_map_encoder()); }
 
+// A tensor map is a pure function of its arguments, and a layer calls with the same few (pointer, shape)
+// sets step after step: each host thread keeps the last sixteen maps it encoded instead of asking the driver
+// for five of them on every launch.
+struct MapKey {
+  const void* base; cuuint64_t d0, d1, stride; cuuint32_t b0, b1; int type, swizzle, promotion;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && d0 == o.d0 && d1 == o.d1 && stride == o.stride && b0 == o.b0 && b1 == o.b1 && type == o.type &&
+           swizzle == o.swizzle && promotion == o.promotion;
+  }
+};
+CUresult encode_cached(EncodeTiledFn fn, CUtensorMap* map, CUtensorMapDataType type, const void* base, const cuuint64_t* dims,
+                       const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle, CUtensorMapL2promotion promotion) {
+  struct Entry { MapKey key; CUtensorMap map; bool used; };
+  static thread_local Entry cache[16] = {};
+  static thread_local int next = 0;
+  const MapKey key{base, dims[0], dims[1], strides[0], box[0], box[1], (int)type, (int)swizzle, (int)promotion};
+  for (const Entry& e : cache)
+    if (e.used && e.key == key) { *map = e.map; return CUDA_SUCCESS; }
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promotion,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) { cache[next] = Entry{key, *map, true}; next = (next + 1) & 15; }
+  return r;
+}
+
 int make_operand_map(CUtensorMap* map, const void* q, int64_t rows, int64_t depth, int box_rows) {
   EncodeTiledFn fn = encode_tiled();
   if (!fn) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[2] = {(cuuint64_t)depth, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)depth};
   const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(q), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = encode_cached(fn, map, CU_TENSOR_MAP_DATA_TYPE_UINT8, q, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
   if (r != CUDA_SUCCESS) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return PB_OK;
 }
@@ -1088,11 +1111,9 @@ int make_store_map(CUtensorMap* map, void* d, int d_dtype, int64_t M, int64_t N,
   const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
   const cuuint64_t strides[1] = {(cuuint64_t)(ldd * es)};
   const cuuint32_t box[2] = {32, 32};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(map, d_dtype == PB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, d, dims, strides,
-                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        d_dtype == PB_BF16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = encode_cached(fn, map, d_dtype == PB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, d, dims,
+                                   strides, box, d_dtype == PB_BF16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_NONE);
   if (r != CUDA_SUCCESS) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
   return PB_OK;
 }
@@ -1104,10 +1125,8 @@ int make_sf_map(CUtensorMap* map, const void* sf, int64_t atoms, int atoms_per_b
   const cuuint64_t dims[2] = {128, (cuuint64_t)atoms};
   const cuuint64_t strides[1] = {512};
   const cuuint32_t box[2] = {128, (cuuint32_t)atoms_per_box};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(sf), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = encode_cached(fn, map, CU_TENSOR_MAP_DATA_TYPE_UINT32, sf, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                   CU_TENSOR_MAP_L2_PROMOTION_NONE);
   if (r != CUDA_SUCCESS) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled (scale factors) failed with CUresult %d", (int)r);
   return PB_OK;
 }

@@ -28,12 +28,14 @@ namespace {
 constexpr int kH = 64;            // head size
 constexpr int kPairs = 4;         // ring depth in pairs of timesteps: eight timesteps of input in flight
 constexpr int kVecs = 6;          // decay, iclr, removal_k, replacement_k, v, r
+constexpr int kCk = 16;           // spacing of the state checkpoints the backward pass restarts from
 
 struct WkvParams {
   const float* in[kVecs];
   const float* state_in;          // [B, N, H, H] or null (zeros)
   float* y;                       // [B, T, C]
   float* state_out;               // [B, N, H, H] or null
+  float* ckpt;                    // [B, N, ceil(T / kCk), H, H] or null: the state before timesteps 0, kCk, 2*kCk, ...
   int T, N;                       // timesteps, heads
 };
 
@@ -125,6 +127,11 @@ wkv7_forward_kernel(const __grid_constant__ WkvParams p) {
     bk[1][i] = step1[1][i] * step1[2][i];
     __syncthreads();
     const int t = 2 * pr;
+    if (p.ckpt && (t & (kCk - 1)) == 0) {
+      float4* dst = reinterpret_cast<float4*>(p.ckpt + ((((size_t)b * p.N + n) * ((p.T + kCk - 1) / kCk) + t / kCk) * kH + i) * kH);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) dst[j] = make_float4(S[2 * j].x, S[2 * j].y, S[2 * j + 1].x, S[2 * j + 1].y);
+    }
     yp[(size_t)t * C] = wkv_step(S, step0, bk[0], i);
     if (t + 1 < p.T) yp[(size_t)(t + 1) * C] = wkv_step(S, step1, bk[1], i);
   }
@@ -136,6 +143,167 @@ wkv7_forward_kernel(const __grid_constant__ WkvParams p) {
   }
 }
 
+// ---- backward of the scan ------------------------------------------------------------------------------------
+// With G_t = dS_t + dy_t r_t^T the gradient of the loss with respect to S_t (dS_t arriving from timestep t+1):
+//     dr_t   = S_t^T dy_t                    dv_t  = G_t kt_t                 dkt_t = G_t^T v_t
+//     dsa_t  = -G_t b_t   (b = a * kap)      db_t  = -G_t^T sa_t              dw_t  = sum_i G_t[i][:] * S_{t-1}[i][:]
+//     dkap_t = S_{t-1}^T dsa_t + db_t * a_t  da_t  = db_t * kap_t             dS_{t-1} = G_t diag(w_t) + dsa_t kap_t^T
+// Half of these are sums along a row of the state, half along a column, so a CTA of 128 threads keeps two
+// copies of S_{t-1} and of dS in registers: threads 0..63 one row each, threads 64..127 one column each; the
+// row threads publish sa and dsa (64 floats each) through shared memory, two block barriers per timestep.
+// S_{t-1} is not stored by the forward pass for every t: it writes a checkpoint every kCk timesteps, and the
+// backward pass recomputes the kCk states of a chunk from its checkpoint into a per-head scratch buffer
+// (256 KB per head: it stays in L2), then walks the chunk backwards reading them from there.
+struct WkvBwdParams {
+  const float* in[kVecs];
+  const float* dy;                // [B, T, C]
+  const float* ckpt;              // [B, N, ceil(T / kCk), H, H]
+  const float* dstate_out;        // [B, N, H, H] or null: gradient with respect to the final state
+  float* din[kVecs];              // gradients of the six inputs, [B, T, C] each
+  float* dstate_in;               // [B, N, H, H] or null: gradient with respect to the initial state
+  float* scratch;                 // [B * N, kCk, H, H]
+  int T, N;
+};
+
+__global__ void __launch_bounds__(2 * kH, 1)
+wkv7_backward_kernel(const __grid_constant__ WkvBwdParams p) {
+  __shared__ __align__(16) float vec[kCk][kVecs + 1][kH];       // the chunk's inputs and dy
+  __shared__ __align__(16) float sa_s[kH], dsa_s[kH];
+  const int n = blockIdx.x % p.N, b = blockIdx.x / p.N;
+  const int C = p.N * kH;
+  const int tid = threadIdx.x;
+  const bool row_thread = tid < kH;
+  const int idx = row_thread ? tid : tid - kH;                  // the row i, or the column j, this thread owns
+  const size_t head_base = (size_t)b * p.T * C + (size_t)n * kH;
+  const size_t head = (size_t)b * p.N + n;
+  const int n_ck = (p.T + kCk - 1) / kCk;
+  float* scratch = p.scratch + head * (size_t)kCk * kH * kH;
+
+  float dS[kH];                   // row idx (row threads) or column idx (column threads) of dS
+  if (p.dstate_out) {
+#pragma unroll
+    for (int e = 0; e < kH; ++e)
+      dS[e] = row_thread ? p.dstate_out[(head * kH + idx) * kH + e] : p.dstate_out[(head * kH + e) * kH + idx];
+  } else {
+#pragma unroll
+    for (int e = 0; e < kH; ++e) dS[e] = 0.0f;
+  }
+
+  for (int ck = n_ck - 1; ck >= 0; --ck) {
+    const int t0 = ck * kCk, steps = min(kCk, p.T - t0);
+    __syncthreads();              // everyone is done with the previous chunk's vectors and scratch
+    for (int e = tid; e < steps * (kVecs + 1) * (kH / 4); e += 2 * kH) {
+      const int s = e / ((kVecs + 1) * (kH / 4)), rem = e % ((kVecs + 1) * (kH / 4)), v = rem / (kH / 4), c4 = rem % (kH / 4);
+      const float* src = (v < kVecs ? p.in[v] : p.dy) + head_base + (size_t)(t0 + s) * C + c4 * 4;
+      *reinterpret_cast<float4*>(&vec[s][v][c4 * 4]) = __ldg(reinterpret_cast<const float4*>(src));
+    }
+    __syncthreads();
+    if (row_thread) {
+      // recompute the chunk's states forward from its checkpoint; the state BEFORE timestep t0 + s goes to scratch[s]
+      float S[kH];
+      const float4* c4p = reinterpret_cast<const float4*>(p.ckpt + ((head * n_ck + ck) * kH + idx) * kH);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) { const float4 q = __ldg(c4p + j); S[4 * j] = q.x; S[4 * j + 1] = q.y; S[4 * j + 2] = q.z; S[4 * j + 3] = q.w; }
+      for (int s = 0; s < steps; ++s) {
+        float4* dst = reinterpret_cast<float4*>(scratch + ((size_t)s * kH + idx) * kH);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) dst[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+        if (s + 1 < steps) {      // the state after the chunk's last timestep is not needed
+          float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f;
+#pragma unroll
+          for (int j = 0; j < kH; j += 4) {
+            sa0 = fmaf(S[j], vec[s][2][j], sa0); sa1 = fmaf(S[j + 1], vec[s][2][j + 1], sa1);
+            sa2 = fmaf(S[j + 2], vec[s][2][j + 2], sa2); sa3 = fmaf(S[j + 3], vec[s][2][j + 3], sa3);
+          }
+          const float sa = (sa0 + sa1) + (sa2 + sa3), vi = vec[s][4][idx];
+#pragma unroll
+          for (int j = 0; j < kH; ++j)
+            S[j] = fmaf(vi, vec[s][3][j], fmaf(-sa, vec[s][1][j] * vec[s][2][j], S[j] * vec[s][0][j]));
+        }
+      }
+    }
+    __syncthreads();              // the chunk's states are in scratch (written and read by this block only)
+
+    for (int s = steps - 1; s >= 0; --s) {
+      const size_t out = head_base + (size_t)(t0 + s) * C + idx;
+      const float* w = vec[s][0]; const float* a = vec[s][1]; const float* kap = vec[s][2];
+      const float* kt = vec[s][3]; const float* v = vec[s][4]; const float* r = vec[s][5]; const float* dy = vec[s][6];
+      float Sp[kH];               // row / column idx of S_{t-1}
+      if (row_thread) {
+        const float4* src = reinterpret_cast<const float4*>(scratch + ((size_t)s * kH + idx) * kH);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { const float4 q = src[j]; Sp[4 * j] = q.x; Sp[4 * j + 1] = q.y; Sp[4 * j + 2] = q.z; Sp[4 * j + 3] = q.w; }
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+        for (int j = 0; j < kH; j += 4) {
+          s0 = fmaf(Sp[j], kap[j], s0); s1 = fmaf(Sp[j + 1], kap[j + 1], s1);
+          s2 = fmaf(Sp[j + 2], kap[j + 2], s2); s3 = fmaf(Sp[j + 3], kap[j + 3], s3);
+        }
+        sa_s[idx] = (s0 + s1) + (s2 + s3);
+      } else {
+#pragma unroll
+        for (int i = 0; i < kH; ++i) Sp[i] = scratch[((size_t)s * kH + i) * kH + idx];
+      }
+      __syncthreads();            // sa is published
+      float db_keep = 0.0f;
+      if (row_thread) {
+        const float dyi = dy[idx];
+        float dv0 = 0.f, dv1 = 0.f, ds0 = 0.f, ds1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < kH; j += 2) {
+          const float g0 = fmaf(dyi, r[j], dS[j]), g1 = fmaf(dyi, r[j + 1], dS[j + 1]);
+          dS[j] = g0; dS[j + 1] = g1;
+          dv0 = fmaf(g0, kt[j], dv0); dv1 = fmaf(g1, kt[j + 1], dv1);
+          ds0 = fmaf(g0, a[j] * kap[j], ds0); ds1 = fmaf(g1, a[j + 1] * kap[j + 1], ds1);
+        }
+        const float dsa = -(ds0 + ds1);
+        dsa_s[idx] = dsa;
+        p.din[4][out] = dv0 + dv1;
+#pragma unroll
+        for (int j = 0; j < kH; ++j) dS[j] = fmaf(dsa, kap[j], dS[j] * w[j]);
+      } else {
+        const float wj = w[idx], bj = a[idx] * kap[idx], ktj = kt[idx], rj = r[idx];
+        float dr0 = 0.f, dr1 = 0.f, dkt0 = 0.f, dkt1 = 0.f, db0 = 0.f, db1 = 0.f, dw0 = 0.f, dw1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < kH; i += 2) {
+          const float st0 = fmaf(v[i], ktj, fmaf(-sa_s[i], bj, Sp[i] * wj));
+          const float st1 = fmaf(v[i + 1], ktj, fmaf(-sa_s[i + 1], bj, Sp[i + 1] * wj));
+          const float g0 = fmaf(dy[i], rj, dS[i]), g1 = fmaf(dy[i + 1], rj, dS[i + 1]);
+          dS[i] = g0; dS[i + 1] = g1;
+          dr0 = fmaf(st0, dy[i], dr0); dr1 = fmaf(st1, dy[i + 1], dr1);
+          dkt0 = fmaf(g0, v[i], dkt0); dkt1 = fmaf(g1, v[i + 1], dkt1);
+          db0 = fmaf(g0, sa_s[i], db0); db1 = fmaf(g1, sa_s[i + 1], db1);
+          dw0 = fmaf(g0, Sp[i], dw0); dw1 = fmaf(g1, Sp[i + 1], dw1);
+        }
+        db_keep = -(db0 + db1);
+        p.din[5][out] = dr0 + dr1;
+        p.din[3][out] = dkt0 + dkt1;
+        p.din[0][out] = dw0 + dw1;
+      }
+      __syncthreads();            // dsa is published
+      if (!row_thread) {
+        const float db = db_keep, wj = w[idx];
+        const float kapj = kap[idx];
+        float dk0 = 0.f, dk1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < kH; i += 2) {
+          dk0 = fmaf(Sp[i], dsa_s[i], dk0); dk1 = fmaf(Sp[i + 1], dsa_s[i + 1], dk1);
+          dS[i] = fmaf(dsa_s[i], kapj, dS[i] * wj);
+          dS[i + 1] = fmaf(dsa_s[i + 1], kapj, dS[i + 1] * wj);
+        }
+        p.din[2][out] = (dk0 + dk1) + db * a[idx];
+        p.din[1][out] = db * kapj;
+      }
+      __syncthreads();            // sa_s / dsa_s may be overwritten by the next timestep
+    }
+  }
+  if (p.dstate_in && row_thread) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      reinterpret_cast<float4*>(p.dstate_in + (head * kH + idx) * kH)[j] = make_float4(dS[4 * j], dS[4 * j + 1], dS[4 * j + 2], dS[4 * j + 3]);
+  }
+}
+
 }  // namespace
 }  // namespace pb
 
@@ -144,17 +312,51 @@ using namespace pb;
 extern "C" int pb_wkv7_forward(const float* decay, const float* iclr, const float* removal_k, const float* replacement_k,
                                const float* v, const float* r, const float* state_in,
                                int64_t batch, int64_t steps, int64_t heads, int head_dim,
-                               float* y, float* state_out, void* stream) {
+                               float* y, float* state_out, float* checkpoints, void* stream) {
   if (!decay || !iclr || !removal_k || !replacement_k || !v || !r || !y)
     return fail(PB_ERR_NULL_POINTER, "pb_wkv7_forward: the six inputs and y must be non-null");
   if (head_dim != kH) return fail(PB_ERR_UNSUPPORTED, "pb_wkv7_forward: head size %d (this kernel is built for %d)", head_dim, kH);
   if (batch <= 0 || steps <= 0 || heads <= 0 || batch * heads > 0x7fffffffll || steps > 0x7fffffffll)
     return fail(PB_ERR_BAD_SHAPE, "pb_wkv7_forward: batch=%lld steps=%lld heads=%lld", (long long)batch, (long long)steps, (long long)heads);
-  const void* ptrs[] = {decay, iclr, removal_k, replacement_k, v, r, state_in, state_out};
+  const void* ptrs[] = {decay, iclr, removal_k, replacement_k, v, r, state_in, state_out, checkpoints};
   for (const void* ptr : ptrs)
     if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(PB_ERR_MISALIGNED, "pb_wkv7_forward: every array must be 16-byte aligned");
-  WkvParams p{{decay, iclr, removal_k, replacement_k, v, r}, state_in, y, state_out, (int)steps, (int)heads};
+  WkvParams p{{decay, iclr, removal_k, replacement_k, v, r}, state_in, y, state_out, checkpoints, (int)steps, (int)heads};
   wkv7_forward_kernel<<<(unsigned)(batch * heads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   PB_LAUNCH_CHECK("wkv7_forward_kernel");
+  return PB_OK;
+}
+
+extern "C" size_t pb_wkv7_checkpoint_floats(int64_t batch, int64_t steps, int64_t heads, int head_dim) {
+  if (batch <= 0 || steps <= 0 || heads <= 0 || head_dim != kH) return 0;
+  return (size_t)batch * heads * ((steps + kCk - 1) / kCk) * kH * kH;
+}
+
+extern "C" size_t pb_wkv7_backward_workspace_size(int64_t batch, int64_t heads, int head_dim) {
+  if (batch <= 0 || heads <= 0 || head_dim != kH) return 0;
+  return (size_t)batch * heads * kCk * kH * kH * sizeof(float);
+}
+
+extern "C" int pb_wkv7_backward(const float* decay, const float* iclr, const float* removal_k, const float* replacement_k,
+                                const float* v, const float* r, const float* checkpoints, const float* dy, const float* dstate_out,
+                                int64_t batch, int64_t steps, int64_t heads, int head_dim,
+                                float* d_decay, float* d_iclr, float* d_removal_k, float* d_replacement_k, float* d_v, float* d_r,
+                                float* dstate_in, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!decay || !iclr || !removal_k || !replacement_k || !v || !r || !checkpoints || !dy || !d_decay || !d_iclr || !d_removal_k ||
+      !d_replacement_k || !d_v || !d_r)
+    return fail(PB_ERR_NULL_POINTER, "pb_wkv7_backward: the six inputs, the checkpoints, dy and the six gradients must be non-null");
+  if (head_dim != kH) return fail(PB_ERR_UNSUPPORTED, "pb_wkv7_backward: head size %d (this kernel is built for %d)", head_dim, kH);
+  if (batch <= 0 || steps <= 0 || heads <= 0 || batch * heads > 0x7fffffffll || steps > 0x7fffffffll)
+    return fail(PB_ERR_BAD_SHAPE, "pb_wkv7_backward: batch=%lld steps=%lld heads=%lld", (long long)batch, (long long)steps, (long long)heads);
+  const size_t need = pb_wkv7_backward_workspace_size(batch, heads, head_dim);
+  if (!workspace || workspace_bytes < need)
+    return fail(PB_ERR_WORKSPACE_TOO_SMALL, "pb_wkv7_backward: needs %zu bytes of workspace, got %zu", need, workspace_bytes);
+  const void* ptrs[] = {decay, iclr, removal_k, replacement_k, v, r, checkpoints, dy, dstate_out, dstate_in, workspace};
+  for (const void* ptr : ptrs)
+    if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(PB_ERR_MISALIGNED, "pb_wkv7_backward: every array must be 16-byte aligned");
+  WkvBwdParams p{{decay, iclr, removal_k, replacement_k, v, r}, dy, checkpoints, dstate_out,
+                 {d_decay, d_iclr, d_removal_k, d_replacement_k, d_v, d_r}, dstate_in, static_cast<float*>(workspace), (int)steps, (int)heads};
+  wkv7_backward_kernel<<<(unsigned)(batch * heads), 2 * kH, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  PB_LAUNCH_CHECK("wkv7_backward_kernel");
   return PB_OK;
 }
