@@ -267,6 +267,8 @@ def time_model_step(world: int, rank: int, dev, barrier, steps: int = 2):
     import torch
     import torch.distributed as dist
     from pratchya_b200._nnx_impl._model import PratchyaCausalLM, PratchyaConfig
+    from pratchya_b200._qualia import set_literal_dot_precision
+    set_literal_dot_precision("tf32")   # the (128,1)-grid layers' backward dots (LoRA, lm_head): what an f32 dot gets under XLA on a GPU
     cfg = PratchyaConfig()
     seqs, ctx = 8, 4096
     model = PratchyaCausalLM(cfg, seed=11, device=dev, remat=True)
@@ -321,7 +323,8 @@ def time_model_step(world: int, rank: int, dev, barrier, steps: int = 2):
     barrier()
     ms = e0.elapsed_time(e1) / steps
     out = {"ms_per_step": ms, "tokens_per_gpu": seqs * ctx, "parameters": n_params, "losses": [float(l) for l in losses],
-           "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9}
+           "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9, "literal_dot_precision": "tf32"}
+    set_literal_dot_precision("f32")
     del model, params, momentum
     torch.cuda.empty_cache()
     return out
@@ -782,6 +785,20 @@ def run_profile_case(name: str):
         v, r = torch.randn(shape, device="cuda", generator=g), torch.randn(shape, device="cuda", generator=g)
         for _ in range(3):
             wkv_state_scan(None, decay, iclr, rk, k * iclr, v, r, heads)
+    elif name == "wkv7_backward":
+        from pratchya_b200._nnx_impl import wkv_state_scan
+        bsz, steps, heads = 8, 512, 32
+        g = torch.Generator(device="cuda").manual_seed(0)
+        shape = (bsz, steps, heads * 64)
+        decay = torch.exp(-torch.exp(torch.randn(shape, device="cuda", generator=g) * 0.5 - 1.0))
+        iclr = torch.sigmoid(torch.randn(shape, device="cuda", generator=g))
+        k = torch.randn(shape, device="cuda", generator=g)
+        rk = torch.nn.functional.normalize(k.view(bsz, steps, heads, 64), dim=-1).reshape(shape)
+        ins = [decay, iclr, rk, k * iclr, torch.randn(shape, device="cuda", generator=g), torch.randn(shape, device="cuda", generator=g)]
+        ins = [t.requires_grad_(True) for t in ins]
+        dy = torch.randn(shape, device="cuda", generator=g)
+        for _ in range(3):
+            wkv_state_scan(None, *ins, heads)[1].backward(dy)
     elif name == "gemm_full":
         m, n, k = M, N, K                                   # the benchmark's own launch, for DRAM-byte counters only
         x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
@@ -809,7 +826,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--headline-only", action="store_true",
                     help="only the headline step and its per-kernel pass (for launch lists under a profiler): no e2e, triple, scaleout or CPU leg")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "transposed", "dequantize", "wkv7"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "transposed", "dequantize", "wkv7", "wkv7_backward"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
     ap.add_argument("--skip-model-step", action="store_true", help="leave out the end-to-end training-step record (about half a minute)")
     ap.add_argument("--cpu-child", action="store_true", help=argparse.SUPPRESS)

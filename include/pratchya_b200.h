@@ -249,8 +249,8 @@ PB_API int pb_quantize_dual(const void* x, int x_dtype, int64_t batch, int64_t r
  *      are f32 [batch, steps, heads*head_dim]; state_in / state_out are f32 [batch, heads, head_dim, head_dim]
  *      (state_in may be null for a zero state, state_out may be null); y is f32 [batch, steps, heads*head_dim],
  *      the order the reference has after its transpose (:210).  head_dim must be 64.  16-byte aligned arrays.
- *      `checkpoints` (may be null) receives the state before timesteps 0, 16, 32, ... as f32
- *      [batch, heads, ceil(steps/16), head_dim, head_dim] (pb_wkv7_checkpoint_floats elements): what
+ *      `checkpoints` (may be null) receives the state before timesteps 0, 8, 16, ... as f32
+ *      [batch, heads, ceil(steps/8), head_dim, head_dim] (pb_wkv7_checkpoint_floats elements): what
  *      pb_wkv7_backward restarts from. */
 PB_API int pb_wkv7_forward(const float* decay, const float* iclr, const float* removal_k, const float* replacement_k,
                     const float* v, const float* r, const float* state_in,
@@ -259,14 +259,13 @@ PB_API int pb_wkv7_forward(const float* decay, const float* iclr, const float* r
 PB_API size_t pb_wkv7_checkpoint_floats(int64_t batch, int64_t steps, int64_t heads, int head_dim);
 /* Cotangents of the scan: what jax.grad derives from `wkv_state_scan` (pratchya/_nnx_impl/_module.py:187-207) for the
  * six inputs and the initial state, given dy [batch, steps, heads*head_dim] and (optionally) the cotangent of the final
- * state.  The states the derivatives need are recomputed sixteen timesteps at a time from the forward pass's checkpoints
- * into `workspace` (pb_wkv7_backward_workspace_size bytes: 256 KB per (batch, head), caller-owned).  All arrays f32. */
-PB_API size_t pb_wkv7_backward_workspace_size(int64_t batch, int64_t heads, int head_dim);
+ * state.  The states the derivatives need are recomputed eight timesteps at a time from the forward pass's checkpoints
+ * and stay in shared memory: the call needs no workspace.  All arrays f32. */
 PB_API int pb_wkv7_backward(const float* decay, const float* iclr, const float* removal_k, const float* replacement_k,
                      const float* v, const float* r, const float* checkpoints, const float* dy, const float* dstate_out,
                      int64_t batch, int64_t steps, int64_t heads, int head_dim,
                      float* d_decay, float* d_iclr, float* d_removal_k, float* d_replacement_k, float* d_v, float* d_r,
-                     float* dstate_in, void* workspace, size_t workspace_bytes, void* stream);
+                     float* dstate_in, void* stream);
 
 /* byte transpose [rows, cols] -> [cols, rows] of an fp8 matrix (weight prepared for the forward GEMM) */
 PB_API int pb_transpose_bytes(const void* src, int64_t rows, int64_t cols, void* dst, void* stream);

@@ -64,13 +64,11 @@ class _WkvScanFn(torch.autograd.Function):
             d_state = d_state_out.to(torch.float32).contiguous() if d_state_out is not None else None
             grads = [torch.empty_like(ins[0]) for _ in range(6)]
             d_state_in = torch.empty((bsz, n_head, head_dim, head_dim), dtype=torch.float32, device=dev) if ctx.has_state else None
-            ws_bytes = lib.pb_wkv7_backward_workspace_size(bsz, n_head, head_dim)
-            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
             check(lib.pb_wkv7_backward(*[t.data_ptr() for t in ins], ckpt.data_ptr(), d_out.data_ptr(),
                                        d_state.data_ptr() if d_state is not None else None,
                                        bsz, steps, n_head, head_dim, *[g.data_ptr() for g in grads],
                                        d_state_in.data_ptr() if d_state_in is not None else None,
-                                       ws.data_ptr(), ws_bytes, torch.cuda.current_stream(dev).cuda_stream))
+                                       torch.cuda.current_stream(dev).cuda_stream))
         return (d_state_in, *grads, None)
 
 

@@ -376,9 +376,23 @@ def matmul_impl(x_fp8, x_sc8, x_sc32, y_fp8, y_sc8, y_sc32, block_grid_x, block_
     return _matmul_f32(x, y).to(out_dtype)
 
 
+_LITERAL_DOT_TF32 = False
+
+
+def set_literal_dot_precision(precision: str) -> None:
+    """Precision of the library f32 matmul behind the grids the block-scaled kernel cannot take (the reference's
+    literal recipe there: dequantize, then an f32 dot).  "f32" (default) keeps full f32 products; "tf32" lets the
+    library round the operands to 10 mantissa bits, which is what an f32 dot gets on a GPU under XLA's default
+    precision, and is several times faster."""
+    global _LITERAL_DOT_TF32
+    if precision not in ("f32", "tf32"):
+        raise ValueError(f"precision must be 'f32' or 'tf32', got {precision!r}")
+    _LITERAL_DOT_TF32 = precision == "tf32"
+
+
 def _matmul_f32(x, y):
     prev = torch.backends.cuda.matmul.allow_tf32
-    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = _LITERAL_DOT_TF32
     try:
         return torch.matmul(x, y)
     finally:

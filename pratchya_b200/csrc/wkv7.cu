@@ -28,7 +28,7 @@ namespace {
 constexpr int kH = 64;            // head size
 constexpr int kPairs = 4;         // ring depth in pairs of timesteps: eight timesteps of input in flight
 constexpr int kVecs = 6;          // decay, iclr, removal_k, replacement_k, v, r
-constexpr int kCk = 16;           // spacing of the state checkpoints the backward pass restarts from
+constexpr int kCk = 8;            // spacing of the state checkpoints the backward pass restarts from
 
 struct WkvParams {
   const float* in[kVecs];
@@ -148,12 +148,23 @@ wkv7_forward_kernel(const __grid_constant__ WkvParams p) {
 //     dr_t   = S_t^T dy_t                    dv_t  = G_t kt_t                 dkt_t = G_t^T v_t
 //     dsa_t  = -G_t b_t   (b = a * kap)      db_t  = -G_t^T sa_t              dw_t  = sum_i G_t[i][:] * S_{t-1}[i][:]
 //     dkap_t = S_{t-1}^T dsa_t + db_t * a_t  da_t  = db_t * kap_t             dS_{t-1} = G_t diag(w_t) + dsa_t kap_t^T
-// Half of these are sums along a row of the state, half along a column, so a CTA of 128 threads keeps two
-// copies of S_{t-1} and of dS in registers: threads 0..63 one row each, threads 64..127 one column each; the
-// row threads publish sa and dsa (64 floats each) through shared memory, two block barriers per timestep.
-// S_{t-1} is not stored by the forward pass for every t: it writes a checkpoint every kCk timesteps, and the
-// backward pass recomputes the kCk states of a chunk from its checkpoint into a per-head scratch buffer
-// (256 KB per head: it stays in L2), then walks the chunk backwards reading them from there.
+// Half of these are sums along a row of the state, half along a column, so a CTA of 128 threads keeps two copies
+// of dS in registers: threads 0..63 one row each, threads 64..127 one column each.  The row threads need S_{t-1}
+// only through sa_t = S_{t-1} kap_t; the column threads need its columns.
+//
+// S_{t-1} is not stored by the forward pass for every t: it writes a checkpoint every kCk = 8 timesteps.  The
+// backward pass walks the chunks from the last to the first.  Per chunk the row threads recompute the states
+// from the checkpoint (pass 1), keeping every sa_t (64 floats) and the states before the chunk's last four
+// timesteps in four shared-memory slots; both groups then run those four timesteps backwards; the row threads
+// recompute the states before the first four timesteps into the same slots (pass 2, from the checkpoint and the
+// kept sa_t, so without the dot products) and the four timesteps run backwards.  The recomputed states never
+// leave the SM.  A slot is H x H floats with the 16-byte groups of row i stored at group ^ (i & 15): the row
+// threads' 16-byte row stores and the column threads' 4-byte column loads are both free of bank conflicts.
+// One block barrier per timestep (dsa, row threads -> column threads, double-buffered by the parity of t).
+// The chunk's seven input vectors per timestep arrive by cp.async one chunk ahead, and the checkpoint the next
+// recomputation starts from is loaded into the row threads' registers before the timesteps that precede it.
+constexpr int kSub = 4;           // timesteps whose states are kept at once
+
 struct WkvBwdParams {
   const float* in[kVecs];
   const float* dy;                // [B, T, C]
@@ -161,14 +172,56 @@ struct WkvBwdParams {
   const float* dstate_out;        // [B, N, H, H] or null: gradient with respect to the final state
   float* din[kVecs];              // gradients of the six inputs, [B, T, C] each
   float* dstate_in;               // [B, N, H, H] or null: gradient with respect to the initial state
-  float* scratch;                 // [B * N, kCk, H, H]
   int T, N;
 };
 
-__global__ void __launch_bounds__(2 * kH, 1)
+struct WkvBwdSmem {
+  float slot[kSub][kH * kH];                // recomputed states, swizzled
+  float vec[2][kCk][kVecs + 1][kH];         // the chunk's inputs and dy, two chunks
+  float bk[kCk][kH];                        // iclr * removal_k
+  float sa[kCk][kH];                        // S_{t-1} removal_k_t
+  float dsa[2][kH];
+};
+
+__device__ __forceinline__ float sum4(const float2 a, const float2 b) { return (a.x + a.y) + (b.x + b.y); }
+
+// sa_i = sum_j S[i][j] * kap_j in the forward kernel's order of additions
+__device__ __forceinline__ float wkv_sa(const float2 (&S)[32], const float* kap) {
+  float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float4 k4 = *reinterpret_cast<const float4*>(&kap[4 * j]);
+    acc[(2 * j) & 3] = __ffma2_rn(S[2 * j], make_float2(k4.x, k4.y), acc[(2 * j) & 3]);
+    acc[(2 * j + 1) & 3] = __ffma2_rn(S[2 * j + 1], make_float2(k4.z, k4.w), acc[(2 * j + 1) & 3]);
+  }
+  return ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
+}
+
+// S[i][:] <- S[i][:] * w - sa_i * b + v_i * kt, as the forward kernel forms it
+__device__ __forceinline__ void wkv_update(float2 (&S)[32], const float (*buf)[kH], const float* bk, float sa, float vi) {
+  const float2 nsa2 = make_float2(-sa, -sa), vi2 = make_float2(vi, vi);
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float4 w4 = *reinterpret_cast<const float4*>(&buf[0][4 * j]);
+    const float4 b4 = *reinterpret_cast<const float4*>(&bk[4 * j]);
+    const float4 kt4 = *reinterpret_cast<const float4*>(&buf[3][4 * j]);
+    float2 s0 = __ffma2_rn(nsa2, make_float2(b4.x, b4.y), __fmul2_rn(S[2 * j], make_float2(w4.x, w4.y)));
+    float2 s1 = __ffma2_rn(nsa2, make_float2(b4.z, b4.w), __fmul2_rn(S[2 * j + 1], make_float2(w4.z, w4.w)));
+    S[2 * j] = __ffma2_rn(vi2, make_float2(kt4.x, kt4.y), s0);
+    S[2 * j + 1] = __ffma2_rn(vi2, make_float2(kt4.z, kt4.w), s1);
+  }
+}
+
+__device__ __forceinline__ void slot_store_row(float* slot, int i, const float2 (&S)[32]) {
+#pragma unroll
+  for (int g = 0; g < 16; ++g)
+    *reinterpret_cast<float4*>(&slot[i * kH + ((g ^ (i & 15)) << 2)]) = make_float4(S[2 * g].x, S[2 * g].y, S[2 * g + 1].x, S[2 * g + 1].y);
+}
+
+__global__ void __launch_bounds__(2 * kH, 2)
 wkv7_backward_kernel(const __grid_constant__ WkvBwdParams p) {
-  __shared__ __align__(16) float vec[kCk][kVecs + 1][kH];       // the chunk's inputs and dy
-  __shared__ __align__(16) float sa_s[kH], dsa_s[kH];
+  extern __shared__ __align__(16) unsigned char wkv_bwd_smem[];
+  WkvBwdSmem& sm = *reinterpret_cast<WkvBwdSmem*>(wkv_bwd_smem);
   const int n = blockIdx.x % p.N, b = blockIdx.x / p.N;
   const int C = p.N * kH;
   const int tid = threadIdx.x;
@@ -177,130 +230,179 @@ wkv7_backward_kernel(const __grid_constant__ WkvBwdParams p) {
   const size_t head_base = (size_t)b * p.T * C + (size_t)n * kH;
   const size_t head = (size_t)b * p.N + n;
   const int n_ck = (p.T + kCk - 1) / kCk;
-  float* scratch = p.scratch + head * (size_t)kCk * kH * kH;
 
-  float dS[kH];                   // row idx (row threads) or column idx (column threads) of dS
-  if (p.dstate_out) {
+  // element (i, idx) of a slot, for a column thread: i * kH + joff[i & 15]
+  int joff[16];
 #pragma unroll
-    for (int e = 0; e < kH; ++e)
-      dS[e] = row_thread ? p.dstate_out[(head * kH + idx) * kH + e] : p.dstate_out[(head * kH + e) * kH + idx];
+  for (int c = 0; c < 16; ++c) joff[c] = ((((idx >> 2) ^ c) << 2) | (idx & 3));
+
+  float2 dS[32];                  // row idx (row threads: pairs of columns) or column idx (column threads: pairs of rows) of dS
+  if (p.dstate_out) {
+    if (row_thread) {
+#pragma unroll
+      for (int g = 0; g < 16; ++g) {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(p.dstate_out + (head * kH + idx) * kH) + g);
+        dS[2 * g] = make_float2(q.x, q.y); dS[2 * g + 1] = make_float2(q.z, q.w);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e)
+        dS[e] = make_float2(__ldg(p.dstate_out + (head * kH + 2 * e) * kH + idx), __ldg(p.dstate_out + (head * kH + 2 * e + 1) * kH + idx));
+    }
   } else {
 #pragma unroll
-    for (int e = 0; e < kH; ++e) dS[e] = 0.0f;
+    for (int e = 0; e < 32; ++e) dS[e] = make_float2(0.0f, 0.0f);
   }
 
-  for (int ck = n_ck - 1; ck >= 0; --ck) {
-    const int t0 = ck * kCk, steps = min(kCk, p.T - t0);
-    __syncthreads();              // everyone is done with the previous chunk's vectors and scratch
-    for (int e = tid; e < steps * (kVecs + 1) * (kH / 4); e += 2 * kH) {
-      const int s = e / ((kVecs + 1) * (kH / 4)), rem = e % ((kVecs + 1) * (kH / 4)), v = rem / (kH / 4), c4 = rem % (kH / 4);
-      const float* src = (v < kVecs ? p.in[v] : p.dy) + head_base + (size_t)(t0 + s) * C + c4 * 4;
-      *reinterpret_cast<float4*>(&vec[s][v][c4 * 4]) = __ldg(reinterpret_cast<const float4*>(src));
-    }
-    __syncthreads();
-    if (row_thread) {
-      // recompute the chunk's states forward from its checkpoint; the state BEFORE timestep t0 + s goes to scratch[s]
-      float S[kH];
-      const float4* c4p = reinterpret_cast<const float4*>(p.ckpt + ((head * n_ck + ck) * kH + idx) * kH);
-#pragma unroll
-      for (int j = 0; j < 16; ++j) { const float4 q = __ldg(c4p + j); S[4 * j] = q.x; S[4 * j + 1] = q.y; S[4 * j + 2] = q.z; S[4 * j + 3] = q.w; }
-      for (int s = 0; s < steps; ++s) {
-        float4* dst = reinterpret_cast<float4*>(scratch + ((size_t)s * kH + idx) * kH);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) dst[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
-        if (s + 1 < steps) {      // the state after the chunk's last timestep is not needed
-          float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f;
-#pragma unroll
-          for (int j = 0; j < kH; j += 4) {
-            sa0 = fmaf(S[j], vec[s][2][j], sa0); sa1 = fmaf(S[j + 1], vec[s][2][j + 1], sa1);
-            sa2 = fmaf(S[j + 2], vec[s][2][j + 2], sa2); sa3 = fmaf(S[j + 3], vec[s][2][j + 3], sa3);
-          }
-          const float sa = (sa0 + sa1) + (sa2 + sa3), vi = vec[s][4][idx];
-#pragma unroll
-          for (int j = 0; j < kH; ++j)
-            S[j] = fmaf(vi, vec[s][3][j], fmaf(-sa, vec[s][1][j] * vec[s][2][j], S[j] * vec[s][0][j]));
-        }
+  // the seven vectors of every timestep of chunk ck -> vec[ck & 1]; every thread commits one group per call
+  auto issue_vec = [&](int ck) {
+    if (ck >= 0) {
+      const int t0 = ck * kCk, steps = min(kCk, p.T - t0);
+      for (int e = tid; e < steps * (kVecs + 1) * (kH / 4); e += 2 * kH) {
+        const int s = e / ((kVecs + 1) * (kH / 4)), rem = e % ((kVecs + 1) * (kH / 4)), v = rem / (kH / 4), c4 = rem % (kH / 4);
+        const float* src = (v < kVecs ? p.in[v] : p.dy) + head_base + (size_t)(t0 + s) * C + c4 * 4;
+        cp_async16((uint32_t)__cvta_generic_to_shared(&sm.vec[ck & 1][s][v][c4 * 4]), src);
       }
     }
-    __syncthreads();              // the chunk's states are in scratch (written and read by this block only)
+    cp_async_commit();
+  };
 
-    for (int s = steps - 1; s >= 0; --s) {
+  // row threads: the state being recomputed (in flight from the checkpoint while timesteps run backwards);
+  // column threads: column idx of S_{t-1} within a timestep.  One array, so that the two uses share registers.
+  float2 S[32];
+  auto load_ckpt = [&](int ck) {
+    const float4* c4p = reinterpret_cast<const float4*>(p.ckpt + ((head * n_ck + ck) * kH + idx) * kH);
+#pragma unroll
+    for (int g = 0; g < 16; ++g) { const float4 q = __ldg(c4p + g); S[2 * g] = make_float2(q.x, q.y); S[2 * g + 1] = make_float2(q.z, q.w); }
+  };
+
+  // timesteps hi-1 .. lo of the chunk at t0 backwards; the state before local timestep s is in slot[s - lo]
+  // (S below is the column threads' copy of column idx of S_{t-1})
+  auto run_backwards = [&](const float (*V)[kVecs + 1][kH], int t0, int lo, int hi) {
+    for (int s = hi - 1; s >= lo; --s) {
       const size_t out = head_base + (size_t)(t0 + s) * C + idx;
-      const float* w = vec[s][0]; const float* a = vec[s][1]; const float* kap = vec[s][2];
-      const float* kt = vec[s][3]; const float* v = vec[s][4]; const float* r = vec[s][5]; const float* dy = vec[s][6];
-      float Sp[kH];               // row / column idx of S_{t-1}
-      if (row_thread) {
-        const float4* src = reinterpret_cast<const float4*>(scratch + ((size_t)s * kH + idx) * kH);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) { const float4 q = src[j]; Sp[4 * j] = q.x; Sp[4 * j + 1] = q.y; Sp[4 * j + 2] = q.z; Sp[4 * j + 3] = q.w; }
-        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll
-        for (int j = 0; j < kH; j += 4) {
-          s0 = fmaf(Sp[j], kap[j], s0); s1 = fmaf(Sp[j + 1], kap[j + 1], s1);
-          s2 = fmaf(Sp[j + 2], kap[j + 2], s2); s3 = fmaf(Sp[j + 3], kap[j + 3], s3);
-        }
-        sa_s[idx] = (s0 + s1) + (s2 + s3);
-      } else {
-#pragma unroll
-        for (int i = 0; i < kH; ++i) Sp[i] = scratch[((size_t)s * kH + i) * kH + idx];
-      }
-      __syncthreads();            // sa is published
-      float db_keep = 0.0f;
+      const float* w = V[s][0]; const float* a = V[s][1]; const float* kap = V[s][2];
+      const float* kt = V[s][3]; const float* v = V[s][4]; const float* r = V[s][5]; const float* dy = V[s][6];
+      const float* bk = sm.bk[s];
+      float db = 0.0f;
       if (row_thread) {
         const float dyi = dy[idx];
-        float dv0 = 0.f, dv1 = 0.f, ds0 = 0.f, ds1 = 0.f;
+        const float2 dy2 = make_float2(dyi, dyi);
+        float2 dv0 = make_float2(0.f, 0.f), dv1 = dv0, ds0 = dv0, ds1 = dv0;
 #pragma unroll
-        for (int j = 0; j < kH; j += 2) {
-          const float g0 = fmaf(dyi, r[j], dS[j]), g1 = fmaf(dyi, r[j + 1], dS[j + 1]);
-          dS[j] = g0; dS[j + 1] = g1;
-          dv0 = fmaf(g0, kt[j], dv0); dv1 = fmaf(g1, kt[j + 1], dv1);
-          ds0 = fmaf(g0, a[j] * kap[j], ds0); ds1 = fmaf(g1, a[j + 1] * kap[j + 1], ds1);
+        for (int g = 0; g < 16; ++g) {
+          const float4 r4 = *reinterpret_cast<const float4*>(&r[4 * g]);
+          const float4 kt4 = *reinterpret_cast<const float4*>(&kt[4 * g]);
+          const float4 b4 = *reinterpret_cast<const float4*>(&bk[4 * g]);
+          const float2 g0 = __ffma2_rn(dy2, make_float2(r4.x, r4.y), dS[2 * g]);
+          const float2 g1 = __ffma2_rn(dy2, make_float2(r4.z, r4.w), dS[2 * g + 1]);
+          dS[2 * g] = g0; dS[2 * g + 1] = g1;
+          dv0 = __ffma2_rn(g0, make_float2(kt4.x, kt4.y), dv0); dv1 = __ffma2_rn(g1, make_float2(kt4.z, kt4.w), dv1);
+          ds0 = __ffma2_rn(g0, make_float2(b4.x, b4.y), ds0); ds1 = __ffma2_rn(g1, make_float2(b4.z, b4.w), ds1);
         }
-        const float dsa = -(ds0 + ds1);
-        dsa_s[idx] = dsa;
-        p.din[4][out] = dv0 + dv1;
+        const float dsa = -sum4(ds0, ds1);
+        sm.dsa[s & 1][idx] = dsa;
+        p.din[4][out] = sum4(dv0, dv1);
+        const float2 dsa2 = make_float2(dsa, dsa);
 #pragma unroll
-        for (int j = 0; j < kH; ++j) dS[j] = fmaf(dsa, kap[j], dS[j] * w[j]);
+        for (int g = 0; g < 16; ++g) {
+          const float4 w4 = *reinterpret_cast<const float4*>(&w[4 * g]);
+          const float4 k4 = *reinterpret_cast<const float4*>(&kap[4 * g]);
+          dS[2 * g] = __ffma2_rn(dsa2, make_float2(k4.x, k4.y), __fmul2_rn(dS[2 * g], make_float2(w4.x, w4.y)));
+          dS[2 * g + 1] = __ffma2_rn(dsa2, make_float2(k4.z, k4.w), __fmul2_rn(dS[2 * g + 1], make_float2(w4.z, w4.w)));
+        }
       } else {
-        const float wj = w[idx], bj = a[idx] * kap[idx], ktj = kt[idx], rj = r[idx];
-        float dr0 = 0.f, dr1 = 0.f, dkt0 = 0.f, dkt1 = 0.f, db0 = 0.f, db1 = 0.f, dw0 = 0.f, dw1 = 0.f;
+        const float* slot = sm.slot[s - lo];
 #pragma unroll
-        for (int i = 0; i < kH; i += 2) {
-          const float st0 = fmaf(v[i], ktj, fmaf(-sa_s[i], bj, Sp[i] * wj));
-          const float st1 = fmaf(v[i + 1], ktj, fmaf(-sa_s[i + 1], bj, Sp[i + 1] * wj));
-          const float g0 = fmaf(dy[i], rj, dS[i]), g1 = fmaf(dy[i + 1], rj, dS[i + 1]);
-          dS[i] = g0; dS[i + 1] = g1;
-          dr0 = fmaf(st0, dy[i], dr0); dr1 = fmaf(st1, dy[i + 1], dr1);
-          dkt0 = fmaf(g0, v[i], dkt0); dkt1 = fmaf(g1, v[i + 1], dkt1);
-          db0 = fmaf(g0, sa_s[i], db0); db1 = fmaf(g1, sa_s[i + 1], db1);
-          dw0 = fmaf(g0, Sp[i], dw0); dw1 = fmaf(g1, Sp[i + 1], dw1);
-        }
-        db_keep = -(db0 + db1);
-        p.din[5][out] = dr0 + dr1;
-        p.din[3][out] = dkt0 + dkt1;
-        p.din[0][out] = dw0 + dw1;
-      }
-      __syncthreads();            // dsa is published
-      if (!row_thread) {
-        const float db = db_keep, wj = w[idx];
-        const float kapj = kap[idx];
-        float dk0 = 0.f, dk1 = 0.f;
+        for (int e = 0; e < 32; ++e)
+          S[e] = make_float2(slot[(2 * e) * kH + joff[(2 * e) & 15]], slot[(2 * e + 1) * kH + joff[(2 * e + 1) & 15]]);
+        const float wj = w[idx], kapj = kap[idx], ktj = kt[idx], rj = r[idx], bj = bk[idx];
+        const float2 wj2 = make_float2(wj, wj), nbj2 = make_float2(-bj, -bj), ktj2 = make_float2(ktj, ktj), rj2 = make_float2(rj, rj);
+        float2 dr0 = make_float2(0.f, 0.f), dr1 = dr0, dkt0 = dr0, dkt1 = dr0, db0 = dr0, db1 = dr0, dw0 = dr0, dw1 = dr0;
 #pragma unroll
-        for (int i = 0; i < kH; i += 2) {
-          dk0 = fmaf(Sp[i], dsa_s[i], dk0); dk1 = fmaf(Sp[i + 1], dsa_s[i + 1], dk1);
-          dS[i] = fmaf(dsa_s[i], kapj, dS[i] * wj);
-          dS[i + 1] = fmaf(dsa_s[i + 1], kapj, dS[i + 1] * wj);
+        for (int g = 0; g < 16; ++g) {
+          const float4 sa4 = *reinterpret_cast<const float4*>(&sm.sa[s][4 * g]);
+          const float4 v4 = *reinterpret_cast<const float4*>(&v[4 * g]);
+          const float4 dy4 = *reinterpret_cast<const float4*>(&dy[4 * g]);
+          const float2 sa_a = make_float2(sa4.x, sa4.y), sa_b = make_float2(sa4.z, sa4.w);
+          const float2 v_a = make_float2(v4.x, v4.y), v_b = make_float2(v4.z, v4.w);
+          const float2 dy_a = make_float2(dy4.x, dy4.y), dy_b = make_float2(dy4.z, dy4.w);
+          const float2 st_a = __ffma2_rn(v_a, ktj2, __ffma2_rn(sa_a, nbj2, __fmul2_rn(S[2 * g], wj2)));
+          const float2 st_b = __ffma2_rn(v_b, ktj2, __ffma2_rn(sa_b, nbj2, __fmul2_rn(S[2 * g + 1], wj2)));
+          const float2 g_a = __ffma2_rn(dy_a, rj2, dS[2 * g]), g_b = __ffma2_rn(dy_b, rj2, dS[2 * g + 1]);
+          dS[2 * g] = g_a; dS[2 * g + 1] = g_b;
+          dr0 = __ffma2_rn(st_a, dy_a, dr0); dr1 = __ffma2_rn(st_b, dy_b, dr1);
+          dkt0 = __ffma2_rn(g_a, v_a, dkt0); dkt1 = __ffma2_rn(g_b, v_b, dkt1);
+          db0 = __ffma2_rn(g_a, sa_a, db0); db1 = __ffma2_rn(g_b, sa_b, db1);
+          dw0 = __ffma2_rn(g_a, S[2 * g], dw0); dw1 = __ffma2_rn(g_b, S[2 * g + 1], dw1);
         }
-        p.din[2][out] = (dk0 + dk1) + db * a[idx];
+        db = -sum4(db0, db1);
+        p.din[5][out] = sum4(dr0, dr1);
+        p.din[3][out] = sum4(dkt0, dkt1);
+        p.din[0][out] = sum4(dw0, dw1);
         p.din[1][out] = db * kapj;
       }
-      __syncthreads();            // sa_s / dsa_s may be overwritten by the next timestep
+      __syncthreads();            // dsa of this timestep is published (the row threads go on to the timestep before)
+      if (!row_thread) {
+        const float wj = w[idx], aj = a[idx], kapj = kap[idx];
+        const float2 wj2 = make_float2(wj, wj), kapj2 = make_float2(kapj, kapj);
+        float2 dk0 = make_float2(0.f, 0.f), dk1 = dk0;
+#pragma unroll
+        for (int g = 0; g < 16; ++g) {
+          const float4 d4 = *reinterpret_cast<const float4*>(&sm.dsa[s & 1][4 * g]);
+          const float2 d_a = make_float2(d4.x, d4.y), d_b = make_float2(d4.z, d4.w);
+          dk0 = __ffma2_rn(S[2 * g], d_a, dk0); dk1 = __ffma2_rn(S[2 * g + 1], d_b, dk1);
+          dS[2 * g] = __ffma2_rn(d_a, kapj2, __fmul2_rn(dS[2 * g], wj2));
+          dS[2 * g + 1] = __ffma2_rn(d_b, kapj2, __fmul2_rn(dS[2 * g + 1], wj2));
+        }
+        p.din[2][out] = sum4(dk0, dk1) + db * aj;
+      }
+    }
+  };
+
+  issue_vec(n_ck - 1);
+  if (row_thread) load_ckpt(n_ck - 1);
+  for (int ck = n_ck - 1; ck >= 0; --ck) {
+    const int t0 = ck * kCk, steps = min(kCk, p.T - t0);
+    const int lo = steps > kSub ? kSub : 0;      // the chunk runs as [lo, steps) and then, if lo > 0, [0, lo)
+    __syncthreads();              // everyone is done with the chunk after this one: its vectors, sa, bk and slots
+    issue_vec(ck - 1);            // into the buffer that chunk used
+    cp_async_wait<1>();           // this thread's copies of chunk ck have landed
+    __syncthreads();              // ... and everyone's
+    const float (*V)[kVecs + 1][kH] = sm.vec[ck & 1];
+    for (int e = tid; e < steps * kH; e += 2 * kH) sm.bk[e / kH][e % kH] = V[e / kH][1][e % kH] * V[e / kH][2][e % kH];
+    __syncthreads();
+    if (row_thread) {             // pass 1: every sa of the chunk, the states before timesteps lo .. steps-1
+      for (int s = 0; s < steps; ++s) {
+        if (s >= lo) slot_store_row(sm.slot[s - lo], idx, S);
+        const float sa = wkv_sa(S, V[s][2]);
+        sm.sa[s][idx] = sa;
+        if (s + 1 < steps) wkv_update(S, V[s], sm.bk[s], sa, V[s][4][idx]);
+      }
+      if (lo > 0) load_ckpt(ck); else if (ck > 0) load_ckpt(ck - 1);
+    }
+    __syncthreads();
+    run_backwards(V, t0, lo, steps);
+    if (lo > 0) {
+      __syncthreads();            // the column threads are done with the slots
+      if (row_thread) {           // pass 2: the states before timesteps 0 .. lo-1, from the checkpoint and the kept sa
+        for (int s = 0; s < lo; ++s) {
+          slot_store_row(sm.slot[s], idx, S);
+          if (s + 1 < lo) wkv_update(S, V[s], sm.bk[s], sm.sa[s][idx], V[s][4][idx]);
+        }
+        if (ck > 0) load_ckpt(ck - 1);
+      }
+      __syncthreads();
+      run_backwards(V, t0, 0, lo);
     }
   }
-  if (p.dstate_in && row_thread) {
+  cp_async_wait<0>();
+  if (p.dstate_in) {
+    if (row_thread) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
-      reinterpret_cast<float4*>(p.dstate_in + (head * kH + idx) * kH)[j] = make_float4(dS[4 * j], dS[4 * j + 1], dS[4 * j + 2], dS[4 * j + 3]);
+      for (int g = 0; g < 16; ++g)
+        reinterpret_cast<float4*>(p.dstate_in + (head * kH + idx) * kH)[g] = make_float4(dS[2 * g].x, dS[2 * g].y, dS[2 * g + 1].x, dS[2 * g + 1].y);
+    }
   }
 }
 
@@ -332,31 +434,24 @@ extern "C" size_t pb_wkv7_checkpoint_floats(int64_t batch, int64_t steps, int64_
   return (size_t)batch * heads * ((steps + kCk - 1) / kCk) * kH * kH;
 }
 
-extern "C" size_t pb_wkv7_backward_workspace_size(int64_t batch, int64_t heads, int head_dim) {
-  if (batch <= 0 || heads <= 0 || head_dim != kH) return 0;
-  return (size_t)batch * heads * kCk * kH * kH * sizeof(float);
-}
-
 extern "C" int pb_wkv7_backward(const float* decay, const float* iclr, const float* removal_k, const float* replacement_k,
                                 const float* v, const float* r, const float* checkpoints, const float* dy, const float* dstate_out,
                                 int64_t batch, int64_t steps, int64_t heads, int head_dim,
                                 float* d_decay, float* d_iclr, float* d_removal_k, float* d_replacement_k, float* d_v, float* d_r,
-                                float* dstate_in, void* workspace, size_t workspace_bytes, void* stream) {
+                                float* dstate_in, void* stream) {
   if (!decay || !iclr || !removal_k || !replacement_k || !v || !r || !checkpoints || !dy || !d_decay || !d_iclr || !d_removal_k ||
       !d_replacement_k || !d_v || !d_r)
     return fail(PB_ERR_NULL_POINTER, "pb_wkv7_backward: the six inputs, the checkpoints, dy and the six gradients must be non-null");
   if (head_dim != kH) return fail(PB_ERR_UNSUPPORTED, "pb_wkv7_backward: head size %d (this kernel is built for %d)", head_dim, kH);
   if (batch <= 0 || steps <= 0 || heads <= 0 || batch * heads > 0x7fffffffll || steps > 0x7fffffffll)
     return fail(PB_ERR_BAD_SHAPE, "pb_wkv7_backward: batch=%lld steps=%lld heads=%lld", (long long)batch, (long long)steps, (long long)heads);
-  const size_t need = pb_wkv7_backward_workspace_size(batch, heads, head_dim);
-  if (!workspace || workspace_bytes < need)
-    return fail(PB_ERR_WORKSPACE_TOO_SMALL, "pb_wkv7_backward: needs %zu bytes of workspace, got %zu", need, workspace_bytes);
-  const void* ptrs[] = {decay, iclr, removal_k, replacement_k, v, r, checkpoints, dy, dstate_out, dstate_in, workspace};
+  const void* ptrs[] = {decay, iclr, removal_k, replacement_k, v, r, checkpoints, dy, dstate_out, dstate_in};
   for (const void* ptr : ptrs)
     if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(PB_ERR_MISALIGNED, "pb_wkv7_backward: every array must be 16-byte aligned");
   WkvBwdParams p{{decay, iclr, removal_k, replacement_k, v, r}, dy, checkpoints, dstate_out,
-                 {d_decay, d_iclr, d_removal_k, d_replacement_k, d_v, d_r}, dstate_in, static_cast<float*>(workspace), (int)steps, (int)heads};
-  wkv7_backward_kernel<<<(unsigned)(batch * heads), 2 * kH, 0, static_cast<cudaStream_t>(stream)>>>(p);
+                 {d_decay, d_iclr, d_removal_k, d_replacement_k, d_v, d_r}, dstate_in, (int)steps, (int)heads};
+  PB_CUDA_TRY(cudaFuncSetAttribute(wkv7_backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(WkvBwdSmem)));   // per device
+  wkv7_backward_kernel<<<(unsigned)(batch * heads), 2 * kH, sizeof(WkvBwdSmem), static_cast<cudaStream_t>(stream)>>>(p);
   PB_LAUNCH_CHECK("wkv7_backward_kernel");
   return PB_OK;
 }

@@ -89,9 +89,10 @@ def _torch_reference(state, ins, n_head):
     return S, torch.stack(outs, dim=1)
 
 
-@pytest.mark.parametrize("bsz,steps,n_head,with_state", [(2, 40, 2, True), (1, 16, 1, False), (2, 97, 3, True)])
+@pytest.mark.parametrize("bsz,steps,n_head,with_state", [(2, 40, 2, True), (1, 16, 1, False), (2, 97, 3, True), (1, 3, 1, True), (2, 6, 2, False), (1, 13, 2, True), (1, 8, 1, True)])
 def test_wkv7_scan_gradients_match_autograd_of_the_reference_recurrence(built_lib, bsz, steps, n_head, with_state):
-    """pb_wkv7_backward (checkpoints every 16 timesteps, recomputation in between) against torch.autograd in float64
+    """pb_wkv7_backward (checkpoints every 8 timesteps, recomputation in between; the step counts cover full chunks and
+    tails of 1 to 7 timesteps) against torch.autograd in float64
     on the CPU; tolerance 1e-4 of each gradient's largest magnitude (fp32 sums of up to 64 terms per timestep,
     chained over the sequence)."""
     state, *ins = make_inputs(bsz, steps, n_head, seed=100 + steps)
