@@ -267,6 +267,41 @@ PB_API int pb_wkv7_backward(const float* decay, const float* iclr, const float* 
                      float* d_decay, float* d_iclr, float* d_removal_k, float* d_replacement_k, float* d_v, float* d_r,
                      float* dstate_in, void* stream);
 
+/* ---- the f32 element-wise work of the modified RWKV-7 block around its linears and its scan
+ *      (pratchya/_nnx_impl/_module.py:129-258), fused.  All arrays f32, 16-byte aligned where stated.
+ *
+ * Token shift and lerps (TimeMix :137-151 with six mixes, ChannelMix :240-247 with one):
+ *   out[k][b][t][c] = x[b][t][c] + (prev - x[b][t][c]) * mu[k][c],  prev = x[b][t-1][c], or state[b][c] for t = 0
+ * (state may be null: zeros).  out is [n_mix, batch, steps, channels]; channels a multiple of 4; n_mix <= 8. */
+PB_API int pb_token_shift_lerp(const float* x, const float* state, const float* mu, int64_t batch, int64_t steps, int64_t channels,
+                        int n_mix, float* out, void* stream);
+/* Its cotangents from g [n_mix, batch, steps, channels]: dx, dstate [batch, channels] (may be null) and
+ * dmu [n_mix, channels] (summed over tokens per tile and then in tile order: deterministic).  n_mix is 1 or 6. */
+PB_API size_t pb_token_shift_lerp_bwd_workspace_size(int64_t batch, int64_t steps, int64_t channels, int n_mix);
+PB_API int pb_token_shift_lerp_bwd(const float* g, const float* x, const float* state, const float* mu,
+                            int64_t batch, int64_t steps, int64_t channels, int n_mix,
+                            float* dx, float* dstate, float* dmu, void* workspace, size_t workspace_bytes, void* stream);
+/* TimeMix between its linears and its scan (:157-184), per token and head of 64 channels:
+ *   r, k    = rotary embedding of r_raw, k_raw with the angle tables cos_tab / sin_tab [steps, 32] (:275-283)
+ *   iclr    = sigmoid(iclr_raw);  decay = exp(-exp(d))
+ *   v       = v_prime, or v_prime + (v0 - v_prime) * sigmoid(nu_raw) when v0 / nu_raw are given (not the first layer)
+ *   removal_k     = normalized(k * rk_mult) over the head's channels (eps 1e-12, :15-18)
+ *   replacement_k = k + (k * iclr - k) * mix_amt
+ * rk_mult and mix_amt are [channels] (the parameters as read through their quantization). */
+PB_API int pb_wkv_prepare(const float* r_raw, const float* k_raw, const float* d, const float* iclr_raw, const float* v_prime,
+                   const float* v0, const float* nu_raw, const float* cos_tab, const float* sin_tab,
+                   const float* rk_mult, const float* mix_amt, int64_t batch, int64_t steps, int64_t heads, int head_dim,
+                   float* decay, float* iclr, float* removal_k, float* replacement_k, float* v, float* r, float* k, void* stream);
+/* Cotangents of pb_wkv_prepare's seven inputs and two parameters from those of its seven outputs. */
+PB_API size_t pb_wkv_prepare_bwd_workspace_size(int64_t batch, int64_t steps, int64_t heads, int head_dim);
+PB_API int pb_wkv_prepare_bwd(const float* r_raw, const float* k_raw, const float* d, const float* iclr_raw, const float* v_prime,
+                       const float* v0, const float* nu_raw, const float* cos_tab, const float* sin_tab,
+                       const float* rk_mult, const float* mix_amt, int64_t batch, int64_t steps, int64_t heads, int head_dim,
+                       const float* g_decay, const float* g_iclr, const float* g_removal_k, const float* g_replacement_k,
+                       const float* g_v, const float* g_r, const float* g_k,
+                       float* d_r_raw, float* d_k_raw, float* d_d, float* d_iclr_raw, float* d_v_prime, float* d_v0, float* d_nu_raw,
+                       float* d_rk_mult, float* d_mix_amt, void* workspace, size_t workspace_bytes, void* stream);
+
 /* byte transpose [rows, cols] -> [cols, rows] of an fp8 matrix (weight prepared for the forward GEMM) */
 PB_API int pb_transpose_bytes(const void* src, int64_t rows, int64_t cols, void* dst, void* stream);
 

@@ -63,6 +63,12 @@ _SIGNATURES = {
     "pb_fake_quantize": (_int, [_ptr, _int, _i64, _i64, _i64, _int, _int, _int, _ptr, _int, _ptr]),
     "pb_gemm_check": (_int, [_ptr]),
     "pb_transpose_bytes": (_int, [_ptr, _i64, _i64, _ptr, _ptr]),
+    "pb_token_shift_lerp": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr, _ptr]),
+    "pb_token_shift_lerp_bwd_workspace_size": (_sz, [_i64, _i64, _i64, _int]),
+    "pb_token_shift_lerp_bwd": (_int, [_ptr] * 4 + [_i64, _i64, _i64, _int] + [_ptr] * 4 + [_sz, _ptr]),
+    "pb_wkv_prepare": (_int, [_ptr] * 11 + [_i64, _i64, _i64, _int] + [_ptr] * 8),
+    "pb_wkv_prepare_bwd_workspace_size": (_sz, [_i64, _i64, _i64, _int]),
+    "pb_wkv_prepare_bwd": (_int, [_ptr] * 11 + [_i64, _i64, _i64, _int] + [_ptr] * 17 + [_sz, _ptr]),
     "pb_wkv7_forward": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr, _ptr, _ptr, _ptr]),
     "pb_wkv7_checkpoint_floats": (_sz, [_i64, _i64, _i64, _int]),
     "pb_wkv7_backward": (_int, [_ptr] * 9 + [_i64, _i64, _i64, _int] + [_ptr] * 8),

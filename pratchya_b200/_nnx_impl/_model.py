@@ -18,6 +18,7 @@ from dataclasses import dataclass
 import torch
 
 from .._qualia import _ops
+from ._glue import token_shift_lerp, wkv_prepare
 from ._module import linear_fp8
 from ._wkv7 import wkv_state_scan
 
@@ -34,6 +35,7 @@ class PratchyaConfig:
     n_layers: int = 24
     blksize: int = 128
     rope_theta: float = 1e4
+    fused_glue: bool = True      # the element-wise work on the kernels of _glue.py instead of op-by-op torch (same values)
 
 
 def lerp(i, j, w):                                   # _module.py:12-13
@@ -112,6 +114,10 @@ class RotaryEmbedding(torch.nn.Module):              # _module.py:261-283
         h = cfg.head_dim
         self.register_buffer("inv_freq", 1.0 / (cfg.rope_theta ** (torch.arange(0, h, 2, dtype=torch.float32, device=device) / h)))
 
+    def tables(self, t):                             # cos and sin of the angles, [T, H/2] each
+        freqs = torch.outer(t.to(torch.float32), self.inv_freq)
+        return torch.cos(freqs), torch.sin(freqs)
+
     def forward(self, x, t):                         # x [B, T, N, H], t [T]
         freqs = torch.outer(t.to(torch.float32), self.inv_freq)
         emb = torch.cat([freqs, freqs], dim=-1)[:, None, :]
@@ -155,29 +161,42 @@ class TimeMix(torch.nn.Module):                      # _module.py:92-225
     def forward(self, x, v_prime_0, t_positions, tm_state, wkv_state):
         bsz, steps, c = x.shape
         n, h, blk = self.n_head, self.head_dim, self.cfg.blksize
-        x_shifted = torch.cat([tm_state, x[:, :-1, :]], dim=1)
-        tm_state = x[:, -1:, :]
-        _x, _xs = x.to(torch.float32), x_shifted.to(torch.float32)
         mu = read_param(self.mu, (1, blk))
-        x_r, x_d, x_k, x_v, x_i, x_g = (lerp(_x, _xs, mu[j]) for j in range(6))
+        if self.cfg.fused_glue:
+            x_r, x_d, x_k, x_v, x_i, x_g = token_shift_lerp(x, tm_state, mu).unbind(0)
+        else:
+            x_shifted = torch.cat([tm_state, x[:, :-1, :]], dim=1)
+            _x, _xs = x.to(torch.float32), x_shifted.to(torch.float32)
+            x_r, x_d, x_k, x_v, x_i, x_g = (lerp(_x, _xs, mu[j]) for j in range(6))
+        tm_state = x[:, -1:, :]
         r = self.w_receptance(x_r)
         d = self.decay_lora(x_d)
         k = self.w_key(x_k)
         v_prime = self.w_value(x_v)
         gate = self.gate_lora(x_g)
-        iclr = torch.sigmoid(self.iclr_lora(x_i))
-        k = self.rotary(k.to(torch.float32).reshape(bsz, steps, n, h), t_positions).reshape(bsz, steps, c)
-        r = self.rotary(r.to(torch.float32).reshape(bsz, steps, n, h), t_positions).reshape(bsz, steps, c)
-        if self.first_layer:
-            v = v_prime_0 = v_prime.to(torch.float32)
+        iclr = self.iclr_lora(x_i)
+        rk_mult = read_param(self.removal_key_multiplier, (1, blk))
+        mix_amt = read_param(self.iclr_mix_amt, (1, blk))
+        if self.cfg.fused_glue:
+            cos_tab, sin_tab = self.rotary.tables(t_positions)
+            nu_raw = None if self.first_layer else self.nu_lora(x_v)
+            decay, iclr, removal_k, replacement_k, v, r, k = wkv_prepare(
+                r, k, d, iclr, v_prime, None if self.first_layer else v_prime_0, nu_raw, cos_tab, sin_tab, rk_mult, mix_amt, n)
+            if self.first_layer:
+                v_prime_0 = v
         else:
-            nu = torch.sigmoid(self.nu_lora(x_v)).to(torch.float32)
-            v = lerp(v_prime.to(torch.float32), v_prime_0.to(torch.float32), nu)
-        decay = torch.exp(-torch.exp(d))
-        removal_k = k * read_param(self.removal_key_multiplier, (1, blk))
-        removal_k = normalized(removal_k.reshape(bsz, steps, n, h), dim=-1).reshape(bsz, steps, c)
-        iclr = iclr.to(torch.float32)
-        replacement_k = lerp(k, k * iclr, read_param(self.iclr_mix_amt, (1, blk)))
+            iclr = torch.sigmoid(iclr)
+            k = self.rotary(k.to(torch.float32).reshape(bsz, steps, n, h), t_positions).reshape(bsz, steps, c)
+            r = self.rotary(r.to(torch.float32).reshape(bsz, steps, n, h), t_positions).reshape(bsz, steps, c)
+            if self.first_layer:
+                v = v_prime_0 = v_prime.to(torch.float32)
+            else:
+                nu = torch.sigmoid(self.nu_lora(x_v)).to(torch.float32)
+                v = lerp(v_prime.to(torch.float32), v_prime_0.to(torch.float32), nu)
+            decay = torch.exp(-torch.exp(d))
+            removal_k = normalized((k * rk_mult).reshape(bsz, steps, n, h), dim=-1).reshape(bsz, steps, c)
+            iclr = iclr.to(torch.float32)
+            replacement_k = lerp(k, k * iclr, mix_amt)
         wkv_state, out = wkv_state_scan(wkv_state, decay, iclr, removal_k, replacement_k, v, r, n)
         out = group_norm(out, n, n * 1e-5, self.gn_scale, self.gn_bias)
         bonus = torch.sum(r * k * read_param(self.bonus_multiplier, (1, blk)), dim=-1, keepdim=True) * v
@@ -189,15 +208,19 @@ class ChannelMix(torch.nn.Module):                   # _module.py:228-258
     def __init__(self, cfg, gen, device):
         super().__init__()
         grid = (cfg.blksize, cfg.blksize)
-        self.blk = cfg.blksize
+        self.blk, self.fused_glue = cfg.blksize, cfg.fused_glue
         self.w_k = Linear(cfg.hidden_size, cfg.intermediate_size, grid, gen, device)
         self.w_v = Linear(cfg.intermediate_size, cfg.hidden_size, grid, gen, device)
         self.mu_x = torch.nn.Parameter(_lecun(1, (1, cfg.hidden_size), gen, device))
 
     def forward(self, x, cm_state):
-        x_shifted = torch.cat([cm_state, x[:, :-1, :]], dim=1)
+        mu_x = read_param(self.mu_x, (1, self.blk))
+        if self.fused_glue:
+            x_k = token_shift_lerp(x, cm_state, mu_x)[0]
+        else:
+            x_shifted = torch.cat([cm_state, x[:, :-1, :]], dim=1)
+            x_k = lerp(x.to(torch.float32), x_shifted.to(torch.float32), mu_x)
         cm_state = x[:, -1:, :]
-        x_k = lerp(x.to(torch.float32), x_shifted.to(torch.float32), read_param(self.mu_x, (1, self.blk)))
         k = self.w_k(x_k).to(torch.float32)
         k = torch.relu(k) ** 2
         return self.w_v(k), cm_state

@@ -1,0 +1,103 @@
+"""The fused element-wise kernels of the RWKV-7 block (csrc/rwkv_glue.cu through pratchya_b200/_nnx_impl/_glue.py)
+against the same formulas evaluated operation by operation in torch f32 (the text of the reference's TimeMix and
+ChannelMix, pratchya/_nnx_impl/_module.py:129-258), values and gradients.
+
+Forward values: bit-equal where the kernel performs the same f32 operations in the same order (lerps, rotary
+embedding, sigmoid, exp); 1e-6 of the largest magnitude where a 64-term sum is formed in another order (normalized).
+Gradients: 2e-5 of each gradient's largest magnitude against torch.autograd (sums over tokens in another order)."""
+import pytest
+import torch
+
+from pratchya_b200._nnx_impl._glue import token_shift_lerp, wkv_prepare
+from pratchya_b200._nnx_impl._model import PratchyaCausalLM, PratchyaConfig, lerp, normalized, RotaryEmbedding
+
+pytestmark = pytest.mark.gpu
+
+
+def close(got, want, what, tol):
+    scale = want.abs().max().item()
+    err = (got - want).abs().max().item()
+    assert err <= tol * max(scale, 1e-30), f"{what}: error {err:.3e} against a largest magnitude of {scale:.3e}"
+
+
+@pytest.mark.parametrize("bsz,steps,chans,n_mix,with_state", [(2, 37, 1024, 6, True), (3, 300, 2048, 1, True), (1, 513, 1024, 6, False),
+                                                              (2, 256, 2048, 6, True), (5, 1, 1024, 1, True)])
+def test_token_shift_lerp_matches_torch(built_lib, bsz, steps, chans, n_mix, with_state):
+    gen = torch.Generator(device="cuda").manual_seed(steps + n_mix)
+    x = torch.randn(bsz, steps, chans, device="cuda", generator=gen).requires_grad_(True)
+    state = torch.randn(bsz, 1, chans, device="cuda", generator=gen).requires_grad_(True) if with_state else None
+    mu = torch.randn(n_mix, chans, device="cuda", generator=gen).requires_grad_(True)
+    g = torch.randn(n_mix, bsz, steps, chans, device="cuda", generator=gen)
+    got = token_shift_lerp(x, state, mu)
+    first = state if with_state else torch.zeros(bsz, 1, chans, device="cuda")
+    shifted = torch.cat([first, x[:, :-1, :]], dim=1)
+    want = torch.stack([lerp(x, shifted, mu[k]) for k in range(n_mix)])
+    assert torch.equal(got, want)
+    leaves = [x, mu] + ([state] if with_state else [])
+    got_grads = torch.autograd.grad(got, leaves, g)
+    want_grads = torch.autograd.grad(want, leaves, g)
+    for name, a, b in zip(["dx", "dmu", "dstate"], got_grads, want_grads):
+        close(a, b, name, 2e-5)
+
+
+@pytest.mark.parametrize("bsz,steps,n_head,first_layer", [(2, 33, 4, True), (2, 200, 3, False), (1, 129, 32, False)])
+def test_wkv_prepare_matches_torch(built_lib, bsz, steps, n_head, first_layer):
+    gen = torch.Generator(device="cuda").manual_seed(steps)
+    c = n_head * 64
+    mk = lambda scale=1.0: (torch.randn(bsz, steps, c, device="cuda", generator=gen) * scale).requires_grad_(True)
+    r_raw, k_raw, d, iclr_raw, v_prime = mk(), mk(), mk(0.5), mk(), mk()
+    v0, nu_raw = (None, None) if first_layer else (mk(), mk())
+    rk_mult = torch.randn(1, c, device="cuda", generator=gen).requires_grad_(True)
+    mix_amt = torch.randn(1, c, device="cuda", generator=gen).requires_grad_(True)
+    cfg = PratchyaConfig()
+    rotary = RotaryEmbedding(cfg, "cuda")
+    t = torch.arange(steps, device="cuda", dtype=torch.int32)
+    cos_tab, sin_tab = rotary.tables(t)
+    got = wkv_prepare(r_raw, k_raw, d, iclr_raw, v_prime, v0, nu_raw, cos_tab, sin_tab, rk_mult, mix_amt, n_head)
+
+    k = rotary(k_raw.reshape(bsz, steps, n_head, 64), t).reshape(bsz, steps, c)
+    r = rotary(r_raw.reshape(bsz, steps, n_head, 64), t).reshape(bsz, steps, c)
+    iclr = torch.sigmoid(iclr_raw)
+    v = v_prime if first_layer else lerp(v_prime, v0, torch.sigmoid(nu_raw))
+    decay = torch.exp(-torch.exp(d))
+    removal_k = normalized((k * rk_mult).reshape(bsz, steps, n_head, 64), dim=-1).reshape(bsz, steps, c)
+    replacement_k = lerp(k, k * iclr, mix_amt)
+    want = (decay, iclr, removal_k, replacement_k, v, r, k)
+    names = ["decay", "iclr", "removal_k", "replacement_k", "v", "r", "k"]
+    for name, a, b in zip(names, got, want):
+        if name == "removal_k":
+            close(a, b, name, 1e-6)
+        elif name in ("decay", "iclr", "replacement_k", "v"):      # through exp / sigmoid: the same library functions, allow an ulp
+            close(a, b, name, 3e-7)
+        else:
+            assert torch.equal(a, b), name
+    leaves = [r_raw, k_raw, d, iclr_raw, v_prime, rk_mult, mix_amt] + ([] if first_layer else [v0, nu_raw])
+    gs = [torch.randn(bsz, steps, c, device="cuda", generator=gen) for _ in range(7)]
+    got_grads = torch.autograd.grad(got, leaves, gs)
+    want_grads = torch.autograd.grad(want, leaves, gs)
+    leaf_names = ["d_r_raw", "d_k_raw", "d_d", "d_iclr_raw", "d_v_prime", "d_rk_mult", "d_mix_amt", "d_v0", "d_nu_raw"]
+    for name, a, b in zip(leaf_names, got_grads, want_grads):
+        close(a, b, name, 2e-5)
+
+
+def test_model_with_fused_glue_matches_the_op_by_op_model(built_lib):
+    kw = dict(vocab_size=1024, hidden_size=1024, intermediate_size=2048, n_layers=2)
+    fused = PratchyaCausalLM(PratchyaConfig(fused_glue=True, **kw), seed=3, remat=False)
+    plain = PratchyaCausalLM(PratchyaConfig(fused_glue=False, **kw), seed=3, remat=False)
+    plain.load_state_dict(fused.state_dict())
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    ids = torch.randint(0, 1024, (2, 48), device="cuda", generator=gen)
+    logits_f, loss_f = fused(ids, ids)
+    logits_p, loss_p = plain(ids, ids)
+    # the products are re-quantized to fp8 after every linear: an ulp of difference in a 64-term sum moves a rounding
+    # now and then, so the comparison is statistical, as between the device and the oracle
+    diff = (logits_f - logits_p).abs()
+    scale = logits_p.abs().max()
+    print(f"logits: mean difference {diff.mean() / scale:.2e}, largest {diff.max() / scale:.2e}; loss {loss_f.item():.5f} vs {loss_p.item():.5f}")
+    assert diff.mean() <= 2e-3 * scale and abs(loss_f.item() - loss_p.item()) <= 5e-3
+    loss_f.backward()
+    loss_p.backward()
+    for (name, a), (_, b) in zip(fused.named_parameters(), plain.named_parameters()):
+        assert a.grad is not None and torch.isfinite(a.grad).all(), name
+        cos = torch.nn.functional.cosine_similarity(a.grad.flatten(), b.grad.flatten(), dim=0).item()
+        assert cos > 0.98, f"gradient of {name}: cosine {cos:.4f} between the fused and the op-by-op model"
