@@ -275,10 +275,10 @@ PB_API int pb_wkv7_backward(const float* decay, const float* iclr, const float* 
  * (state may be null: zeros).  out is [n_mix, batch, steps, channels]; channels a multiple of 4; n_mix <= 8. */
 PB_API int pb_token_shift_lerp(const float* x, const float* state, const float* mu, int64_t batch, int64_t steps, int64_t channels,
                         int n_mix, float* out, void* stream);
-/* Its cotangents from g [n_mix, batch, steps, channels]: dx, dstate [batch, channels] (may be null) and
+/* Its cotangents from g[k] [batch, steps, channels], k < n_mix (a host array of n_mix device pointers): dx, dstate [batch, channels] (may be null) and
  * dmu [n_mix, channels] (summed over tokens per tile and then in tile order: deterministic).  n_mix is 1 or 6. */
 PB_API size_t pb_token_shift_lerp_bwd_workspace_size(int64_t batch, int64_t steps, int64_t channels, int n_mix);
-PB_API int pb_token_shift_lerp_bwd(const float* g, const float* x, const float* state, const float* mu,
+PB_API int pb_token_shift_lerp_bwd(const float* const* g, const float* x, const float* state, const float* mu,
                             int64_t batch, int64_t steps, int64_t channels, int n_mix,
                             float* dx, float* dstate, float* dmu, void* workspace, size_t workspace_bytes, void* stream);
 /* TimeMix between its linears and its scan (:157-184), per token and head of 64 channels:
@@ -301,6 +301,33 @@ PB_API int pb_wkv_prepare_bwd(const float* r_raw, const float* k_raw, const floa
                        const float* g_v, const float* g_r, const float* g_k,
                        float* d_r_raw, float* d_k_raw, float* d_d, float* d_iclr_raw, float* d_v_prime, float* d_v0, float* d_nu_raw,
                        float* d_rk_mult, float* d_mix_amt, void* workspace, size_t workspace_bytes, void* stream);
+
+/* RMSNorm (pratchya/_nnx_impl/_module.py:61-72): y = (x * rsqrt(mean(x^2) + eps)) * scale over the last dimension of
+ * x [rows, channels]; scale [channels] as read through its quantization; inv_rms [rows] is kept for the backward call.
+ * channels a multiple of 128. */
+PB_API int pb_rms_norm(const float* x, const float* scale, int64_t rows, int64_t channels, float eps, float* y, float* inv_rms, void* stream);
+PB_API size_t pb_rms_norm_bwd_workspace_size(int64_t rows, int64_t channels);
+PB_API int pb_rms_norm_bwd(const float* dy, const float* x, const float* scale, const float* inv_rms, int64_t rows, int64_t channels,
+                    float* dx, float* dscale, void* workspace, size_t workspace_bytes, void* stream);
+/* relu(x)^2 (ChannelMix between its linears, :249) and its cotangent g * 2 * relu(x); n elements, a multiple of 4. */
+PB_API int pb_relu2(const float* x, int64_t n, float* y, void* stream);
+PB_API int pb_relu2_bwd(const float* g, const float* x, int64_t n, float* dx, void* stream);
+/* TimeMix after its scan (:208-216): out = (GroupNorm(y) + sum_c(r k bonus_mult) * v) * gate, GroupNorm as flax builds
+ * it with one group per head (:118-123): per batch element and head, mean and variance (E[x^2] - E[x]^2, clamped at 0)
+ * over the steps x 64 values, then gn_scale and gn_bias per channel.  stats [batch * heads][2] receives (mean, rstd)
+ * for the backward call. */
+PB_API size_t pb_wkv_finish_workspace_size(int64_t batch, int64_t steps, int64_t heads, int head_dim);
+PB_API int pb_wkv_finish(const float* y, const float* r, const float* k, const float* v, const float* gate,
+                  const float* gn_scale, const float* gn_bias, const float* bonus_mult, float eps,
+                  int64_t batch, int64_t steps, int64_t heads, int head_dim,
+                  float* out, float* stats, void* workspace, size_t workspace_bytes, void* stream);
+PB_API size_t pb_wkv_finish_bwd_workspace_size(int64_t batch, int64_t steps, int64_t heads, int head_dim);
+PB_API int pb_wkv_finish_bwd(const float* g, const float* y, const float* r, const float* k, const float* v, const float* gate,
+                      const float* gn_scale, const float* gn_bias, const float* bonus_mult, const float* stats,
+                      int64_t batch, int64_t steps, int64_t heads, int head_dim,
+                      float* d_y, float* d_r, float* d_k, float* d_v, float* d_gate,
+                      float* d_gn_scale, float* d_gn_bias, float* d_bonus_mult,
+                      void* workspace, size_t workspace_bytes, void* stream);
 
 /* byte transpose [rows, cols] -> [cols, rows] of an fp8 matrix (weight prepared for the forward GEMM) */
 PB_API int pb_transpose_bytes(const void* src, int64_t rows, int64_t cols, void* dst, void* stream);

@@ -4,6 +4,8 @@ differentiable (torch.autograd.Function around the forward and the backward kern
 tensors [B, T, C]."""
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
 from .. import _lib
@@ -29,23 +31,24 @@ class _ShiftLerpFn(torch.autograd.Function):
             check(lib.pb_token_shift_lerp(x.data_ptr(), state.data_ptr() if state is not None else None, mu.data_ptr(),
                                           bsz, steps, chans, n_mix, out.data_ptr(), _stream(x.device)))
         ctx.save_for_backward(x, state, mu)
-        return out
+        return tuple(out.unbind(0))          # separate outputs: their cotangents arrive separately, with no stacking copy
 
     @staticmethod
-    def backward(ctx, g):
+    def backward(ctx, *gs):
         x, state, mu = ctx.saved_tensors
         lib = _lib.load()
         bsz, steps, chans = x.shape
         n_mix = mu.shape[0]
-        g = _f32c(g)
         dev = x.device
         with torch.cuda.device(dev):
+            gs = [_f32c(g) if g is not None else torch.zeros_like(x) for g in gs]
+            g_ptrs = (C.c_void_p * n_mix)(*[g.data_ptr() for g in gs])
             dx = torch.empty_like(x)
             dstate = torch.empty_like(state) if state is not None else None
             dmu = torch.empty_like(mu)
             ws_bytes = lib.pb_token_shift_lerp_bwd_workspace_size(bsz, steps, chans, n_mix)
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-            check(lib.pb_token_shift_lerp_bwd(g.data_ptr(), x.data_ptr(), state.data_ptr() if state is not None else None, mu.data_ptr(),
+            check(lib.pb_token_shift_lerp_bwd(g_ptrs, x.data_ptr(), state.data_ptr() if state is not None else None, mu.data_ptr(),
                                               bsz, steps, chans, n_mix, dx.data_ptr(), dstate.data_ptr() if dstate is not None else None,
                                               dmu.data_ptr(), ws.data_ptr(), ws_bytes, _stream(dev)))
         return dx, dstate, dmu
@@ -53,7 +56,7 @@ class _ShiftLerpFn(torch.autograd.Function):
 
 def token_shift_lerp(x, state, mu):
     """[lerp(x, shifted(x), mu[k]) for k]: x [B, T, C], state [B, 1, C] (the token before the first; None: zeros),
-    mu [n_mix, C] with n_mix 1 or 6.  Returns [n_mix, B, T, C].  _module.py:137-151, :240-247."""
+    mu [n_mix, C] with n_mix 1 or 6.  Returns a tuple of n_mix tensors [B, T, C].  _module.py:137-151, :240-247."""
     if x.dim() != 3 or mu.dim() != 2 or mu.shape[1] != x.shape[2] or mu.shape[0] not in (1, 6):
         raise ValueError(f"token_shift_lerp: x {tuple(x.shape)}, mu {tuple(mu.shape)}")
     if not x.is_cuda:
@@ -124,3 +127,124 @@ def wkv_prepare(r_raw, k_raw, d, iclr_raw, v_prime, v0, nu_raw, cos_tab, sin_tab
     ins = [_f32c(t) for t in ins]
     opt = [_f32c(t) if t is not None else None for t in (v0, nu_raw)]
     return _WkvPrepareFn.apply(*ins, *opt, _f32c(cos_tab), _f32c(sin_tab), _f32c(rk_mult).reshape(-1), _f32c(mix_amt).reshape(-1), n_head)
+
+
+class _RmsNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scale, eps):
+        lib = _lib.load()
+        chans = x.shape[-1]
+        rows = x.numel() // chans
+        y = torch.empty_like(x)
+        inv = torch.empty(rows, dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            check(lib.pb_rms_norm(x.data_ptr(), scale.data_ptr(), rows, chans, eps, y.data_ptr(), inv.data_ptr(), _stream(x.device)))
+        ctx.save_for_backward(x, scale, inv)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, scale, inv = ctx.saved_tensors
+        lib = _lib.load()
+        chans = x.shape[-1]
+        rows = x.numel() // chans
+        dy = _f32c(dy)
+        dev = x.device
+        with torch.cuda.device(dev):
+            dx, dscale = torch.empty_like(x), torch.empty_like(scale)
+            ws_bytes = lib.pb_rms_norm_bwd_workspace_size(rows, chans)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+            check(lib.pb_rms_norm_bwd(dy.data_ptr(), x.data_ptr(), scale.data_ptr(), inv.data_ptr(), rows, chans,
+                                      dx.data_ptr(), dscale.data_ptr(), ws.data_ptr(), ws_bytes, _stream(dev)))
+        return dx, dscale, None
+
+
+def rms_norm(x, scale, eps: float):
+    """(x * rsqrt(mean(x^2, -1) + eps)) * scale, _module.py:61-72; x [..., C] f32, scale [C] or [1, C] as read through its
+    quantization; C a multiple of 128."""
+    if not x.is_cuda:
+        raise RuntimeError("rms_norm needs CUDA tensors: pratchya_b200 has no CPU path")
+    if scale.numel() != x.shape[-1] or x.shape[-1] % 128 != 0:
+        raise ValueError(f"rms_norm: x {tuple(x.shape)}, scale {tuple(scale.shape)} (the last dimension must be a multiple of 128)")
+    return _RmsNormFn.apply(_f32c(x), _f32c(scale).reshape(-1), float(eps))
+
+
+class _Relu2Fn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        lib = _lib.load()
+        y = torch.empty_like(x)
+        with torch.cuda.device(x.device):
+            check(lib.pb_relu2(x.data_ptr(), x.numel(), y.data_ptr(), _stream(x.device)))
+        ctx.save_for_backward(x)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        (x,) = ctx.saved_tensors
+        lib = _lib.load()
+        g = _f32c(g)
+        dx = torch.empty_like(x)
+        with torch.cuda.device(x.device):
+            check(lib.pb_relu2_bwd(g.data_ptr(), x.data_ptr(), x.numel(), dx.data_ptr(), _stream(x.device)))
+        return dx
+
+
+def relu2(x):
+    """relu(x) ** 2, _module.py:249; the element count must be a multiple of 4."""
+    if not x.is_cuda:
+        raise RuntimeError("relu2 needs CUDA tensors: pratchya_b200 has no CPU path")
+    return _Relu2Fn.apply(_f32c(x))
+
+
+class _WkvFinishFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, r, k, v, gate, gn_scale, gn_bias, bonus_mult, eps, n_head):
+        lib = _lib.load()
+        bsz, steps, chans = y.shape
+        dev = y.device
+        out = torch.empty_like(y)
+        stats = torch.empty((bsz * n_head, 2), dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            ws_bytes = lib.pb_wkv_finish_workspace_size(bsz, steps, n_head, chans // n_head)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+            check(lib.pb_wkv_finish(y.data_ptr(), r.data_ptr(), k.data_ptr(), v.data_ptr(), gate.data_ptr(), gn_scale.data_ptr(),
+                                    gn_bias.data_ptr(), bonus_mult.data_ptr(), eps, bsz, steps, n_head, chans // n_head,
+                                    out.data_ptr(), stats.data_ptr(), ws.data_ptr(), ws_bytes, _stream(dev)))
+        ctx.save_for_backward(y, r, k, v, gate, gn_scale, gn_bias, bonus_mult, stats)
+        ctx.n_head = n_head
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        y, r, k, v, gate, gn_scale, gn_bias, bonus_mult, stats = ctx.saved_tensors
+        lib = _lib.load()
+        bsz, steps, chans = y.shape
+        n_head = ctx.n_head
+        dev = y.device
+        g = _f32c(g)
+        with torch.cuda.device(dev):
+            d_y, d_r, d_k, d_v, d_gate = (torch.empty_like(y) for _ in range(5))
+            d_gs, d_gb, d_bm = torch.empty_like(gn_scale), torch.empty_like(gn_bias), torch.empty_like(bonus_mult)
+            ws_bytes = lib.pb_wkv_finish_bwd_workspace_size(bsz, steps, n_head, chans // n_head)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+            check(lib.pb_wkv_finish_bwd(g.data_ptr(), y.data_ptr(), r.data_ptr(), k.data_ptr(), v.data_ptr(), gate.data_ptr(),
+                                        gn_scale.data_ptr(), gn_bias.data_ptr(), bonus_mult.data_ptr(), stats.data_ptr(),
+                                        bsz, steps, n_head, chans // n_head, d_y.data_ptr(), d_r.data_ptr(), d_k.data_ptr(),
+                                        d_v.data_ptr(), d_gate.data_ptr(), d_gs.data_ptr(), d_gb.data_ptr(), d_bm.data_ptr(),
+                                        ws.data_ptr(), ws_bytes, _stream(dev)))
+        return d_y, d_r, d_k, d_v, d_gate, d_gs, d_gb, d_bm, None, None
+
+
+def wkv_finish(y, r, k, v, gate, gn_scale, gn_bias, bonus_mult, eps: float, n_head: int):
+    """(GroupNorm(y) + sum_c(r * k * bonus_mult) * v) * gate of TimeMix (_module.py:208-216): y the scan's output, all
+    [B, T, C] f32 with C = n_head * 64; gn_scale, gn_bias, bonus_mult [C] (or [1, C]); one norm group per head with
+    statistics over the T x 64 values of a batch element (flax GroupNorm on [B, T, C], :118-123)."""
+    ins = [y, r, k, v, gate]
+    shape = tuple(y.shape)
+    if len(shape) != 3 or any(tuple(t.shape) != shape for t in ins) or shape[2] != n_head * 64:
+        raise ValueError(f"wkv_finish: inputs must share a shape [B, T, {n_head} * 64], got {[tuple(t.shape) for t in ins]}")
+    if not y.is_cuda:
+        raise RuntimeError("wkv_finish needs CUDA tensors: pratchya_b200 has no CPU path")
+    return _WkvFinishFn.apply(*[_f32c(t) for t in ins], _f32c(gn_scale).reshape(-1), _f32c(gn_bias).reshape(-1),
+                              _f32c(bonus_mult).reshape(-1), float(eps), n_head)

@@ -18,7 +18,7 @@ from dataclasses import dataclass
 import torch
 
 from .._qualia import _ops
-from ._glue import token_shift_lerp, wkv_prepare
+from ._glue import relu2, rms_norm, token_shift_lerp, wkv_finish, wkv_prepare
 from ._module import linear_fp8
 from ._wkv7 import wkv_state_scan
 
@@ -97,12 +97,14 @@ class LowRankFFN(torch.nn.Module):                   # _module.py:74-89
 
 
 class RMSNorm(torch.nn.Module):                      # _module.py:61-72
-    def __init__(self, hidden, blk, eps, device):
+    def __init__(self, hidden, blk, eps, device, fused=True):
         super().__init__()
-        self.eps, self.blk = eps, blk
+        self.eps, self.blk, self.fused = eps, blk, fused
         self.scale = torch.nn.Parameter(torch.ones(1, hidden, device=device))
 
     def forward(self, x):
+        if self.fused:
+            return rms_norm(x, read_param(self.scale, (1, self.blk)), self.eps).to(x.dtype)
         x32 = x.to(torch.float32)
         inv_rms = torch.rsqrt(torch.mean(torch.square(x32), dim=-1, keepdim=True) + self.eps)
         return (x32 * inv_rms * read_param(self.scale, (1, self.blk))).to(x.dtype)
@@ -163,7 +165,7 @@ class TimeMix(torch.nn.Module):                      # _module.py:92-225
         n, h, blk = self.n_head, self.head_dim, self.cfg.blksize
         mu = read_param(self.mu, (1, blk))
         if self.cfg.fused_glue:
-            x_r, x_d, x_k, x_v, x_i, x_g = token_shift_lerp(x, tm_state, mu).unbind(0)
+            x_r, x_d, x_k, x_v, x_i, x_g = token_shift_lerp(x, tm_state, mu)
         else:
             x_shifted = torch.cat([tm_state, x[:, :-1, :]], dim=1)
             _x, _xs = x.to(torch.float32), x_shifted.to(torch.float32)
@@ -198,9 +200,13 @@ class TimeMix(torch.nn.Module):                      # _module.py:92-225
             iclr = iclr.to(torch.float32)
             replacement_k = lerp(k, k * iclr, mix_amt)
         wkv_state, out = wkv_state_scan(wkv_state, decay, iclr, removal_k, replacement_k, v, r, n)
-        out = group_norm(out, n, n * 1e-5, self.gn_scale, self.gn_bias)
-        bonus = torch.sum(r * k * read_param(self.bonus_multiplier, (1, blk)), dim=-1, keepdim=True) * v
-        out = (out + bonus) * gate.to(torch.float32)
+        bonus_mult = read_param(self.bonus_multiplier, (1, blk))
+        if self.cfg.fused_glue:
+            out = wkv_finish(out, r, k, v, gate, self.gn_scale, self.gn_bias, bonus_mult, n * 1e-5, n)
+        else:
+            out = group_norm(out, n, n * 1e-5, self.gn_scale, self.gn_bias)
+            bonus = torch.sum(r * k * bonus_mult, dim=-1, keepdim=True) * v
+            out = (out + bonus) * gate.to(torch.float32)
         return self.w_output(out), v, tm_state, wkv_state
 
 
@@ -222,7 +228,7 @@ class ChannelMix(torch.nn.Module):                   # _module.py:228-258
             x_k = lerp(x.to(torch.float32), x_shifted.to(torch.float32), mu_x)
         cm_state = x[:, -1:, :]
         k = self.w_k(x_k).to(torch.float32)
-        k = torch.relu(k) ** 2
+        k = relu2(k) if self.fused_glue else torch.relu(k) ** 2
         return self.w_v(k), cm_state
 
 
@@ -231,8 +237,8 @@ class RWKVBlock(torch.nn.Module):                    # _module.py:286-317
         super().__init__()
         self.tm = TimeMix(cfg, gen, device, first_layer)
         self.cm = ChannelMix(cfg, gen, device)
-        self.pre_rmsnorm = RMSNorm(cfg.hidden_size, cfg.blksize, cfg.rmsnorm_epsilon, device)
-        self.post_rmsnorm = RMSNorm(cfg.hidden_size, cfg.blksize, cfg.rmsnorm_epsilon, device)
+        self.pre_rmsnorm = RMSNorm(cfg.hidden_size, cfg.blksize, cfg.rmsnorm_epsilon, device, cfg.fused_glue)
+        self.post_rmsnorm = RMSNorm(cfg.hidden_size, cfg.blksize, cfg.rmsnorm_epsilon, device, cfg.fused_glue)
 
     def forward(self, x, v_0, t_positions, tm_state, cm_state, wkv_state):
         x = self.pre_rmsnorm(x)
@@ -241,6 +247,33 @@ class RWKVBlock(torch.nn.Module):                    # _module.py:286-317
         x = self.post_rmsnorm(x)
         dx, cm_state = self.cm(x, cm_state)
         return x + dx, v_0, tm_state, cm_state, wkv_state
+
+
+class _RematBlock(torch.autograd.Function):
+    """A block whose activations are recomputed in the backward pass (the reference's nnx.remat, _model.py:26-30).
+    Forward: the block under no_grad from zero states, so none of its layers keeps anything for a backward pass (no X^T
+    quantization, no scan checkpoints); only the block's inputs are kept.  Backward: the block again with gradients
+    enabled, then its own backward pass; the parameters' gradients accumulate there, the inputs' are returned."""
+
+    @staticmethod
+    def forward(ctx, blk, t_positions, zero_state, x, v_0):
+        ctx.blk, ctx.t_positions, ctx.zero_state = blk, t_positions, zero_state
+        ctx.set_materialize_grads(False)
+        ctx.save_for_backward(x, v_0)
+        with torch.no_grad():
+            y, v, _, _, _ = blk(x, v_0, t_positions, zero_state, zero_state, None)
+        return y, v
+
+    @staticmethod
+    def backward(ctx, g_y, g_v):
+        x, v_0 = ctx.saved_tensors
+        x_in = x.detach().requires_grad_(True)
+        v_in = v_0.detach().requires_grad_(True) if v_0 is not None else None
+        with torch.enable_grad():
+            y, v, _, _, _ = ctx.blk(x_in, v_in, ctx.t_positions, ctx.zero_state, ctx.zero_state, None)
+        outs = [(y, g_y), (v, g_v)]
+        torch.autograd.backward([o for o, g in outs if g is not None], [g for _, g in outs if g is not None])
+        return None, None, None, x_in.grad, v_in.grad if v_in is not None else None
 
 
 class PratchyaCausalLM(torch.nn.Module):
@@ -253,8 +286,8 @@ class PratchyaCausalLM(torch.nn.Module):
         self.cfg, self.remat = cfg, remat
         self.embedding = torch.nn.Parameter(torch.randn(cfg.vocab_size, cfg.hidden_size, generator=gen, device=device) / math.sqrt(cfg.hidden_size))
         self.blocks = torch.nn.ModuleList([RWKVBlock(cfg, gen, device, first_layer=i == 0) for i in range(cfg.n_layers)])
-        self.pre_rmsnorm = RMSNorm(cfg.hidden_size, cfg.blksize, cfg.rmsnorm_epsilon, device)
-        self.final_rmsnorm = RMSNorm(cfg.hidden_size, cfg.blksize, cfg.rmsnorm_epsilon, device)
+        self.pre_rmsnorm = RMSNorm(cfg.hidden_size, cfg.blksize, cfg.rmsnorm_epsilon, device, cfg.fused_glue)
+        self.final_rmsnorm = RMSNorm(cfg.hidden_size, cfg.blksize, cfg.rmsnorm_epsilon, device, cfg.fused_glue)
         self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, (cfg.blksize, 1), gen, device)
 
     def embed(self, input_ids):                      # EmbeddingScaled, _module.py:21-37
@@ -270,24 +303,29 @@ class PratchyaCausalLM(torch.nn.Module):
         v = None
         zeros_c = torch.zeros(bsz, 1, cfg.hidden_size, device=dev)
         for blk in self.blocks:
-            args = (x, v, t_positions, zeros_c, zeros_c, None)
             if self.remat and torch.is_grad_enabled():
-                x, v, _, _, _ = torch.utils.checkpoint.checkpoint(blk, *args, use_reentrant=False)
+                x, v = _RematBlock.apply(blk, t_positions, zeros_c, x, v)
             else:
-                x, v, _, _, _ = blk(*args)
+                x, v, _, _, _ = blk(x, v, t_positions, zeros_c, zeros_c, None)
         x = self.final_rmsnorm(x)
         logits = self.lm_head(x)
         loss = None
         if label is not None:
-            loss = smoothed_cross_entropy(logits[:, :-1, :], label[:, 1:])
+            loss = smoothed_cross_entropy(logits, label)
         return logits, loss
 
 
 def smoothed_cross_entropy(logits, labels, alpha: float = 0.1):
-    """compute_loss, _utils.py:7-13: one-hot labels smoothed by alpha (optax.smooth_labels), softmax cross entropy in
-    f32, mean over batch and positions."""
+    """compute_loss, _utils.py:7-13, on logits [B, T, V] and labels [B, T]: position t predicts label t+1 (the caller of
+    the reference passes logits[:, :-1] and label[:, 1:]); one-hot labels smoothed by alpha (optax.smooth_labels),
+    softmax cross entropy in f32, mean over batch and the T-1 positions.  Everything runs on the whole contiguous
+    array and the last position gets weight zero, which avoids strided copies of the logits and of their gradient."""
+    bsz, steps, _ = logits.shape
     logp = torch.log_softmax(logits.to(torch.float32), dim=-1)
-    n_cls = logits.shape[-1]
-    nll = -logp.gather(-1, labels.unsqueeze(-1).to(torch.int64)).squeeze(-1)
+    target = torch.cat([labels[:, 1:], labels[:, :1]], dim=1).to(torch.int64)        # the last column is a placeholder
+    nll = -logp.gather(-1, target.unsqueeze(-1)).squeeze(-1)
     uniform = -logp.mean(dim=-1)
-    return ((1.0 - alpha) * nll + alpha * uniform).mean()
+    per_position = (1.0 - alpha) * nll + alpha * uniform
+    weight = torch.ones(steps, device=logits.device, dtype=torch.float32)
+    weight[-1] = 0.0
+    return (per_position * weight).sum() / (bsz * (steps - 1))

@@ -159,14 +159,14 @@ class _LinearFn(torch.autograd.Function):
     grid, as the reference returns them (:637-640, :522-526)."""
 
     @staticmethod
-    def forward(ctx, x, weight, grid, fake_quant_output, recipe, grad_format):
+    def forward(ctx, x, weight, grid, fake_quant_output, recipe, grad_format, for_backward=True):
         a, b = grid
         x2 = x.reshape(-1, x.shape[-1])
         wq = _ops.quantize_impl(weight, grid)
         # the tensor-core backward needs the weight as a K-major operand in both directions: (128,128) blocks only.
         # A (128,1) weight (LoRA, gate, lm_head) has one scale per column and 128 rows, which no 128-deep block
         # along its columns can carry: its forward runs on the tensor cores, its backward on the literal recipe.
-        want_xt = recipe == "fp8" and (a, b) == (128, 128) and x2.shape[0] % 1024 == 0
+        want_xt = for_backward and recipe == "fp8" and (a, b) == (128, 128) and x2.shape[0] % 1024 == 0
         if want_xt:       # both forms of x in one call (x itself is not kept for the backward pass)
             xq, xt = _ops.quantize_dual_impl(x2)
         else:
@@ -218,7 +218,7 @@ class _LinearFn(torch.autograd.Function):
             gw = _ops._matmul_f32(x_hat.t(), g32)
         gx = _ops.fake_quantize_impl(gx, (1, a), torch.float32)                                  # :637 then :522-526
         gw = _ops.dequantize_impl(*_ops.quantize_impl(gw, ctx.grid), torch.float32, ctx.grid)    # :638; the optimizer dequantizes it
-        return gx.reshape(ctx.x_shape).to(ctx.x_dtype), gw.to(ctx.w_dtype), None, None, None, None
+        return gx.reshape(ctx.x_shape).to(ctx.x_dtype), gw.to(ctx.w_dtype), None, None, None, None, None
 
 
 def linear_fp8(x: torch.Tensor, weight: torch.Tensor, tgrid=(128, 128), *, fake_quant_output: bool = True,
@@ -228,4 +228,7 @@ def linear_fp8(x: torch.Tensor, weight: torch.Tensor, tgrid=(128, 128), *, fake_
     (an extension: the reference has no e5m2 anywhere)."""
     if recipe not in ("fp8", "reference"):
         raise ValueError("recipe must be 'fp8' or 'reference'")
-    return _LinearFn.apply(x, weight, (int(tgrid[0]), int(tgrid[1])), fake_quant_output, recipe, grad_format)
+    # X^T is quantized in the forward pass only when a backward pass can follow (not under torch.no_grad, as in the first
+    # pass of a recomputed block)
+    for_backward = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
+    return _LinearFn.apply(x, weight, (int(tgrid[0]), int(tgrid[1])), fake_quant_output, recipe, grad_format, for_backward)

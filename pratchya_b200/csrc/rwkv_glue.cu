@@ -57,7 +57,8 @@ __global__ void __launch_bounds__(kGlueThreads) shift_lerp_fwd_kernel(const Shif
 //   dmu_k[c] = sum_r g_k[r][c] * (prev[r][c] - x[r][c]).
 // A CTA walks kLerpTileRows tokens of 1024 channels (four per thread), carrying x[r-1] and the unfinished dx[r-1].
 struct ShiftLerpBwdParams {
-  const float* g; const float* x; const float* state; const float* mu;
+  const float* g[kMaxMix];                         // cotangent of each mix, [R][C]
+  const float* x; const float* state; const float* mu;
   float* dx; float* dstate; float* partial;        // partial [tiles][n_mix][C]
   int64_t R; int T, C, n_mix;
 };
@@ -75,7 +76,7 @@ __global__ void __launch_bounds__(kGlueThreads) shift_lerp_bwd_kernel(const Shif
   auto weighted = [&](int64_t r, float4& gsum, float4& s, float4 d, bool accumulate) {
 #pragma unroll
     for (int k = 0; k < NMIX; ++k) {
-      const float4 g = ld4(p.g + ((size_t)k * p.R + r) * p.C + c);
+      const float4 g = ld4(p.g[k] + (size_t)r * p.C + c);
       gsum.x += g.x; gsum.y += g.y; gsum.z += g.z; gsum.w += g.w;
       s.x = fmaf(g.x, mu[k].x, s.x); s.y = fmaf(g.y, mu[k].y, s.y); s.z = fmaf(g.z, mu[k].z, s.z); s.w = fmaf(g.w, mu[k].w, s.w);
       if (accumulate) {
@@ -275,7 +276,7 @@ extern "C" size_t pb_token_shift_lerp_bwd_workspace_size(int64_t batch, int64_t 
   return (size_t)tiles * n_mix * channels * sizeof(float);
 }
 
-extern "C" int pb_token_shift_lerp_bwd(const float* g, const float* x, const float* state, const float* mu,
+extern "C" int pb_token_shift_lerp_bwd(const float* const* g, const float* x, const float* state, const float* mu,
                                        int64_t batch, int64_t steps, int64_t channels, int n_mix,
                                        float* dx, float* dstate, float* dmu, void* workspace, size_t workspace_bytes, void* stream) {
   if (!g || !x || !mu || !dx || !dmu) return fail(PB_ERR_NULL_POINTER, "pb_token_shift_lerp_bwd: g, x, mu, dx and dmu must be non-null");
@@ -285,11 +286,14 @@ extern "C" int pb_token_shift_lerp_bwd(const float* g, const float* x, const flo
   const size_t need = pb_token_shift_lerp_bwd_workspace_size(batch, steps, channels, n_mix);
   if (!workspace || workspace_bytes < need)
     return fail(PB_ERR_WORKSPACE_TOO_SMALL, "pb_token_shift_lerp_bwd: needs %zu bytes of workspace, got %zu", need, workspace_bytes);
-  if (misaligned({g, x, state, mu, dx, dstate, dmu, workspace})) return fail(PB_ERR_MISALIGNED, "pb_token_shift_lerp_bwd: every array must be 16-byte aligned");
+  if (misaligned({x, state, mu, dx, dstate, dmu, workspace})) return fail(PB_ERR_MISALIGNED, "pb_token_shift_lerp_bwd: every array must be 16-byte aligned");
+  for (int k = 0; k < n_mix; ++k)
+    if (!g[k] || (reinterpret_cast<uintptr_t>(g[k]) & 15)) return fail(PB_ERR_MISALIGNED, "pb_token_shift_lerp_bwd: g[%d] must be non-null and 16-byte aligned", k);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t R = batch * steps;
   const int tiles = (int)((R + kLerpTileRows - 1) / kLerpTileRows);
-  ShiftLerpBwdParams p{g, x, state, mu, dx, dstate, static_cast<float*>(workspace), R, (int)steps, (int)channels, n_mix};
+  ShiftLerpBwdParams p{{}, x, state, mu, dx, dstate, static_cast<float*>(workspace), R, (int)steps, (int)channels, n_mix};
+  for (int k = 0; k < n_mix; ++k) p.g[k] = g[k];
   const dim3 grid((unsigned)((channels / 4 + kGlueThreads - 1) / kGlueThreads), (unsigned)tiles);
   if (n_mix == 6) shift_lerp_bwd_kernel<6><<<grid, kGlueThreads, 0, st>>>(p);
   else shift_lerp_bwd_kernel<1><<<grid, kGlueThreads, 0, st>>>(p);

@@ -136,3 +136,19 @@ def test_block_gradients_agree_with_and_without_recomputation(built_lib):
         out.square().mean().backward()
         grads.append((xin.grad.clone(), blk.tm.w_key.kernel.grad.clone()))
     assert torch.equal(grads[0][0], grads[1][0]) and torch.equal(grads[0][1], grads[1][1])
+
+
+def test_model_gradients_are_the_same_bits_with_and_without_recomputation(built_lib):
+    """PratchyaCausalLM(remat=True) runs each block without a graph in the forward pass and recomputes it in the backward
+    pass; every kernel is deterministic, so loss and gradients equal those of the stored-activation model bit for bit."""
+    gen = torch.Generator(device="cuda").manual_seed(6)
+    ids = torch.randint(0, CFG.vocab_size, (2, 40), device="cuda", generator=gen)
+    results = []
+    for remat in (False, True):
+        model = PratchyaCausalLM(CFG, seed=7, remat=remat)
+        _, loss = model(ids, ids)
+        loss.backward()
+        results.append((loss.detach(), {n: p.grad.clone() for n, p in model.named_parameters()}))
+    assert torch.equal(results[0][0], results[1][0])
+    for name, grad in results[0][1].items():
+        assert torch.equal(grad, results[1][1][name]), f"gradient of {name}"
