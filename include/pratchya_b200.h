@@ -251,18 +251,19 @@ PB_API int pb_quantize_dual(const void* x, int x_dtype, int64_t batch, int64_t r
  *      the order the reference has after its transpose (:210).  head_dim must be 64.  16-byte aligned arrays.
  *      `checkpoints` (may be null) receives the state before timesteps 0, 8, 16, ... as f32
  *      [batch, heads, ceil(steps/8), head_dim, head_dim] (pb_wkv7_checkpoint_floats elements): what
- *      pb_wkv7_backward restarts from. */
+ *      pb_wkv7_backward restarts from.  `sa` (may be null) receives, for every timestep, the state before the step times
+ *      removal_k (f32 [batch, steps, heads*head_dim]): with it the backward pass recomputes the states element-wise. */
 PB_API int pb_wkv7_forward(const float* decay, const float* iclr, const float* removal_k, const float* replacement_k,
                     const float* v, const float* r, const float* state_in,
                     int64_t batch, int64_t steps, int64_t heads, int head_dim,
-                    float* y, float* state_out, float* checkpoints, void* stream);
+                    float* y, float* state_out, float* checkpoints, float* sa, void* stream);
 PB_API size_t pb_wkv7_checkpoint_floats(int64_t batch, int64_t steps, int64_t heads, int head_dim);
 /* Cotangents of the scan: what jax.grad derives from `wkv_state_scan` (pratchya/_nnx_impl/_module.py:187-207) for the
  * six inputs and the initial state, given dy [batch, steps, heads*head_dim] and (optionally) the cotangent of the final
  * state.  The states the derivatives need are recomputed eight timesteps at a time from the forward pass's checkpoints
- * and stay in shared memory: the call needs no workspace.  All arrays f32. */
+ * and its `sa` array, and stay in shared memory: the call needs no workspace.  All arrays f32. */
 PB_API int pb_wkv7_backward(const float* decay, const float* iclr, const float* removal_k, const float* replacement_k,
-                     const float* v, const float* r, const float* checkpoints, const float* dy, const float* dstate_out,
+                     const float* v, const float* r, const float* checkpoints, const float* sa, const float* dy, const float* dstate_out,
                      int64_t batch, int64_t steps, int64_t heads, int head_dim,
                      float* d_decay, float* d_iclr, float* d_removal_k, float* d_replacement_k, float* d_v, float* d_r,
                      float* dstate_in, void* stream);

@@ -78,9 +78,9 @@ _SIGNATURES = {
     "pb_wkv_finish": (_int, [_ptr] * 8 + [C.c_float, _i64, _i64, _i64, _int] + [_ptr] * 3 + [_sz, _ptr]),
     "pb_wkv_finish_bwd_workspace_size": (_sz, [_i64, _i64, _i64, _int]),
     "pb_wkv_finish_bwd": (_int, [_ptr] * 10 + [_i64, _i64, _i64, _int] + [_ptr] * 9 + [_sz, _ptr]),
-    "pb_wkv7_forward": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr, _ptr, _ptr, _ptr]),
+    "pb_wkv7_forward": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "pb_wkv7_checkpoint_floats": (_sz, [_i64, _i64, _i64, _int]),
-    "pb_wkv7_backward": (_int, [_ptr] * 9 + [_i64, _i64, _i64, _int] + [_ptr] * 8),
+    "pb_wkv7_backward": (_int, [_ptr] * 10 + [_i64, _i64, _i64, _int] + [_ptr] * 8),
 }
 # extra exports of the diagnostics build (libpratchya_b200_diag.so): test hooks, not part of the C ABI
 _DIAG_SIGNATURES = {

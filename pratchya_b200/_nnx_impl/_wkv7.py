@@ -30,30 +30,32 @@ def _forward(state_in, ins, n_head, want_checkpoints):
     with torch.cuda.device(dev):
         out = torch.empty((bsz, steps, chans), dtype=torch.float32, device=dev)
         state_out = torch.empty((bsz, n_head, head_dim, head_dim), dtype=torch.float32, device=dev)
-        ckpt = None
+        ckpt = sa = None
         if want_checkpoints:
             n_floats = lib.pb_wkv7_checkpoint_floats(bsz, steps, n_head, head_dim)
             if n_floats == 0:
                 raise _lib.PbError(_lib.PB_ERR_UNSUPPORTED, f"wkv_state_scan: head size {head_dim} is not supported")
             ckpt = torch.empty(n_floats, dtype=torch.float32, device=dev)
+            sa = torch.empty((bsz, steps, chans), dtype=torch.float32, device=dev)
         check(lib.pb_wkv7_forward(*[t.data_ptr() for t in ins], state_in.data_ptr() if state_in is not None else None,
                                   bsz, steps, n_head, head_dim, out.data_ptr(), state_out.data_ptr(),
-                                  ckpt.data_ptr() if ckpt is not None else None, torch.cuda.current_stream(dev).cuda_stream))
-    return state_out, out, ckpt
+                                  ckpt.data_ptr() if ckpt is not None else None, sa.data_ptr() if sa is not None else None,
+                                  torch.cuda.current_stream(dev).cuda_stream))
+    return state_out, out, ckpt, sa
 
 
 class _WkvScanFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, state_in, decay, iclr, removal_k, replacement_k, v, r, n_head):
         ins = [t.contiguous() for t in (decay, iclr, removal_k, replacement_k, v, r)]
-        state_out, out, ckpt = _forward(state_in, ins, n_head, True)
-        ctx.save_for_backward(*ins, ckpt)
+        state_out, out, ckpt, sa = _forward(state_in, ins, n_head, True)
+        ctx.save_for_backward(*ins, ckpt, sa)
         ctx.n_head, ctx.has_state = n_head, state_in is not None
         return state_out, out
 
     @staticmethod
     def backward(ctx, d_state_out, d_out):
-        *ins, ckpt = ctx.saved_tensors
+        *ins, ckpt, sa = ctx.saved_tensors
         bsz, steps, chans = ins[0].shape
         n_head = ctx.n_head
         head_dim = chans // n_head
@@ -64,7 +66,7 @@ class _WkvScanFn(torch.autograd.Function):
             d_state = d_state_out.to(torch.float32).contiguous() if d_state_out is not None else None
             grads = [torch.empty_like(ins[0]) for _ in range(6)]
             d_state_in = torch.empty((bsz, n_head, head_dim, head_dim), dtype=torch.float32, device=dev) if ctx.has_state else None
-            check(lib.pb_wkv7_backward(*[t.data_ptr() for t in ins], ckpt.data_ptr(), d_out.data_ptr(),
+            check(lib.pb_wkv7_backward(*[t.data_ptr() for t in ins], ckpt.data_ptr(), sa.data_ptr(), d_out.data_ptr(),
                                        d_state.data_ptr() if d_state is not None else None,
                                        bsz, steps, n_head, head_dim, *[g.data_ptr() for g in grads],
                                        d_state_in.data_ptr() if d_state_in is not None else None,
@@ -89,5 +91,5 @@ def wkv_state_scan(wkv_state, decay, iclr, removal_k, replacement_k, v, r, n_hea
     needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in ins + ([state_in] if state_in is not None else []))
     if needs_grad:
         return _WkvScanFn.apply(state_in, *ins, n_head)
-    state_out, out, _ = _forward(state_in, ins, n_head, False)
+    state_out, out, _, _ = _forward(state_in, ins, n_head, False)
     return state_out, out

@@ -36,6 +36,7 @@ struct WkvParams {
   float* y;                       // [B, T, C]
   float* state_out;               // [B, N, H, H] or null
   float* ckpt;                    // [B, N, ceil(T / kCk), H, H] or null: the state before timesteps 0, kCk, 2*kCk, ...
+  float* sa;                      // [B, T, C] or null: sa of every timestep (S before the step, times removal_k), for the backward pass
   int T, N;                       // timesteps, heads
 };
 
@@ -46,7 +47,7 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // One timestep for row i of S.  `buf` holds the step's decay, iclr, removal_k, replacement_k, v, r; `bk` = iclr * removal_k.
-__device__ __forceinline__ float wkv_step(float2 (&S)[32], const float (*buf)[kH], const float* bk, int i) {
+__device__ __forceinline__ float wkv_step(float2 (&S)[32], const float (*buf)[kH], const float* bk, int i, float& sa_out) {
   // sa_i = sum_j S[i][j] * kap_j, four partial sums
   float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
@@ -56,6 +57,7 @@ __device__ __forceinline__ float wkv_step(float2 (&S)[32], const float (*buf)[kH
     acc[(2 * j + 1) & 3] = __ffma2_rn(S[2 * j + 1], make_float2(k4.z, k4.w), acc[(2 * j + 1) & 3]);
   }
   const float sa = ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
+  sa_out = sa;
   const float vi = buf[4][i];
   const float2 nsa2 = make_float2(-sa, -sa), vi2 = make_float2(vi, vi);
   float2 y[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
@@ -132,8 +134,13 @@ wkv7_forward_kernel(const __grid_constant__ WkvParams p) {
 #pragma unroll
       for (int j = 0; j < 16; ++j) dst[j] = make_float4(S[2 * j].x, S[2 * j].y, S[2 * j + 1].x, S[2 * j + 1].y);
     }
-    yp[(size_t)t * C] = wkv_step(S, step0, bk[0], i);
-    if (t + 1 < p.T) yp[(size_t)(t + 1) * C] = wkv_step(S, step1, bk[1], i);
+    float sa0, sa1;
+    yp[(size_t)t * C] = wkv_step(S, step0, bk[0], i, sa0);
+    if (p.sa) p.sa[head_base + (size_t)t * C + i] = sa0;
+    if (t + 1 < p.T) {
+      yp[(size_t)(t + 1) * C] = wkv_step(S, step1, bk[1], i, sa1);
+      if (p.sa) p.sa[head_base + (size_t)(t + 1) * C + i] = sa1;
+    }
   }
   cp_async_wait<0>();
   if (p.state_out) {
@@ -148,26 +155,31 @@ wkv7_forward_kernel(const __grid_constant__ WkvParams p) {
 //     dr_t   = S_t^T dy_t                    dv_t  = G_t kt_t                 dkt_t = G_t^T v_t
 //     dsa_t  = -G_t b_t   (b = a * kap)      db_t  = -G_t^T sa_t              dw_t  = sum_i G_t[i][:] * S_{t-1}[i][:]
 //     dkap_t = S_{t-1}^T dsa_t + db_t * a_t  da_t  = db_t * kap_t             dS_{t-1} = G_t diag(w_t) + dsa_t kap_t^T
-// Half of these are sums along a row of the state, half along a column, so a CTA of 128 threads keeps two copies
-// of dS in registers: threads 0..63 one row each, threads 64..127 one column each.  The row threads need S_{t-1}
-// only through sa_t = S_{t-1} kap_t; the column threads need its columns.
+// Half of these are sums along a row of the state, half along a column, so a CTA keeps dS twice: 128 row
+// threads (row i, one half of its columns each) and 128 column threads (column j, one half of its rows each).
+// The halves of a row or column sit in different warps, so a warp still reads every input vector at one
+// address per instruction (a broadcast), and the two partial sums meet in shared memory.
 //
-// S_{t-1} is not stored by the forward pass for every t: it writes a checkpoint every kCk = 8 timesteps.  The
-// backward pass walks the chunks from the last to the first.  Per chunk the row threads recompute the states
-// from the checkpoint (pass 1), keeping every sa_t (64 floats) and the states before the chunk's last four
-// timesteps in four shared-memory slots; both groups then run those four timesteps backwards; the row threads
-// recompute the states before the first four timesteps into the same slots (pass 2, from the checkpoint and the
-// kept sa_t, so without the dot products) and the four timesteps run backwards.  The recomputed states never
-// leave the SM.  A slot is H x H floats with the 16-byte groups of row i stored at group ^ (i & 15): the row
-// threads' 16-byte row stores and the column threads' 4-byte column loads are both free of bank conflicts.
-// One block barrier per timestep (dsa, row threads -> column threads, double-buffered by the parity of t).
-// The chunk's seven input vectors per timestep arrive by cp.async one chunk ahead, and the checkpoint the next
-// recomputation starts from is loaded into the row threads' registers before the timesteps that precede it.
-constexpr int kSub = 4;           // timesteps whose states are kept at once
+// S_{t-1} is needed for every t and is not stored by the forward pass, which writes a checkpoint every
+// kCk = 8 timesteps and sa_t = S_{t-1} kap_t (64 floats) for every t.  With sa_t known the recurrence is
+// element-wise, so per chunk the row threads recompute the states from the checkpoint without any sum: first
+// the states before the chunk's last four timesteps into four shared-memory slots, those four timesteps run
+// backwards, then the states before the first four into the same slots, and those run backwards.  A slot is
+// H x H floats with the 16-byte groups of row i stored at group ^ (i & 15): the row threads' 16-byte row stores
+// and the column threads' 4-byte column loads are both free of bank conflicts.
+// One block barrier per timestep: before it the row threads publish the halves of dv and of -dsa, after it
+// everyone forms dsa.  The column threads' five sums are published as halves too and added one timestep later
+// (three buffers in rotation).  The chunk's eight vectors per timestep arrive by cp.async one chunk ahead, and
+// the checkpoint the next recomputation starts from is loaded into the row threads' registers before the
+// timesteps that precede it.
+constexpr int kSub = 4;                  // timesteps whose states are kept at once
+constexpr int kBwdThreads = 4 * kH;
+constexpr int kBwdVecs = kVecs + 2;      // the six inputs, dy and sa
 
 struct WkvBwdParams {
   const float* in[kVecs];
   const float* dy;                // [B, T, C]
+  const float* sa;                // [B, T, C]: S_{t-1} kap_t, from the forward pass
   const float* ckpt;              // [B, N, ceil(T / kCk), H, H]
   const float* dstate_out;        // [B, N, H, H] or null: gradient with respect to the final state
   float* din[kVecs];              // gradients of the six inputs, [B, T, C] each
@@ -177,153 +189,153 @@ struct WkvBwdParams {
 
 struct WkvBwdSmem {
   float slot[kSub][kH * kH];                // recomputed states, swizzled
-  float vec[2][kCk][kVecs + 1][kH];         // the chunk's inputs and dy, two chunks
+  float vec[2][kCk][kBwdVecs][kH];          // the chunk's vectors, two chunks
   float bk[kCk][kH];                        // iclr * removal_k
-  float sa[kCk][kH];                        // S_{t-1} removal_k_t
-  float dsa[2][kH];
+  float ds_part[2][2][kH];                  // [parity of t][column half][row]: halves of sum_j G b
+  float dv_part[2][2][kH];                  // ... of sum_j G kt
+  float col_part[3][2][5][kH];              // [t mod 3][row half][dr, dkt, sum G sa, dw, S^T dsa][column]
 };
 
 __device__ __forceinline__ float sum4(const float2 a, const float2 b) { return (a.x + a.y) + (b.x + b.y); }
 
-// sa_i = sum_j S[i][j] * kap_j in the forward kernel's order of additions
-__device__ __forceinline__ float wkv_sa(const float2 (&S)[32], const float* kap) {
-  float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    const float4 k4 = *reinterpret_cast<const float4*>(&kap[4 * j]);
-    acc[(2 * j) & 3] = __ffma2_rn(S[2 * j], make_float2(k4.x, k4.y), acc[(2 * j) & 3]);
-    acc[(2 * j + 1) & 3] = __ffma2_rn(S[2 * j + 1], make_float2(k4.z, k4.w), acc[(2 * j + 1) & 3]);
-  }
-  return ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
-}
-
-// S[i][:] <- S[i][:] * w - sa_i * b + v_i * kt, as the forward kernel forms it
-__device__ __forceinline__ void wkv_update(float2 (&S)[32], const float (*buf)[kH], const float* bk, float sa, float vi) {
-  const float2 nsa2 = make_float2(-sa, -sa), vi2 = make_float2(vi, vi);
-#pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    const float4 w4 = *reinterpret_cast<const float4*>(&buf[0][4 * j]);
-    const float4 b4 = *reinterpret_cast<const float4*>(&bk[4 * j]);
-    const float4 kt4 = *reinterpret_cast<const float4*>(&buf[3][4 * j]);
-    float2 s0 = __ffma2_rn(nsa2, make_float2(b4.x, b4.y), __fmul2_rn(S[2 * j], make_float2(w4.x, w4.y)));
-    float2 s1 = __ffma2_rn(nsa2, make_float2(b4.z, b4.w), __fmul2_rn(S[2 * j + 1], make_float2(w4.z, w4.w)));
-    S[2 * j] = __ffma2_rn(vi2, make_float2(kt4.x, kt4.y), s0);
-    S[2 * j + 1] = __ffma2_rn(vi2, make_float2(kt4.z, kt4.w), s1);
-  }
-}
-
-__device__ __forceinline__ void slot_store_row(float* slot, int i, const float2 (&S)[32]) {
-#pragma unroll
-  for (int g = 0; g < 16; ++g)
-    *reinterpret_cast<float4*>(&slot[i * kH + ((g ^ (i & 15)) << 2)]) = make_float4(S[2 * g].x, S[2 * g].y, S[2 * g + 1].x, S[2 * g + 1].y);
-}
-
-__global__ void __launch_bounds__(2 * kH, 2)
+__global__ void __launch_bounds__(kBwdThreads, 2)
 wkv7_backward_kernel(const __grid_constant__ WkvBwdParams p) {
   extern __shared__ __align__(16) unsigned char wkv_bwd_smem[];
   WkvBwdSmem& sm = *reinterpret_cast<WkvBwdSmem*>(wkv_bwd_smem);
   const int n = blockIdx.x % p.N, b = blockIdx.x / p.N;
   const int C = p.N * kH;
   const int tid = threadIdx.x;
-  const bool row_thread = tid < kH;
-  const int idx = row_thread ? tid : tid - kH;                  // the row i, or the column j, this thread owns
+  const bool row_thread = tid < 2 * kH;
+  const int half = (tid >> 6) & 1;             // row threads: which 32 columns; column threads: which 32 rows
+  const int idx = tid & (kH - 1);              // the row i, or the column j
+  const int h0 = 32 * half;
   const size_t head_base = (size_t)b * p.T * C + (size_t)n * kH;
   const size_t head = (size_t)b * p.N + n;
   const int n_ck = (p.T + kCk - 1) / kCk;
 
-  // element (i, idx) of a slot, for a column thread: i * kH + joff[i & 15]
+  // element (h0 + e, idx) of a slot, for a column thread: (h0 + e) * kH + joff[e & 15]
   int joff[16];
 #pragma unroll
   for (int c = 0; c < 16; ++c) joff[c] = ((((idx >> 2) ^ c) << 2) | (idx & 3));
 
-  float2 dS[32];                  // row idx (row threads: pairs of columns) or column idx (column threads: pairs of rows) of dS
+  float2 dS[16];                  // row threads: dS[idx][h0 + 2e, +1]; column threads: dS[h0 + 2e, +1][idx]
   if (p.dstate_out) {
     if (row_thread) {
 #pragma unroll
-      for (int g = 0; g < 16; ++g) {
-        const float4 q = __ldg(reinterpret_cast<const float4*>(p.dstate_out + (head * kH + idx) * kH) + g);
+      for (int g = 0; g < 8; ++g) {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(p.dstate_out + (head * kH + idx) * kH + h0) + g);
         dS[2 * g] = make_float2(q.x, q.y); dS[2 * g + 1] = make_float2(q.z, q.w);
       }
     } else {
 #pragma unroll
-      for (int e = 0; e < 32; ++e)
-        dS[e] = make_float2(__ldg(p.dstate_out + (head * kH + 2 * e) * kH + idx), __ldg(p.dstate_out + (head * kH + 2 * e + 1) * kH + idx));
+      for (int e = 0; e < 16; ++e)
+        dS[e] = make_float2(__ldg(p.dstate_out + (head * kH + h0 + 2 * e) * kH + idx), __ldg(p.dstate_out + (head * kH + h0 + 2 * e + 1) * kH + idx));
     }
   } else {
 #pragma unroll
-    for (int e = 0; e < 32; ++e) dS[e] = make_float2(0.0f, 0.0f);
+    for (int e = 0; e < 16; ++e) dS[e] = make_float2(0.0f, 0.0f);
   }
 
-  // the seven vectors of every timestep of chunk ck -> vec[ck & 1]; every thread commits one group per call
+  // the eight vectors of every timestep of chunk ck -> vec[ck & 1]; every thread commits one group per call
   auto issue_vec = [&](int ck) {
     if (ck >= 0) {
       const int t0 = ck * kCk, steps = min(kCk, p.T - t0);
-      for (int e = tid; e < steps * (kVecs + 1) * (kH / 4); e += 2 * kH) {
-        const int s = e / ((kVecs + 1) * (kH / 4)), rem = e % ((kVecs + 1) * (kH / 4)), v = rem / (kH / 4), c4 = rem % (kH / 4);
-        const float* src = (v < kVecs ? p.in[v] : p.dy) + head_base + (size_t)(t0 + s) * C + c4 * 4;
+      for (int e = tid; e < steps * kBwdVecs * (kH / 4); e += kBwdThreads) {
+        const int s = e / (kBwdVecs * (kH / 4)), rem = e % (kBwdVecs * (kH / 4)), v = rem / (kH / 4), c4 = rem % (kH / 4);
+        const float* src = (v < kVecs ? p.in[v] : (v == kVecs ? p.dy : p.sa)) + head_base + (size_t)(t0 + s) * C + c4 * 4;
         cp_async16((uint32_t)__cvta_generic_to_shared(&sm.vec[ck & 1][s][v][c4 * 4]), src);
       }
     }
     cp_async_commit();
   };
 
-  // row threads: the state being recomputed (in flight from the checkpoint while timesteps run backwards);
-  // column threads: column idx of S_{t-1} within a timestep.  One array, so that the two uses share registers.
-  float2 S[32];
+  // row threads: their half of the row of the state being recomputed (in flight from the checkpoint while
+  // timesteps run backwards); column threads: their half of column idx of S_{t-1} within a timestep.
+  float2 S[16];
   auto load_ckpt = [&](int ck) {
-    const float4* c4p = reinterpret_cast<const float4*>(p.ckpt + ((head * n_ck + ck) * kH + idx) * kH);
+    const float4* c4p = reinterpret_cast<const float4*>(p.ckpt + ((head * n_ck + ck) * kH + idx) * kH + h0);
 #pragma unroll
-    for (int g = 0; g < 16; ++g) { const float4 q = __ldg(c4p + g); S[2 * g] = make_float2(q.x, q.y); S[2 * g + 1] = make_float2(q.z, q.w); }
+    for (int g = 0; g < 8; ++g) { const float4 q = __ldg(c4p + g); S[2 * g] = make_float2(q.x, q.y); S[2 * g + 1] = make_float2(q.z, q.w); }
+  };
+  auto store_slot = [&](float* slot) {
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+      *reinterpret_cast<float4*>(&slot[idx * kH + (((8 * half + g) ^ (idx & 15)) << 2)]) = make_float4(S[2 * g].x, S[2 * g].y, S[2 * g + 1].x, S[2 * g + 1].y);
+  };
+  // S[idx][h0..] <- S * w - sa_idx * b + v_idx * kt
+  auto update = [&](const float (*buf)[kH], const float* bk) {
+    const float sa = buf[kVecs + 1][idx], vi = buf[4][idx];
+    const float2 nsa2 = make_float2(-sa, -sa), vi2 = make_float2(vi, vi);
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      const float4 w4 = *reinterpret_cast<const float4*>(&buf[0][h0 + 4 * g]);
+      const float4 b4 = *reinterpret_cast<const float4*>(&bk[h0 + 4 * g]);
+      const float4 kt4 = *reinterpret_cast<const float4*>(&buf[3][h0 + 4 * g]);
+      const float2 s0 = __ffma2_rn(nsa2, make_float2(b4.x, b4.y), __fmul2_rn(S[2 * g], make_float2(w4.x, w4.y)));
+      const float2 s1 = __ffma2_rn(nsa2, make_float2(b4.z, b4.w), __fmul2_rn(S[2 * g + 1], make_float2(w4.z, w4.w)));
+      S[2 * g] = __ffma2_rn(vi2, make_float2(kt4.x, kt4.y), s0);
+      S[2 * g + 1] = __ffma2_rn(vi2, make_float2(kt4.z, kt4.w), s1);
+    }
   };
 
+  // the column sums of the timestep before this one in the walk: their halves are complete once a barrier has passed
+  int pend_buf = -1;
+  size_t pend_out = 0;
+  float pend_kap = 0.f, pend_a = 0.f;
+  auto finish_pending = [&]() {
+    if (pend_buf >= 0 && !row_thread && half == 0) {
+      const float (*c0)[kH] = sm.col_part[pend_buf][0];
+      const float (*c1)[kH] = sm.col_part[pend_buf][1];
+      const float db = -(c0[2][idx] + c1[2][idx]);
+      p.din[5][pend_out] = c0[0][idx] + c1[0][idx];
+      p.din[3][pend_out] = c0[1][idx] + c1[1][idx];
+      p.din[0][pend_out] = c0[3][idx] + c1[3][idx];
+      p.din[1][pend_out] = db * pend_kap;
+      p.din[2][pend_out] = (c0[4][idx] + c1[4][idx]) + db * pend_a;
+    }
+    pend_buf = -1;
+  };
+
+  int buf3 = 0;                   // rotates over the three col_part buffers, one per timestep
   // timesteps hi-1 .. lo of the chunk at t0 backwards; the state before local timestep s is in slot[s - lo]
-  // (S below is the column threads' copy of column idx of S_{t-1})
-  auto run_backwards = [&](const float (*V)[kVecs + 1][kH], int t0, int lo, int hi) {
+  auto run_backwards = [&](const float (*V)[kBwdVecs][kH], int t0, int lo, int hi) {
     for (int s = hi - 1; s >= lo; --s) {
+      const int par = s & 1;      // chunks start at multiples of 8: the parity of the timestep
       const size_t out = head_base + (size_t)(t0 + s) * C + idx;
       const float* w = V[s][0]; const float* a = V[s][1]; const float* kap = V[s][2];
       const float* kt = V[s][3]; const float* v = V[s][4]; const float* r = V[s][5]; const float* dy = V[s][6];
+      const float* sa = V[s][7];
       const float* bk = sm.bk[s];
-      float db = 0.0f;
       if (row_thread) {
         const float dyi = dy[idx];
         const float2 dy2 = make_float2(dyi, dyi);
         float2 dv0 = make_float2(0.f, 0.f), dv1 = dv0, ds0 = dv0, ds1 = dv0;
 #pragma unroll
-        for (int g = 0; g < 16; ++g) {
-          const float4 r4 = *reinterpret_cast<const float4*>(&r[4 * g]);
-          const float4 kt4 = *reinterpret_cast<const float4*>(&kt[4 * g]);
-          const float4 b4 = *reinterpret_cast<const float4*>(&bk[4 * g]);
+        for (int g = 0; g < 8; ++g) {
+          const float4 r4 = *reinterpret_cast<const float4*>(&r[h0 + 4 * g]);
+          const float4 kt4 = *reinterpret_cast<const float4*>(&kt[h0 + 4 * g]);
+          const float4 b4 = *reinterpret_cast<const float4*>(&bk[h0 + 4 * g]);
           const float2 g0 = __ffma2_rn(dy2, make_float2(r4.x, r4.y), dS[2 * g]);
           const float2 g1 = __ffma2_rn(dy2, make_float2(r4.z, r4.w), dS[2 * g + 1]);
           dS[2 * g] = g0; dS[2 * g + 1] = g1;
           dv0 = __ffma2_rn(g0, make_float2(kt4.x, kt4.y), dv0); dv1 = __ffma2_rn(g1, make_float2(kt4.z, kt4.w), dv1);
           ds0 = __ffma2_rn(g0, make_float2(b4.x, b4.y), ds0); ds1 = __ffma2_rn(g1, make_float2(b4.z, b4.w), ds1);
         }
-        const float dsa = -sum4(ds0, ds1);
-        sm.dsa[s & 1][idx] = dsa;
-        p.din[4][out] = sum4(dv0, dv1);
-        const float2 dsa2 = make_float2(dsa, dsa);
-#pragma unroll
-        for (int g = 0; g < 16; ++g) {
-          const float4 w4 = *reinterpret_cast<const float4*>(&w[4 * g]);
-          const float4 k4 = *reinterpret_cast<const float4*>(&kap[4 * g]);
-          dS[2 * g] = __ffma2_rn(dsa2, make_float2(k4.x, k4.y), __fmul2_rn(dS[2 * g], make_float2(w4.x, w4.y)));
-          dS[2 * g + 1] = __ffma2_rn(dsa2, make_float2(k4.z, k4.w), __fmul2_rn(dS[2 * g + 1], make_float2(w4.z, w4.w)));
-        }
+        sm.ds_part[par][half][idx] = sum4(ds0, ds1);
+        sm.dv_part[par][half][idx] = sum4(dv0, dv1);
       } else {
         const float* slot = sm.slot[s - lo];
 #pragma unroll
-        for (int e = 0; e < 32; ++e)
-          S[e] = make_float2(slot[(2 * e) * kH + joff[(2 * e) & 15]], slot[(2 * e + 1) * kH + joff[(2 * e + 1) & 15]]);
-        const float wj = w[idx], kapj = kap[idx], ktj = kt[idx], rj = r[idx], bj = bk[idx];
+        for (int e = 0; e < 16; ++e)
+          S[e] = make_float2(slot[(h0 + 2 * e) * kH + joff[(2 * e) & 15]], slot[(h0 + 2 * e + 1) * kH + joff[(2 * e + 1) & 15]]);
+        const float wj = w[idx], ktj = kt[idx], rj = r[idx], bj = bk[idx];
         const float2 wj2 = make_float2(wj, wj), nbj2 = make_float2(-bj, -bj), ktj2 = make_float2(ktj, ktj), rj2 = make_float2(rj, rj);
         float2 dr0 = make_float2(0.f, 0.f), dr1 = dr0, dkt0 = dr0, dkt1 = dr0, db0 = dr0, db1 = dr0, dw0 = dr0, dw1 = dr0;
 #pragma unroll
-        for (int g = 0; g < 16; ++g) {
-          const float4 sa4 = *reinterpret_cast<const float4*>(&sm.sa[s][4 * g]);
-          const float4 v4 = *reinterpret_cast<const float4*>(&v[4 * g]);
-          const float4 dy4 = *reinterpret_cast<const float4*>(&dy[4 * g]);
+        for (int g = 0; g < 8; ++g) {
+          const float4 sa4 = *reinterpret_cast<const float4*>(&sa[h0 + 4 * g]);
+          const float4 v4 = *reinterpret_cast<const float4*>(&v[h0 + 4 * g]);
+          const float4 dy4 = *reinterpret_cast<const float4*>(&dy[h0 + 4 * g]);
           const float2 sa_a = make_float2(sa4.x, sa4.y), sa_b = make_float2(sa4.z, sa4.w);
           const float2 v_a = make_float2(v4.x, v4.y), v_b = make_float2(v4.z, v4.w);
           const float2 dy_a = make_float2(dy4.x, dy4.y), dy_b = make_float2(dy4.z, dy4.w);
@@ -336,27 +348,43 @@ wkv7_backward_kernel(const __grid_constant__ WkvBwdParams p) {
           db0 = __ffma2_rn(g_a, sa_a, db0); db1 = __ffma2_rn(g_b, sa_b, db1);
           dw0 = __ffma2_rn(g_a, S[2 * g], dw0); dw1 = __ffma2_rn(g_b, S[2 * g + 1], dw1);
         }
-        db = -sum4(db0, db1);
-        p.din[5][out] = sum4(dr0, dr1);
-        p.din[3][out] = sum4(dkt0, dkt1);
-        p.din[0][out] = sum4(dw0, dw1);
-        p.din[1][out] = db * kapj;
+        float (*cp)[kH] = sm.col_part[buf3][half];
+        cp[0][idx] = sum4(dr0, dr1);
+        cp[1][idx] = sum4(dkt0, dkt1);
+        cp[2][idx] = sum4(db0, db1);
+        cp[3][idx] = sum4(dw0, dw1);
       }
-      __syncthreads();            // dsa of this timestep is published (the row threads go on to the timestep before)
-      if (!row_thread) {
-        const float wj = w[idx], aj = a[idx], kapj = kap[idx];
+      __syncthreads();            // the halves of this timestep's dv and -dsa, and all of the previous timestep's column sums, are published
+      finish_pending();
+      if (row_thread) {
+        const float dsa = -(sm.ds_part[par][0][idx] + sm.ds_part[par][1][idx]);
+        if (half == 0) p.din[4][out] = sm.dv_part[par][0][idx] + sm.dv_part[par][1][idx];
+        const float2 dsa2 = make_float2(dsa, dsa);
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const float4 w4 = *reinterpret_cast<const float4*>(&w[h0 + 4 * g]);
+          const float4 k4 = *reinterpret_cast<const float4*>(&kap[h0 + 4 * g]);
+          dS[2 * g] = __ffma2_rn(dsa2, make_float2(k4.x, k4.y), __fmul2_rn(dS[2 * g], make_float2(w4.x, w4.y)));
+          dS[2 * g + 1] = __ffma2_rn(dsa2, make_float2(k4.z, k4.w), __fmul2_rn(dS[2 * g + 1], make_float2(w4.z, w4.w)));
+        }
+      } else {
+        const float wj = w[idx], kapj = kap[idx];
         const float2 wj2 = make_float2(wj, wj), kapj2 = make_float2(kapj, kapj);
         float2 dk0 = make_float2(0.f, 0.f), dk1 = dk0;
 #pragma unroll
-        for (int g = 0; g < 16; ++g) {
-          const float4 d4 = *reinterpret_cast<const float4*>(&sm.dsa[s & 1][4 * g]);
-          const float2 d_a = make_float2(d4.x, d4.y), d_b = make_float2(d4.z, d4.w);
+        for (int g = 0; g < 8; ++g) {
+          const float4 p0 = *reinterpret_cast<const float4*>(&sm.ds_part[par][0][h0 + 4 * g]);
+          const float4 p1 = *reinterpret_cast<const float4*>(&sm.ds_part[par][1][h0 + 4 * g]);
+          const float2 d_a = make_float2(-(p0.x + p1.x), -(p0.y + p1.y)), d_b = make_float2(-(p0.z + p1.z), -(p0.w + p1.w));
           dk0 = __ffma2_rn(S[2 * g], d_a, dk0); dk1 = __ffma2_rn(S[2 * g + 1], d_b, dk1);
           dS[2 * g] = __ffma2_rn(d_a, kapj2, __fmul2_rn(dS[2 * g], wj2));
           dS[2 * g + 1] = __ffma2_rn(d_b, kapj2, __fmul2_rn(dS[2 * g + 1], wj2));
         }
-        p.din[2][out] = sum4(dk0, dk1) + db * aj;
+        sm.col_part[buf3][half][4][idx] = sum4(dk0, dk1);
+        pend_kap = kapj; pend_a = a[idx];
       }
+      pend_buf = buf3; pend_out = out;
+      buf3 = buf3 == 2 ? 0 : buf3 + 1;
     }
   };
 
@@ -365,19 +393,18 @@ wkv7_backward_kernel(const __grid_constant__ WkvBwdParams p) {
   for (int ck = n_ck - 1; ck >= 0; --ck) {
     const int t0 = ck * kCk, steps = min(kCk, p.T - t0);
     const int lo = steps > kSub ? kSub : 0;      // the chunk runs as [lo, steps) and then, if lo > 0, [0, lo)
-    __syncthreads();              // everyone is done with the chunk after this one: its vectors, sa, bk and slots
+    __syncthreads();              // everyone is done with the chunk after this one: its vectors, bk and slots
+    finish_pending();             // (reads col_part only)
     issue_vec(ck - 1);            // into the buffer that chunk used
     cp_async_wait<1>();           // this thread's copies of chunk ck have landed
     __syncthreads();              // ... and everyone's
-    const float (*V)[kVecs + 1][kH] = sm.vec[ck & 1];
-    for (int e = tid; e < steps * kH; e += 2 * kH) sm.bk[e / kH][e % kH] = V[e / kH][1][e % kH] * V[e / kH][2][e % kH];
+    const float (*V)[kBwdVecs][kH] = sm.vec[ck & 1];
+    for (int e = tid; e < steps * kH; e += kBwdThreads) sm.bk[e / kH][e % kH] = V[e / kH][1][e % kH] * V[e / kH][2][e % kH];
     __syncthreads();
-    if (row_thread) {             // pass 1: every sa of the chunk, the states before timesteps lo .. steps-1
+    if (row_thread) {             // the states before timesteps lo .. steps-1
       for (int s = 0; s < steps; ++s) {
-        if (s >= lo) slot_store_row(sm.slot[s - lo], idx, S);
-        const float sa = wkv_sa(S, V[s][2]);
-        sm.sa[s][idx] = sa;
-        if (s + 1 < steps) wkv_update(S, V[s], sm.bk[s], sa, V[s][4][idx]);
+        if (s >= lo) store_slot(sm.slot[s - lo]);
+        if (s + 1 < steps) update(V[s], sm.bk[s]);
       }
       if (lo > 0) load_ckpt(ck); else if (ck > 0) load_ckpt(ck - 1);
     }
@@ -385,10 +412,11 @@ wkv7_backward_kernel(const __grid_constant__ WkvBwdParams p) {
     run_backwards(V, t0, lo, steps);
     if (lo > 0) {
       __syncthreads();            // the column threads are done with the slots
-      if (row_thread) {           // pass 2: the states before timesteps 0 .. lo-1, from the checkpoint and the kept sa
+      finish_pending();
+      if (row_thread) {           // the states before timesteps 0 .. lo-1
         for (int s = 0; s < lo; ++s) {
-          slot_store_row(sm.slot[s], idx, S);
-          if (s + 1 < lo) wkv_update(S, V[s], sm.bk[s], sm.sa[s][idx], V[s][4][idx]);
+          store_slot(sm.slot[s]);
+          if (s + 1 < lo) update(V[s], sm.bk[s]);
         }
         if (ck > 0) load_ckpt(ck - 1);
       }
@@ -397,12 +425,12 @@ wkv7_backward_kernel(const __grid_constant__ WkvBwdParams p) {
     }
   }
   cp_async_wait<0>();
-  if (p.dstate_in) {
-    if (row_thread) {
+  __syncthreads();
+  finish_pending();
+  if (p.dstate_in && row_thread) {
 #pragma unroll
-      for (int g = 0; g < 16; ++g)
-        reinterpret_cast<float4*>(p.dstate_in + (head * kH + idx) * kH)[g] = make_float4(dS[2 * g].x, dS[2 * g].y, dS[2 * g + 1].x, dS[2 * g + 1].y);
-    }
+    for (int g = 0; g < 8; ++g)
+      reinterpret_cast<float4*>(p.dstate_in + (head * kH + idx) * kH + h0)[g] = make_float4(dS[2 * g].x, dS[2 * g].y, dS[2 * g + 1].x, dS[2 * g + 1].y);
   }
 }
 
@@ -414,16 +442,16 @@ using namespace pb;
 extern "C" int pb_wkv7_forward(const float* decay, const float* iclr, const float* removal_k, const float* replacement_k,
                                const float* v, const float* r, const float* state_in,
                                int64_t batch, int64_t steps, int64_t heads, int head_dim,
-                               float* y, float* state_out, float* checkpoints, void* stream) {
+                               float* y, float* state_out, float* checkpoints, float* sa, void* stream) {
   if (!decay || !iclr || !removal_k || !replacement_k || !v || !r || !y)
     return fail(PB_ERR_NULL_POINTER, "pb_wkv7_forward: the six inputs and y must be non-null");
   if (head_dim != kH) return fail(PB_ERR_UNSUPPORTED, "pb_wkv7_forward: head size %d (this kernel is built for %d)", head_dim, kH);
   if (batch <= 0 || steps <= 0 || heads <= 0 || batch * heads > 0x7fffffffll || steps > 0x7fffffffll)
     return fail(PB_ERR_BAD_SHAPE, "pb_wkv7_forward: batch=%lld steps=%lld heads=%lld", (long long)batch, (long long)steps, (long long)heads);
-  const void* ptrs[] = {decay, iclr, removal_k, replacement_k, v, r, state_in, state_out, checkpoints};
+  const void* ptrs[] = {decay, iclr, removal_k, replacement_k, v, r, state_in, state_out, checkpoints, sa};
   for (const void* ptr : ptrs)
     if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(PB_ERR_MISALIGNED, "pb_wkv7_forward: every array must be 16-byte aligned");
-  WkvParams p{{decay, iclr, removal_k, replacement_k, v, r}, state_in, y, state_out, checkpoints, (int)steps, (int)heads};
+  WkvParams p{{decay, iclr, removal_k, replacement_k, v, r}, state_in, y, state_out, checkpoints, sa, (int)steps, (int)heads};
   wkv7_forward_kernel<<<(unsigned)(batch * heads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   PB_LAUNCH_CHECK("wkv7_forward_kernel");
   return PB_OK;
@@ -435,23 +463,23 @@ extern "C" size_t pb_wkv7_checkpoint_floats(int64_t batch, int64_t steps, int64_
 }
 
 extern "C" int pb_wkv7_backward(const float* decay, const float* iclr, const float* removal_k, const float* replacement_k,
-                                const float* v, const float* r, const float* checkpoints, const float* dy, const float* dstate_out,
+                                const float* v, const float* r, const float* checkpoints, const float* sa, const float* dy, const float* dstate_out,
                                 int64_t batch, int64_t steps, int64_t heads, int head_dim,
                                 float* d_decay, float* d_iclr, float* d_removal_k, float* d_replacement_k, float* d_v, float* d_r,
                                 float* dstate_in, void* stream) {
-  if (!decay || !iclr || !removal_k || !replacement_k || !v || !r || !checkpoints || !dy || !d_decay || !d_iclr || !d_removal_k ||
+  if (!decay || !iclr || !removal_k || !replacement_k || !v || !r || !checkpoints || !sa || !dy || !d_decay || !d_iclr || !d_removal_k ||
       !d_replacement_k || !d_v || !d_r)
-    return fail(PB_ERR_NULL_POINTER, "pb_wkv7_backward: the six inputs, the checkpoints, dy and the six gradients must be non-null");
+    return fail(PB_ERR_NULL_POINTER, "pb_wkv7_backward: the six inputs, the checkpoints, sa, dy and the six gradients must be non-null");
   if (head_dim != kH) return fail(PB_ERR_UNSUPPORTED, "pb_wkv7_backward: head size %d (this kernel is built for %d)", head_dim, kH);
   if (batch <= 0 || steps <= 0 || heads <= 0 || batch * heads > 0x7fffffffll || steps > 0x7fffffffll)
     return fail(PB_ERR_BAD_SHAPE, "pb_wkv7_backward: batch=%lld steps=%lld heads=%lld", (long long)batch, (long long)steps, (long long)heads);
-  const void* ptrs[] = {decay, iclr, removal_k, replacement_k, v, r, checkpoints, dy, dstate_out, dstate_in};
+  const void* ptrs[] = {decay, iclr, removal_k, replacement_k, v, r, checkpoints, sa, dy, dstate_out, dstate_in};
   for (const void* ptr : ptrs)
     if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(PB_ERR_MISALIGNED, "pb_wkv7_backward: every array must be 16-byte aligned");
-  WkvBwdParams p{{decay, iclr, removal_k, replacement_k, v, r}, dy, checkpoints, dstate_out,
+  WkvBwdParams p{{decay, iclr, removal_k, replacement_k, v, r}, dy, sa, checkpoints, dstate_out,
                  {d_decay, d_iclr, d_removal_k, d_replacement_k, d_v, d_r}, dstate_in, (int)steps, (int)heads};
   PB_CUDA_TRY(cudaFuncSetAttribute(wkv7_backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(WkvBwdSmem)));   // per device
-  wkv7_backward_kernel<<<(unsigned)(batch * heads), 2 * kH, sizeof(WkvBwdSmem), static_cast<cudaStream_t>(stream)>>>(p);
+  wkv7_backward_kernel<<<(unsigned)(batch * heads), kBwdThreads, sizeof(WkvBwdSmem), static_cast<cudaStream_t>(stream)>>>(p);
   PB_LAUNCH_CHECK("wkv7_backward_kernel");
   return PB_OK;
 }
