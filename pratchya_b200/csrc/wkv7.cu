@@ -1,5 +1,6 @@
 // WKV-7 state scan of the modified RWKV-7 TimeMix block (sm_100a): the per-timestep recurrence of
-// pratchya/_nnx_impl/_module.py:187-207 as one kernel instead of a scan of T small matmuls.
+// pratchya/_nnx_impl/_module.py:187-207 as one kernel instead of a scan of T small matmuls, and its
+// cotangents (what jax.grad derives from that scan) as a second kernel.
 //
 // Per (batch b, head n) the state S is an H x H fp32 matrix (rows: value channel i, columns: key
 // channel j).  With, at timestep t, w = decay, a = iclr, kap = removal_k, kt = replacement_k, v and r
@@ -10,35 +11,34 @@
 //     y_i   = sum_j S[i][j] * r_j                           (:199)
 // All arithmetic is fp32, as in the reference (its inputs are cast to f32 before the scan).
 //
-// One CTA of 64 threads per (b, n), H = 64: thread i keeps row i of S (64 floats, as 32 float2) in
-// registers for the whole sequence, so both dot products run inside a thread (packed f32x2 FMAs, four
-// independent partial sums) and need no shuffle, and every shared-memory read of an input vector is a
-// 16-byte broadcast (all lanes read the same address: one pass, where distinct 16-byte reads take four).
-// A first form with four threads per row was bound by exactly that shared-memory traffic.  The six
-// input vectors of a timestep (1.5 KB) are brought into a ring of shared-memory buffers by cp.async
-// eight steps ahead, two timesteps per block-wide barrier; a * kap is formed once per step by the
-// block (one element per thread).  The only serial dependence is S.
-// HBM traffic is the algorithmic minimum: every input read once (6 x 4 B per channel and step), y
-// written once (4 B), the state read and written once per sequence.
+// Layout of the work.  One CTA of 128 threads (four warps) per (b, n), H = 64.  Warp q owns rows 16q .. 16q+15 of
+// the state; its 32 lanes form a 4 x 8 grid (ti, tj) and lane (ti, tj) keeps the 4 x 8 tile of rows
+// 16q + 4ti .. +3 and columns 4tj .. +3 and 32 + 4tj .. +3 in registers (as float2 pairs along the columns) for the
+// whole sequence.  A lane therefore reads 8 elements of each input vector per timestep, not 64: the first forms of
+// these kernels kept a whole row (or column) per thread and were bound by the 128 bytes per clock that
+// shared memory returns to the registers of an SM, because every thread loaded every vector in full and a
+// same-address broadcast still delivers 512 bytes per warp and load.  Sums along a row finish with three
+// xor-shuffles across tj; they never leave the warp, so nothing in the recurrence crosses warps.
+// Sums along a column (backward pass only) are reduced across ti by two butterfly shuffle levels and the two
+// warps' parts meet in shared memory; they are outputs, not part of the recurrence.
+// The input vectors of a timestep arrive by cp.async ahead of time.  HBM traffic is the algorithmic minimum:
+// every input read once, every output written once, the state once per sequence, plus what the backward pass
+// needs when one follows (below).
 #include "common.cuh"
 
 namespace pb {
 namespace {
 
 constexpr int kH = 64;            // head size
-constexpr int kPairs = 4;         // ring depth in pairs of timesteps: eight timesteps of input in flight
+constexpr int kR = 4;             // rows of a lane's tile (measured: 4 beats 8 and 2 on batch 8 x 32 heads x 4096 timesteps)
+constexpr int kWarps = 16 / kR;   // a warp owns 4 * kR rows
+constexpr int kThreads = 32 * kWarps;      // per head
+constexpr int kPairs = 4;         // forward ring depth in pairs of timesteps: eight timesteps of input in flight
 constexpr int kVecs = 6;          // decay, iclr, removal_k, replacement_k, v, r
 constexpr int kCk = 8;            // spacing of the state checkpoints the backward pass restarts from
-
-struct WkvParams {
-  const float* in[kVecs];
-  const float* state_in;          // [B, N, H, H] or null (zeros)
-  float* y;                       // [B, T, C]
-  float* state_out;               // [B, N, H, H] or null
-  float* ckpt;                    // [B, N, ceil(T / kCk), H, H] or null: the state before timesteps 0, kCk, 2*kCk, ...
-  float* sa;                      // [B, T, C] or null: sa of every timestep (S before the step, times removal_k), for the backward pass
-  int T, N;                       // timesteps, heads
-};
+constexpr int kSub = 4;           // timesteps whose recomputed states the backward pass keeps at once
+constexpr int kBwdVecs = kVecs + 2;      // the six inputs, dy and sa
+constexpr int kTileQuads = kH * kH / 4;  // float4 per state
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -46,108 +46,205 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// One timestep for row i of S.  `buf` holds the step's decay, iclr, removal_k, replacement_k, v, r; `bk` = iclr * removal_k.
-__device__ __forceinline__ float wkv_step(float2 (&S)[32], const float (*buf)[kH], const float* bk, int i, float& sa_out) {
-  // sa_i = sum_j S[i][j] * kap_j, four partial sums
-  float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    const float4 k4 = *reinterpret_cast<const float4*>(&buf[2][4 * j]);
-    acc[(2 * j) & 3] = __ffma2_rn(S[2 * j], make_float2(k4.x, k4.y), acc[(2 * j) & 3]);
-    acc[(2 * j + 1) & 3] = __ffma2_rn(S[2 * j + 1], make_float2(k4.z, k4.w), acc[(2 * j + 1) & 3]);
+__device__ __forceinline__ float2 dup(float x) { return make_float2(x, x); }
+
+// a lane's eight columns of a shared-memory vector (four at p, four at p + 32) as four float2
+__device__ __forceinline__ void ld8(const float* p, float2 (&out)[4]) {
+  const float4 lo = *reinterpret_cast<const float4*>(p), hi = *reinterpret_cast<const float4*>(p + 32);
+  out[0] = make_float2(lo.x, lo.y); out[1] = make_float2(lo.z, lo.w); out[2] = make_float2(hi.x, hi.y); out[3] = make_float2(hi.z, hi.w);
+}
+// kR consecutive floats
+__device__ __forceinline__ void ldr(const float* p, float (&out)[kR]) {
+  if constexpr (kR == 8) {
+    const float4 lo = *reinterpret_cast<const float4*>(p), hi = *reinterpret_cast<const float4*>(p + 4);
+    out[0] = lo.x; out[1] = lo.y; out[2] = lo.z; out[3] = lo.w; out[4] = hi.x; out[5] = hi.y; out[6] = hi.z; out[7] = hi.w;
+  } else if constexpr (kR == 4) {
+    const float4 lo = *reinterpret_cast<const float4*>(p);
+    out[0] = lo.x; out[1] = lo.y; out[2] = lo.z; out[3] = lo.w;
+  } else {
+    const float2 lo = *reinterpret_cast<const float2*>(p);
+    out[0] = lo.x; out[1] = lo.y;
   }
-  const float sa = ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
-  sa_out = sa;
-  const float vi = buf[4][i];
-  const float2 nsa2 = make_float2(-sa, -sa), vi2 = make_float2(vi, vi);
-  float2 y[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    const float4 w4 = *reinterpret_cast<const float4*>(&buf[0][4 * j]);
-    const float4 b4 = *reinterpret_cast<const float4*>(&bk[4 * j]);
-    const float4 kt4 = *reinterpret_cast<const float4*>(&buf[3][4 * j]);
-    const float4 r4 = *reinterpret_cast<const float4*>(&buf[5][4 * j]);
-    float2 s0 = __ffma2_rn(nsa2, make_float2(b4.x, b4.y), __fmul2_rn(S[2 * j], make_float2(w4.x, w4.y)));
-    float2 s1 = __ffma2_rn(nsa2, make_float2(b4.z, b4.w), __fmul2_rn(S[2 * j + 1], make_float2(w4.z, w4.w)));
-    s0 = __ffma2_rn(vi2, make_float2(kt4.x, kt4.y), s0);
-    s1 = __ffma2_rn(vi2, make_float2(kt4.z, kt4.w), s1);
-    S[2 * j] = s0; S[2 * j + 1] = s1;
-    y[(2 * j) & 3] = __ffma2_rn(s0, make_float2(r4.x, r4.y), y[(2 * j) & 3]);
-    y[(2 * j + 1) & 3] = __ffma2_rn(s1, make_float2(r4.z, r4.w), y[(2 * j + 1) & 3]);
-  }
-  return ((y[0].x + y[0].y) + (y[1].x + y[1].y)) + ((y[2].x + y[2].y) + (y[3].x + y[3].y));
 }
 
-constexpr int kThreads = kH;      // one thread per state row
+// every lane's v[a] becomes the sum over the eight lanes that share ti (lane bits 0..2)
+__device__ __forceinline__ void row_allreduce(float (&v)[kR]) {
+#pragma unroll
+  for (int m = 1; m < 8; m <<= 1) {
+#pragma unroll
+    for (int a = 0; a < kR; ++a) v[a] += __shfl_xor_sync(0xffffffffu, v[a], m);
+  }
+}
+// four column sums over the four lanes that share tj (lane bits 3, 4): lane ti ends up with column ti of the four
+__device__ __forceinline__ float col_reduce_scatter(const float2 (&v)[2], int ti) {
+  bool up = ti & 2;
+  const float2 keep = up ? v[1] : v[0], send = up ? v[0] : v[1];
+  const float2 w2 = make_float2(keep.x + __shfl_xor_sync(0xffffffffu, send.x, 16), keep.y + __shfl_xor_sync(0xffffffffu, send.y, 16));
+  up = ti & 1;
+  return (up ? w2.y : w2.x) + __shfl_xor_sync(0xffffffffu, up ? w2.x : w2.y, 8);
+}
+__device__ __forceinline__ float pick(const float (&v)[kR], int a) {
+  float r = v[0];
+#pragma unroll
+  for (int k = 1; k < kR; ++k) r = a == k ? v[k] : r;
+  return r;
+}
+
+// Where lane (ti, tj) of warp q sits: rows row0 .. row0 + kR - 1, columns col0 .. col0+3 and 32 + col0 .. +3 (so that the
+// eight lanes of a tile row read 128 contiguous bytes of a vector with each 16-byte load: no bank conflicts).
+struct Tile {
+  int tid, ti, tj, row0, col0;
+  __device__ Tile() {
+    tid = threadIdx.x;
+    const int lane = tid & 31;
+    ti = lane >> 3; tj = lane & 7;
+    row0 = 4 * kR * (tid >> 5) + kR * ti; col0 = 4 * tj;
+  }
+};
+
+// the 8 x 8 tile of a row-major H x H matrix in global memory
+__device__ __forceinline__ void load_tile_rowmajor(const float* m, const Tile& tl, float2 (&S)[kR][4]) {
+#pragma unroll
+  for (int a = 0; a < kR; ++a) {
+    const float4 lo = __ldg(reinterpret_cast<const float4*>(m + (tl.row0 + a) * kH + tl.col0));
+    const float4 hi = __ldg(reinterpret_cast<const float4*>(m + (tl.row0 + a) * kH + tl.col0 + 32));
+    S[a][0] = make_float2(lo.x, lo.y); S[a][1] = make_float2(lo.z, lo.w); S[a][2] = make_float2(hi.x, hi.y); S[a][3] = make_float2(hi.z, hi.w);
+  }
+}
+__device__ __forceinline__ void store_tile_rowmajor(float* m, const Tile& tl, const float2 (&S)[kR][4]) {
+#pragma unroll
+  for (int a = 0; a < kR; ++a) {
+    *reinterpret_cast<float4*>(m + (tl.row0 + a) * kH + tl.col0) = make_float4(S[a][0].x, S[a][0].y, S[a][1].x, S[a][1].y);
+    *reinterpret_cast<float4*>(m + (tl.row0 + a) * kH + tl.col0 + 32) = make_float4(S[a][2].x, S[a][2].y, S[a][3].x, S[a][3].y);
+  }
+}
+// The tile in the kernels' own layout, [2 kR quarters][threads] float4: consecutive threads, consecutive 16 bytes
+// (checkpoints in global memory, recomputed states in shared memory).
+template <typename Ptr>
+__device__ __forceinline__ void store_tile_private(Ptr base, const Tile& tl, const float2 (&S)[kR][4]) {
+#pragma unroll
+  for (int a = 0; a < kR; ++a) {
+    base[(2 * a) * kThreads + tl.tid] = make_float4(S[a][0].x, S[a][0].y, S[a][1].x, S[a][1].y);
+    base[(2 * a + 1) * kThreads + tl.tid] = make_float4(S[a][2].x, S[a][2].y, S[a][3].x, S[a][3].y);
+  }
+}
+template <typename Ptr>
+__device__ __forceinline__ void load_tile_private(Ptr base, const Tile& tl, float2 (&S)[kR][4]) {
+#pragma unroll
+  for (int a = 0; a < kR; ++a) {
+    const float4 lo = base[(2 * a) * kThreads + tl.tid], hi = base[(2 * a + 1) * kThreads + tl.tid];
+    S[a][0] = make_float2(lo.x, lo.y); S[a][1] = make_float2(lo.z, lo.w); S[a][2] = make_float2(hi.x, hi.y); S[a][3] = make_float2(hi.z, hi.w);
+  }
+}
+
+// ---- forward ---------------------------------------------------------------------------------------------------
+struct WkvParams {
+  const float* in[kVecs];
+  const float* state_in;          // [B, N, H, H] or null (zeros)
+  float* y;                       // [B, T, C]
+  float* state_out;               // [B, N, H, H] or null
+  float4* ckpt;                   // [B, N, ceil(T / kCk)][16][64] float4 or null: the state before timesteps 0, kCk, 2*kCk, ... (tile layout)
+  float* sa;                      // [B, T, C] or null: sa of every timestep, for the backward pass
+  int T, N;                       // timesteps, heads
+};
+
+// One timestep on the lane's tile.  buf: the step's decay, iclr, removal_k, replacement_k, v, r.  Leaves sa and y of the
+// tile's rows in sa[] and yq[] (in every lane of the tile row).
+__device__ __forceinline__ void wkv_step(float2 (&S)[kR][4], const float (*buf)[kH], const Tile& tl, float (&sa)[kR], float (&yq)[kR]) {
+  float2 kap[4], w[4], b[4], kt[4], r[4];
+  float v[kR];
+  ld8(buf[2] + tl.col0, kap);
+  ld8(buf[1] + tl.col0, b);
+  ld8(buf[0] + tl.col0, w);
+  ld8(buf[3] + tl.col0, kt);
+  ld8(buf[5] + tl.col0, r);
+  ldr(buf[4] + tl.row0, v);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) b[k] = __fmul2_rn(b[k], kap[k]);
+#pragma unroll
+  for (int a = 0; a < kR; ++a) {
+    float2 acc = __fmul2_rn(S[a][0], kap[0]);
+#pragma unroll
+    for (int k = 1; k < 4; ++k) acc = __ffma2_rn(S[a][k], kap[k], acc);
+    sa[a] = acc.x + acc.y;
+  }
+  row_allreduce(sa);
+#pragma unroll
+  for (int a = 0; a < kR; ++a) {
+    const float2 nsa2 = dup(-sa[a]), v2 = dup(v[a]);
+    float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      S[a][k] = __ffma2_rn(v2, kt[k], __ffma2_rn(nsa2, b[k], __fmul2_rn(S[a][k], w[k])));
+      acc = __ffma2_rn(S[a][k], r[k], acc);
+    }
+    yq[a] = acc.x + acc.y;
+  }
+  row_allreduce(yq);
+}
 
 __global__ void __launch_bounds__(kThreads)
 wkv7_forward_kernel(const __grid_constant__ WkvParams p) {
   __shared__ __align__(16) float ring[kPairs][2][kVecs][kH];      // [pair slot][step of the pair][vector][channel]
-  __shared__ __align__(16) float bk[2][kH];                       // iclr * removal_k of the two steps of the current pair
+  const Tile tl;
   const int n = blockIdx.x % p.N, b = blockIdx.x / p.N;
   const int C = p.N * kH;
-  const int i = threadIdx.x;
   const size_t head_base = (size_t)b * p.T * C + (size_t)n * kH;      // element (b, t = 0, channel n*H)
+  const size_t head = (size_t)b * p.N + n;
+  const int n_ck = (p.T + kCk - 1) / kCk;
 
-  // a pair of timesteps is 2 x 6 vectors x 16 chunks of 16 bytes = 192 chunks: three per thread
+  // a pair of timesteps is 2 x 6 vectors x 16 chunks of 16 bytes = 192 chunks
   auto issue = [&](int pair) {
+    constexpr int kChunks = 2 * kVecs * (kH / 4);
 #pragma unroll
-    for (int c = 0; c < 3; ++c) {
-      const int id = c * kThreads + i;                         // 0 .. 191
+    for (int c = 0; c < (kChunks + kThreads - 1) / kThreads; ++c) {
+      const int id = c * kThreads + tl.tid;                    // 0 .. 191
       const int step = id / (kVecs * (kH / 4)), vec = (id / (kH / 4)) % kVecs, chunk = id % (kH / 4);
       const int t = 2 * pair + step;
-      if (t < p.T)
+      if (id < kChunks && t < p.T)
         cp_async16((uint32_t)__cvta_generic_to_shared(&ring[pair % kPairs][step][vec][chunk * 4]),
                    p.in[vec] + head_base + (size_t)t * C + chunk * 4);
     }
     cp_async_commit();            // every thread commits a (possibly empty) group per pair: the counts stay aligned
   };
 
-  float2 S[32];                   // row i of this head's state
-  const size_t srow = (((size_t)b * p.N + n) * kH + i) * kH;
+  float2 S[kR][4];
   if (p.state_in) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.state_in + srow) + j);
-      S[2 * j] = make_float2(s4.x, s4.y); S[2 * j + 1] = make_float2(s4.z, s4.w);
-    }
+    load_tile_rowmajor(p.state_in + head * kH * kH, tl, S);
   } else {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) S[j] = make_float2(0.0f, 0.0f);
+    for (int a = 0; a < kR; ++a)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) S[a][k] = make_float2(0.0f, 0.0f);
   }
 
   const int n_pairs = (p.T + 1) >> 1;
   for (int pr = 0; pr < kPairs - 1; ++pr) issue(pr);
-  float* yp = p.y + head_base + i;
+  const bool writer = tl.tj < kR;                                  // lane (ti, tj < kR) writes row row0 + tj of y and sa
+  float* yp = p.y + head_base + tl.row0 + tl.tj;
+  float* sap = p.sa ? p.sa + head_base + tl.row0 + tl.tj : nullptr;
   for (int pr = 0; pr < n_pairs; ++pr) {
     cp_async_wait<kPairs - 2>();      // this thread's copies for this pair have landed
-    __syncthreads();                  // ... and everyone's; every thread is also done with the previous pair (ring slot and bk)
+    __syncthreads();                  // ... and everyone's; every thread is also done with the previous pair's ring slot
     issue(pr + kPairs - 1);           // into the slot the previous pair used
-    const float (*step0)[kH] = ring[pr % kPairs][0];
-    const float (*step1)[kH] = ring[pr % kPairs][1];
-    bk[0][i] = step0[1][i] * step0[2][i];
-    bk[1][i] = step1[1][i] * step1[2][i];
-    __syncthreads();
     const int t = 2 * pr;
-    if (p.ckpt && (t & (kCk - 1)) == 0) {
-      float4* dst = reinterpret_cast<float4*>(p.ckpt + ((((size_t)b * p.N + n) * ((p.T + kCk - 1) / kCk) + t / kCk) * kH + i) * kH);
-#pragma unroll
-      for (int j = 0; j < 16; ++j) dst[j] = make_float4(S[2 * j].x, S[2 * j].y, S[2 * j + 1].x, S[2 * j + 1].y);
+    if (p.ckpt && (t & (kCk - 1)) == 0) store_tile_private(p.ckpt + (head * n_ck + t / kCk) * kTileQuads, tl, S);
+    float sa[kR], yq[kR];
+    wkv_step(S, ring[pr % kPairs][0], tl, sa, yq);
+    if (writer) {
+      yp[(size_t)t * C] = pick(yq, tl.tj);
+      if (sap) sap[(size_t)t * C] = pick(sa, tl.tj);
     }
-    float sa0, sa1;
-    yp[(size_t)t * C] = wkv_step(S, step0, bk[0], i, sa0);
-    if (p.sa) p.sa[head_base + (size_t)t * C + i] = sa0;
     if (t + 1 < p.T) {
-      yp[(size_t)(t + 1) * C] = wkv_step(S, step1, bk[1], i, sa1);
-      if (p.sa) p.sa[head_base + (size_t)(t + 1) * C + i] = sa1;
+      wkv_step(S, ring[pr % kPairs][1], tl, sa, yq);
+      if (writer) {
+        yp[(size_t)(t + 1) * C] = pick(yq, tl.tj);
+        if (sap) sap[(size_t)(t + 1) * C] = pick(sa, tl.tj);
+      }
     }
   }
   cp_async_wait<0>();
-  if (p.state_out) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j)
-      reinterpret_cast<float4*>(p.state_out + srow)[j] = make_float4(S[2 * j].x, S[2 * j].y, S[2 * j + 1].x, S[2 * j + 1].y);
-  }
+  if (p.state_out) store_tile_rowmajor(p.state_out + head * kH * kH, tl, S);
 }
 
 // ---- backward of the scan ------------------------------------------------------------------------------------
@@ -155,32 +252,24 @@ wkv7_forward_kernel(const __grid_constant__ WkvParams p) {
 //     dr_t   = S_t^T dy_t                    dv_t  = G_t kt_t                 dkt_t = G_t^T v_t
 //     dsa_t  = -G_t b_t   (b = a * kap)      db_t  = -G_t^T sa_t              dw_t  = sum_i G_t[i][:] * S_{t-1}[i][:]
 //     dkap_t = S_{t-1}^T dsa_t + db_t * a_t  da_t  = db_t * kap_t             dS_{t-1} = G_t diag(w_t) + dsa_t kap_t^T
-// Half of these are sums along a row of the state, half along a column, so a CTA keeps dS twice: 128 row
-// threads (row i, one half of its columns each) and 128 column threads (column j, one half of its rows each).
-// The halves of a row or column sit in different warps, so a warp still reads every input vector at one
-// address per instruction (a broadcast), and the two partial sums meet in shared memory.
+// Each lane keeps its tile of dS and, within a timestep, of S_{t-1}.  dsa is a row sum (needed at once: three
+// xor-shuffles); dv a row sum that is only written out; the other five are column sums that are only written out:
+// two shuffle levels inside the warp, then the warps' parts go to shared memory and are added after the
+// timestep's one block barrier (two buffers, by the parity of t).
 //
-// S_{t-1} is needed for every t and is not stored by the forward pass, which writes a checkpoint every
-// kCk = 8 timesteps and sa_t = S_{t-1} kap_t (64 floats) for every t.  With sa_t known the recurrence is
-// element-wise, so per chunk the row threads recompute the states from the checkpoint without any sum: first
-// the states before the chunk's last four timesteps into four shared-memory slots, those four timesteps run
-// backwards, then the states before the first four into the same slots, and those run backwards.  A slot is
-// H x H floats with the 16-byte groups of row i stored at group ^ (i & 15): the row threads' 16-byte row stores
-// and the column threads' 4-byte column loads are both free of bank conflicts.
-// One block barrier per timestep: before it the row threads publish the halves of dv and of -dsa, after it
-// everyone forms dsa.  The column threads' five sums are published as halves too and added one timestep later
-// (three buffers in rotation).  The chunk's eight vectors per timestep arrive by cp.async one chunk ahead, and
-// the checkpoint the next recomputation starts from is loaded into the row threads' registers before the
-// timesteps that precede it.
-constexpr int kSub = 4;                  // timesteps whose states are kept at once
-constexpr int kBwdThreads = 4 * kH;
-constexpr int kBwdVecs = kVecs + 2;      // the six inputs, dy and sa
-
+// S_{t-1} is needed for every t and is not stored by the forward pass; inverting the recurrence would divide by the
+// decay, which the reference lets go to zero.  The forward pass writes a checkpoint every kCk = 8 timesteps and
+// sa_t for every t; with sa_t known the recurrence is element-wise, so every lane recomputes its own tile of the
+// states from the checkpoint with no sums and no exchange: first the states before the chunk's last four
+// timesteps into four shared-memory slots (the lane's private 64 floats of each), those four timesteps run
+// backwards, then the states before the first four into the same slots, and those run backwards.  The chunk's
+// eight vectors per timestep arrive by cp.async one chunk ahead, and the checkpoint that the next recomputation
+// starts from by cp.async into the first slot that the timesteps before it have emptied.
 struct WkvBwdParams {
   const float* in[kVecs];
   const float* dy;                // [B, T, C]
   const float* sa;                // [B, T, C]: S_{t-1} kap_t, from the forward pass
-  const float* ckpt;              // [B, N, ceil(T / kCk), H, H]
+  const float4* ckpt;             // as the forward pass wrote it
   const float* dstate_out;        // [B, N, H, H] or null: gradient with respect to the final state
   float* din[kVecs];              // gradients of the six inputs, [B, T, C] each
   float* dstate_in;               // [B, N, H, H] or null: gradient with respect to the initial state
@@ -188,59 +277,38 @@ struct WkvBwdParams {
 };
 
 struct WkvBwdSmem {
-  float slot[kSub][kH * kH];                // recomputed states, swizzled
+  float4 slot[kSub][kTileQuads];            // recomputed states, every lane its own tile
   float vec[2][kCk][kBwdVecs][kH];          // the chunk's vectors, two chunks
-  float bk[kCk][kH];                        // iclr * removal_k
-  float ds_part[2][2][kH];                  // [parity of t][column half][row]: halves of sum_j G b
-  float dv_part[2][2][kH];                  // ... of sum_j G kt
-  float col_part[3][2][5][kH];              // [t mod 3][row half][dr, dkt, sum G sa, dw, S^T dsa][column]
+  float col_part[2][kWarps][5][kH];         // [parity of t][warp][dr, dkt, sum G sa, dw, S^T dsa][column]
 };
 
-__device__ __forceinline__ float sum4(const float2 a, const float2 b) { return (a.x + a.y) + (b.x + b.y); }
-
-__global__ void __launch_bounds__(kBwdThreads, 2)
+__global__ void __launch_bounds__(kThreads)
 wkv7_backward_kernel(const __grid_constant__ WkvBwdParams p) {
   extern __shared__ __align__(16) unsigned char wkv_bwd_smem[];
   WkvBwdSmem& sm = *reinterpret_cast<WkvBwdSmem*>(wkv_bwd_smem);
+  const Tile tl;
+  const int warp = tl.tid >> 5;
   const int n = blockIdx.x % p.N, b = blockIdx.x / p.N;
   const int C = p.N * kH;
-  const int tid = threadIdx.x;
-  const bool row_thread = tid < 2 * kH;
-  const int half = (tid >> 6) & 1;             // row threads: which 32 columns; column threads: which 32 rows
-  const int idx = tid & (kH - 1);              // the row i, or the column j
-  const int h0 = 32 * half;
   const size_t head_base = (size_t)b * p.T * C + (size_t)n * kH;
   const size_t head = (size_t)b * p.N + n;
   const int n_ck = (p.T + kCk - 1) / kCk;
 
-  // element (h0 + e, idx) of a slot, for a column thread: (h0 + e) * kH + joff[e & 15]
-  int joff[16];
-#pragma unroll
-  for (int c = 0; c < 16; ++c) joff[c] = ((((idx >> 2) ^ c) << 2) | (idx & 3));
-
-  float2 dS[16];                  // row threads: dS[idx][h0 + 2e, +1]; column threads: dS[h0 + 2e, +1][idx]
+  float2 dS[kR][4];
   if (p.dstate_out) {
-    if (row_thread) {
-#pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        const float4 q = __ldg(reinterpret_cast<const float4*>(p.dstate_out + (head * kH + idx) * kH + h0) + g);
-        dS[2 * g] = make_float2(q.x, q.y); dS[2 * g + 1] = make_float2(q.z, q.w);
-      }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 16; ++e)
-        dS[e] = make_float2(__ldg(p.dstate_out + (head * kH + h0 + 2 * e) * kH + idx), __ldg(p.dstate_out + (head * kH + h0 + 2 * e + 1) * kH + idx));
-    }
+    load_tile_rowmajor(p.dstate_out + head * kH * kH, tl, dS);
   } else {
 #pragma unroll
-    for (int e = 0; e < 16; ++e) dS[e] = make_float2(0.0f, 0.0f);
+    for (int a = 0; a < kR; ++a)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) dS[a][k] = make_float2(0.0f, 0.0f);
   }
 
   // the eight vectors of every timestep of chunk ck -> vec[ck & 1]; every thread commits one group per call
   auto issue_vec = [&](int ck) {
     if (ck >= 0) {
       const int t0 = ck * kCk, steps = min(kCk, p.T - t0);
-      for (int e = tid; e < steps * kBwdVecs * (kH / 4); e += kBwdThreads) {
+      for (int e = tl.tid; e < steps * kBwdVecs * (kH / 4); e += kThreads) {
         const int s = e / (kBwdVecs * (kH / 4)), rem = e % (kBwdVecs * (kH / 4)), v = rem / (kH / 4), c4 = rem % (kH / 4);
         const float* src = (v < kVecs ? p.in[v] : (v == kVecs ? p.dy : p.sa)) + head_base + (size_t)(t0 + s) * C + c4 * 4;
         cp_async16((uint32_t)__cvta_generic_to_shared(&sm.vec[ck & 1][s][v][c4 * 4]), src);
@@ -249,189 +317,172 @@ wkv7_backward_kernel(const __grid_constant__ WkvBwdParams p) {
     cp_async_commit();
   };
 
-  // row threads: their half of the row of the state being recomputed (in flight from the checkpoint while
-  // timesteps run backwards); column threads: their half of column idx of S_{t-1} within a timestep.
-  float2 S[16];
-  auto load_ckpt = [&](int ck) {
-    const float4* c4p = reinterpret_cast<const float4*>(p.ckpt + ((head * n_ck + ck) * kH + idx) * kH + h0);
+  float2 S[kR][4];                // the tile being recomputed, or S_{t-1} within a timestep
+  // The checkpoint a recomputation starts from is copied (this thread's 16 quarters of it) into a slot the walk has
+  // just emptied, well before it is needed; the thread that copies is the thread that reads, so its own
+  // cp.async wait is all the ordering this needs.
+  auto prefetch_ckpt = [&](int ck, int slot) {
+    if (ck >= 0) {
+      const float4* src = p.ckpt + (head * n_ck + ck) * kTileQuads;
 #pragma unroll
-    for (int g = 0; g < 8; ++g) { const float4 q = __ldg(c4p + g); S[2 * g] = make_float2(q.x, q.y); S[2 * g + 1] = make_float2(q.z, q.w); }
+      for (int q = 0; q < 2 * kR; ++q)
+        cp_async16((uint32_t)__cvta_generic_to_shared(&sm.slot[slot][q * kThreads + tl.tid]), src + q * kThreads + tl.tid);
+    }
+    cp_async_commit();
   };
-  auto store_slot = [&](float* slot) {
+  // S <- S * w - sa b^T + v kt^T on the tile
+  auto update = [&](const float (*buf)[kH]) {
+    float2 kap[4], w[4], bb[4], kt[4];
+    float v[kR], sa[kR];
+    ld8(buf[2] + tl.col0, kap); ld8(buf[1] + tl.col0, bb); ld8(buf[0] + tl.col0, w); ld8(buf[3] + tl.col0, kt);
+    ldr(buf[4] + tl.row0, v); ldr(buf[kVecs + 1] + tl.row0, sa);
 #pragma unroll
-    for (int g = 0; g < 8; ++g)
-      *reinterpret_cast<float4*>(&slot[idx * kH + (((8 * half + g) ^ (idx & 15)) << 2)]) = make_float4(S[2 * g].x, S[2 * g].y, S[2 * g + 1].x, S[2 * g + 1].y);
-  };
-  // S[idx][h0..] <- S * w - sa_idx * b + v_idx * kt
-  auto update = [&](const float (*buf)[kH], const float* bk) {
-    const float sa = buf[kVecs + 1][idx], vi = buf[4][idx];
-    const float2 nsa2 = make_float2(-sa, -sa), vi2 = make_float2(vi, vi);
+    for (int k = 0; k < 4; ++k) bb[k] = __fmul2_rn(bb[k], kap[k]);
 #pragma unroll
-    for (int g = 0; g < 8; ++g) {
-      const float4 w4 = *reinterpret_cast<const float4*>(&buf[0][h0 + 4 * g]);
-      const float4 b4 = *reinterpret_cast<const float4*>(&bk[h0 + 4 * g]);
-      const float4 kt4 = *reinterpret_cast<const float4*>(&buf[3][h0 + 4 * g]);
-      const float2 s0 = __ffma2_rn(nsa2, make_float2(b4.x, b4.y), __fmul2_rn(S[2 * g], make_float2(w4.x, w4.y)));
-      const float2 s1 = __ffma2_rn(nsa2, make_float2(b4.z, b4.w), __fmul2_rn(S[2 * g + 1], make_float2(w4.z, w4.w)));
-      S[2 * g] = __ffma2_rn(vi2, make_float2(kt4.x, kt4.y), s0);
-      S[2 * g + 1] = __ffma2_rn(vi2, make_float2(kt4.z, kt4.w), s1);
+    for (int a = 0; a < kR; ++a) {
+      const float2 nsa2 = dup(-sa[a]), v2 = dup(v[a]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) S[a][k] = __ffma2_rn(v2, kt[k], __ffma2_rn(nsa2, bb[k], __fmul2_rn(S[a][k], w[k])));
     }
   };
 
-  // the column sums of the timestep before this one in the walk: their halves are complete once a barrier has passed
-  int pend_buf = -1;
-  size_t pend_out = 0;
-  float pend_kap = 0.f, pend_a = 0.f;
-  auto finish_pending = [&]() {
-    if (pend_buf >= 0 && !row_thread && half == 0) {
-      const float (*c0)[kH] = sm.col_part[pend_buf][0];
-      const float (*c1)[kH] = sm.col_part[pend_buf][1];
-      const float db = -(c0[2][idx] + c1[2][idx]);
-      p.din[5][pend_out] = c0[0][idx] + c1[0][idx];
-      p.din[3][pend_out] = c0[1][idx] + c1[1][idx];
-      p.din[0][pend_out] = c0[3][idx] + c1[3][idx];
-      p.din[1][pend_out] = db * pend_kap;
-      p.din[2][pend_out] = (c0[4][idx] + c1[4][idx]) + db * pend_a;
-    }
-    pend_buf = -1;
-  };
-
-  int buf3 = 0;                   // rotates over the three col_part buffers, one per timestep
-  // timesteps hi-1 .. lo of the chunk at t0 backwards; the state before local timestep s is in slot[s - lo]
-  auto run_backwards = [&](const float (*V)[kBwdVecs][kH], int t0, int lo, int hi) {
+  // Timesteps hi-1 .. lo of the chunk at t0 backwards; the state before local timestep s is in slot (s - lo + shift) & 3.
+  // The slot of the first timestep is free as soon as its tile is in registers: checkpoint `next_ck` goes there.
+  auto run_backwards = [&](const float (*V)[kBwdVecs][kH], int t0, int lo, int hi, int shift, int next_ck) {
     for (int s = hi - 1; s >= lo; --s) {
-      const int par = s & 1;      // chunks start at multiples of 8: the parity of the timestep
-      const size_t out = head_base + (size_t)(t0 + s) * C + idx;
-      const float* w = V[s][0]; const float* a = V[s][1]; const float* kap = V[s][2];
-      const float* kt = V[s][3]; const float* v = V[s][4]; const float* r = V[s][5]; const float* dy = V[s][6];
-      const float* sa = V[s][7];
-      const float* bk = sm.bk[s];
-      if (row_thread) {
-        const float dyi = dy[idx];
-        const float2 dy2 = make_float2(dyi, dyi);
-        float2 dv0 = make_float2(0.f, 0.f), dv1 = dv0, ds0 = dv0, ds1 = dv0;
+      const float (*buf)[kH] = V[s];
+      const int slot = (s - lo + shift) & (kSub - 1);
+      load_tile_private(sm.slot[slot], tl, S);
+      if (s == hi - 1) prefetch_ckpt(next_ck, slot);
+      float dy[kR], v[kR], sa[kR];
+      ldr(buf[kVecs] + tl.row0, dy); ldr(buf[4] + tl.row0, v); ldr(buf[kVecs + 1] + tl.row0, sa);
+      float dvp[kR], dsp[kR];
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 r4 = *reinterpret_cast<const float4*>(&r[h0 + 4 * g]);
-          const float4 kt4 = *reinterpret_cast<const float4*>(&kt[h0 + 4 * g]);
-          const float4 b4 = *reinterpret_cast<const float4*>(&bk[h0 + 4 * g]);
-          const float2 g0 = __ffma2_rn(dy2, make_float2(r4.x, r4.y), dS[2 * g]);
-          const float2 g1 = __ffma2_rn(dy2, make_float2(r4.z, r4.w), dS[2 * g + 1]);
-          dS[2 * g] = g0; dS[2 * g + 1] = g1;
-          dv0 = __ffma2_rn(g0, make_float2(kt4.x, kt4.y), dv0); dv1 = __ffma2_rn(g1, make_float2(kt4.z, kt4.w), dv1);
-          ds0 = __ffma2_rn(g0, make_float2(b4.x, b4.y), ds0); ds1 = __ffma2_rn(g1, make_float2(b4.z, b4.w), ds1);
+      for (int a = 0; a < kR; ++a) { dvp[a] = 0.f; dsp[a] = 0.f; }
+      const int par = (t0 + s) & 1;
+      float (*cp)[kH] = sm.col_part[par][warp];
+      // first pass over the tile, four columns at a time: G, the row sums' parts, four of the five column sums
+#pragma unroll
+      for (int hc = 0; hc < 2; ++hc) {
+        float2 w[2], bb[2], kap[2], kt[2], r[2];
+        {
+          const int c = tl.col0 + 32 * hc;
+          const float4 w4 = *reinterpret_cast<const float4*>(buf[0] + c), a4 = *reinterpret_cast<const float4*>(buf[1] + c);
+          const float4 k4 = *reinterpret_cast<const float4*>(buf[2] + c), kt4 = *reinterpret_cast<const float4*>(buf[3] + c);
+          const float4 r4 = *reinterpret_cast<const float4*>(buf[5] + c);
+          w[0] = make_float2(w4.x, w4.y); w[1] = make_float2(w4.z, w4.w);
+          kap[0] = make_float2(k4.x, k4.y); kap[1] = make_float2(k4.z, k4.w);
+          bb[0] = __fmul2_rn(make_float2(a4.x, a4.y), kap[0]); bb[1] = __fmul2_rn(make_float2(a4.z, a4.w), kap[1]);
+          kt[0] = make_float2(kt4.x, kt4.y); kt[1] = make_float2(kt4.z, kt4.w);
+          r[0] = make_float2(r4.x, r4.y); r[1] = make_float2(r4.z, r4.w);
         }
-        sm.ds_part[par][half][idx] = sum4(ds0, ds1);
-        sm.dv_part[par][half][idx] = sum4(dv0, dv1);
-      } else {
-        const float* slot = sm.slot[s - lo];
+        float2 dr[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)}, dkt[2] = {dr[0], dr[0]}, db[2] = {dr[0], dr[0]}, dw[2] = {dr[0], dr[0]};
 #pragma unroll
-        for (int e = 0; e < 16; ++e)
-          S[e] = make_float2(slot[(h0 + 2 * e) * kH + joff[(2 * e) & 15]], slot[(h0 + 2 * e + 1) * kH + joff[(2 * e + 1) & 15]]);
-        const float wj = w[idx], ktj = kt[idx], rj = r[idx], bj = bk[idx];
-        const float2 wj2 = make_float2(wj, wj), nbj2 = make_float2(-bj, -bj), ktj2 = make_float2(ktj, ktj), rj2 = make_float2(rj, rj);
-        float2 dr0 = make_float2(0.f, 0.f), dr1 = dr0, dkt0 = dr0, dkt1 = dr0, db0 = dr0, db1 = dr0, dw0 = dr0, dw1 = dr0;
+        for (int a = 0; a < kR; ++a) {
+          const float2 dy2 = dup(dy[a]), v2 = dup(v[a]), sa2 = dup(sa[a]), nsa2 = dup(-sa[a]);
+          float2 rdv = make_float2(0.f, 0.f), rds = rdv;
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 sa4 = *reinterpret_cast<const float4*>(&sa[h0 + 4 * g]);
-          const float4 v4 = *reinterpret_cast<const float4*>(&v[h0 + 4 * g]);
-          const float4 dy4 = *reinterpret_cast<const float4*>(&dy[h0 + 4 * g]);
-          const float2 sa_a = make_float2(sa4.x, sa4.y), sa_b = make_float2(sa4.z, sa4.w);
-          const float2 v_a = make_float2(v4.x, v4.y), v_b = make_float2(v4.z, v4.w);
-          const float2 dy_a = make_float2(dy4.x, dy4.y), dy_b = make_float2(dy4.z, dy4.w);
-          const float2 st_a = __ffma2_rn(v_a, ktj2, __ffma2_rn(sa_a, nbj2, __fmul2_rn(S[2 * g], wj2)));
-          const float2 st_b = __ffma2_rn(v_b, ktj2, __ffma2_rn(sa_b, nbj2, __fmul2_rn(S[2 * g + 1], wj2)));
-          const float2 g_a = __ffma2_rn(dy_a, rj2, dS[2 * g]), g_b = __ffma2_rn(dy_b, rj2, dS[2 * g + 1]);
-          dS[2 * g] = g_a; dS[2 * g + 1] = g_b;
-          dr0 = __ffma2_rn(st_a, dy_a, dr0); dr1 = __ffma2_rn(st_b, dy_b, dr1);
-          dkt0 = __ffma2_rn(g_a, v_a, dkt0); dkt1 = __ffma2_rn(g_b, v_b, dkt1);
-          db0 = __ffma2_rn(g_a, sa_a, db0); db1 = __ffma2_rn(g_b, sa_b, db1);
-          dw0 = __ffma2_rn(g_a, S[2 * g], dw0); dw1 = __ffma2_rn(g_b, S[2 * g + 1], dw1);
+          for (int k = 0; k < 2; ++k) {
+            const float2 sp = S[a][2 * hc + k];
+            const float2 g = __ffma2_rn(dy2, r[k], dS[a][2 * hc + k]);
+            dS[a][2 * hc + k] = g;
+            rdv = __ffma2_rn(g, kt[k], rdv);
+            rds = __ffma2_rn(g, bb[k], rds);
+            const float2 st = __ffma2_rn(v2, kt[k], __ffma2_rn(nsa2, bb[k], __fmul2_rn(sp, w[k])));
+            dr[k] = __ffma2_rn(st, dy2, dr[k]);
+            dkt[k] = __ffma2_rn(g, v2, dkt[k]);
+            db[k] = __ffma2_rn(g, sa2, db[k]);
+            dw[k] = __ffma2_rn(g, sp, dw[k]);
+          }
+          dvp[a] += rdv.x + rdv.y;
+          dsp[a] += rds.x + rds.y;
         }
-        float (*cp)[kH] = sm.col_part[buf3][half];
-        cp[0][idx] = sum4(dr0, dr1);
-        cp[1][idx] = sum4(dkt0, dkt1);
-        cp[2][idx] = sum4(db0, db1);
-        cp[3][idx] = sum4(dw0, dw1);
+        const int col = tl.col0 + 32 * hc + tl.ti;
+        cp[0][col] = col_reduce_scatter(dr, tl.ti);
+        cp[1][col] = col_reduce_scatter(dkt, tl.ti);
+        cp[2][col] = col_reduce_scatter(db, tl.ti);
+        cp[3][col] = col_reduce_scatter(dw, tl.ti);
       }
-      __syncthreads();            // the halves of this timestep's dv and -dsa, and all of the previous timestep's column sums, are published
-      finish_pending();
-      if (row_thread) {
-        const float dsa = -(sm.ds_part[par][0][idx] + sm.ds_part[par][1][idx]);
-        if (half == 0) p.din[4][out] = sm.dv_part[par][0][idx] + sm.dv_part[par][1][idx];
-        const float2 dsa2 = make_float2(dsa, dsa);
+      row_allreduce(dsp);         // dsp[a] = sum_j G b of row row0 + a; dsa = -dsp
+      const size_t out = head_base + (size_t)(t0 + s) * C;
+      row_allreduce(dvp);
+      if (tl.tj < kR) p.din[4][out + tl.row0 + tl.tj] = pick(dvp, tl.tj);
+      // second pass: S_{t-1}^T dsa and dS_{t-1}
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 w4 = *reinterpret_cast<const float4*>(&w[h0 + 4 * g]);
-          const float4 k4 = *reinterpret_cast<const float4*>(&kap[h0 + 4 * g]);
-          dS[2 * g] = __ffma2_rn(dsa2, make_float2(k4.x, k4.y), __fmul2_rn(dS[2 * g], make_float2(w4.x, w4.y)));
-          dS[2 * g + 1] = __ffma2_rn(dsa2, make_float2(k4.z, k4.w), __fmul2_rn(dS[2 * g + 1], make_float2(w4.z, w4.w)));
-        }
-      } else {
-        const float wj = w[idx], kapj = kap[idx];
-        const float2 wj2 = make_float2(wj, wj), kapj2 = make_float2(kapj, kapj);
-        float2 dk0 = make_float2(0.f, 0.f), dk1 = dk0;
+      for (int hc = 0; hc < 2; ++hc) {
+        const int c = tl.col0 + 32 * hc;
+        const float4 w4 = *reinterpret_cast<const float4*>(buf[0] + c), k4 = *reinterpret_cast<const float4*>(buf[2] + c);
+        const float2 w[2] = {make_float2(w4.x, w4.y), make_float2(w4.z, w4.w)};
+        const float2 kap[2] = {make_float2(k4.x, k4.y), make_float2(k4.z, k4.w)};
+        float2 dk[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 p0 = *reinterpret_cast<const float4*>(&sm.ds_part[par][0][h0 + 4 * g]);
-          const float4 p1 = *reinterpret_cast<const float4*>(&sm.ds_part[par][1][h0 + 4 * g]);
-          const float2 d_a = make_float2(-(p0.x + p1.x), -(p0.y + p1.y)), d_b = make_float2(-(p0.z + p1.z), -(p0.w + p1.w));
-          dk0 = __ffma2_rn(S[2 * g], d_a, dk0); dk1 = __ffma2_rn(S[2 * g + 1], d_b, dk1);
-          dS[2 * g] = __ffma2_rn(d_a, kapj2, __fmul2_rn(dS[2 * g], wj2));
-          dS[2 * g + 1] = __ffma2_rn(d_b, kapj2, __fmul2_rn(dS[2 * g + 1], wj2));
+        for (int a = 0; a < kR; ++a) {
+          const float2 dsa2 = dup(-dsp[a]);
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            dk[k] = __ffma2_rn(S[a][2 * hc + k], dsa2, dk[k]);
+            dS[a][2 * hc + k] = __ffma2_rn(dsa2, kap[k], __fmul2_rn(dS[a][2 * hc + k], w[k]));
+          }
         }
-        sm.col_part[buf3][half][4][idx] = sum4(dk0, dk1);
-        pend_kap = kapj; pend_a = a[idx];
+        cp[4][c + tl.ti] = col_reduce_scatter(dk, tl.ti);
       }
-      pend_buf = buf3; pend_out = out;
-      buf3 = buf3 == 2 ? 0 : buf3 + 1;
+      // the five column sums of this timestep: each warp's half is in shared memory after the barrier; thread j adds column j.
+      // (The buffer of the other parity is written by the next timestep, and this one again only after the next barrier.)
+      const int j = tl.tid & (kH - 1);
+      const float kap_j = buf[2][j], a_j = buf[1][j];
+      __syncthreads();
+      if (tl.tid < kH) {
+        float sum[5];
+#pragma unroll
+        for (int q = 0; q < 5; ++q) {
+          sum[q] = sm.col_part[par][0][q][j];
+#pragma unroll
+          for (int w = 1; w < kWarps; ++w) sum[q] += sm.col_part[par][w][q][j];
+        }
+        p.din[5][out + j] = sum[0];
+        p.din[3][out + j] = sum[1];
+        p.din[0][out + j] = sum[3];
+        p.din[1][out + j] = -sum[2] * kap_j;
+        p.din[2][out + j] = sum[4] - sum[2] * a_j;
+      }
     }
   };
 
   issue_vec(n_ck - 1);
-  if (row_thread) load_ckpt(n_ck - 1);
+  int pre_slot = 0;               // the slot that holds the checkpoint the next recomputation starts from
+  prefetch_ckpt(n_ck - 1, pre_slot);
   for (int ck = n_ck - 1; ck >= 0; --ck) {
     const int t0 = ck * kCk, steps = min(kCk, p.T - t0);
     const int lo = steps > kSub ? kSub : 0;      // the chunk runs as [lo, steps) and then, if lo > 0, [0, lo)
-    __syncthreads();              // everyone is done with the chunk after this one: its vectors, bk and slots
-    finish_pending();             // (reads col_part only)
+    __syncthreads();              // everyone is done with the vectors of the chunk after this one
     issue_vec(ck - 1);            // into the buffer that chunk used
-    cp_async_wait<1>();           // this thread's copies of chunk ck have landed
-    __syncthreads();              // ... and everyone's
+    cp_async_wait<1>();           // this thread's copies of chunk ck, and of its checkpoint, have landed
+    __syncthreads();              // ... and everyone's vectors
     const float (*V)[kBwdVecs][kH] = sm.vec[ck & 1];
-    for (int e = tid; e < steps * kH; e += kBwdThreads) sm.bk[e / kH][e % kH] = V[e / kH][1][e % kH] * V[e / kH][2][e % kH];
-    __syncthreads();
-    if (row_thread) {             // the states before timesteps lo .. steps-1
-      for (int s = 0; s < steps; ++s) {
-        if (s >= lo) store_slot(sm.slot[s - lo]);
-        if (s + 1 < steps) update(V[s], sm.bk[s]);
-      }
-      if (lo > 0) load_ckpt(ck); else if (ck > 0) load_ckpt(ck - 1);
+    load_tile_private(sm.slot[pre_slot], tl, S);
+    for (int s = 0; s < steps; ++s) {            // the states before timesteps lo .. steps-1 -> slots 0 ..
+      if (s >= lo) store_tile_private(sm.slot[s - lo], tl, S);
+      if (s + 1 < steps) update(V[s]);
     }
-    __syncthreads();
-    run_backwards(V, t0, lo, steps);
     if (lo > 0) {
-      __syncthreads();            // the column threads are done with the slots
-      finish_pending();
-      if (row_thread) {           // the states before timesteps 0 .. lo-1
-        for (int s = 0; s < lo; ++s) {
-          store_slot(sm.slot[s]);
-          if (s + 1 < lo) update(V[s], sm.bk[s]);
-        }
-        if (ck > 0) load_ckpt(ck - 1);
+      run_backwards(V, t0, lo, steps, 0, ck);    // its first timestep empties slot steps-1-lo: this chunk's checkpoint goes there again
+      pre_slot = steps - 1 - lo;
+      cp_async_wait<0>();
+      load_tile_private(sm.slot[pre_slot], tl, S);
+      // the states before timesteps 0 .. lo-1 -> slots pre_slot, pre_slot+1, ... (mod 4): the first is there already
+      for (int s = 0; s + 1 < lo; ++s) {
+        update(V[s]);
+        store_tile_private(sm.slot[(s + 1 + pre_slot) & (kSub - 1)], tl, S);
       }
-      __syncthreads();
-      run_backwards(V, t0, 0, lo);
+      run_backwards(V, t0, 0, lo, pre_slot, ck - 1);
+      pre_slot = (lo - 1 + pre_slot) & (kSub - 1);
+    } else {
+      run_backwards(V, t0, 0, steps, 0, ck - 1);
+      pre_slot = steps - 1;
     }
   }
   cp_async_wait<0>();
-  __syncthreads();
-  finish_pending();
-  if (p.dstate_in && row_thread) {
-#pragma unroll
-    for (int g = 0; g < 8; ++g)
-      reinterpret_cast<float4*>(p.dstate_in + (head * kH + idx) * kH + h0)[g] = make_float4(dS[2 * g].x, dS[2 * g].y, dS[2 * g + 1].x, dS[2 * g + 1].y);
-  }
+  if (p.dstate_in) store_tile_rowmajor(p.dstate_in + head * kH * kH, tl, dS);
 }
 
 }  // namespace
@@ -451,7 +502,7 @@ extern "C" int pb_wkv7_forward(const float* decay, const float* iclr, const floa
   const void* ptrs[] = {decay, iclr, removal_k, replacement_k, v, r, state_in, state_out, checkpoints, sa};
   for (const void* ptr : ptrs)
     if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(PB_ERR_MISALIGNED, "pb_wkv7_forward: every array must be 16-byte aligned");
-  WkvParams p{{decay, iclr, removal_k, replacement_k, v, r}, state_in, y, state_out, checkpoints, sa, (int)steps, (int)heads};
+  WkvParams p{{decay, iclr, removal_k, replacement_k, v, r}, state_in, y, state_out, reinterpret_cast<float4*>(checkpoints), sa, (int)steps, (int)heads};
   wkv7_forward_kernel<<<(unsigned)(batch * heads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   PB_LAUNCH_CHECK("wkv7_forward_kernel");
   return PB_OK;
@@ -476,10 +527,10 @@ extern "C" int pb_wkv7_backward(const float* decay, const float* iclr, const flo
   const void* ptrs[] = {decay, iclr, removal_k, replacement_k, v, r, checkpoints, sa, dy, dstate_out, dstate_in};
   for (const void* ptr : ptrs)
     if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(PB_ERR_MISALIGNED, "pb_wkv7_backward: every array must be 16-byte aligned");
-  WkvBwdParams p{{decay, iclr, removal_k, replacement_k, v, r}, dy, sa, checkpoints, dstate_out,
+  WkvBwdParams p{{decay, iclr, removal_k, replacement_k, v, r}, dy, sa, reinterpret_cast<const float4*>(checkpoints), dstate_out,
                  {d_decay, d_iclr, d_removal_k, d_replacement_k, d_v, d_r}, dstate_in, (int)steps, (int)heads};
   PB_CUDA_TRY(cudaFuncSetAttribute(wkv7_backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(WkvBwdSmem)));   // per device
-  wkv7_backward_kernel<<<(unsigned)(batch * heads), kBwdThreads, sizeof(WkvBwdSmem), static_cast<cudaStream_t>(stream)>>>(p);
+  wkv7_backward_kernel<<<(unsigned)(batch * heads), kThreads, sizeof(WkvBwdSmem), static_cast<cudaStream_t>(stream)>>>(p);
   PB_LAUNCH_CHECK("wkv7_backward_kernel");
   return PB_OK;
 }
