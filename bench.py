@@ -266,6 +266,7 @@ def time_model_step(world: int, rank: int, dev, barrier, steps: int = 2):
     CUDA events around each step, barrier on both sides, mean of `steps` after one warm-up."""
     import torch
     import torch.distributed as dist
+    from pratchya_b200._nnx_impl._dp import allreduce_gradients
     from pratchya_b200._nnx_impl._model import PratchyaCausalLM, PratchyaConfig
     from pratchya_b200._qualia import set_literal_dot_precision
     set_literal_dot_precision("tf32")   # the (128,1)-grid layers' backward dots (LoRA, lm_head): what an f32 dot gets under XLA on a GPU
@@ -285,14 +286,7 @@ def time_model_step(world: int, rank: int, dev, barrier, steps: int = 2):
         _, loss = model(ids, ids)
         loss.backward()
         if world > 1 and exchange:
-            flat = torch.cat([p.grad.reshape(-1) for p in params]).to(torch.bfloat16)
-            dist.all_reduce(flat)
-            flat = flat.to(torch.float32) / world
-            off = 0
-            for p in params:
-                p.grad.copy_(flat[off:off + p.numel()].view_as(p))
-                off += p.numel()
-            del flat
+            allreduce_gradients(params, world)
         grads = [p.grad for p in params]
         with torch.no_grad():
             torch._foreach_mul_(momentum, 0.9)

@@ -109,3 +109,39 @@ def test_batched_bf16_input_with_e5m2_gradients_matches_the_oracle(built_lib):
     gw = oracle.dequantize_impl(*oracle.quantize_impl((xT_hat @ gT_hat.T).astype(np.float32), (128, 128)), np.float32, (128, 128))
     assert_fake_quantized_close(from_torch(xt.grad).astype(np.float32).reshape(1024, 256), gx.astype(oracle.BF16).astype(np.float32), "dX", boundary_fraction=0.03, bf16=True)
     assert_fake_quantized_close(from_torch(wt.grad), gw, "dW", boundary_fraction=0.03)
+
+
+def test_literal_dot_precision_switch(built_lib):
+    """The (128,1)-grid layers' backward dots run on the library matmul: full f32 by default, TF32 operands after
+    set_literal_dot_precision("tf32") (what an f32 dot gets on a GPU under XLA's default precision).  TF32 rounds the
+    operands to 10 mantissa bits: the gradients move by at most a few 1e-3 of their largest magnitude, and the switch
+    changes nothing on the (128,128) tensor-core path."""
+    from pratchya_b200._qualia import set_literal_dot_precision
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    x = torch.randn(1024, 2048, device="cuda", generator=gen)
+    g = torch.randn(1024, 128, device="cuda", generator=gen)
+    w = (torch.randn(2048, 128, device="cuda", generator=gen) * 0.02)
+    w2 = (torch.randn(2048, 2048, device="cuda", generator=gen) * 0.02)
+    g2 = torch.randn(1024, 2048, device="cuda", generator=gen)
+
+    def grads(weight, grid, cot):
+        xi, wi = x.clone().requires_grad_(True), weight.clone().requires_grad_(True)
+        linear_fp8(xi, wi, grid, fake_quant_output=grid[1] != 1).backward(cot)
+        return xi.grad, wi.grad
+
+    try:
+        exact = grads(w, (128, 1), g)
+        exact_tc = grads(w2, (128, 128), g2)
+        set_literal_dot_precision("tf32")
+        fast = grads(w, (128, 1), g)
+        fast_tc = grads(w2, (128, 128), g2)
+    finally:
+        set_literal_dot_precision("f32")
+    for a, b in zip(exact, fast):
+        # both results are re-quantized to fp8 on their way out, so a moved rounding shows as one fp8 step on that element
+        diff = (a - b).abs()
+        assert diff.mean().item() <= 2e-3 * a.abs().max().item()
+    for a, b in zip(exact_tc, fast_tc):
+        assert torch.equal(a, b)
+    with pytest.raises(ValueError):
+        set_literal_dot_precision("bf16")
