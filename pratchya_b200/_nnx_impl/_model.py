@@ -81,9 +81,14 @@ class Linear(torch.nn.Module):
         super().__init__()
         self.tgrid = (int(tgrid[0]), int(tgrid[1]))
         self.kernel = torch.nn.Parameter(_lecun(fan_in, (fan_in, fan_out), gen, device))
+        self._prepared = (None, None)        # (kernel version, {"wq": fp8 triple, "w_t": its byte transpose})
 
     def forward(self, x):
-        return linear_fp8(x, self.kernel, self.tgrid, fake_quant_output=self.tgrid[1] != 1)
+        # the kernel's fp8 form is the same in every pass of a step: keep it until the kernel is written to
+        version = (self.kernel._version, self.kernel.data_ptr())
+        if self._prepared[0] != version:
+            self._prepared = (version, {})
+        return linear_fp8(x, self.kernel, self.tgrid, fake_quant_output=self.tgrid[1] != 1, prepared=self._prepared[1])
 
 
 class LowRankFFN(torch.nn.Module):                   # _module.py:74-89

@@ -159,10 +159,15 @@ class _LinearFn(torch.autograd.Function):
     grid, as the reference returns them (:637-640, :522-526)."""
 
     @staticmethod
-    def forward(ctx, x, weight, grid, fake_quant_output, recipe, grad_format, for_backward=True):
+    def forward(ctx, x, weight, grid, fake_quant_output, recipe, grad_format, for_backward=True, prepared=None):
         a, b = grid
         x2 = x.reshape(-1, x.shape[-1])
-        wq = _ops.quantize_impl(weight, grid)
+        if prepared is not None and "wq" in prepared:
+            wq = prepared["wq"]
+        else:
+            wq = _ops.quantize_impl(weight, grid)
+            if prepared is not None:
+                prepared["wq"] = wq
         # the tensor-core backward needs the weight as a K-major operand in both directions: (128,128) blocks only.
         # A (128,1) weight (LoRA, gate, lm_head) has one scale per column and 128 rows, which no 128-deep block
         # along its columns can carry: its forward runs on the tensor cores, its backward on the literal recipe.
@@ -172,7 +177,13 @@ class _LinearFn(torch.autograd.Function):
         else:
             xq, xt = _ops.quantize_impl(x2, (1, a)), None
         eligible = _ops._tensor_core_eligible(xq[0], wq[0], (1, a), grid)
-        w_t = _ops.transpose_bytes(wq[0]) if eligible else None
+        w_t = None
+        if eligible:
+            w_t = prepared.get("w_t") if prepared is not None else None
+            if w_t is None:
+                w_t = _ops.transpose_bytes(wq[0])
+                if prepared is not None:
+                    prepared["w_t"] = w_t
         y = _ops.matmul_impl(*xq, *wq, (1, a), grid, y_fp8_t=w_t, out_dtype=torch.float32)
         ctx.grid, ctx.recipe, ctx.grad_format, ctx.fake = grid, recipe, grad_format, fake_quant_output
         ctx.x_shape, ctx.x_dtype, ctx.w_dtype = x.shape, x.dtype, weight.dtype
@@ -218,17 +229,19 @@ class _LinearFn(torch.autograd.Function):
             gw = _ops._matmul_f32(x_hat.t(), g32)
         gx = _ops.fake_quantize_impl(gx, (1, a), torch.float32)                                  # :637 then :522-526
         gw = _ops.dequantize_impl(*_ops.quantize_impl(gw, ctx.grid), torch.float32, ctx.grid)    # :638; the optimizer dequantizes it
-        return gx.reshape(ctx.x_shape).to(ctx.x_dtype), gw.to(ctx.w_dtype), None, None, None, None, None
+        return gx.reshape(ctx.x_shape).to(ctx.x_dtype), gw.to(ctx.w_dtype), None, None, None, None, None, None
 
 
 def linear_fp8(x: torch.Tensor, weight: torch.Tensor, tgrid=(128, 128), *, fake_quant_output: bool = True,
-               recipe: str = "fp8", grad_format: str = "e4m3") -> torch.Tensor:
+               recipe: str = "fp8", grad_format: str = "e4m3", prepared: dict | None = None) -> torch.Tensor:
     """y = Linear(x) with a dense master `weight` [fan_in, fan_out] that is quantized on `tgrid` in
     the forward pass; differentiable in x and weight.  `grad_format="e5m2"` stores dY in e5m2
-    (an extension: the reference has no e5m2 anywhere)."""
+    (an extension: the reference has no e5m2 anywhere).  `prepared`: a dict the caller keeps for as long as
+    `weight` does not change; the weight's fp8 triple and its byte transpose are put there by the first call and
+    reused by the later ones (the passes of one training step quantize the same weight three times otherwise)."""
     if recipe not in ("fp8", "reference"):
         raise ValueError("recipe must be 'fp8' or 'reference'")
     # X^T is quantized in the forward pass only when a backward pass can follow (not under torch.no_grad, as in the first
     # pass of a recomputed block)
     for_backward = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
-    return _LinearFn.apply(x, weight, (int(tgrid[0]), int(tgrid[1])), fake_quant_output, recipe, grad_format, for_backward)
+    return _LinearFn.apply(x, weight, (int(tgrid[0]), int(tgrid[1])), fake_quant_output, recipe, grad_format, for_backward, prepared)

@@ -26,6 +26,8 @@ __device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<floa
 // i + (j - i) * w with the three roundings of the op-by-op evaluation
 __device__ __forceinline__ float lerp_rn(float i, float j, float w) { return __fadd_rn(i, __fmul_rn(__fsub_rn(j, i), w)); }
 __device__ __forceinline__ float sigmoid_rn(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
+// for the backward kernels, which are compared with autograd to 2e-5 and not bit for bit: hardware exp2 and reciprocal
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 // out[k][r][c] = x[r][c] + (prev[r][c] - x[r][c]) * mu[k][c], prev = the token before (the carried state for the first)
 struct ShiftLerpParams {
@@ -200,14 +202,14 @@ __global__ void __launch_bounds__(kGlueThreads) wkv_prepare_bwd_kernel(const Pre
     const float cs = __ldg(f.cos_tab + t * 32 + lane), sn = __ldg(f.sin_tab + t * 32 + lane);
     const float ka = f.k_raw[i1], kb = f.k_raw[i2];
     const float k1 = __fadd_rn(__fmul_rn(ka, cs), __fmul_rn(-kb, sn)), k2 = __fadd_rn(__fmul_rn(kb, cs), __fmul_rn(ka, sn));
-    const float a1 = sigmoid_rn(f.iclr_raw[i1]), a2 = sigmoid_rn(f.iclr_raw[i2]);
+    const float a1 = sigmoid_fast(f.iclr_raw[i1]), a2 = sigmoid_fast(f.iclr_raw[i2]);
     // removal_k = u / nrm, u = k * m: d_u = (g - removal_k * sum(g * removal_k)) / nrm
     const float u1 = __fmul_rn(k1, m1), u2 = __fmul_rn(k2, m2);
-    const float nrm = sqrtf(__fadd_rn(warp_sum(__fadd_rn(__fmul_rn(u1, u1), __fmul_rn(u2, u2))), 1e-12f));
-    const float q1 = u1 / nrm, q2 = u2 / nrm;
+    const float inv_nrm = rsqrtf(warp_sum(u1 * u1 + u2 * u2) + 1e-12f);
+    const float q1 = u1 * inv_nrm, q2 = u2 * inv_nrm;
     const float gq1 = p.g_removal_k[i1], gq2 = p.g_removal_k[i2];
     const float dot = warp_sum(gq1 * q1 + gq2 * q2);
-    const float du1 = (gq1 - q1 * dot) / nrm, du2 = (gq2 - q2 * dot) / nrm;
+    const float du1 = (gq1 - q1 * dot) * inv_nrm, du2 = (gq2 - q2 * dot) * inv_nrm;
     dm1 = fmaf(du1, k1, dm1); dm2 = fmaf(du2, k2, dm2);
     // replacement_k = k + (k * a - k) * x
     const float gp1 = p.g_replacement_k[i1], gp2 = p.g_replacement_k[i2];
@@ -221,11 +223,11 @@ __global__ void __launch_bounds__(kGlueThreads) wkv_prepare_bwd_kernel(const Pre
     const float gr1 = p.g_r[i1], gr2 = p.g_r[i2];
     p.d_r_raw[i1] = gr1 * cs + gr2 * sn; p.d_r_raw[i2] = gr2 * cs - gr1 * sn;
     // decay = exp(-e), e = exp(d)
-    const float e1 = expf(f.d[i1]), e2 = expf(f.d[i2]);
-    p.d_d[i1] = -p.g_decay[i1] * expf(-e1) * e1; p.d_d[i2] = -p.g_decay[i2] * expf(-e2) * e2;
+    const float e1 = __expf(f.d[i1]), e2 = __expf(f.d[i2]);
+    p.d_d[i1] = -p.g_decay[i1] * __expf(-e1) * e1; p.d_d[i2] = -p.g_decay[i2] * __expf(-e2) * e2;
     const float gv1 = p.g_v[i1], gv2 = p.g_v[i2];
     if (f.v0) {
-      const float nu1 = sigmoid_rn(f.nu_raw[i1]), nu2 = sigmoid_rn(f.nu_raw[i2]);
+      const float nu1 = sigmoid_fast(f.nu_raw[i1]), nu2 = sigmoid_fast(f.nu_raw[i2]);
       p.d_v_prime[i1] = gv1 - gv1 * nu1; p.d_v_prime[i2] = gv2 - gv2 * nu2;
       p.d_v0[i1] = gv1 * nu1; p.d_v0[i2] = gv2 * nu2;
       p.d_nu_raw[i1] = gv1 * (f.v0[i1] - f.v_prime[i1]) * nu1 * (1.0f - nu1);
