@@ -330,6 +330,16 @@ PB_API int pb_wkv_finish_bwd(const float* g, const float* y, const float* r, con
                       float* d_gn_scale, float* d_gn_bias, float* d_bonus_mult,
                       void* workspace, size_t workspace_bytes, void* stream);
 
+/* The training loss, compute_loss (pratchya/_nnx_impl/_utils.py:7-13): softmax cross entropy of logits [rows, vocab] (f32)
+ * against one-hot targets smoothed by alpha (optax.smooth_labels).  row_loss[r] = weight[r] * (lse_r - (1 - alpha) * z[r][target[r]]
+ * - alpha * mean_j z[r][j]); the caller sums the rows and divides by the number of positions that count (weight 0 leaves a
+ * row out: the last position of every sequence has no next token).  lse [rows] is kept for the backward call, which writes
+ * dlogits = upstream[0] * weight[r] / denominator * (softmax - (1 - alpha) * onehot - alpha / vocab).  vocab a multiple of 4. */
+PB_API int pb_smoothed_xent(const float* logits, const int64_t* target, const float* weight, int64_t rows, int64_t vocab, float alpha,
+                     float* row_loss, float* lse, void* stream);
+PB_API int pb_smoothed_xent_bwd(const float* logits, const int64_t* target, const float* weight, const float* lse, const float* upstream,
+                         float denominator, int64_t rows, int64_t vocab, float alpha, float* dlogits, void* stream);
+
 /* byte transpose [rows, cols] -> [cols, rows] of an fp8 matrix (weight prepared for the forward GEMM) */
 PB_API int pb_transpose_bytes(const void* src, int64_t rows, int64_t cols, void* dst, void* stream);
 

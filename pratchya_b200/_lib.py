@@ -78,6 +78,8 @@ _SIGNATURES = {
     "pb_wkv_finish": (_int, [_ptr] * 8 + [C.c_float, _i64, _i64, _i64, _int] + [_ptr] * 3 + [_sz, _ptr]),
     "pb_wkv_finish_bwd_workspace_size": (_sz, [_i64, _i64, _i64, _int]),
     "pb_wkv_finish_bwd": (_int, [_ptr] * 10 + [_i64, _i64, _i64, _int] + [_ptr] * 9 + [_sz, _ptr]),
+    "pb_smoothed_xent": (_int, [_ptr, _ptr, _ptr, _i64, _i64, C.c_float, _ptr, _ptr, _ptr]),
+    "pb_smoothed_xent_bwd": (_int, [_ptr] * 5 + [C.c_float, _i64, _i64, C.c_float, _ptr, _ptr]),
     "pb_wkv7_forward": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "pb_wkv7_checkpoint_floats": (_sz, [_i64, _i64, _i64, _int]),
     "pb_wkv7_backward": (_int, [_ptr] * 10 + [_i64, _i64, _i64, _int] + [_ptr] * 8),

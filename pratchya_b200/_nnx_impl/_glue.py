@@ -248,3 +248,47 @@ def wkv_finish(y, r, k, v, gate, gn_scale, gn_bias, bonus_mult, eps: float, n_he
         raise RuntimeError("wkv_finish needs CUDA tensors: pratchya_b200 has no CPU path")
     return _WkvFinishFn.apply(*[_f32c(t) for t in ins], _f32c(gn_scale).reshape(-1), _f32c(gn_bias).reshape(-1),
                               _f32c(bonus_mult).reshape(-1), float(eps), n_head)
+
+
+class _SmoothedXentFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, target, weight, alpha, denominator):
+        lib = _lib.load()
+        rows, vocab = logits.shape
+        dev = logits.device
+        row_loss = torch.empty(rows, dtype=torch.float32, device=dev)
+        lse = torch.empty(rows, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            check(lib.pb_smoothed_xent(logits.data_ptr(), target.data_ptr(), weight.data_ptr(), rows, vocab, alpha,
+                                       row_loss.data_ptr(), lse.data_ptr(), _stream(dev)))
+        ctx.save_for_backward(logits, target, weight, lse)
+        ctx.alpha, ctx.denominator = alpha, denominator
+        return row_loss.sum() / denominator
+
+    @staticmethod
+    def backward(ctx, g):
+        logits, target, weight, lse = ctx.saved_tensors
+        lib = _lib.load()
+        rows, vocab = logits.shape
+        dev = logits.device
+        g = g.to(torch.float32).reshape(1).contiguous()
+        dlogits = torch.empty_like(logits)
+        with torch.cuda.device(dev):
+            check(lib.pb_smoothed_xent_bwd(logits.data_ptr(), target.data_ptr(), weight.data_ptr(), lse.data_ptr(), g.data_ptr(),
+                                           ctx.denominator, rows, vocab, ctx.alpha, dlogits.data_ptr(), _stream(dev)))
+        return dlogits, None, None, None, None
+
+
+def smoothed_cross_entropy(logits, labels, alpha: float = 0.1):
+    """compute_loss, pratchya/_nnx_impl/_utils.py:7-13, on logits [B, T, V] f32 and labels [B, T]: position t predicts label
+    t+1 (the reference's caller passes logits[:, :-1] and label[:, 1:]), one-hot labels smoothed by alpha, softmax cross
+    entropy, mean over the B * (T-1) positions.  One pass over the logits forward and one backward."""
+    if not logits.is_cuda:
+        raise RuntimeError("smoothed_cross_entropy needs CUDA tensors: pratchya_b200 has no CPU path")
+    bsz, steps, vocab = logits.shape
+    if steps < 2 or tuple(labels.shape) != (bsz, steps) or vocab % 4 != 0:
+        raise ValueError(f"smoothed_cross_entropy: logits {tuple(logits.shape)}, labels {tuple(labels.shape)}")
+    target = torch.cat([labels[:, 1:], labels[:, :1]], dim=1).to(torch.int64).reshape(-1).contiguous()      # the last column is a placeholder
+    weight = torch.ones(bsz, steps, dtype=torch.float32, device=logits.device)
+    weight[:, -1] = 0.0
+    return _SmoothedXentFn.apply(_f32c(logits).reshape(bsz * steps, vocab), target, weight.reshape(-1), float(alpha), float(bsz * (steps - 1)))

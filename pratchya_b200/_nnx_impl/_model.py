@@ -19,6 +19,7 @@ import torch
 
 from .._qualia import _ops
 from ._glue import relu2, rms_norm, token_shift_lerp, wkv_finish, wkv_prepare
+from ._glue import smoothed_cross_entropy as fused_cross_entropy
 from ._module import linear_fp8
 from ._wkv7 import wkv_state_scan
 
@@ -316,7 +317,7 @@ class PratchyaCausalLM(torch.nn.Module):
         logits = self.lm_head(x)
         loss = None
         if label is not None:
-            loss = smoothed_cross_entropy(logits, label)
+            loss = fused_cross_entropy(logits, label) if cfg.fused_glue else smoothed_cross_entropy(logits, label)
         return logits, loss
 
 

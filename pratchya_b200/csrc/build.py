@@ -19,7 +19,7 @@ HERE = Path(__file__).resolve().parent
 INCLUDE = HERE.parent.parent / "include"
 LIB = HERE / "libpratchya_b200.so"
 DIAG_LIB = HERE / "libpratchya_b200_diag.so"
-SOURCES = ["api.cu", "quantize.cu", "dequantize.cu", "transpose_quantize.cu", "optimizer.cu", "gemm_sm100.cu", "wkv7.cu", "rwkv_glue.cu", "rwkv_norms.cu"]
+SOURCES = ["api.cu", "quantize.cu", "dequantize.cu", "transpose_quantize.cu", "optimizer.cu", "gemm_sm100.cu", "wkv7.cu", "rwkv_glue.cu", "rwkv_norms.cu", "loss.cu"]
 DIAG_SOURCES = SOURCES + ["selftest.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

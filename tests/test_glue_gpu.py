@@ -149,3 +149,18 @@ def test_wkv_finish_matches_torch(built_lib, bsz, steps, n_head):
     for name, a, b in zip(["d_y", "d_r", "d_k", "d_v", "d_gate", "d_gn_scale", "d_gn_bias", "d_bonus_mult"],
                           torch.autograd.grad(got, leaves, g), torch.autograd.grad(want, leaves, g)):
         close(a, b, name, 3e-5)
+
+
+@pytest.mark.parametrize("bsz,steps,vocab", [(2, 9, 1024), (3, 33, 65536), (1, 2, 4)])
+def test_fused_cross_entropy_matches_torch(built_lib, bsz, steps, vocab):
+    from pratchya_b200._nnx_impl._glue import smoothed_cross_entropy as fused
+    from pratchya_b200._nnx_impl._model import smoothed_cross_entropy as plain
+    gen = torch.Generator(device="cuda").manual_seed(vocab + steps)
+    logits = (torch.randn(bsz, steps, vocab, device="cuda", generator=gen) * 3).requires_grad_(True)
+    labels = torch.randint(0, vocab, (bsz, steps), device="cuda", generator=gen)
+    got, want = fused(logits, labels), plain(logits, labels)
+    assert abs(got.item() - want.item()) <= 2e-6 * abs(want.item()), (got.item(), want.item())
+    g_got, = torch.autograd.grad(got * 1.7, logits)
+    g_want, = torch.autograd.grad(want * 1.7, logits)
+    close(g_got, g_want, "dlogits", 2e-5)
+    assert torch.count_nonzero(g_got[:, -1, :]).item() == 0      # the last position predicts nothing

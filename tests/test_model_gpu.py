@@ -138,6 +138,25 @@ def test_block_gradients_agree_with_and_without_recomputation(built_lib):
     assert torch.equal(grads[0][0], grads[1][0]) and torch.equal(grads[0][1], grads[1][1])
 
 
+def test_linear_refreshes_its_fp8_weight_when_the_kernel_changes(built_lib):
+    """The model's Linear keeps the kernel's fp8 triple across the passes of a step; any in-place write to the
+    kernel (an optimizer update, a loaded checkpoint) must make the next call quantize it again."""
+    from pratchya_b200._nnx_impl._model import Linear
+    from pratchya_b200._nnx_impl import linear_fp8
+    gen = torch.Generator(device="cuda").manual_seed(8)
+    lin = Linear(1024, 1024, (128, 128), gen, "cuda")
+    x = torch.randn(256, 1024, device="cuda", generator=gen)
+    with torch.no_grad():
+        y0 = lin(x)
+        assert torch.equal(y0, lin(x)) and "wq" in lin._prepared[1]
+        assert torch.equal(y0, linear_fp8(x, lin.kernel, (128, 128)))
+        lin.kernel.mul_(1.5)
+        y1 = lin(x)
+        assert torch.equal(y1, linear_fp8(x, lin.kernel, (128, 128))) and not torch.equal(y1, y0)
+        lin.kernel.copy_(torch.randn(1024, 1024, device="cuda", generator=gen) * 0.03)
+        assert torch.equal(lin(x), linear_fp8(x, lin.kernel, (128, 128)))
+
+
 def test_model_gradients_are_the_same_bits_with_and_without_recomputation(built_lib):
     """PratchyaCausalLM(remat=True) runs each block without a graph in the forward pass and recomputes it in the backward
     pass; every kernel is deterministic, so loss and gradients equal those of the stored-activation model bit for bit."""
