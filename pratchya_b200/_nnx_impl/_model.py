@@ -1,11 +1,12 @@
 """The modified RWKV-7 model of pratchya/_nnx_impl/_module.py and _model.py (quantized variant) with every
 linear layer on the FP8 path of this package and the WKV-7 state scan on its CUDA kernels.
 
-This is the caller of the hot path, kept as close to the reference's text as torch allows: the token shift,
-lerps, gates, normalisations, rotary embedding and the loss are plain torch operations on f32 tensors (model
-glue), differentiated by torch.autograd; the pieces that carry the arithmetic are `linear_fp8` (quantize,
-block-scaled tensor-core matmuls forward and backward), `FakeQuant` (the quantize -> dequantize a QArrayImpl
-parameter goes through when it is read, with the reference's cotangent rule) and `wkv_state_scan`.
+This is the caller of the hot path, kept as close to the reference's text as torch allows.  The pieces that carry
+the arithmetic are `linear_fp8` (quantize, block-scaled tensor-core matmuls forward and backward), `FakeQuant` (the
+quantize -> dequantize a QArrayImpl parameter goes through when it is read, with the reference's cotangent rule) and
+`wkv_state_scan`.  The f32 element-wise work between them (token shift, lerps, rotary embedding, gates,
+normalisations, the loss) runs on the fused kernels of `_glue.py` by default; `PratchyaConfig.fused_glue=False` runs
+the same formulas as plain torch operations differentiated by torch.autograd, which is what the tests compare with.
 
 Parameters are dense master tensors that are quantized on their grid every time they are used (the
 benchmark configuration trains bf16/f32 masters); the reference stores the fp8 triple itself as the
