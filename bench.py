@@ -793,6 +793,28 @@ def run_profile_case(name: str):
         dy = torch.randn(shape, device="cuda", generator=g)
         for _ in range(3):
             wkv_state_scan(None, *ins, heads)[1].backward(dy)
+    elif name == "glue":
+        # the fused element-wise kernels of the RWKV-7 block, forward and backward, on 8 x 1024 tokens of 2048 channels
+        # (67 MB per array: the prepare kernels move 14 and 21 of them)
+        from pratchya_b200._nnx_impl._glue import rms_norm, token_shift_lerp, wkv_finish, wkv_prepare
+        bsz, steps, heads = 8, 1024, 32
+        c = heads * 64
+        g = torch.Generator(device="cuda").manual_seed(0)
+        mk = lambda: torch.randn(bsz, steps, c, device="cuda", generator=g).requires_grad_(True)
+        par = lambda *s: torch.randn(*s, device="cuda", generator=g).requires_grad_(True)
+        t = torch.arange(steps, device="cuda", dtype=torch.float32)
+        freqs = torch.outer(t, 1.0 / (1e4 ** (torch.arange(0, 64, 2, device="cuda", dtype=torch.float32) / 64)))
+        cos_tab, sin_tab = torch.cos(freqs), torch.sin(freqs)
+        x, state, mu = mk(), par(bsz, 1, c), par(6, c)
+        outs = token_shift_lerp(x, state, mu)
+        torch.autograd.backward(list(outs), [torch.ones_like(o) for o in outs])
+        ins = [mk() for _ in range(7)]
+        pre = wkv_prepare(*ins[:5], ins[5], ins[6], cos_tab, sin_tab, par(1, c), par(1, c), heads)
+        torch.autograd.backward(list(pre), [torch.ones_like(o) for o in pre])
+        fin = wkv_finish(mk(), mk(), mk(), mk(), mk(), par(c), par(c), par(1, c), heads * 1e-5, heads)
+        fin.backward(torch.ones_like(fin))
+        y = rms_norm(mk(), par(1, c), 1e-6)
+        y.backward(torch.ones_like(y))
     elif name == "gemm_full":
         m, n, k = M, N, K                                   # the benchmark's own launch, for DRAM-byte counters only
         x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
@@ -820,7 +842,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--headline-only", action="store_true",
                     help="only the headline step and its per-kernel pass (for launch lists under a profiler): no e2e, triple, scaleout or CPU leg")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "transposed", "dequantize", "wkv7", "wkv7_backward"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "transposed", "dequantize", "wkv7", "wkv7_backward", "glue"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
     ap.add_argument("--skip-model-step", action="store_true", help="leave out the end-to-end training-step record (about half a minute)")
     ap.add_argument("--cpu-child", action="store_true", help=argparse.SUPPRESS)

@@ -17,8 +17,8 @@ namespace {
 
 constexpr int kGlueThreads = 256;
 constexpr int kGlueH = 64;               // head size of the rotary / normalisation kernels
-constexpr int kLerpTileRows = 256;       // tokens per CTA of the lerp backward kernel
-constexpr int kPrepTileRows = 128;       // tokens per warp of the prepare backward kernel
+constexpr int kLerpTileRows = 64;        // tokens per CTA of the lerp backward kernel
+constexpr int kPrepTileRows = 32;        // tokens per warp of the prepare backward kernel
 constexpr int kMaxMix = 8;
 
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -115,13 +115,23 @@ __global__ void __launch_bounds__(kGlueThreads) shift_lerp_bwd_kernel(const Shif
   for (int k = 0; k < NMIX; ++k) st4(p.partial + ((size_t)blockIdx.y * NMIX + k) * p.C + c, acc[k]);
 }
 
-// out[j] = sum over tiles of partial[tile][j], in tile order
+// out[j] = sum over tiles of partial[tile][j]: eight partial sums per column (tiles g, g + 8, ...), added in a fixed order.
+// A block takes 32 columns; out may be the first tile's slot of partial (a column is read and written by its block only).
 __global__ void __launch_bounds__(kGlueThreads) reduce_partials_kernel(const float* partial, float* out, int tiles, int64_t n) {
-  const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= n) return;
+  __shared__ float red[kGlueThreads / 32][32];
+  const int cx = threadIdx.x & 31, gy = threadIdx.x >> 5;
+  const int64_t j = (int64_t)blockIdx.x * 32 + cx;
   float s = 0.0f;
-  for (int t = 0; t < tiles; ++t) s += partial[(size_t)t * n + j];
-  out[j] = s;
+  if (j < n)
+    for (int t = gy; t < tiles; t += kGlueThreads / 32) s += partial[(size_t)t * n + j];
+  red[gy][cx] = s;
+  __syncthreads();
+  if (gy == 0 && j < n) {
+    float r = red[0][cx];
+#pragma unroll
+    for (int g = 1; g < kGlueThreads / 32; ++g) r += red[g][cx];
+    out[j] = r;
+  }
 }
 
 // ---- TimeMix between its linears and the scan ----------------------------------------------------------------
@@ -301,7 +311,7 @@ extern "C" int pb_token_shift_lerp_bwd(const float* const* g, const float* x, co
   else shift_lerp_bwd_kernel<1><<<grid, kGlueThreads, 0, st>>>(p);
   PB_LAUNCH_CHECK("shift_lerp_bwd_kernel");
   const int64_t n = (int64_t)n_mix * channels;
-  reduce_partials_kernel<<<(unsigned)((n + kGlueThreads - 1) / kGlueThreads), kGlueThreads, 0, st>>>(p.partial, dmu, tiles, n);
+  reduce_partials_kernel<<<(unsigned)((n + 31) / 32), kGlueThreads, 0, st>>>(p.partial, dmu, tiles, n);
   PB_LAUNCH_CHECK("reduce_partials_kernel");
   return PB_OK;
 }
@@ -365,7 +375,7 @@ extern "C" int pb_wkv_prepare_bwd(const float* r_raw, const float* k_raw, const 
   PB_LAUNCH_CHECK("wkv_prepare_bwd_kernel");
   // partial is [tiles][2][C]: the two parameters' sums come out as one [2][C] array, split below
   float* sums = static_cast<float*>(workspace);      // reduced in place into the first tile's slot after the reduction reads it
-  reduce_partials_kernel<<<(unsigned)((2 * C + kGlueThreads - 1) / kGlueThreads), kGlueThreads, 0, st>>>(p.partial, sums, tiles, 2 * C);
+  reduce_partials_kernel<<<(unsigned)((2 * C + 31) / 32), kGlueThreads, 0, st>>>(p.partial, sums, tiles, 2 * C);
   PB_LAUNCH_CHECK("reduce_partials_kernel");
   PB_CUDA_TRY(cudaMemcpyAsync(d_rk_mult, sums, (size_t)C * sizeof(float), cudaMemcpyDeviceToDevice, st));
   PB_CUDA_TRY(cudaMemcpyAsync(d_mix_amt, sums + C, (size_t)C * sizeof(float), cudaMemcpyDeviceToDevice, st));

@@ -17,7 +17,8 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kH = 64;
-constexpr int kTileRows = 256;            // tokens per CTA / per warp where a parameter gradient is summed over tokens
+constexpr int kTileRows = 32;             // tokens per CTA / per warp where a parameter gradient is summed over tokens
+constexpr int kStatTileSteps = 256;       // timesteps per CTA of the group statistics
 
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
@@ -27,12 +28,23 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// out[j] = sum over tiles of partial[tile][j]: eight partial sums per column (tiles g, g + 8, ...), added in a fixed order.
+// A block takes 32 columns; out may be the first tile's slot of partial (a column is read and written by its block only).
 __global__ void __launch_bounds__(kThreads) reduce_tiles_kernel(const float* partial, float* out, int tiles, int64_t n) {
-  const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= n) return;
+  __shared__ float red[kWarps][32];
+  const int cx = threadIdx.x & 31, gy = threadIdx.x >> 5;
+  const int64_t j = (int64_t)blockIdx.x * 32 + cx;
   float s = 0.0f;
-  for (int t = 0; t < tiles; ++t) s += partial[(size_t)t * n + j];
-  out[j] = s;
+  if (j < n)
+    for (int t = gy; t < tiles; t += kWarps) s += partial[(size_t)t * n + j];
+  red[gy][cx] = s;
+  __syncthreads();
+  if (gy == 0 && j < n) {
+    float r = red[0][cx];
+#pragma unroll
+    for (int g = 1; g < kWarps; ++g) r += red[g][cx];
+    out[j] = r;
+  }
 }
 
 // ---- RMSNorm: y = (x * rsqrt(mean(x^2) + eps)) * scale, one warp per row --------------------------------------
@@ -118,16 +130,16 @@ __global__ void __launch_bounds__(kThreads) relu2_bwd_kernel(const float4* g, co
 // ---- TimeMix after the scan ------------------------------------------------------------------------------------
 // GroupNorm as flax builds it on [B, T, C] with one group per head (_module.py:118-123): per (batch element, head)
 // the mean and the variance E[x^2] - E[x]^2 (clamped at 0) over the T x 64 values.
-// group_sums_kernel: partial[b][n][tile][2] = (sum, sum of squares) over a tile of kTileRows timesteps.
+// group_sums_kernel: partial[b][n][tile][2] = (sum, sum of squares) over a tile of kStatTileSteps timesteps.
 __global__ void __launch_bounds__(kThreads) group_sums_kernel(const float* y, float* partial, int T, int N, int tiles) {
   __shared__ float red[kWarps][2];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int bn = blockIdx.x, tile = blockIdx.y;
   const int b = bn / N, n = bn - b * N;
   const int C = N * kH;
-  const int t1 = min(T, (tile + 1) * kTileRows);
+  const int t1 = min(T, (tile + 1) * kStatTileSteps);
   float s = 0.f, q = 0.f;
-  for (int t = tile * kTileRows + warp; t < t1; t += kWarps) {
+  for (int t = tile * kStatTileSteps + warp; t < t1; t += kWarps) {
     const float* p = y + ((size_t)b * T + t) * C + n * kH + lane;
     const float a = p[0], c = p[32];
     s += a + c; q += a * a + c * c;
@@ -346,7 +358,7 @@ extern "C" int pb_rms_norm_bwd(const float* dy, const float* x, const float* sca
   const dim3 grid((unsigned)((channels / 4 + kThreads - 1) / kThreads), (unsigned)tiles);
   rms_norm_bwd_dscale_kernel<<<grid, kThreads, 0, st>>>(dy, x, inv_rms, static_cast<float*>(workspace), rows, (int)channels);
   PB_LAUNCH_CHECK("rms_norm_bwd_dscale_kernel");
-  reduce_tiles_kernel<<<(unsigned)((channels + kThreads - 1) / kThreads), kThreads, 0, st>>>(static_cast<const float*>(workspace), dscale, tiles, channels);
+  reduce_tiles_kernel<<<(unsigned)((channels + 31) / 32), kThreads, 0, st>>>(static_cast<const float*>(workspace), dscale, tiles, channels);
   PB_LAUNCH_CHECK("reduce_tiles_kernel");
   return PB_OK;
 }
@@ -380,7 +392,7 @@ static int check_finish(const char* who, int64_t batch, int64_t steps, int64_t h
 // workspace of the forward call: the per-tile sums of the group statistics
 extern "C" size_t pb_wkv_finish_workspace_size(int64_t batch, int64_t steps, int64_t heads, int head_dim) {
   if (batch <= 0 || steps <= 0 || heads <= 0 || head_dim != kH) return 0;
-  return (size_t)batch * heads * ((steps + kTileRows - 1) / kTileRows) * 2 * sizeof(float);
+  return (size_t)batch * heads * ((steps + kStatTileSteps - 1) / kStatTileSteps) * 2 * sizeof(float);
 }
 
 extern "C" int pb_wkv_finish(const float* y, const float* r, const float* k, const float* v, const float* gate,
@@ -393,7 +405,7 @@ extern "C" int pb_wkv_finish(const float* y, const float* r, const float* k, con
   const size_t need = pb_wkv_finish_workspace_size(batch, steps, heads, head_dim);
   if (!workspace || workspace_bytes < need) return fail(PB_ERR_WORKSPACE_TOO_SMALL, "pb_wkv_finish: needs %zu bytes of workspace, got %zu", need, workspace_bytes);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int tiles = (int)((steps + kTileRows - 1) / kTileRows);
+  const int tiles = (int)((steps + kStatTileSteps - 1) / kStatTileSteps);
   const int groups = (int)(batch * heads);
   group_sums_kernel<<<dim3((unsigned)groups, (unsigned)tiles), kThreads, 0, st>>>(y, static_cast<float*>(workspace), (int)steps, (int)heads, tiles);
   PB_LAUNCH_CHECK("group_sums_kernel");
@@ -442,7 +454,7 @@ extern "C" int pb_wkv_finish_bwd(const float* g, const float* y, const float* r,
   const int64_t warps = (int64_t)tiles * heads;
   wkv_finish_bwd_main_kernel<<<(unsigned)((warps + kWarps - 1) / kWarps), kThreads, 0, st>>>(p);
   PB_LAUNCH_CHECK("wkv_finish_bwd_main_kernel");
-  reduce_tiles_kernel<<<(unsigned)((3 * C + kThreads - 1) / kThreads), kThreads, 0, st>>>(partial, partial, tiles, 3 * C);
+  reduce_tiles_kernel<<<(unsigned)((3 * C + 31) / 32), kThreads, 0, st>>>(partial, partial, tiles, 3 * C);
   PB_LAUNCH_CHECK("reduce_tiles_kernel");
   PB_CUDA_TRY(cudaMemcpyAsync(d_gn_scale, partial, (size_t)C * 4, cudaMemcpyDeviceToDevice, st));
   PB_CUDA_TRY(cudaMemcpyAsync(d_gn_bias, partial + C, (size_t)C * 4, cudaMemcpyDeviceToDevice, st));
