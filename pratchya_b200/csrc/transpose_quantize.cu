@@ -520,6 +520,135 @@ transpose_quantize1024_bf16_ring_kernel(const __grid_constant__ CUtensorMap map_
   }
 }
 
+// The same persistent kernel for f32 input (what the reference's model quantizes: its activations are f32).  A tile is
+// still 1024 rows of 64 bytes, now 16 f32 columns: a thread keeps 32 rows of ONE column, its maximum is an f32
+// maximum, and pairs of rows go through the f32 division straight to a bf16 pair.  Everything else (three TMA-filled
+// buffers, two groups of 512 threads, the swapped row pairs of the upper half-warp, the two-level maxima) is as above.
+template <int FMT>
+__global__ void __launch_bounds__(1024, 1)
+transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x, uint8_t* __restrict__ q_t, uint8_t* __restrict__ sc8,
+                                       float* __restrict__ sc32, int rows, int cols, int tiles_x, int tiles_y, int n_tiles) {
+  extern __shared__ uint8_t ring_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ring_raw) + 1023) & ~(uintptr_t)1023);
+  float (*part_amax)[32][16] = reinterpret_cast<float (*)[32][16]>(smem + kRingBufs * kRingTileBytes);   // [group * 2 + parity]
+  float (*block_amax)[8][16] = reinterpret_cast<float (*)[8][16]>(smem + kRingBufs * kRingTileBytes + kRingPartBytes);
+  const uint32_t s_tiles = (uint32_t)__cvta_generic_to_shared(smem);
+  const uint32_t s_bar = s_tiles + kRingBufs * kRingTileBytes + kRingPartBytes + kRingBlockBytes;
+  const int tid = threadIdx.x, grp = tid >> 9, gt = tid & 511;
+
+  if (tid == 0) {
+    for (int b = 0; b < kRingBufs; ++b) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_bar + 8u * b));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  auto issue = [&](int seq) {
+    const int tl = blockIdx.x + seq * gridDim.x;
+    if (tl >= n_tiles) return;
+    const int cx = tl % tiles_x, rest = tl / tiles_x, ry = rest % tiles_y, z = rest / tiles_y;
+    const uint32_t bar = s_bar + 8u * (seq % kRingBufs), dst = s_tiles + (uint32_t)(seq % kRingBufs) * kRingTileBytes;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)kRingTileBytes) : "memory");
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                   ::"r"(dst + j * 16384u), "l"(&map_x), "r"(cx * 16), "r"(z * rows + ry * 1024 + j * 256), "r"(bar) : "memory");
+  };
+  if (tid == 0) { issue(0); issue(1); issue(2); }
+
+  const int cp = gt & 15, blk = (gt >> 4) & 7, quarter = gt >> 7;        // cp: the column of the tile this thread owns
+  const int row_first = blk * 128 + quarter * 32;
+  const int swap = (gt >> 4) & 1;                 // upper half-warp: rows in swapped pairs
+  const int nsg = rows >> 10;
+  int local = 0;
+  for (int seq = grp; blockIdx.x + seq * (int)gridDim.x < n_tiles; seq += 2, ++local) {
+    const int tl = blockIdx.x + seq * gridDim.x;
+    const int cx = tl % tiles_x, rest = tl / tiles_x, ry = rest % tiles_y, z = rest / tiles_y;
+    const int c0 = cx * 16, r0 = ry * 1024;
+    const bool landed = ring_wait(s_bar + 8u * (seq % kRingBufs), (uint32_t)(seq / kRingBufs) & 1u);
+    if (!landed) atomicExch(&g_tq_status, (unsigned int)PB_ERR_DEVICE_TIMEOUT);
+    const uint8_t* tile = smem + (size_t)(seq % kRingBufs) * kRingTileBytes;
+    float w[32];
+    float cm = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      w[i] = *reinterpret_cast<const float*>(tile + (row_first + (i ^ swap)) * 64 + cp * 4);
+      cm = fmaxf(cm, fabsf(w[i]));
+    }
+    float (*pa)[16] = part_amax[grp * 2 + (local & 1)];
+    pa[blk * 4 + quarter][cp] = cm;
+    int give_up;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbarrier.cta.red.or.pred q, %2, 512, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(give_up) : "r"(landed ? 0 : 1), "r"(grp + 1) : "memory");
+    if (give_up) break;
+    if (gt == 0) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the group's reads of the buffer come before the copy that refills it
+      issue(seq + kRingBufs);
+    }
+    const float mb = fmaxf(fmaxf(pa[blk * 4][cp], pa[blk * 4 + 1][cp]), fmaxf(pa[blk * 4 + 2][cp], pa[blk * 4 + 3][cp]));
+    float (*pb)[16] = block_amax[grp * 2 + (local & 1)];
+    if (quarter == 0) pb[blk][cp] = mb;
+    asm volatile("barrier.cta.sync %0, 512;" ::"r"(grp + 1) : "memory");
+    float mg = fmaxf(fmaxf(pb[0][cp], pb[1][cp]), fmaxf(pb[2][cp], pb[3][cp]));
+    mg = fmaxf(mg, fmaxf(fmaxf(pb[4][cp], pb[5][cp]), fmaxf(pb[6][cp], pb[7][cp])));
+    uint32_t sbv; float D;
+    block_scale(mb, mg, sbv, D);
+    const size_t col = (size_t)z * cols + c0 + cp;
+    const size_t grpi = col * nsg + ry;
+    if (quarter == 0) {
+      sc8[grpi * 8 + blk] = (uint8_t)sbv;
+      if (blk == 0) sc32[grpi] = mg;
+    }
+    const float rcp = __frcp_rn(D);
+    const float2 nD2 = make_float2(-D, -D), r2 = make_float2(rcp, rcp);
+    uint32_t out[8];
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      // rows i..i+3 of the column; the registers of the upper half-warp hold each pair of rows swapped
+      const uint32_t p0 = div_hoisted_pack2(swap ? w[i + 1] : w[i], swap ? w[i] : w[i + 1], nD2, r2);
+      const uint32_t p1 = div_hoisted_pack2(swap ? w[i + 3] : w[i + 2], swap ? w[i + 2] : w[i + 3], nD2, r2);
+      out[i >> 2] = bf16x2_to_fp8x2<FMT>(p0) | (bf16x2_to_fp8x2<FMT>(p1) << 16);
+    }
+    uint8_t* o = q_t + col * rows + r0 + row_first;
+    asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(o), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7]) : "memory");
+  }
+}
+
+template <int FMT>
+int launch_one_pass_f32_ring(const void* x, uint8_t* q_t, uint8_t* sc8, float* sc32, int64_t batch, int64_t rows, int64_t cols, cudaStream_t st) {
+  using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  EncodeFn encode = reinterpret_cast<EncodeFn>(tensor_map_encoder());
+  if (!encode) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)(batch * rows)};
+  const cuuint64_t strides[1] = {(cuuint64_t)(cols * 4)};
+  const cuuint32_t box[2] = {16, 256};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(x), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(PB_ERR_CUDA, "cuTensorMapEncodeTiled (transposed quantizer, f32) failed with CUresult %d", (int)r);
+  static std::mutex mu;
+  static bool configured[64] = {false};
+  int dev = 0;
+  PB_CUDA_TRY(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      PB_CUDA_TRY(cudaFuncSetAttribute(transpose_quantize1024_f32_ring_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem));
+      configured[dev] = true;
+    }
+  }
+  const int tiles_x = (int)(cols / 16), tiles_y = (int)(rows / 1024);
+  const int64_t n_tiles = (int64_t)tiles_x * tiles_y * batch;
+  const int grid = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
+  transpose_quantize1024_f32_ring_kernel<FMT><<<grid, 1024, kRingSmem, st>>>(map, q_t, sc8, sc32, (int)rows, (int)cols, tiles_x, tiles_y, (int)n_tiles);
+  PB_LAUNCH_CHECK("transpose_quantize1024_f32_ring_kernel");
+  return PB_OK;
+}
+
 template <int FMT>
 int launch_one_pass_bf16_ring(const void* x, uint8_t* q_t, uint8_t* sc8, float* sc32, int64_t batch, int64_t rows, int64_t cols, cudaStream_t st) {
   using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -635,6 +764,10 @@ extern "C" int pb_quantize_transposed(const void* x, int x_dtype, int64_t batch,
         return out_format == PB_E4M3 ? launch_one_pass_bf16<PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
                                      : launch_one_pass_bf16<PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
       }
+      const bool ring32 = batch * rows < (1ll << 31) && (cols / 16) * (rows / 1024) * batch >= 2 * sm_count() && env_switch("PB_TQ_RING", 1) != 0;
+      if (ring32)
+        return out_format == PB_E4M3 ? launch_one_pass_f32_ring<PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
+                                     : launch_one_pass_f32_ring<PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
       return out_format == PB_E4M3 ? launch_one_pass<float, PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
                                    : launch_one_pass<float, PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
     }

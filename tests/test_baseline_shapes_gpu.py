@@ -132,12 +132,13 @@ def test_config3_quantizers_at_full_size(built_lib):
     assert_token_band_bits((q2, s2, t2), x, 5120)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("shape,fmt", [((4096, 4096), "e4m3"), ((3, 2048, 2048), "e5m2"), ((1024, 16384), "e4m3")])
-def test_persistent_transposed_quantizer_against_the_full_oracle(built_lib, shape, fmt):
-    """Shapes with enough 1024-row x 32-column tiles to run the persistent TMA-staged form of the single-pass
-    transposed quantizer, compared with the oracle over the whole array (not bands), twice in a row (the second
-    call reuses the kernel's barriers and buffers from a fresh launch)."""
-    x = seeded(shape, 61, scale=3.0)
+def test_persistent_transposed_quantizer_against_the_full_oracle(built_lib, shape, fmt, dtype):
+    """Shapes with enough 1024-row x 64-byte tiles (32 bf16 or 16 f32 columns) to run the persistent TMA-staged form of
+    the single-pass transposed quantizer, compared with the oracle over the whole array (not bands), twice in a row
+    (the second call reuses the kernel's barriers and buffers from a fresh launch)."""
+    x = seeded(shape, 61, scale=3.0, dtype=dtype)
     x.view(-1)[::4097] *= 64.0                      # outliers
     x[..., :1024, 5] = 0.0                         # an all-zero super-group
     xn = to_np(x)
