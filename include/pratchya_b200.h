@@ -282,6 +282,18 @@ PB_API size_t pb_token_shift_lerp_bwd_workspace_size(int64_t batch, int64_t step
 PB_API int pb_token_shift_lerp_bwd(const float* const* g, const float* x, const float* state, const float* mu,
                             int64_t batch, int64_t steps, int64_t channels, int n_mix,
                             float* dx, float* dstate, float* dmu, void* workspace, size_t workspace_bytes, void* stream);
+/* Token shift and lerps fused into the activation quantizers of the Linears that consume the mixes
+ * (Linear.__call__, pratchya/_nnx_impl/_module.py:46-47, applied to the mixes of :137-151 and :240-247): with
+ * v_k = x + (prev - x) * mu[k] as above, every mix k < n_mix leaves as the triple of quantize_impl(v_k, (1,128)),
+ *   q [n_mix][batch*steps][channels] e4m3, sc8 [n_mix][batch*steps*channels/128], sc32 [n_mix][batch*steps*channels/1024],
+ * and every mix whose bit is set in transposed_mask also as the triple of quantize_impl(v_k^T, (1,128)) (what
+ * pb_quantize_transposed gives for v_k), stacked in the order of the set bits:
+ *   q_t [n_t][channels][batch*steps], sc8_t [n_t][channels*batch*steps/128], sc32_t [n_t][channels*batch*steps/1024].
+ * No v_k is written.  The bytes are those of pb_token_shift_lerp followed by pb_quantize / pb_quantize_transposed.
+ * channels a multiple of 1024; with a transposed form steps a multiple of 1024 and q_t 32-byte aligned. */
+PB_API int pb_shift_lerp_quantize(const float* x, const float* state, const float* mu, int64_t batch, int64_t steps, int64_t channels,
+                           int n_mix, uint8_t* q, uint8_t* sc8, float* sc32, unsigned int transposed_mask,
+                           uint8_t* q_t, uint8_t* sc8_t, float* sc32_t, void* stream);
 /* TimeMix between its linears and its scan (:157-184), per token and head of 64 channels:
  *   r, k    = rotary embedding of r_raw, k_raw with the angle tables cos_tab / sin_tab [steps, 32] (:275-283)
  *   iclr    = sigmoid(iclr_raw);  decay = exp(-exp(d))

@@ -69,6 +69,89 @@ def token_shift_lerp(x, state, mu):
     return _ShiftLerpFn.apply(_f32c(x), st, _f32c(mu))
 
 
+class QuantizedMix:
+    """One output of token_shift_lerp_quantized: everything a Linear needs of its input, without the input.
+    `handle` is a [B, T, C] f32 tensor of stride zero (no memory behind it) that carries the autograd edge: a Linear
+    takes it as its x, never reads it, and returns the cotangent of the mix for it.  `row` is the triple of
+    quantize_impl(mix, (1,128)) over [B*T, C]; `tokens` the triple of quantize_impl(mix^T, (1,128)) or None."""
+    __slots__ = ("handle", "row", "tokens")
+
+    def __init__(self, handle, row, tokens):
+        self.handle, self.row, self.tokens = handle, row, tokens
+
+    @property
+    def shape(self):
+        return self.handle.shape
+
+
+class _ShiftLerpQuantFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, state, mu, mask):
+        lib = _lib.load()
+        bsz, steps, chans = x.shape
+        n_mix, rows = mu.shape[0], bsz * steps
+        n_t = bin(mask).count("1")
+        dev = x.device
+        groups = rows * chans // 1024
+        with torch.cuda.device(dev):
+            q = torch.empty((n_mix, rows, chans), dtype=torch.float8_e4m3fn, device=dev)
+            sc8 = torch.empty((n_mix, groups, 8), dtype=torch.float8_e8m0fnu, device=dev)
+            sc32 = torch.empty((n_mix, groups, 1, 1), dtype=torch.float32, device=dev)
+            q_t = torch.empty((n_t, chans, rows), dtype=torch.float8_e4m3fn, device=dev)
+            sc8_t = torch.empty((n_t, groups, 8), dtype=torch.float8_e8m0fnu, device=dev)
+            sc32_t = torch.empty((n_t, groups, 1, 1), dtype=torch.float32, device=dev)
+            check(lib.pb_shift_lerp_quantize(x.data_ptr(), state.data_ptr() if state is not None else None, mu.data_ptr(), bsz, steps, chans, n_mix,
+                                             q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(), mask,
+                                             q_t.data_ptr() if n_t else None, sc8_t.data_ptr() if n_t else None, sc32_t.data_ptr() if n_t else None,
+                                             _stream(dev)))
+            handles = tuple(torch.zeros(1, dtype=torch.float32, device=dev).expand(bsz, steps, chans) for _ in range(n_mix))
+        ctx.save_for_backward(x, state, mu)
+        ctx.mark_non_differentiable(q, sc8, sc32, q_t, sc8_t, sc32_t)
+        return (*handles, q, sc8, sc32, q_t, sc8_t, sc32_t)
+
+    @staticmethod
+    def backward(ctx, *gs):
+        n_mix = ctx.saved_tensors[2].shape[0]
+        return (*_ShiftLerpFn.backward(ctx, *gs[:n_mix]), None)
+
+
+def token_shift_lerp_quantized(x, state, mu, transposed=()):
+    """token_shift_lerp whose mixes leave as fp8 triples for the Linears that consume them (a Linear quantizes its
+    input on (1,128) first, _module.py:46-47): returns one QuantizedMix per row of mu.  `transposed`: the indices of
+    the mixes that also get the triple of their transpose (the wgrad operand of a (128,128) Linear); it needs
+    T % 1024 == 0.  C must be a multiple of 1024.  The bytes are those of token_shift_lerp + quantize_impl /
+    quantize_transposed_impl; the mixes themselves are never written."""
+    if x.dim() != 3 or mu.dim() != 2 or mu.shape[1] != x.shape[2] or mu.shape[0] not in (1, 6):
+        raise ValueError(f"token_shift_lerp_quantized: x {tuple(x.shape)}, mu {tuple(mu.shape)}")
+    if not x.is_cuda:
+        raise RuntimeError("token_shift_lerp_quantized needs CUDA tensors: pratchya_b200 has no CPU path")
+    st = None
+    if state is not None:
+        if tuple(state.shape) != (x.shape[0], 1, x.shape[2]):
+            raise ValueError(f"token_shift_lerp_quantized: state {tuple(state.shape)} for x {tuple(x.shape)}")
+        st = _f32c(state)
+    n_mix = mu.shape[0]
+    mask = 0
+    for k in transposed:
+        if not 0 <= k < n_mix:
+            raise ValueError(f"token_shift_lerp_quantized: transposed index {k} of {n_mix} mixes")
+        mask |= 1 << k
+    out = _ShiftLerpQuantFn.apply(_f32c(x), st, _f32c(mu), mask)
+    handles, (q, sc8, sc32, q_t, sc8_t, sc32_t) = out[:n_mix], out[n_mix:]
+    mixes, slot = [], 0
+    for k in range(n_mix):
+        tokens = None
+        if mask >> k & 1:
+            tokens, slot = (q_t[slot], sc8_t[slot], sc32_t[slot]), slot + 1
+        mixes.append(QuantizedMix(handles[k], (q[k], sc8[k], sc32[k]), tokens))
+    return tuple(mixes)
+
+
+def can_quantize_mixes(x, want_transposed):
+    """Whether token_shift_lerp_quantized applies to x [B, T, C]."""
+    return x.dim() == 3 and x.shape[2] % 1024 == 0 and x.numel() > 0 and (not want_transposed or x.shape[1] % 1024 == 0)
+
+
 class _WkvPrepareFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, r_raw, k_raw, d, iclr_raw, v_prime, v0, nu_raw, cos_tab, sin_tab, rk_mult, mix_amt, n_head):

@@ -19,7 +19,7 @@ from dataclasses import dataclass
 import torch
 
 from .._qualia import _ops
-from ._glue import relu2, rms_norm, token_shift_lerp, wkv_finish, wkv_prepare
+from ._glue import can_quantize_mixes, relu2, rms_norm, token_shift_lerp, token_shift_lerp_quantized, wkv_finish, wkv_prepare
 from ._glue import smoothed_cross_entropy as fused_cross_entropy
 from ._module import linear_fp8
 from ._wkv7 import wkv_state_scan
@@ -171,7 +171,11 @@ class TimeMix(torch.nn.Module):                      # _module.py:92-225
         bsz, steps, c = x.shape
         n, h, blk = self.n_head, self.head_dim, self.cfg.blksize
         mu = read_param(self.mu, (1, blk))
-        if self.cfg.fused_glue:
+        if self.cfg.fused_glue and can_quantize_mixes(x, torch.is_grad_enabled()):
+            # every mix only feeds linears: they leave the lerp kernel as fp8 triples (the three that feed a (128,128)
+            # kernel also in the token-major form its wgrad wants) and are never written as f32
+            x_r, x_d, x_k, x_v, x_i, x_g = token_shift_lerp_quantized(x, tm_state, mu, (0, 2, 3) if torch.is_grad_enabled() else ())
+        elif self.cfg.fused_glue:
             x_r, x_d, x_k, x_v, x_i, x_g = token_shift_lerp(x, tm_state, mu)
         else:
             x_shifted = torch.cat([tm_state, x[:, :-1, :]], dim=1)
@@ -228,7 +232,9 @@ class ChannelMix(torch.nn.Module):                   # _module.py:228-258
 
     def forward(self, x, cm_state):
         mu_x = read_param(self.mu_x, (1, self.blk))
-        if self.fused_glue:
+        if self.fused_glue and can_quantize_mixes(x, torch.is_grad_enabled()):
+            x_k = token_shift_lerp_quantized(x, cm_state, mu_x, (0,) if torch.is_grad_enabled() else ())[0]
+        elif self.fused_glue:
             x_k = token_shift_lerp(x, cm_state, mu_x)[0]
         else:
             x_shifted = torch.cat([cm_state, x[:, :-1, :]], dim=1)

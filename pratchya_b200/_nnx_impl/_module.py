@@ -159,7 +159,7 @@ class _LinearFn(torch.autograd.Function):
     grid, as the reference returns them (:637-640, :522-526)."""
 
     @staticmethod
-    def forward(ctx, x, weight, grid, fake_quant_output, recipe, grad_format, for_backward=True, prepared=None):
+    def forward(ctx, x, weight, grid, fake_quant_output, recipe, grad_format, for_backward=True, prepared=None, prepared_x=None):
         a, b = grid
         x2 = x.reshape(-1, x.shape[-1])
         if prepared is not None and "wq" in prepared:
@@ -172,7 +172,12 @@ class _LinearFn(torch.autograd.Function):
         # A (128,1) weight (LoRA, gate, lm_head) has one scale per column and 128 rows, which no 128-deep block
         # along its columns can carry: its forward runs on the tensor cores, its backward on the literal recipe.
         want_xt = for_backward and recipe == "fp8" and (a, b) == (128, 128) and x2.shape[0] % 1024 == 0
-        if want_xt:       # both forms of x in one call (x itself is not kept for the backward pass)
+        if prepared_x is not None:      # x arrives quantized (its producer wrote the triples); x itself is a handle that is not read
+            xq, xt = prepared_x
+            if a != 128 or xq[0].shape != x2.shape or (want_xt and xt is None):
+                raise ValueError("linear_fp8: the quantized input does not fit this layer (grid (1,128), same shape, "
+                                 "with its transposed form when a tensor-core backward pass follows)")
+        elif want_xt:     # both forms of x in one call (x itself is not kept for the backward pass)
             xq, xt = _ops.quantize_dual_impl(x2)
         else:
             xq, xt = _ops.quantize_impl(x2, (1, a)), None
@@ -229,10 +234,10 @@ class _LinearFn(torch.autograd.Function):
             gw = _ops._matmul_f32(x_hat.t(), g32)
         gx = _ops.fake_quantize_impl(gx, (1, a), torch.float32)                                  # :637 then :522-526
         gw = _ops.dequantize_impl(*_ops.quantize_impl(gw, ctx.grid), torch.float32, ctx.grid)    # :638; the optimizer dequantizes it
-        return gx.reshape(ctx.x_shape).to(ctx.x_dtype), gw.to(ctx.w_dtype), None, None, None, None, None, None
+        return gx.reshape(ctx.x_shape).to(ctx.x_dtype), gw.to(ctx.w_dtype), None, None, None, None, None, None, None
 
 
-def linear_fp8(x: torch.Tensor, weight: torch.Tensor, tgrid=(128, 128), *, fake_quant_output: bool = True,
+def linear_fp8(x, weight: torch.Tensor, tgrid=(128, 128), *, fake_quant_output: bool = True,
                recipe: str = "fp8", grad_format: str = "e4m3", prepared: dict | None = None) -> torch.Tensor:
     """y = Linear(x) with a dense master `weight` [fan_in, fan_out] that is quantized on `tgrid` in
     the forward pass; differentiable in x and weight.  `grad_format="e5m2"` stores dY in e5m2
@@ -243,5 +248,8 @@ def linear_fp8(x: torch.Tensor, weight: torch.Tensor, tgrid=(128, 128), *, fake_
         raise ValueError("recipe must be 'fp8' or 'reference'")
     # X^T is quantized in the forward pass only when a backward pass can follow (not under torch.no_grad, as in the first
     # pass of a recomputed block)
+    prepared_x = None
+    if hasattr(x, "handle"):          # a QuantizedMix: the input's fp8 triples from the kernel that produced it
+        x, prepared_x = x.handle, (x.row, x.tokens)
     for_backward = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
-    return _LinearFn.apply(x, weight, (int(tgrid[0]), int(tgrid[1])), fake_quant_output, recipe, grad_format, for_backward, prepared)
+    return _LinearFn.apply(x, weight, (int(tgrid[0]), int(tgrid[1])), fake_quant_output, recipe, grad_format, for_backward, prepared, prepared_x)

@@ -393,6 +393,72 @@ fake_quantize_row128_f32_kernel(const float4* __restrict__ x, typename Out4<OutT
   }
 }
 
+// The head of TimeMix and of ChannelMix (pratchya/_nnx_impl/_module.py:126-134, 235-237) fused into the activation
+// quantizers of the Linears that follow (Linear.__call__, :46-47): for mix k
+//     v_k[r][c] = x[r][c] + (prev[r][c] - x[r][c]) * mu[k][c],   prev = the token before, the carried state for a first token,
+// evaluated with the three roundings of the op-by-op form, and the kernel writes quantize_impl(v_k, (1,128)) for every k:
+// x is read once (its previous row comes from the cache) and no v_k goes to memory.  A warp owns one super-group of 1024
+// channels of one token and walks the mixes with x and prev - x in registers.
+template <int FMT>
+__global__ void __launch_bounds__(kRowThreads)
+shift_lerp_quantize_row128_kernel(const float4* __restrict__ x, const float4* __restrict__ state, const float4* __restrict__ mu,
+                                  uint32_t* __restrict__ q, uint8_t* __restrict__ sc8, float* __restrict__ sc32,
+                                  int64_t n_groups, int segs, int steps, int n_mix) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (int64_t)gridDim.x * (kRowThreads / 32);
+  for (int64_t g = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); g < n_groups; g += warps_total) {
+    const int64_t row = g / segs;
+    const int seg = (int)(g - row * segs);
+    const int64_t seq = row / steps;
+    const bool first = row - seq * steps == 0;
+    const float4* src = x + g * (kGroupElems / 4);
+    const float4* psrc = first ? (state ? state + (seq * segs + seg) * (kGroupElems / 4) : nullptr) : src - (int64_t)segs * (kGroupElems / 4);
+    float4 w[8], d[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) w[it] = __ldg(src + it * 32 + lane);
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const float4 pv = psrc ? __ldg(psrc + it * 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+      d[it] = make_float4(__fsub_rn(pv.x, w[it].x), __fsub_rn(pv.y, w[it].y), __fsub_rn(pv.z, w[it].z), __fsub_rn(pv.w, w[it].w));
+    }
+    for (int k = 0; k < n_mix; ++k) {
+      const float4* mk = mu + ((int64_t)k * segs + seg) * (kGroupElems / 4);
+      const int64_t gk = (int64_t)k * n_groups + g;
+      float4 v[8];
+      float m[8];
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const float4 c = __ldg(mk + it * 32 + lane);
+        v[it] = make_float4(__fadd_rn(w[it].x, __fmul_rn(d[it].x, c.x)), __fadd_rn(w[it].y, __fmul_rn(d[it].y, c.y)),
+                            __fadd_rn(w[it].z, __fmul_rn(d[it].z, c.z)), __fadd_rn(w[it].w, __fmul_rn(d[it].w, c.w)));
+        m[it] = fmaxf(fmaxf(fabsf(v[it].x), fabsf(v[it].y)), fmaxf(fabsf(v[it].z), fabsf(v[it].w)));
+      }
+      butterfly_max<8, 2>(m, lane);                 // m[0]: amax of block it_own over the warp
+      const int it_own = bitrev<3>(lane & 7);
+      float Mj = m[0];
+      Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 1));
+      Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 2));
+      Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 4));
+      uint32_t sb; float D;
+      block_scale(m[0], Mj, sb, D);
+      const float r = __frcp_rn(D);
+      if (lane < 8) sc8[gk * 8 + it_own] = (uint8_t)sb;
+      if (lane == 0) sc32[gk] = Mj;
+      uint32_t* dst = q + gk * (kGroupElems / 4);
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int srcl = bitrev<3>(it);
+        const float Di = __shfl_sync(0xffffffffu, D, srcl);
+        const float ri = __shfl_sync(0xffffffffu, r, srcl);
+        const float2 nD2 = make_float2(-Di, -Di), r2 = make_float2(ri, ri);
+        const uint32_t p0 = div_hoisted_pack2(v[it].x, v[it].y, nD2, r2);
+        const uint32_t p1 = div_hoisted_pack2(v[it].z, v[it].w, nD2, r2);
+        __stcs(dst + it * 32 + lane, bf16x2_to_fp8x2<FMT>(p0) | (bf16x2_to_fp8x2<FMT>(p1) << 16));
+      }
+    }
+  }
+}
+
 // The middle of ChannelMix (pratchya/_nnx_impl/_module.py:246-251) in one pass over the f32 product
 // y of its first Linear:  k = dq(q(y, (1,128))) in f32 (what Linear.__call__ returns for an f32 input,
 // :46-50), k = relu(k)^2 (:249), then the second Linear's own quantize_impl(k, (1,128)) (:46-47).  Both
@@ -796,6 +862,52 @@ extern "C" int pb_relu2_requantize(const void* y, int64_t rows, int64_t cols, in
     else    relu2_requantize_row128_f32_kernel<PB_E5M2, false><<<grid, kRowThreads, 0, st>>>((const float4*)y, (uint32_t*)q, sc8, sc32, n_groups, prep);
   }
   PB_LAUNCH_CHECK("relu2_requantize_row128_f32_kernel");
+  return PB_OK;
+}
+
+namespace pb {   // transpose_quantize.cu
+int launch_shift_lerp_transposed(const float* x, const float* state, const float* mu, uint8_t* q_t, uint8_t* sc8, float* sc32,
+                                 int64_t rows, int64_t steps, int64_t cols, cudaStream_t st);
+}
+
+extern "C" int pb_shift_lerp_quantize(const float* x, const float* state, const float* mu, int64_t batch, int64_t steps, int64_t channels,
+                                      int n_mix, uint8_t* q, uint8_t* sc8, float* sc32, unsigned int transposed_mask,
+                                      uint8_t* q_t, uint8_t* sc8_t, float* sc32_t, void* stream) {
+  if (!x || !mu || !q || !sc8 || !sc32) return fail(PB_ERR_NULL_POINTER, "pb_shift_lerp_quantize: x, mu, q, sc8 and sc32 must be non-null");
+  if (n_mix <= 0 || n_mix > 8) return fail(PB_ERR_UNSUPPORTED, "pb_shift_lerp_quantize: n_mix=%d (1..8)", n_mix);
+  if (batch <= 0 || steps <= 0 || channels <= 0 || channels % 1024 != 0 || steps > 0x7fffffffll)
+    return fail(PB_ERR_UNSUPPORTED, "pb_shift_lerp_quantize: batch=%lld steps=%lld channels=%lld: channels must be a positive multiple of 1024 "
+                "(whole super-groups per token)", (long long)batch, (long long)steps, (long long)channels);
+  const int64_t rows = batch * steps;
+  if (rows * (channels / 128) * n_mix > kMaxIndexed) return fail(PB_ERR_UNSUPPORTED, "pb_shift_lerp_quantize: too many blocks");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(state) & 15) || (reinterpret_cast<uintptr_t>(mu) & 15) ||
+      (reinterpret_cast<uintptr_t>(q) & 3))
+    return fail(PB_ERR_MISALIGNED, "pb_shift_lerp_quantize: x, state and mu must be 16-byte and q 4-byte aligned");
+  transposed_mask &= (1u << n_mix) - 1u;
+  if (transposed_mask) {
+    if (!q_t || !sc8_t || !sc32_t) return fail(PB_ERR_NULL_POINTER, "pb_shift_lerp_quantize: a transposed form was asked for without its outputs");
+    if (steps % 1024 != 0)
+      return fail(PB_ERR_UNSUPPORTED, "pb_shift_lerp_quantize: the transposed forms need steps %% 1024 == 0 (a 1024-token super-group inside one sequence), got %lld",
+                  (long long)steps);
+    if (reinterpret_cast<uintptr_t>(q_t) & 31) return fail(PB_ERR_MISALIGNED, "pb_shift_lerp_quantize: q_t must be 32-byte aligned");
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int segs = (int)(channels / 1024);
+  const int64_t n_groups = rows * segs;
+  const int grid = grid_for(n_groups * 32, kRowThreads, 4);
+  shift_lerp_quantize_row128_kernel<PB_E4M3><<<grid, kRowThreads, 0, st>>>(
+      reinterpret_cast<const float4*>(x), reinterpret_cast<const float4*>(state), reinterpret_cast<const float4*>(mu),
+      reinterpret_cast<uint32_t*>(q), sc8, sc32, n_groups, segs, (int)steps, n_mix);
+  PB_LAUNCH_CHECK("shift_lerp_quantize_row128_kernel");
+  int slot = 0;
+  for (int k = 0; k < n_mix; ++k) {
+    if (!(transposed_mask >> k & 1u)) continue;
+    const int64_t n = rows * channels;
+    if (int s = pb::launch_shift_lerp_transposed(x, state, mu + (int64_t)k * channels, q_t + slot * n, sc8_t + slot * (n / 128), sc32_t + slot * (n / 1024),
+                                                 rows, steps, channels, st))
+      return s;
+    ++slot;
+  }
   return PB_OK;
 }
 

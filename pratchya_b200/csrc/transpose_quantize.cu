@@ -524,10 +524,20 @@ transpose_quantize1024_bf16_ring_kernel(const __grid_constant__ CUtensorMap map_
 // still 1024 rows of 64 bytes, now 16 f32 columns: a thread keeps 32 rows of ONE column, its maximum is an f32
 // maximum, and pairs of rows go through the f32 division straight to a bf16 pair.  Everything else (three TMA-filled
 // buffers, two groups of 512 threads, the swapped row pairs of the upper half-warp, the two-level maxima) is as above.
-template <int FMT>
+//
+// LERP: the token-shift lerp of TimeMix / ChannelMix as a prologue (pratchya/_nnx_impl/_module.py:126-134, 235-237): the
+// value quantized is v[r][c] = x[r][c] + (prev[r][c] - x[r][c]) * mu[c] with prev the row before (the carried state for the
+// first row of a sequence; sequences are whole tiles long), three roundings as in the op-by-op form.  The row before a
+// thread's first row is in the tile, except for the tile's first row, which sixteen threads fetch with a plain load.
+struct LerpPrologue {
+  const float* x; const float* state; const float* mu; int steps;
+};
+
+template <int FMT, bool LERP>
 __global__ void __launch_bounds__(1024, 1)
 transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x, uint8_t* __restrict__ q_t, uint8_t* __restrict__ sc8,
-                                       float* __restrict__ sc32, int rows, int cols, int tiles_x, int tiles_y, int n_tiles) {
+                                       float* __restrict__ sc32, int rows, int cols, int tiles_x, int tiles_y, int n_tiles,
+                                       const LerpPrologue lerp) {
   extern __shared__ uint8_t ring_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ring_raw) + 1023) & ~(uintptr_t)1023);
   float (*part_amax)[32][16] = reinterpret_cast<float (*)[32][16]>(smem + kRingBufs * kRingTileBytes);   // [group * 2 + parity]
@@ -564,16 +574,42 @@ transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x
     const int tl = blockIdx.x + seq * gridDim.x;
     const int cx = tl % tiles_x, rest = tl / tiles_x, ry = rest % tiles_y, z = rest / tiles_y;
     const int c0 = cx * 16, r0 = ry * 1024;
+    float before = 0.0f, mu_c = 0.0f;             // LERP: the row before the tile's first row (threads of rows 0..31), mu of the column
+    if (LERP) {
+      mu_c = __ldg(lerp.mu + c0 + cp);
+      if (row_first == 0) {
+        const int64_t row = (int64_t)z * rows + r0;
+        if (row % lerp.steps != 0) before = __ldg(lerp.x + (row - 1) * cols + c0 + cp);
+        else if (lerp.state) before = __ldg(lerp.state + (row / lerp.steps) * cols + c0 + cp);
+      }
+    }
     const bool landed = ring_wait(s_bar + 8u * (seq % kRingBufs), (uint32_t)(seq / kRingBufs) & 1u);
     if (!landed) atomicExch(&g_tq_status, (unsigned int)PB_ERR_DEVICE_TIMEOUT);
     const uint8_t* tile = smem + (size_t)(seq % kRingBufs) * kRingTileBytes;
     float w[32];
     float cm = 0.0f;
+    if (LERP) {
+      if (row_first != 0) before = *reinterpret_cast<const float*>(tile + (row_first - 1) * 64 + cp * 4);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      w[i] = *reinterpret_cast<const float*>(tile + (row_first + (i ^ swap)) * 64 + cp * 4);
-      cm = fmaxf(cm, fabsf(w[i]));
+      for (int i = 0; i < 32; i += 2) {           // the two loads of a pair in the half-warp's own order, then rows in their natural order
+        const float first = *reinterpret_cast<const float*>(tile + (row_first + (i ^ swap)) * 64 + cp * 4);
+        const float second = *reinterpret_cast<const float*>(tile + (row_first + ((i + 1) ^ swap)) * 64 + cp * 4);
+        w[i] = swap ? second : first;
+        w[i + 1] = swap ? first : second;
+      }
+#pragma unroll
+      for (int i = 31; i > 0; --i) w[i] = __fadd_rn(w[i], __fmul_rn(__fsub_rn(w[i - 1], w[i]), mu_c));
+      w[0] = __fadd_rn(w[0], __fmul_rn(__fsub_rn(before, w[0]), mu_c));
+#pragma unroll
+      for (int i = 0; i < 32; ++i) cm = fmaxf(cm, fabsf(w[i]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        w[i] = *reinterpret_cast<const float*>(tile + (row_first + (i ^ swap)) * 64 + cp * 4);
+        cm = fmaxf(cm, fabsf(w[i]));
+      }
     }
+    const int qswap = LERP ? 0 : swap;            // LERP leaves the registers in row order
     float (*pa)[16] = part_amax[grp * 2 + (local & 1)];
     pa[blk * 4 + quarter][cp] = cm;
     int give_up;
@@ -604,8 +640,8 @@ transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
       // rows i..i+3 of the column; the registers of the upper half-warp hold each pair of rows swapped
-      const uint32_t p0 = div_hoisted_pack2(swap ? w[i + 1] : w[i], swap ? w[i] : w[i + 1], nD2, r2);
-      const uint32_t p1 = div_hoisted_pack2(swap ? w[i + 3] : w[i + 2], swap ? w[i + 2] : w[i + 3], nD2, r2);
+      const uint32_t p0 = div_hoisted_pack2(qswap ? w[i + 1] : w[i], qswap ? w[i] : w[i + 1], nD2, r2);
+      const uint32_t p1 = div_hoisted_pack2(qswap ? w[i + 3] : w[i + 2], qswap ? w[i + 2] : w[i + 3], nD2, r2);
       out[i >> 2] = bf16x2_to_fp8x2<FMT>(p0) | (bf16x2_to_fp8x2<FMT>(p1) << 16);
     }
     uint8_t* o = q_t + col * rows + r0 + row_first;
@@ -614,8 +650,9 @@ transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x
   }
 }
 
-template <int FMT>
-int launch_one_pass_f32_ring(const void* x, uint8_t* q_t, uint8_t* sc8, float* sc32, int64_t batch, int64_t rows, int64_t cols, cudaStream_t st) {
+template <int FMT, bool LERP>
+int launch_one_pass_f32_ring(const void* x, uint8_t* q_t, uint8_t* sc8, float* sc32, int64_t batch, int64_t rows, int64_t cols, cudaStream_t st,
+                             const LerpPrologue lerp = LerpPrologue{nullptr, nullptr, nullptr, 1}) {
   using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -637,14 +674,14 @@ int launch_one_pass_f32_ring(const void* x, uint8_t* q_t, uint8_t* sc8, float* s
   {
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-      PB_CUDA_TRY(cudaFuncSetAttribute(transpose_quantize1024_f32_ring_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem));
+      PB_CUDA_TRY(cudaFuncSetAttribute(transpose_quantize1024_f32_ring_kernel<FMT, LERP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem));
       configured[dev] = true;
     }
   }
   const int tiles_x = (int)(cols / 16), tiles_y = (int)(rows / 1024);
   const int64_t n_tiles = (int64_t)tiles_x * tiles_y * batch;
   const int grid = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
-  transpose_quantize1024_f32_ring_kernel<FMT><<<grid, 1024, kRingSmem, st>>>(map, q_t, sc8, sc32, (int)rows, (int)cols, tiles_x, tiles_y, (int)n_tiles);
+  transpose_quantize1024_f32_ring_kernel<FMT, LERP><<<grid, 1024, kRingSmem, st>>>(map, q_t, sc8, sc32, (int)rows, (int)cols, tiles_x, tiles_y, (int)n_tiles, lerp);
   PB_LAUNCH_CHECK("transpose_quantize1024_f32_ring_kernel");
   return PB_OK;
 }
@@ -720,6 +757,15 @@ transpose_bytes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ ds
 
 }  // namespace
 
+// quantize_impl(v^T, (1,128)) of one mix v = x + (prev - x) * mu of the token-shift lerp, straight from x [rows, cols] f32
+// (rows and steps multiples of 1024, cols of 16): the persistent f32 kernel with the lerp as its prologue.
+int launch_shift_lerp_transposed(const float* x, const float* state, const float* mu, uint8_t* q_t, uint8_t* sc8, float* sc32,
+                                 int64_t rows, int64_t steps, int64_t cols, cudaStream_t st) {
+  if (rows % 1024 != 0 || steps % 1024 != 0 || cols % 16 != 0 || rows >= (1ll << 31) || (cols / 16) * (rows / 1024) >= (1ll << 31))
+    return fail(PB_ERR_UNSUPPORTED, "shift-lerp transposed quantizer: rows=%lld steps=%lld cols=%lld", (long long)rows, (long long)steps, (long long)cols);
+  return launch_one_pass_f32_ring<PB_E4M3, true>(x, q_t, sc8, sc32, 1, rows, cols, st, LerpPrologue{x, state, mu, (int)steps});
+}
+
 // Reads and clears the transposed quantizer's device status word (see pb_gemm_check).
 int transposed_status_fetch(unsigned int* out) {
   unsigned int zero = 0;
@@ -766,8 +812,8 @@ extern "C" int pb_quantize_transposed(const void* x, int x_dtype, int64_t batch,
       }
       const bool ring32 = batch * rows < (1ll << 31) && (cols / 16) * (rows / 1024) * batch >= 2 * sm_count() && env_switch("PB_TQ_RING", 1) != 0;
       if (ring32)
-        return out_format == PB_E4M3 ? launch_one_pass_f32_ring<PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
-                                     : launch_one_pass_f32_ring<PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
+        return out_format == PB_E4M3 ? launch_one_pass_f32_ring<PB_E4M3, false>(x, o, sc8, sc32, batch, rows, cols, st)
+                                     : launch_one_pass_f32_ring<PB_E5M2, false>(x, o, sc8, sc32, batch, rows, cols, st);
       return out_format == PB_E4M3 ? launch_one_pass<float, PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
                                    : launch_one_pass<float, PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
     }

@@ -8,7 +8,7 @@ Gradients: 2e-5 of each gradient's largest magnitude against torch.autograd (sum
 import pytest
 import torch
 
-from pratchya_b200._nnx_impl._glue import token_shift_lerp, wkv_prepare
+from pratchya_b200._nnx_impl._glue import token_shift_lerp, token_shift_lerp_quantized, wkv_prepare
 from pratchya_b200._nnx_impl._model import PratchyaCausalLM, PratchyaConfig, lerp, normalized, RotaryEmbedding
 
 pytestmark = pytest.mark.gpu
@@ -38,6 +38,57 @@ def test_token_shift_lerp_matches_torch(built_lib, bsz, steps, chans, n_mix, wit
     want_grads = torch.autograd.grad(want, leaves, g)
     for name, a, b in zip(["dx", "dmu", "dstate"], got_grads, want_grads):
         close(a, b, name, 2e-5)
+
+
+@pytest.mark.parametrize("bsz,steps,chans,n_mix,with_state,transposed", [
+    (2, 37, 1024, 6, True, ()), (1, 300, 2048, 1, False, ()),                    # row forms only (any number of steps)
+    (2, 1024, 1024, 6, True, (0, 2, 3)), (3, 2048, 2048, 1, True, (0,)),         # with token-major forms; fewer tiles than SMs, then more
+    (2, 1024, 2048, 6, False, (5,)), (5, 1024, 1024, 6, True, (0, 1, 2, 3, 4, 5))])
+def test_token_shift_lerp_quantized_gives_the_bytes_of_lerp_then_quantize(built_lib, bsz, steps, chans, n_mix, with_state, transposed):
+    """The lerp fused into the activation quantizers: every triple bit for bit that of the quantizer run on the mix
+    the unfused kernel writes (which the test above checks against torch), in the row form and in the token-major
+    form; sequences start at tile boundaries, inside the array too (bsz > 1), with and without a carried state.
+    Gradients flow through the storage-less handles to x, state and mu as they do through the unfused mixes."""
+    from pratchya_b200 import _lib
+    from pratchya_b200._qualia import quantize_impl, quantize_transposed_impl
+    from pratchya_b200._nnx_impl import linear_fp8
+    gen = torch.Generator(device="cuda").manual_seed(steps + 7 * n_mix)
+    x = torch.randn(bsz, steps, chans, device="cuda", generator=gen)
+    x.view(-1)[::4099] *= 50.0
+    x[0, : min(steps, 1024), 3] = 0.0                              # an all-zero token-major super-group when mu or the state is zero there
+    state = torch.randn(bsz, 1, chans, device="cuda", generator=gen) if with_state else None
+    mu = torch.rand(n_mix, chans, device="cuda", generator=gen)
+    mu[:, 3] = 0.0
+    mixes = token_shift_lerp_quantized(x, state, mu, transposed)
+    torch.cuda.synchronize()
+    _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+    plain = token_shift_lerp(x, state, mu)
+    as_bytes = lambda t: t.contiguous().view(torch.uint8)
+    for k in range(n_mix):
+        v = plain[k].reshape(-1, chans)
+        for got, want in zip(mixes[k].row, quantize_impl(v, (1, 128))):
+            assert got.shape == want.shape and torch.equal(as_bytes(got), as_bytes(want)), f"row form of mix {k}"
+        if k in transposed:
+            for got, want in zip(mixes[k].tokens, quantize_transposed_impl(v, 128)):
+                assert got.shape == want.shape and torch.equal(as_bytes(got), as_bytes(want)), f"token-major form of mix {k}"
+        else:
+            assert mixes[k].tokens is None
+    # through a Linear: same output, same gradients as the unfused chain
+    if transposed:
+        w = (torch.randn(chans, 256, device="cuda", generator=gen) * 0.03).requires_grad_(True)
+        g = torch.randn(bsz, steps, 256, device="cuda", generator=gen)
+        k = transposed[0]
+        results = []
+        for fused in (True, False):
+            xx, mm = x.clone().requires_grad_(True), mu.clone().requires_grad_(True)
+            ss = state.clone().requires_grad_(True) if with_state else None
+            mix = (token_shift_lerp_quantized(xx, ss, mm, transposed) if fused else token_shift_lerp(xx, ss, mm))[k]
+            y = linear_fp8(mix, w, (128, 128))
+            grads = torch.autograd.grad(y, [xx, mm, w] + ([ss] if with_state else []), g)
+            results.append((y.detach(), grads))
+        assert torch.equal(results[0][0], results[1][0])
+        for a, b in zip(results[0][1], results[1][1]):
+            assert torch.equal(a, b)
 
 
 @pytest.mark.parametrize("bsz,steps,n_head,first_layer", [(2, 33, 4, True), (2, 200, 3, False), (1, 129, 32, False)])
