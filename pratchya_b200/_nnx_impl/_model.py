@@ -19,7 +19,7 @@ from dataclasses import dataclass
 import torch
 
 from .._qualia import _ops
-from ._glue import can_quantize_mixes, relu2, rms_norm, token_shift_lerp, token_shift_lerp_quantized, wkv_finish, wkv_prepare
+from ._glue import QuantizedMix, can_quantize_mixes, relu2, rms_norm, token_shift_lerp, token_shift_lerp_quantized, wkv_finish, wkv_prepare
 from ._glue import smoothed_cross_entropy as fused_cross_entropy
 from ._module import linear_fp8
 from ._wkv7 import wkv_state_scan
@@ -85,12 +85,14 @@ class Linear(torch.nn.Module):
         self.kernel = torch.nn.Parameter(_lecun(fan_in, (fan_in, fan_out), gen, device))
         self._prepared = (None, None)        # (kernel version, {"wq": fp8 triple, "w_t": its byte transpose})
 
-    def forward(self, x):
+    def forward(self, x, raw=False):
+        """`raw`: return the f32 product itself, without its re-quantization (for a caller that fuses that step
+        into what follows)."""
         # the kernel's fp8 form is the same in every pass of a step: keep it until the kernel is written to
         version = (self.kernel._version, self.kernel.data_ptr())
         if self._prepared[0] != version:
             self._prepared = (version, {})
-        return linear_fp8(x, self.kernel, self.tgrid, fake_quant_output=self.tgrid[1] != 1, prepared=self._prepared[1])
+        return linear_fp8(x, self.kernel, self.tgrid, fake_quant_output=self.tgrid[1] != 1 and not raw, prepared=self._prepared[1])
 
 
 class LowRankFFN(torch.nn.Module):                   # _module.py:74-89
@@ -240,6 +242,12 @@ class ChannelMix(torch.nn.Module):                   # _module.py:228-258
             x_shifted = torch.cat([cm_state, x[:, :-1, :]], dim=1)
             x_k = lerp(x.to(torch.float32), x_shifted.to(torch.float32), mu_x)
         cm_state = x[:, -1:, :]
+        if self.fused_glue and not torch.is_grad_enabled() and x.is_cuda and self.w_k.kernel.shape[1] % 1024 == 0 and self.w_k.tgrid[1] == 128:
+            # no backward pass follows (the first pass of a recomputed block): the first product's re-quantization, relu^2 and
+            # the second Linear's input quantization are one pass over the f32 product, and k is never written
+            y = self.w_k(x_k, raw=True)
+            k = QuantizedMix(y.new_zeros(1).expand(y.shape), _ops.relu2_requantize_impl(y), None)
+            return self.w_v(k), cm_state
         k = self.w_k(x_k).to(torch.float32)
         k = relu2(k) if self.fused_glue else torch.relu(k) ** 2
         return self.w_v(k), cm_state
@@ -291,12 +299,15 @@ class _RematBlock(torch.autograd.Function):
 
 class PratchyaCausalLM(torch.nn.Module):
     """PratchyaModel + lm_head + loss, _model.py:10-96 and _utils.py:7-13, from a zero state (`init_state`,
-    _config.py:41-52).  `remat=True` recomputes each block in the backward pass, as the reference's nnx.remat does."""
+    _config.py:41-52).  `remat=True` recomputes each block in the backward pass, as the reference's nnx.remat does;
+    `remat=n` (an int) recomputes the first n blocks only and keeps the activations of the others, for a device whose
+    memory holds them (loss and gradients are the same bits for every n: all kernels are deterministic)."""
 
-    def __init__(self, cfg: PratchyaConfig, *, seed: int = 42, device="cuda", remat: bool = True):
+    def __init__(self, cfg: PratchyaConfig, *, seed: int = 42, device="cuda", remat: bool | int = True):
         super().__init__()
         gen = torch.Generator(device=device).manual_seed(seed)
-        self.cfg, self.remat = cfg, remat
+        self.cfg = cfg
+        self.remat = (cfg.n_layers if remat else 0) if isinstance(remat, bool) else max(0, min(int(remat), cfg.n_layers))
         self.embedding = torch.nn.Parameter(torch.randn(cfg.vocab_size, cfg.hidden_size, generator=gen, device=device) / math.sqrt(cfg.hidden_size))
         self.blocks = torch.nn.ModuleList([RWKVBlock(cfg, gen, device, first_layer=i == 0) for i in range(cfg.n_layers)])
         self.pre_rmsnorm = RMSNorm(cfg.hidden_size, cfg.blksize, cfg.rmsnorm_epsilon, device, cfg.fused_glue)
@@ -315,8 +326,8 @@ class PratchyaCausalLM(torch.nn.Module):
         x = self.pre_rmsnorm(self.embed(input_ids))
         v = None
         zeros_c = torch.zeros(bsz, 1, cfg.hidden_size, device=dev)
-        for blk in self.blocks:
-            if self.remat and torch.is_grad_enabled():
+        for i, blk in enumerate(self.blocks):
+            if i < self.remat and torch.is_grad_enabled():
                 x, v = _RematBlock.apply(blk, t_positions, zeros_c, x, v)
             else:
                 x, v, _, _, _ = blk(x, v, t_positions, zeros_c, zeros_c, None)

@@ -191,6 +191,27 @@ def fake_quantize_impl(x: torch.Tensor, tgrid, dtype, out_format: str = "e4m3") 
     return out
 
 
+def relu2_requantize_impl(y: torch.Tensor):
+    """quantize_impl(relu(dq(q(y, (1,128))))**2, (1,128)) for an f32 product y [..., cols] with cols % 1024 == 0: the middle
+    of ChannelMix between its two Linears (_module.py:246-251: the first Linear's output re-quantization, relu squared, the
+    second Linear's input quantization) in one pass over y, with the bits of the three steps run one after another.
+    Returns the triple over [rows, cols]."""
+    _require_cuda(y, "relu2_requantize_impl input")
+    if y.dtype != torch.float32 or y.dim() < 2 or y.shape[-1] % 1024 != 0 or y.numel() == 0:
+        raise ValueError(f"relu2_requantize_impl: f32 input with a last dim that is a multiple of 1024, got {y.dtype} {tuple(y.shape)}")
+    lib = _lib.load()
+    y = y.contiguous()
+    cols = y.shape[-1]
+    rows = y.numel() // cols
+    with torch.cuda.device(y.device):
+        q = torch.empty((rows, cols), dtype=E4M3, device=y.device)
+        sc8 = torch.empty((rows * cols // 1024, 8), dtype=E8M0, device=y.device)
+        sc32 = torch.empty((rows * cols // 1024, 1, 1), dtype=torch.float32, device=y.device)
+        check(lib.pb_relu2_requantize(y.data_ptr(), rows, cols, _FMT_CODE["e4m3"], q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(),
+                                      None, None, 0, _stream(y)))
+    return q, sc8, sc32
+
+
 def dequantize_impl_bwd(sc_fp8: torch.Tensor, sc_fp32: torch.Tensor, g_out: torch.Tensor, tgrid):
     """Cotangent of the fp8 value: g * x_sc / 128 in g's dtype, _qarr.py:575-601."""
     _require_cuda(g_out, "dequantize_impl_bwd input")

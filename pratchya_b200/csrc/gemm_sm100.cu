@@ -63,9 +63,13 @@ struct Cfg {
   static constexpr int kSfaBytes = 512;
   static constexpr int kSfbBytes = 512 * kSfbAtoms;
   static constexpr int kSfSlot = kSfaBytes + kSfbBytes;          // one slot holds the atoms of 4 k-blocks
-  static constexpr int kSfSlots = 2;                             // reused every 8 k-blocks (> kStages, see the producer)
+  // Scale-factor slots in shared memory and sets in TMEM, both taken in turn by every fill.  A fill may follow the last one
+  // after a single k-block (a 128-deep product has one per tile), and what the producer knows when it refills a slot, and
+  // the MMA thread when it overwrites a set, is that the k-blocks kStages and more before have completed: so kStages of each.
+  static constexpr int kSfSlots = kStages > 4 ? 8 : 4;
   static constexpr int kSfCols = 12;                             // TMEM columns of one scale-factor set (4 for A, up to 8 for B)
   static constexpr int kSfColBase = kAccBufs * BN;
+  static_assert(kSfSlots >= kStages && kSfColBase + kSfSlots * kSfCols <= 512, "scale-factor slots and TMEM budget");
   static constexpr int kOffB = kStages * kABytes;
   static constexpr int kOffSf = kOffB + kStages * kBBytes;
   static constexpr int kOffStore = ((kOffSf + kSfSlots * kSfSlot + 1023) / 1024) * 1024;   // epilogue staging, 4 KB per warp
@@ -73,7 +77,6 @@ struct Cfg {
   static constexpr int kNumBars = 2 * kStages + 2 * kAccBufs;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;   // +1024: manual alignment slack
   static_assert(kSmemBytes <= 232448, "shared memory budget");
-  static_assert(kSfColBase + 2 * kSfCols <= 512, "TMEM budget");
 };
 
 __device__ unsigned int g_gemm_status;   // 0, or PB_ERR_DEVICE_TIMEOUT once any bounded wait ran out
@@ -468,11 +471,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tma_load_2d(s_a + s * C::kABytes, &map_a, kb * BK, m0, bar_full(s));
           tma_load_2d(s_b + s * C::kBBytes, &map_b, kb * BK, n0, bar_full(s));
           if (with_sf) {
-            // Two slots alternate.  A slot is rewritten 8 k-blocks after the copy that read it was
-            // issued; this fill waited for the commit of k-block it - kStages (kStages < 8), which
+            // The slots are taken in turn.  A slot is rewritten kSfSlots fills, so at least kSfSlots >= kStages k-blocks,
+            // after the copy that read it was issued; this fill waited for the commit of k-block it - kStages, which
             // completes only after every earlier tcgen05 operation, that copy included.
             const int kg = kb >> 2;
-            const uint32_t slot = s_sf + (sf_fills & 1u) * C::kSfSlot;
+            const uint32_t slot = s_sf + (sf_fills % C::kSfSlots) * C::kSfSlot;
             ++sf_fills;
             bulk_load(slot, p.sfa + ((size_t)kg * p.tiles_m + tile % p.tiles_m) * 512, C::kSfaBytes, bar_full(s));
             bulk_load(slot + C::kSfaBytes, p.sfb + ((size_t)kg * p.tiles_n + tile / p.tiles_m) * C::kSfbBytes, C::kSfbBytes, bar_full(s));
@@ -498,7 +501,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t s = 0, phase = 0;                 // pipeline stage and the parity of its current fill
       uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full(0), empty = bar_empty(0);
       const uint32_t sf_lo0 = sf_desc_lo(s_sf);
-      uint32_t sf_reads = 0;                     // scale-factor slots consumed so far
+      uint32_t sf_reads = 0, sf_col = sf_tmem0;  // scale-factor slots consumed so far; the TMEM set of the current group of four k-blocks
       uint32_t g = 0;                            // chunk counter
       long long wait_full = 0, wait_acc = 0;
       const long long t_begin = PROF ? clock64() : 0;
@@ -517,11 +520,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (PROF) t0 = clock64();
             if (!mbar_wait(full, phase, abort_flag, p.wait_polls)) { ok = false; break; }
             if (PROF) wait_full += clock64() - t0;
-            // scale factors of k-blocks 4j..4j+3 live in TMEM set j & 1; the MMAs of set j-2 were
-            // issued (and are ordered) before this copy
-            const uint32_t sf_col = sf_tmem0 + ((uint32_t)(kb >> 2) & 1u) * C::kSfCols;
+            // the scale factors of k-blocks 4j..4j+3 go to the TMEM set of their fill; the MMAs that read that set's
+            // last contents were kSfSlots fills ago: k-blocks whose commits this stage's producer has waited for
             if ((kb & 3) == 0) {
-              const uint32_t sf_lo = sf_lo0 + (sf_reads & 1u) * (C::kSfSlot >> 4);
+              const uint32_t turn = sf_reads % C::kSfSlots;
+              const uint32_t sf_lo = sf_lo0 + turn * (C::kSfSlot >> 4);
+              sf_col = sf_tmem0 + turn * C::kSfCols;
               ++sf_reads;
               tc_cp_sf_lo(sf_col, sf_lo);
 #pragma unroll
@@ -658,7 +662,7 @@ struct Cfg2 {
   static constexpr int kSfaBytes = 512;              // scale factors of this CTA's A rows
   static constexpr int kSfbBytes = 1024;             // scale factors of all 224 B rows (each CTA needs them all)
   static constexpr int kSfSlot = kSfaBytes + kSfbBytes;
-  static constexpr int kSfSlots = 2;
+  static constexpr int kSfSlots = 4;                 // slots in shared memory and sets in TMEM, taken in turn by every fill (>= kSlots)
   static constexpr int kSfCols = 12;
   static constexpr int kSfColBase = kAccBufs * BN;
   static constexpr int kOffB = kStages * kABytes;
@@ -668,7 +672,7 @@ struct Cfg2 {
   static constexpr int kNumBars = 2 * kStages + 2 * kAccBufs;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;
   static_assert(kSmemBytes <= 232448, "shared memory budget");
-  static_assert(kSfColBase + 2 * kSfCols <= 512, "TMEM budget");
+  static_assert(kSfSlots >= kSlots && kSfColBase + kSfSlots * kSfCols <= 512, "scale-factor slots and TMEM budget");
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -813,7 +817,9 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (!mbar_wait(bar_empty(q), ((it / C::kSlots) & 1u) ^ 1u, abort_flag, p.wait_polls)) { ok = false; break; }
             if (PROF) prod_wait += clock64() - tw;
             const bool two = kb + 1 < kb_end;
-            const bool with_sf = (kb & 3) == 0;             // a step of two starts at an even k-block: only its first can open a group of four
+            // a step of two starts at an even k-block: only its first can open a group of four; a unit that starts inside
+            // a group (the second half of a split tile) fetches that group's atom too
+            const bool with_sf = (kb & 3) == 0 || kb == c_begin * p.P;
             const uint32_t full = map_to_cta(bar_full(q), 0);
             // diagnostics build: the very first slot of the launch is neither armed nor filled, so its barrier
             // never completes, nothing is in flight for it, and every role's bounded wait runs out
@@ -824,12 +830,12 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (ld_a) tma_load_2d_pair(s_a + s * C::kABytes, &map_a, kb * BK, m0, full);
             if (ld_b) tma_load_2d_pair(s_b + s * C::kBBytes, &map_b, kb * BK, nb0, full);
             if (with_sf && ld_sf) {
-              // Two slots alternate.  A slot is rewritten 8 k-blocks after the copy that read it was
-              // issued; this fill waited for the commit of the step kSlots before this one, which
-              // came after that copy in the MMA thread and completes only after every earlier
-              // tcgen05 operation of that thread.
+              // The slots are taken in turn.  A slot is rewritten kSfSlots fills, so at least kSfSlots >= kSlots steps,
+              // after the copy that read it was issued (a 128- or 256-deep product fills at every step); this fill
+              // waited for the commit of the step kSlots before this one, which came after that copy in the MMA
+              // thread and completes only after every earlier tcgen05 operation of that thread.
               const int kg = kb >> 2;
-              const uint32_t slot = s_sf + (sf_fills & 1u) * C::kSfSlot;
+              const uint32_t slot = s_sf + (sf_fills % C::kSfSlots) * C::kSfSlot;
               ++sf_fills;
               tma_load_2d_pair(slot, &map_sfa, 0, kg * (2 * p.tiles_m) + 2 * tm + (int)rank, full);
               tma_load_2d_pair(slot + C::kSfaBytes, &map_sfb, 0, (kg * p.tiles_n + tn) * 2, full);
@@ -856,7 +862,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const uint32_t a_lo0 = operand_desc_lo(s_a), b_lo0 = operand_desc_lo(s_b);
       const uint32_t sf_tmem0 = tmem_base + C::kSfColBase;
       const uint32_t sf_lo0 = sf_desc_lo(s_sf);
-      uint32_t q = 0, phase = 0, sf_reads = 0, g = 0;
+      uint32_t q = 0, phase = 0, sf_reads = 0, g = 0, sf_col = sf_tmem0;
       uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full(0), empty = bar_empty(0);
       long long wait_full = 0, wait_acc = 0;
       const long long t_begin = PROF ? clock64() : 0;
@@ -877,9 +883,13 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (PROF) t0 = clock64();
             if (!mbar_wait(full, phase, abort_flag, p.wait_polls)) { ok = false; break; }
             if (PROF) wait_full += clock64() - t0;
-            const uint32_t sf_col = sf_tmem0 + ((uint32_t)(kb >> 2) & 1u) * C::kSfCols;
-            if ((kb & 3) == 0) {
-              const uint32_t sf_lo = sf_lo0 + (sf_reads & 1u) * (C::kSfSlot >> 4);
+            // A new group of four k-blocks: its scale factors go to the next TMEM set in turn.  The MMAs that read that
+            // set's last contents ran kSfSlots fills ago, in steps whose commits this step's producer has waited for
+            // (nothing orders a copy behind an earlier MMA by itself).
+            if ((kb & 3) == 0 || kb == c_begin * P) {
+              const uint32_t turn = sf_reads % C::kSfSlots;
+              const uint32_t sf_lo = sf_lo0 + turn * (C::kSfSlot >> 4);
+              sf_col = sf_tmem0 + turn * C::kSfCols;
               ++sf_reads;
               tc2_cp_sf_lo(sf_col, sf_lo);
               tc2_cp_sf_lo(sf_col + 4, sf_lo + (C::kSfaBytes >> 4));

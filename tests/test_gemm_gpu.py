@@ -161,6 +161,32 @@ def test_random_shapes_against_f64_product(built_lib):
         assert err <= tol * scale, f"{m}x{n}x{k} {out}: max abs err {err:.3e} vs scale {scale:.3e}"
 
 
+@pytest.mark.parametrize("grid", [(128, 128), (128, 1)])
+@pytest.mark.parametrize("m,k,n", [(32768, 128, 2048), (16384, 256, 2048), (32768, 128, 256), (8192, 384, 1024), (64, 128, 65536)])
+def test_shallow_products_with_many_tiles_per_cta(built_lib, m, k, n, grid):
+    """One to three k-blocks per tile and many tiles per CTA (the reference's LoRA up projection at 8 x 4096 tokens:
+    rank 128 -> 2048 channels): every pipeline step then brings new scale factors, so their shared-memory slots and
+    TMEM sets turn over at the pipeline's own pace.  Checked against the f64 product of the dequantized operands
+    and for equal bits from run to run."""
+    from pratchya_b200._qualia import dequantize_impl
+    gen = torch.Generator(device="cuda").manual_seed(m + k + n)
+    x = torch.tanh(torch.randn(m, k, device="cuda", generator=gen) * 2.0)
+    x[::7] *= 1e-3                                                # rows of very different scale: a stale scale factor shows
+    w = torch.randn(k, n, device="cuda", generator=gen) * 0.1
+    w[:, ::5] *= 40.0
+    xq, wq = quantize_impl(x, (1, 128)), quantize_impl(w, grid)
+    ref = dequantize_impl(*xq, torch.float32, (1, 128)).double() @ dequantize_impl(*wq, torch.float32, grid).double()
+    scale = ref.abs().max().item()
+    first = None
+    for _ in range(4):
+        got = matmul_impl(*xq, *wq, (1, 128), grid)
+        _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+        err = (got.double() - ref).abs().max().item()
+        assert err <= 1e-5 * scale, f"{m}x{n}x{k} on {grid}: max abs err {err:.3e} against a largest magnitude of {scale:.3e}"
+        first = got if first is None else first
+        assert torch.equal(got, first)
+
+
 @pytest.mark.parametrize("m,k,n", [(256, 2048, 64), (512, 128, 2048), (384, 1024, 4096), (128, 2048, 48)])
 def test_column_scaled_weights_run_on_the_tensor_cores(built_lib, m, k, n):
     """Weights on the (128,1) grid -- the reference's LoRA down/up, gate and lm_head kernels

@@ -47,6 +47,24 @@ def test_channel_mix_matches_the_oracle(built_lib):
     assert np.array_equal(state.cpu().numpy(), want_state)
 
 
+def test_block_without_a_graph_takes_the_fused_paths_and_gives_the_same_bits(built_lib):
+    """Under torch.no_grad (inference, and the first pass of a recomputed block) the mixes leave the lerp kernel as fp8
+    triples and ChannelMix's middle is one pass over the first product; with gradients enabled (32 tokens: no
+    token-major forms) the unfused kernels run.  Same output bits."""
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    blk = RWKVBlock(CFG, gen, "cuda", first_layer=False)
+    b, t, c = 2, 32, CFG.hidden_size
+    x = torch.randn(b, t, c, device="cuda", generator=gen)
+    v0 = torch.randn(b, t, c, device="cuda", generator=gen)
+    pos = torch.arange(t, device="cuda", dtype=torch.int32)
+    zeros = torch.zeros(b, 1, c, device="cuda")
+    with torch.no_grad():
+        fused = blk(x, v0, pos, zeros, zeros, None)
+    plain = blk(x, v0, pos, zeros, zeros, None)
+    for a, p in zip(fused, plain):
+        assert torch.equal(a, p.detach())
+
+
 @pytest.mark.parametrize("first_layer", [True, False])
 def test_time_mix_matches_the_oracle(built_lib, first_layer):
     gen = torch.Generator(device="cuda").manual_seed(2)
