@@ -261,24 +261,49 @@ def time_triple(tokens: int, d_model: int, ffn: int, dist: str, seed: int, reps:
 def time_model_step(world: int, rank: int, dev, barrier, steps: int = 2):
     """One data-parallel training step of the modified RWKV-7 model with every linear layer on the FP8 path: 24 layers,
     d_model 2048, head size 64, vocabulary 65536, context 4096, 8 sequences per GPU (the configuration's global batch of
-    64 at 8 GPUs) of random token ids, random-init f32 master weights.  A step = forward + backward (blocks recomputed in
-    the backward pass) + all-reduce of the gradients in bf16 over NCCL + a sign-momentum update of the masters.
-    CUDA events around each step, barrier on both sides, mean of `steps` after one warm-up."""
+    64 at 8 GPUs) of random token ids, random-init f32 master weights.  A step = forward + backward + all-reduce of the
+    gradients in bf16 over NCCL + a sign-momentum update of the masters.  The reference recomputes every block in the
+    backward pass (nnx.remat); here as many of the last blocks as the GPU's free memory holds keep their activations
+    instead (10 GB per block at 8 x 4096 tokens, with 30 GB left free) and the others are recomputed: same loss and
+    gradient bits, one forward pass less for the kept blocks.  CUDA events around each step, barrier on both sides,
+    mean of `steps` after one warm-up."""
     import torch
     import torch.distributed as dist
-    from pratchya_b200._nnx_impl._dp import allreduce_gradients
-    from pratchya_b200._nnx_impl._model import PratchyaCausalLM, PratchyaConfig
+    from pratchya_b200._nnx_impl._model import PratchyaConfig
     from pratchya_b200._qualia import set_literal_dot_precision
     set_literal_dot_precision("tf32")   # the (128,1)-grid layers' backward dots (LoRA, lm_head): what an f32 dot gets under XLA on a GPU
     cfg = PratchyaConfig()
     seqs, ctx = 8, 4096
-    model = PratchyaCausalLM(cfg, seed=11, device=dev, remat=True)
-    params = [p for p in model.parameters()]
-    momentum = [torch.zeros_like(p) for p in params]
+    torch.cuda.empty_cache()
+    free_bytes, _ = torch.cuda.mem_get_info(dev)
+    # measured: a step with every block recomputed peaks at 51 GB, and a block that keeps its activations adds 10 GB
+    kept = torch.tensor([max(0, min(cfg.n_layers, int((free_bytes - 52e9 - 30e9) // (10.1e9 * seqs * ctx / 32768))))], device=dev)
+    if world > 1:
+        dist.all_reduce(kept, op=dist.ReduceOp.MIN)
+    kept = int(kept.item())
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
     ids = torch.randint(0, cfg.vocab_size, (seqs, ctx), device=dev, generator=gen)
+    out = None
+    for attempt_kept in ([kept, 0] if kept else [0]):
+        out = _model_step_once(cfg, attempt_kept, world, rank, dev, barrier, steps, ids, seqs, ctx)
+        if "error" not in out:
+            break
+        torch.cuda.empty_cache()
+    set_literal_dot_precision("f32")
+    return out
+
+
+def _model_step_once(cfg, kept, world, rank, dev, barrier, steps, ids, seqs, ctx):
+    import torch
+    import torch.distributed as dist
+    from pratchya_b200._nnx_impl._dp import allreduce_gradients
+    from pratchya_b200._nnx_impl._model import PratchyaCausalLM
+    model = PratchyaCausalLM(cfg, seed=11, device=dev, remat=cfg.n_layers - kept)
+    params = [p for p in model.parameters()]
+    momentum = [torch.zeros_like(p) for p in params]
     n_params = sum(p.numel() for p in params)
     losses = []
+    torch.cuda.reset_peak_memory_stats(dev)
 
     def step(exchange=True):
         for p in params:
@@ -306,7 +331,10 @@ def time_model_step(world: int, rank: int, dev, barrier, steps: int = 2):
     if world > 1:
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if ok.item() == 0:
-        return {"error": failure or "another rank failed in the warm-up step"}
+        for p in params:
+            p.grad = None
+        del model, params, momentum
+        return {"error": failure or "another rank failed in the warm-up step", "kept_blocks": kept}
     step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -317,8 +345,8 @@ def time_model_step(world: int, rank: int, dev, barrier, steps: int = 2):
     barrier()
     ms = e0.elapsed_time(e1) / steps
     out = {"ms_per_step": ms, "tokens_per_gpu": seqs * ctx, "parameters": n_params, "losses": [float(l) for l in losses],
-           "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9, "literal_dot_precision": "tf32"}
-    set_literal_dot_precision("f32")
+           "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9, "literal_dot_precision": "tf32",
+           "recomputed_blocks": cfg.n_layers - kept, "kept_blocks": kept}
     del model, params, momentum
     torch.cuda.empty_cache()
     return out
@@ -732,9 +760,10 @@ def run_ours(args):
                 model_step["tokens_per_s"] = world * model_step["tokens_per_gpu"] / (model_step["ms_per_step"] * 1e-3)
             out["model_step"] = dict(model_step, workload=(
                 "configs[4]: modified RWKV-7, 24 layers, d_model 2048, head size 64, vocabulary 65536, context 4096, 8 sequences per GPU "
-                f"({8 * world} global; the configuration's 64 at 8 GPUs), random token ids, random-init f32 masters; forward + backward with "
-                "block recomputation + bf16 gradient all-reduce (NCCL) + sign-momentum update; every linear layer through linear_fp8, "
-                "the WKV-7 scan and its backward pass through the package's kernels, the remaining elementwise work in torch"),
+                f"({8 * world} global; the configuration's 64 at 8 GPUs), random token ids, random-init f32 masters; forward + backward (the first "
+                "`recomputed_blocks` blocks recomputed in the backward pass, the last `kept_blocks` keep their activations: as many as the "
+                "GPU's free memory holds) + bf16 gradient all-reduce (NCCL) + sign-momentum update; every linear layer through linear_fp8, "
+                "the WKV-7 scan, the block's element-wise work and the loss, forward and backward, through the package's kernels"),
                 scaling="weak", timing="CUDA events around 2 steps after 2 warm-up steps, max over ranks")
         if sustained is not None:
             out["sustained"] = dict(sustained, peak=2.0 * peaks["bf16_tflops_sustained"],
