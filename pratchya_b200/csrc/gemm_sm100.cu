@@ -206,9 +206,20 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
 }
-// acc[off .. off+15] += r * fa * fb[column]; `off` is a constant after unrolling
-__device__ __forceinline__ void promote16(float (&acc)[128], int off, const uint32_t (&r)[16], float fa, float s_uni, const float* fbp, int uniform) {
-  if (uniform) {
+// acc[off .. off+15] += r * fa * fb[column]; `off` is a constant after unrolling.  `uniform`: 1 = one factor for the
+// whole tile (s_uni = fa * fb), 2 = one factor per eight adjacent columns, lane l of the warp holding that of the
+// warp's column group l in fb8 (a weight on the (128,1) grid), 0 = a factor per column, read from fbp.
+__device__ __forceinline__ void promote16(float (&acc)[128], int off, const uint32_t (&r)[16], float fa, float s_uni, const float* fbp, int uniform,
+                                          float fb8 = 0.0f) {
+  if (uniform == 2) {
+    const float s0 = fa * __shfl_sync(0xffffffffu, fb8, off >> 3), s1 = fa * __shfl_sync(0xffffffffu, fb8, (off >> 3) + 1);
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) {
+      const float sj = j < 8 ? s0 : s1;
+      const float2 v = __ffma2_rn(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), make_float2(sj, sj), make_float2(acc[off + j], acc[off + j + 1]));
+      acc[off + j] = v.x; acc[off + j + 1] = v.y;
+    }
+  } else if (uniform) {
     const float2 s2 = make_float2(s_uni, s_uni);
 #pragma unroll
     for (int j = 0; j < 16; j += 2) {
@@ -234,7 +245,7 @@ __device__ __forceinline__ void promote16(float (&acc)[128], int off, const uint
 // `release` hands the TMEM buffer back as soon as the last load has landed.
 template <typename Release>
 __device__ __forceinline__ void drain_later_chunk(float (&acc)[128], uint32_t t_addr, bool four_parts, float fa, float s_uni,
-                                                  const float* fbp, int uniform, Release&& release) {
+                                                  const float* fbp, int uniform, Release&& release, float fb8 = 0.0f) {
   uint32_t r[2][16];
   tc_ld16(t_addr, r[0]);
 #pragma unroll
@@ -244,7 +255,7 @@ __device__ __forceinline__ void drain_later_chunk(float (&acc)[128], uint32_t t_
       const bool more = j + 1 < 6 || (four_parts && j + 1 < 8);
       if (more) tc_ld16(t_addr + 16 * (j + 1), r[(j + 1) & 1]);
       else release();
-      promote16(acc, 16 * j, r[j & 1], fa, s_uni, fbp, uniform);
+      promote16(acc, 16 * j, r[j & 1], fa, s_uni, fbp, uniform, fb8);
     }
   }
 }
@@ -305,6 +316,7 @@ struct GemmParams {
   int splitk;       // pair kernel: 1, or 2 = each tile's chunks are shared by two work units that add into a zeroed f32 D
   int band;         // pair kernel: tile rows per band; a band's tiles are visited column by column before the next band
   int fb_uniform;   // B's fp32 factor is the same for all rows of B within a chunk (selects the kernel instantiation)
+  int fb_groups8;   // ... or the same within aligned runs of eight rows of B (a weight on the (128,1) grid)
   int tma_store;    // D is written through shared memory and TMA stores (needs 16-byte aligned rows)
   int profile;      // diagnostics build only: 1 per-role cycle counters, 2 also no stores of D, 3 also no TMEM reads.  0 in the product build.
   uint32_t wait_polls;   // poll budget of every bounded mbarrier wait
@@ -737,7 +749,10 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
   tm = b * p.band + (within - tn * rows);
 }
 
-template <bool PROF, bool UNI>
+// UNI: how B's fp32 factor varies over a tile's columns within a chunk: 1 = not at all, 2 = in runs of eight adjacent
+// columns (a weight on the (128,1) grid, whose chunks are single k-blocks: its drain runs once per k-block, so the
+// factors of the next chunk are fetched a chunk ahead and nothing in the drain waits on memory), 0 = per column.
+template <bool PROF, int UNI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg2::kThreads, 1)
 gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
@@ -945,14 +960,26 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tile_coords(p, tile, tm, tn);
       const int m0 = tm * 256 + (int)rank * 128, n0 = tn * BN + col_half * 128;
       float acc[128];
+      float fa_next = 0.0f, fb8_next = 0.0f, fb8 = 0.0f;
+      auto fetch = [&](int c) {       // UNI == 2: this row's factor and this lane's column group's, a chunk ahead
+        fa_next = __ldg(p.fa + (size_t)c * p.Mpad + m0 + row_in_tile);
+        fb8_next = lane * 8 < ncols ? __ldg(p.fb + (size_t)c * p.Npad + n0 + lane * 8) : 0.0f;
+      };
+      if (UNI == 2) fetch(c_begin);
       for (int c = c_begin; c < c_end; ++c, ++g) {
         const int buf = g % C::kAccBufs;
-        const float fa = __ldg(p.fa + (size_t)c * p.Mpad + m0 + row_in_tile);
+        float fa, s_uni = 0.0f;
         const float* fbp = p.fb + (size_t)c * p.Npad + n0;
-        const float s_uni = fa * __ldg(fbp);
+        if (UNI == 2) {
+          fa = fa_next; fb8 = fb8_next;
+          if (c + 1 < c_end) fetch(c + 1);
+        } else {
+          fa = __ldg(p.fa + (size_t)c * p.Mpad + m0 + row_in_tile);
+          s_uni = fa * __ldg(fbp);
+        }
         // per-column factors of this chunk: new lines every chunk, so ask for them now; the chunk's MMAs
         // are still running and an L2 round trip per 32 columns would otherwise sit inside the drain
-        if (!UNI && lane * 32 < ncols) asm volatile("prefetch.global.L1 [%0];" ::"l"(fbp + lane * 32));
+        if (UNI == 0 && lane * 32 < ncols) asm volatile("prefetch.global.L1 [%0];" ::"l"(fbp + lane * 32));
         if (!mbar_wait(bar_acc_full(buf), (g / C::kAccBufs) & 1u, abort_flag, p.wait_polls)) { ok = false; break; }
         tc_fence_after();
         const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + col_half * 128;
@@ -968,7 +995,14 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (four_parts) tc_ld32f<96>(t_addr + 96, acc);
           tc_wait_ld();
           release();
-          if (UNI) {
+          if (UNI == 2) {
+#pragma unroll
+            for (int j8 = 0; j8 < 16; ++j8) {
+              const float sj = fa * __shfl_sync(0xffffffffu, fb8, j8);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[8 * j8 + j] *= sj;
+            }
+          } else if (UNI) {
 #pragma unroll
             for (int j = 0; j < 128; ++j) acc[j] *= s_uni;
           } else {
@@ -982,7 +1016,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
           }
         } else {
-          drain_later_chunk(acc, t_addr, four_parts, fa, s_uni, fbp, UNI, release);
+          drain_later_chunk(acc, t_addr, four_parts, fa, s_uni, fbp, UNI, release, fb8);
         }
       }
       if (!ok) break;
@@ -1145,6 +1179,7 @@ struct OperandPlan {
   int64_t Ksg, Mgroups;
   int P;      // largest run of k-blocks with a constant fp32 factor for every row
   bool row_uniform;   // the fp32 factor of a chunk is the same for every row of the operand
+  bool row_groups8;   // ... or for aligned runs of eight rows: blocks of one row each, eight to a super-group (a (128,1) weight)
 };
 
 int plan_operand(const pb_operand* o, const char* name, OperandPlan* plan) {
@@ -1182,6 +1217,7 @@ int plan_operand(const pb_operand* o, const char* name, OperandPlan* plan) {
   // one super-group in all, or blocks numbered along the rows first with whole block-rows per
   // super-group: every row then sees the same fp32 amax in a given k-block
   plan->row_uniform = (g.M == 1) || (o->transposed_blocks && g.K % (o->rows / o->grid_a) == 0);
+  plan->row_groups8 = !plan->row_uniform && o->transposed_blocks && o->grid_a == 1 && g.K == 8 && o->rows % 8 == 0;
   return PB_OK;
 }
 
@@ -1287,7 +1323,7 @@ int launch_gemm_uni(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensor
   return p.fb_uniform ? launch_gemm<BN, PROF, true>(ma, mb, md, p, st) : launch_gemm<BN, PROF, false>(ma, mb, md, p, st);
 }
 
-template <bool PROF, bool UNI>
+template <bool PROF, int UNI>
 int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msfa, const CUtensorMap& msfb,
                      const CUtensorMap& md, const GemmParams& p, cudaStream_t st) {
   static std::mutex mu;
@@ -1311,7 +1347,8 @@ int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
 template <bool PROF>
 int launch_gemm_pair_uni(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msfa, const CUtensorMap& msfb,
                          const CUtensorMap& md, const GemmParams& p, cudaStream_t st) {
-  return p.fb_uniform ? launch_gemm_pair<PROF, true>(ma, mb, msfa, msfb, md, p, st) : launch_gemm_pair<PROF, false>(ma, mb, msfa, msfb, md, p, st);
+  if (p.fb_uniform) return launch_gemm_pair<PROF, 1>(ma, mb, msfa, msfb, md, p, st);
+  return p.fb_groups8 ? launch_gemm_pair<PROF, 2>(ma, mb, msfa, msfb, md, p, st) : launch_gemm_pair<PROF, 0>(ma, mb, msfa, msfb, md, p, st);
 }
 
 }  // namespace
@@ -1390,6 +1427,7 @@ extern "C" int pb_gemm_tn_ex(const pb_operand* a, const pb_operand* b, void* d, 
   p.tiles_m = gp.pair ? gp.Mpad / 256 : gp.tiles_m; p.tiles_n = gp.tiles_n;
   p.a_fmt = a->format; p.b_fmt = b->format; p.d_dtype = d_dtype;
   p.fb_uniform = gp.pb.row_uniform ? 1 : 0;
+  p.fb_groups8 = gp.pb.row_groups8 ? 1 : 0;
   {
     // band height: about 16 MB of A rows (they and B, at most a few tens of MB, then share the 126 MB L2 with the stream of D)
     static const int forced = env_switch("PB_GEMM_BAND", 0);
