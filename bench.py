@@ -791,6 +791,16 @@ def run_profile_case(name: str):
         x = torch.randn(16384, 4096, device="cuda", dtype=torch.bfloat16)
         for _ in range(4):
             quantize_transposed_impl(x, 128)
+    elif name == "activation_f32":
+        # the model's f32 activations: the persistent transposed quantizer on f32, and the token-shift lerps as the prologue of
+        # both quantizers (six mixes, three of them also token-major), on 4 x 2048 tokens of 4096 channels (134 MB in)
+        from pratchya_b200._nnx_impl._glue import token_shift_lerp_quantized
+        g = torch.Generator(device="cuda").manual_seed(0)
+        x = torch.randn(4, 2048, 4096, device="cuda", generator=g)
+        state, mu = torch.randn(4, 1, 4096, device="cuda", generator=g), torch.rand(6, 4096, device="cuda", generator=g)
+        for _ in range(3):
+            quantize_transposed_impl(x.view(-1, 4096), 128)
+            token_shift_lerp_quantized(x, state, mu, (0, 2, 3))
     elif name == "dequantize":
         x = torch.randn(16384, 4096, device="cuda", dtype=torch.bfloat16)
         t = quantize_impl(x, (1, 128))
@@ -871,7 +881,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--headline-only", action="store_true",
                     help="only the headline step and its per-kernel pass (for launch lists under a profiler): no e2e, triple, scaleout or CPU leg")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "transposed", "dequantize", "wkv7", "wkv7_backward", "glue"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "transposed", "activation_f32", "dequantize", "wkv7", "wkv7_backward", "glue"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
     ap.add_argument("--skip-model-step", action="store_true", help="leave out the end-to-end training-step record (about half a minute)")
     ap.add_argument("--cpu-child", action="store_true", help=argparse.SUPPRESS)
