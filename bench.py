@@ -258,7 +258,7 @@ def time_triple(tokens: int, d_model: int, ffn: int, dist: str, seed: int, reps:
 
 
 # --------------------------------------------------------------------------- the end-to-end training step (configs[4])
-def time_model_step(world: int, rank: int, dev, barrier, steps: int = 2):
+def time_model_step(world: int, rank: int, dev, barrier, host_group=None, steps: int = 2):
     """One data-parallel training step of the modified RWKV-7 model with every linear layer on the FP8 path: 24 layers,
     d_model 2048, head size 64, vocabulary 65536, context 4096, 8 sequences per GPU (the configuration's global batch of
     64 at 8 GPUs) of random token ids, random-init f32 master weights.  A step = forward + backward + all-reduce of the
@@ -266,7 +266,11 @@ def time_model_step(world: int, rank: int, dev, barrier, steps: int = 2):
     backward pass (nnx.remat); here as many of the last blocks as the GPU's free memory holds keep their activations
     instead (10 GB per block at 8 x 4096 tokens, with 30 GB left free) and the others are recomputed: same loss and
     gradient bits, one forward pass less for the kept blocks.  CUDA events around each step, barrier on both sides,
-    mean of `steps` after one warm-up."""
+    mean of `steps` after two warm-up steps.
+
+    With more than one rank every step ends its own GPU work (a synchronize) and the ranks then agree on the host, through
+    `host_group` (gloo, CPU tensors), that all of them are healthy before any of them enters the gradient exchange: a rank
+    whose GPU work failed says so there, and all ranks return an error record with no collective in flight."""
     import torch
     import torch.distributed as dist
     from pratchya_b200._nnx_impl._model import PratchyaConfig
@@ -277,39 +281,73 @@ def time_model_step(world: int, rank: int, dev, barrier, steps: int = 2):
     torch.cuda.empty_cache()
     free_bytes, _ = torch.cuda.mem_get_info(dev)
     # measured: a step with every block recomputed peaks at 51 GB, and a block that keeps its activations adds 10 GB
-    kept = torch.tensor([max(0, min(cfg.n_layers, int((free_bytes - 52e9 - 30e9) // (10.1e9 * seqs * ctx / 32768))))], device=dev)
+    kept = torch.tensor([max(0, min(cfg.n_layers, int((free_bytes - 52e9 - 30e9) // (10.1e9 * seqs * ctx / 32768))))], dtype=torch.int32)
     if world > 1:
-        dist.all_reduce(kept, op=dist.ReduceOp.MIN)
+        dist.all_reduce(kept, op=dist.ReduceOp.MIN, group=host_group)
     kept = int(kept.item())
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
     ids = torch.randint(0, cfg.vocab_size, (seqs, ctx), device=dev, generator=gen)
     out = None
     for attempt_kept in ([kept, 0] if kept else [0]):
-        out = _model_step_once(cfg, attempt_kept, world, rank, dev, barrier, steps, ids, seqs, ctx)
-        if "error" not in out:
+        out = _model_step_once(cfg, attempt_kept, world, rank, dev, barrier, host_group, steps, ids, seqs, ctx)
+        if "error" not in out or not out.get("retry"):
             break
-        torch.cuda.empty_cache()
-    set_literal_dot_precision("f32")
+    out.pop("retry", None)
+    try:
+        set_literal_dot_precision("f32")
+    except Exception:      # noqa: BLE001
+        pass
     return out
 
 
-def _model_step_once(cfg, kept, world, rank, dev, barrier, steps, ids, seqs, ctx):
+class _StepFailed(RuntimeError):
+    pass
+
+
+def _model_step_once(cfg, kept, world, rank, dev, barrier, host_group, steps, ids, seqs, ctx):
     import torch
     import torch.distributed as dist
     from pratchya_b200._nnx_impl._dp import allreduce_gradients
     from pratchya_b200._nnx_impl._model import PratchyaCausalLM
-    model = PratchyaCausalLM(cfg, seed=11, device=dev, remat=cfg.n_layers - kept)
-    params = [p for p in model.parameters()]
-    momentum = [torch.zeros_like(p) for p in params]
-    n_params = sum(p.numel() for p in params)
-    losses = []
-    torch.cuda.reset_peak_memory_stats(dev)
 
-    def step(exchange=True):
-        for p in params:
+    def agree(code: int) -> int:
+        """The worst of the ranks' codes (0 healthy, 1 out of memory, 2 any other failure), over CPU tensors only."""
+        if world == 1:
+            return code
+        t = torch.tensor([code], dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=host_group)
+        return int(t.item())
+
+    def guarded(fn):
+        """Runs fn and this rank's GPU work to the end; returns (code, message)."""
+        try:
+            fn()
+            torch.cuda.synchronize(dev)
+            return 0, None
+        except torch.cuda.OutOfMemoryError as e:
+            return 1, f"OutOfMemoryError: {e}"[:300]
+        except Exception as e:      # noqa: BLE001 - reported in the record
+            return 2, f"{type(e).__name__}: {e}"[:300]
+
+    state = {}
+
+    def build():
+        state["model"] = PratchyaCausalLM(cfg, seed=11, device=dev, remat=cfg.n_layers - kept)
+        state["params"] = [p for p in state["model"].parameters()]
+        state["momentum"] = [torch.zeros_like(p) for p in state["params"]]
+        torch.cuda.reset_peak_memory_stats(dev)
+
+    losses = []
+
+    def compute():
+        for p in state["params"]:
             p.grad = None
-        _, loss = model(ids, ids)
+        _, loss = state["model"](ids, ids)
         loss.backward()
+        losses.append(loss.detach())
+
+    def finish(exchange):
+        params, momentum = state["params"], state["momentum"]
         if world > 1 and exchange:
             allreduce_gradients(params, world)
         grads = [p.grad for p in params]
@@ -317,37 +355,47 @@ def _model_step_once(cfg, kept, world, rank, dev, barrier, steps, ids, seqs, ctx
             torch._foreach_mul_(momentum, 0.9)
             torch._foreach_add_(momentum, grads, alpha=0.1)
             torch._foreach_add_(params, [m.sign() for m in momentum], alpha=-1e-4)
-        losses.append(loss.detach())
 
-    # warm-up without the exchange first, so that a rank that cannot run the step says so before any collective waits on it
-    ok = torch.ones(1, device=dev)
-    failure = None
-    try:
-        step(exchange=False)
-        torch.cuda.synchronize()
-    except Exception as e:      # noqa: BLE001 - reported in the record
-        failure = f"{type(e).__name__}: {e}"[:300]
-        ok.zero_()
-    if world > 1:
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-    if ok.item() == 0:
-        for p in params:
+    def step(exchange=True):
+        code, msg = guarded(compute)
+        worst = agree(code)
+        if worst:
+            raise _StepFailed(msg or "another rank failed", worst)
+        finish(exchange)
+
+    def failed(msg, worst):
+        for p in state.get("params", []):
             p.grad = None
-        del model, params, momentum
-        return {"error": failure or "another rank failed in the warm-up step", "kept_blocks": kept}
-    step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
+        state.clear()
+        if worst == 1:
+            try:
+                torch.cuda.empty_cache()
+            except Exception:      # noqa: BLE001
+                pass
+        return {"error": msg, "kept_blocks": kept, "retry": worst == 1 and kept > 0}
+
+    code, msg = guarded(build)
+    worst = agree(code)
+    if worst:
+        return failed(msg or "another rank failed while building the model", worst)
+    try:
+        step(exchange=False)     # the first warm-up step without the exchange
         step()
-    e1.record()
-    barrier()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        barrier()
+    except _StepFailed as e:
+        return failed(e.args[0], e.args[1])
     ms = e0.elapsed_time(e1) / steps
+    n_params = sum(p.numel() for p in state["params"])
     out = {"ms_per_step": ms, "tokens_per_gpu": seqs * ctx, "parameters": n_params, "losses": [float(l) for l in losses],
            "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9, "literal_dot_precision": "tf32",
            "recomputed_blocks": cfg.n_layers - kept, "kept_blocks": kept}
-    del model, params, momentum
+    state.clear()
     torch.cuda.empty_cache()
     return out
 
@@ -393,8 +441,12 @@ def run_ours(args):
             os.sched_setaffinity(0, affinity & os.sched_getaffinity(0) or os.sched_getaffinity(0))
         except OSError:
             affinity = None
+    host_group = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        # a second group on CPU tensors: the ranks agree through it, step by step, that every one of them is still healthy before
+        # they enter a collective of the end-to-end step, so that a rank whose GPU work failed leaves between steps with nothing in flight
+        host_group = dist.new_group(backend="gloo")
     lib = _lib.load()
     stream = torch.cuda.current_stream().cuda_stream
 
@@ -673,22 +725,30 @@ def run_ours(args):
                      "steps": n_sus - n_sus // 3, "clocks": s_clocks}
         _lib.check(lib.pb_gemm_check(stream))
 
-    # ---- the end-to-end training step (configs[4]); its own record, not the headline
-    model_step = None
-    if not args.skip_model_step:
-        torch.cuda.empty_cache()
-        model_step = time_model_step(world, rank, dev, barrier)
-        if "ms_per_step" in model_step:
-            ms_t = torch.tensor([model_step["ms_per_step"]], device=dev, dtype=torch.float64)
-            if world > 1:
-                dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
-            model_step["ms_per_step"] = ms_t.item()
-
     times = torch.tensor([total_ms, e2e_ms, g_ms, q_ms, big_q_ms, big_qt_ms, big_dq_ms, copy_only_ms, scale["ms"], scale["gemm_ms"],
                           allreduce["ms"] if allreduce else 0.0], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     total_ms, e2e_ms, g_ms, q_ms, big_q_ms, big_qt_ms, big_dq_ms, copy_only_ms, scale_ms, scale_gemm_ms, ar_ms = times.tolist()
+
+    # ---- the end-to-end training step (configs[4]); its own record, not the headline.  It comes last, and after it the ranks only
+    # talk through the host group: a rank that failed in it cannot be asked for another GPU collective.
+    model_step = None
+    if not args.skip_model_step:
+        torch.cuda.empty_cache()
+        model_step = time_model_step(world, rank, dev, barrier, host_group)
+        ms_t = torch.tensor([model_step.get("ms_per_step", -1.0)], dtype=torch.float64)
+        bad_t = torch.tensor([0 if "ms_per_step" in model_step else 1], dtype=torch.int32)
+        if world > 1:
+            dist.all_reduce(ms_t, op=dist.ReduceOp.MAX, group=host_group)
+            dist.all_reduce(bad_t, op=dist.ReduceOp.MAX, group=host_group)
+        if "ms_per_step" in model_step:
+            model_step["ms_per_step"] = ms_t.item()
+        if bad_t.item() and "error" not in model_step:
+            model_step = {"error": "another rank failed in the end-to-end step"}
+        model_failed = bool(bad_t.item())
+    else:
+        model_failed = False
 
     if rank == 0:
         peaks = load_peaks()
@@ -771,8 +831,14 @@ def run_ours(args):
                                     note="the step repeated for about a second (rank 0's own rate x ranks); not the headline value")
         if world == 1:
             out["cpu_baseline"] = cpu_baseline()
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
+        if model_failed:
+            # a rank's GPU work failed: its context cannot take part in the collective teardown of the NCCL group.  Every rank
+            # has agreed on that through the host group and has nothing in flight; they leave without another GPU collective.
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)         # the record on rank 0's line carries the error
         dist.destroy_process_group()
     return 0
 
