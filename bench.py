@@ -264,7 +264,7 @@ def time_model_step(world: int, rank: int, dev, barrier, host_group=None, steps:
     64 at 8 GPUs) of random token ids, random-init f32 master weights.  A step = forward + backward + all-reduce of the
     gradients in bf16 over NCCL + a sign-momentum update of the masters.  The reference recomputes every block in the
     backward pass (nnx.remat); here as many of the last blocks as the GPU's free memory holds keep their activations
-    instead (10 GB per block at 8 x 4096 tokens, with 30 GB left free) and the others are recomputed: same loss and
+    instead (10 GB per block at 8 x 4096 tokens, with 20 GB left free) and the others are recomputed: same loss and
     gradient bits, one forward pass less for the kept blocks.  CUDA events around each step, barrier on both sides,
     mean of `steps` after two warm-up steps.
 
@@ -280,8 +280,8 @@ def time_model_step(world: int, rank: int, dev, barrier, host_group=None, steps:
     seqs, ctx = 8, 4096
     torch.cuda.empty_cache()
     free_bytes, _ = torch.cuda.mem_get_info(dev)
-    # measured: a step with every block recomputed peaks at 51 GB, and a block that keeps its activations adds 10 GB
-    kept = torch.tensor([max(0, min(cfg.n_layers, int((free_bytes - 52e9 - 30e9) // (10.1e9 * seqs * ctx / 32768))))], dtype=torch.int32)
+    # measured: a step with every block recomputed peaks at 44 GB, and a block that keeps its activations adds 10.1 GB (10 kept: 144.7 GB)
+    kept = torch.tensor([max(0, min(cfg.n_layers, int((free_bytes - 46e9 - 20e9) // (10.1e9 * seqs * ctx / 32768))))], dtype=torch.int32)
     if world > 1:
         dist.all_reduce(kept, op=dist.ReduceOp.MIN, group=host_group)
     kept = int(kept.item())
