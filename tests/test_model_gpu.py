@@ -190,3 +190,65 @@ def test_model_gradients_are_the_same_bits_with_and_without_recomputation(built_
         assert torch.equal(results[0][0], other[0])
         for name, grad in results[0][1].items():
             assert torch.equal(grad, other[1][name]), f"gradient of {name}"
+
+
+def test_block_at_the_benchmark_size_against_the_literal_route(built_lib):
+    """One block at the end-to-end record's size (8 x 4096 tokens of 2048 channels, 32 heads) run twice from the same
+    parameters: on the product route (tensor-core products with their fp8 backward recipe, fused element-wise kernels,
+    the lerp and relu^2 prologues of the quantizers) and on the literal route (every product as dequantize + f32 matmul,
+    forward and backward, the element-wise work op by op in torch).  The small-size tests above pin the values; this one is
+    about the size: many tiles per CTA in every product, whole waves of every kernel.  Outputs agree like the
+    stage-by-stage checks (a few values per million fall to the other side of an fp8 rounding).  Gradients agree within
+    the noise of the fp8 gradient recipe: on the product route every dY is quantized to e4m3 before its two products
+    (3-4 % per element and stage, more where a block's small entries carry the energy), on the literal route it is
+    not.  Observed: 4e-2 to 9e-2 of the Frobenius norm, 1.35e-1 for w_receptance; the bound is 2e-1 (a product that
+    returned wrong tiles would show as 1 or more)."""
+    from pratchya_b200._qualia import _ops
+    cfg_kw = dict(vocab_size=1024, hidden_size=2048, intermediate_size=8192, lora_rank=128, head_dim=64, n_layers=1, blksize=128)
+    b, t, c = 8, 4096, 2048
+    results = []
+    for literal in (False, True):
+        gen = torch.Generator(device="cuda").manual_seed(21)
+        blk = RWKVBlock(PratchyaConfig(fused_glue=not literal, **cfg_kw), gen, "cuda", first_layer=False)
+        x = (torch.randn(b, t, c, device="cuda", generator=gen)).requires_grad_(True)
+        v0 = torch.randn(b, t, c, device="cuda", generator=gen).requires_grad_(True)
+        g = torch.randn(b, t, c, device="cuda", generator=gen)
+        pos = torch.arange(t, device="cuda", dtype=torch.int32)
+        zeros = torch.zeros(b, 1, c, device="cuda")
+        saved = _ops._tensor_core_eligible
+        if literal:
+            _ops._tensor_core_eligible = lambda *a, **k: False
+        try:
+            out = blk(x, v0, pos, zeros, zeros, None)
+            (out[0] * g).sum().backward()
+        finally:
+            _ops._tensor_core_eligible = saved
+        grads = {"x": x.grad, "v0": v0.grad}
+        for name in ("tm.w_receptance.kernel", "tm.w_output.kernel", "tm.decay_lora.up.kernel", "tm.iclr_lora.down.kernel", "tm.mu", "cm.w_k.kernel",
+                     "cm.w_v.kernel", "tm.gn_scale", "pre_rmsnorm.scale"):
+            grads[name] = dict(blk.named_parameters())[name].grad
+        results.append((out[0].detach(), {k: v.detach().clone() for k, v in grads.items()}))
+        del blk, out, x, v0
+        torch.cuda.empty_cache()
+    _lib_check(built_lib)
+    y, y_lit = results[0][0], results[1][0]
+    scale = y_lit.abs().max().item()
+    diff = (y - y_lit).abs()
+    print(f"block output: mean {diff.mean().item() / scale:.2e}, max {diff.max().item() / scale:.2e} of the largest magnitude")
+    assert diff.mean().item() <= 4e-3 * scale and diff.max().item() <= 2e-1 * scale
+    worst = {}
+    for name, gr in results[0][1].items():
+        ref = results[1][1][name]
+        worst[name] = ((gr - ref).norm() / ref.norm().clamp(min=1e-30)).item()
+        print(f"gradient of {name}: relative Frobenius difference {worst[name]:.2e}")
+        assert torch.isfinite(gr).all()
+    for name, rel in worst.items():
+        assert rel <= GRAD_TOL, f"gradient of {name}: {rel:.2e}"
+
+
+GRAD_TOL = 2e-1
+
+
+def _lib_check(built_lib):
+    from pratchya_b200 import _lib
+    _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
