@@ -187,6 +187,33 @@ def test_shallow_products_with_many_tiles_per_cta(built_lib, m, k, n, grid):
         assert torch.equal(got, first)
 
 
+@pytest.mark.parametrize("m,k,n", [(32768, 2048, 128), (4096, 2048, 65536), (8192, 768, 2048)])
+def test_column_scaled_weights_at_the_model_sizes(built_lib, m, k, n):
+    """(128,1) weights at the sizes the end-to-end model uses them: a LoRA down projection over 8 x 4096 tokens, the
+    lm_head's 65536 columns, and a depth that is not a multiple of four k-blocks.  Their chunks are single k-blocks
+    (the epilogue form with one fp32 factor per eight columns, fetched a chunk ahead); many tiles per CTA."""
+    from pratchya_b200._qualia import dequantize_impl
+    gen = torch.Generator(device="cuda").manual_seed(m + k + n)
+    x = torch.randn(m, k, device="cuda", generator=gen)
+    x[::5] *= 1e-2
+    w = torch.randn(k, n, device="cuda", generator=gen) * 0.05
+    w[:, ::9] *= 30.0                                            # neighbouring column groups with very different factors
+    xq, wq = quantize_impl(x, (1, 128)), quantize_impl(w, (128, 1))
+    assert _ops._tensor_core_eligible(xq[0], wq[0], (1, 128), (128, 1))
+    got = matmul_impl(*xq, *wq, (1, 128), (128, 1))
+    again = matmul_impl(*xq, *wq, (1, 128), (128, 1))
+    _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+    assert torch.equal(got, again)
+    w_hat = dequantize_impl(*wq, torch.float32, (128, 1)).double()
+    x_hat = dequantize_impl(*xq, torch.float32, (1, 128))
+    worst, scale = 0.0, 0.0
+    for r0 in range(0, m, 4096):                                 # the f64 product in row bands
+        ref = x_hat[r0:r0 + 4096].double() @ w_hat
+        worst = max(worst, (got[r0:r0 + 4096].double() - ref).abs().max().item())
+        scale = max(scale, ref.abs().max().item())
+    assert worst <= 1e-5 * scale, f"{m}x{n}x{k}: max abs err {worst:.3e} against a largest magnitude of {scale:.3e}"
+
+
 @pytest.mark.parametrize("m,k,n", [(256, 2048, 64), (512, 128, 2048), (384, 1024, 4096), (128, 2048, 48)])
 def test_column_scaled_weights_run_on_the_tensor_cores(built_lib, m, k, n):
     """Weights on the (128,1) grid -- the reference's LoRA down/up, gate and lm_head kernels
