@@ -107,6 +107,7 @@ class _ShiftLerpQuantFn(torch.autograd.Function):
             handles = tuple(torch.zeros(1, dtype=torch.float32, device=dev).expand(bsz, steps, chans) for _ in range(n_mix))
         ctx.save_for_backward(x, state, mu)
         ctx.mark_non_differentiable(q, sc8, sc32, q_t, sc8_t, sc32_t)
+        ctx.set_materialize_grads(False)      # no zero-filled fp8 arrays for the triples' absent cotangents
         return (*handles, q, sc8, sc32, q_t, sc8_t, sc32_t)
 
     @staticmethod
