@@ -307,27 +307,14 @@ class _StepFailed(RuntimeError):
 def _model_step_once(cfg, kept, world, rank, dev, barrier, host_group, steps, ids, seqs, ctx):
     import torch
     import torch.distributed as dist
-    from pratchya_b200._nnx_impl._dp import allreduce_gradients
+    from pratchya_b200._nnx_impl._dp import agree_on_health, allreduce_gradients, run_guarded
     from pratchya_b200._nnx_impl._model import PratchyaCausalLM
 
-    def agree(code: int) -> int:
-        """The worst of the ranks' codes (0 healthy, 1 out of memory, 2 any other failure), over CPU tensors only."""
-        if world == 1:
-            return code
-        t = torch.tensor([code], dtype=torch.int32)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=host_group)
-        return int(t.item())
+    def agree(code: int) -> int:       # the worst of the ranks' codes (0 healthy, 1 out of memory, 2 any other failure)
+        return agree_on_health(code, world, host_group)
 
-    def guarded(fn):
-        """Runs fn and this rank's GPU work to the end; returns (code, message)."""
-        try:
-            fn()
-            torch.cuda.synchronize(dev)
-            return 0, None
-        except torch.cuda.OutOfMemoryError as e:
-            return 1, f"OutOfMemoryError: {e}"[:300]
-        except Exception as e:      # noqa: BLE001 - reported in the record
-            return 2, f"{type(e).__name__}: {e}"[:300]
+    def guarded(fn):                   # fn, then this rank's GPU work to its end; (code, message)
+        return run_guarded(fn, lambda: torch.cuda.synchronize(dev))
 
     state = {}
 

@@ -62,3 +62,53 @@ def test_single_rank_is_a_no_op():
     p = torch.nn.Parameter(torch.ones(4))
     p.grad = torch.full((4,), 3.0)
     assert allreduce_gradients([p], 1) == 0 and torch.equal(p.grad, torch.full((4,), 3.0))
+
+
+def _health_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from pratchya_b200._nnx_impl._dp import FAILED, HEALTHY, OUT_OF_MEMORY, agree_on_health, run_guarded
+        host_group = dist.new_group(backend="gloo")
+        seen = []
+
+        def work(step):
+            def fn():
+                if step == 1 and rank == 1:
+                    raise RuntimeError("unspecified launch failure (injected on the host)")
+                if step == 2 and rank == 0:
+                    raise torch.OutOfMemoryError("injected")
+            return fn
+
+        for step in range(3):
+            code, msg = run_guarded(work(step), sync=lambda: None)
+            worst = agree_on_health(code, world, host_group)
+            seen.append((code, worst, msg))
+            # a healthy step would now enter the collective; an unhealthy one is left by every rank at this same point
+            if worst == HEALTHY:
+                t = torch.ones(1)
+                dist.all_reduce(t)
+                assert t.item() == world
+        want_codes = {0: [HEALTHY, HEALTHY, OUT_OF_MEMORY], 1: [HEALTHY, FAILED, HEALTHY]}[rank]
+        ok = [c for c, _, _ in seen] == want_codes and [w for _, w, _ in seen] == [HEALTHY, FAILED, OUT_OF_MEMORY]
+        ok = ok and (seen[1][2] is None) == (rank == 0)
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ranks_agree_that_one_of_them_failed_before_the_collective():
+    """The step before the gradient exchange: a rank whose work raised (a kernel fault, an allocation failure: injected
+    on the host here) reports it through the host group, every rank sees the worst code and none enters the
+    collective of that step."""
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _free_port()
+        procs = [ctx.Process(target=_health_worker, args=(r, 2, port, ret)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+        assert ret.get(0) is True and ret.get(1) is True
