@@ -280,8 +280,9 @@ def time_model_step(world: int, rank: int, dev, barrier, host_group=None, steps:
     seqs, ctx = 8, 4096
     torch.cuda.empty_cache()
     free_bytes, _ = torch.cuda.mem_get_info(dev)
-    # measured: a step with every block recomputed peaks at 44 GB, and a block that keeps its activations adds 10.1 GB (10 kept: 144.7 GB)
-    kept = torch.tensor([max(0, min(cfg.n_layers, int((free_bytes - 46e9 - 20e9) // (10.1e9 * seqs * ctx / 32768))))], dtype=torch.int32)
+    # measured: a step with every block recomputed peaks at 35 GB (the logits' cotangent written over the logits), and a block that
+    # keeps its activations adds 10.1 GB
+    kept = torch.tensor([max(0, min(cfg.n_layers, int((free_bytes - 37e9 - 20e9) // (10.1e9 * seqs * ctx / 32768))))], dtype=torch.int32)
     if world > 1:
         dist.all_reduce(kept, op=dist.ReduceOp.MIN, group=host_group)
     kept = int(kept.item())
@@ -329,7 +330,7 @@ def _model_step_once(cfg, kept, world, rank, dev, barrier, host_group, steps, id
     def compute():
         for p in state["params"]:
             p.grad = None
-        _, loss = state["model"](ids, ids)
+        _, loss = state["model"](ids, ids, keep_logits=False)
         loss.backward()
         losses.append(loss.detach())
 

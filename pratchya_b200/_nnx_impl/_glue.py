@@ -336,7 +336,7 @@ def wkv_finish(y, r, k, v, gate, gn_scale, gn_bias, bonus_mult, eps: float, n_he
 
 class _SmoothedXentFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, logits, target, weight, alpha, denominator):
+    def forward(ctx, logits, target, weight, alpha, denominator, reuse_logits=False):
         lib = _lib.load()
         rows, vocab = logits.shape
         dev = logits.device
@@ -346,7 +346,7 @@ class _SmoothedXentFn(torch.autograd.Function):
             check(lib.pb_smoothed_xent(logits.data_ptr(), target.data_ptr(), weight.data_ptr(), rows, vocab, alpha,
                                        row_loss.data_ptr(), lse.data_ptr(), _stream(dev)))
         ctx.save_for_backward(logits, target, weight, lse)
-        ctx.alpha, ctx.denominator = alpha, denominator
+        ctx.alpha, ctx.denominator, ctx.reuse_logits = alpha, denominator, bool(reuse_logits)
         return row_loss.sum() / denominator
 
     @staticmethod
@@ -356,17 +356,20 @@ class _SmoothedXentFn(torch.autograd.Function):
         rows, vocab = logits.shape
         dev = logits.device
         g = g.to(torch.float32).reshape(1).contiguous()
-        dlogits = torch.empty_like(logits)
+        # every element of the cotangent depends on its own logit only: with reuse_logits it is written over the logits
+        dlogits = logits if ctx.reuse_logits else torch.empty_like(logits)
         with torch.cuda.device(dev):
             check(lib.pb_smoothed_xent_bwd(logits.data_ptr(), target.data_ptr(), weight.data_ptr(), lse.data_ptr(), g.data_ptr(),
                                            ctx.denominator, rows, vocab, ctx.alpha, dlogits.data_ptr(), _stream(dev)))
-        return dlogits, None, None, None, None
+        return dlogits, None, None, None, None, None
 
 
-def smoothed_cross_entropy(logits, labels, alpha: float = 0.1):
+def smoothed_cross_entropy(logits, labels, alpha: float = 0.1, reuse_logits: bool = False):
     """compute_loss, pratchya/_nnx_impl/_utils.py:7-13, on logits [B, T, V] f32 and labels [B, T]: position t predicts label
     t+1 (the reference's caller passes logits[:, :-1] and label[:, 1:]), one-hot labels smoothed by alpha, softmax cross
-    entropy, mean over the B * (T-1) positions.  One pass over the logits forward and one backward."""
+    entropy, mean over the B * (T-1) positions.  One pass over the logits forward and one backward.  `reuse_logits`: the
+    backward pass writes the logits' cotangent over the logits themselves (8.6 GB less at the peak of a step with 32768
+    tokens and 65536 words); for a caller that does not read the logits afterwards and runs the backward pass once."""
     if not logits.is_cuda:
         raise RuntimeError("smoothed_cross_entropy needs CUDA tensors: pratchya_b200 has no CPU path")
     bsz, steps, vocab = logits.shape
@@ -375,4 +378,6 @@ def smoothed_cross_entropy(logits, labels, alpha: float = 0.1):
     target = torch.cat([labels[:, 1:], labels[:, :1]], dim=1).to(torch.int64).reshape(-1).contiguous()      # the last column is a placeholder
     weight = torch.ones(bsz, steps, dtype=torch.float32, device=logits.device)
     weight[:, -1] = 0.0
-    return _SmoothedXentFn.apply(_f32c(logits).reshape(bsz * steps, vocab), target, weight.reshape(-1), float(alpha), float(bsz * (steps - 1)))
+    flat = _f32c(logits).reshape(bsz * steps, vocab)
+    reuse = bool(reuse_logits) and flat.data_ptr() == logits.data_ptr()          # only the caller's own array, never a converted copy's alias
+    return _SmoothedXentFn.apply(flat, target, weight.reshape(-1), float(alpha), float(bsz * (steps - 1)), reuse)

@@ -318,7 +318,9 @@ class PratchyaCausalLM(torch.nn.Module):
         rows = self.embedding[input_ids]             # the rows of a (1,blk)-quantized table quantize as the table does: row-local super-groups
         return read_param(rows, (1, self.cfg.blksize)) * math.sqrt(self.cfg.hidden_size)
 
-    def forward(self, input_ids, label=None):
+    def forward(self, input_ids, label=None, keep_logits=True):
+        """(logits, loss).  `keep_logits=False` (with labels, fused kernels): the logits are not returned and the loss's
+        backward pass writes their cotangent over them, for a training step that only wants the loss."""
         cfg = self.cfg
         bsz, steps = input_ids.shape
         dev = input_ids.device
@@ -335,7 +337,12 @@ class PratchyaCausalLM(torch.nn.Module):
         logits = self.lm_head(x)
         loss = None
         if label is not None:
-            loss = fused_cross_entropy(logits, label) if cfg.fused_glue else smoothed_cross_entropy(logits, label)
+            if cfg.fused_glue:
+                loss = fused_cross_entropy(logits, label, reuse_logits=not keep_logits)
+                if not keep_logits:
+                    logits = None
+            else:
+                loss = smoothed_cross_entropy(logits, label)
         return logits, loss
 
 

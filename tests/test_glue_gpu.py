@@ -215,3 +215,8 @@ def test_fused_cross_entropy_matches_torch(built_lib, bsz, steps, vocab):
     g_want, = torch.autograd.grad(want * 1.7, logits)
     close(g_got, g_want, "dlogits", 2e-5)
     assert torch.count_nonzero(g_got[:, -1, :]).item() == 0      # the last position predicts nothing
+    # the cotangent written over the logits: same bits, in the logits' own memory
+    scratch = logits.detach().clone().requires_grad_(True)
+    work = scratch * 1.0                                           # a non-leaf array that nothing else reads
+    g_inplace, = torch.autograd.grad(fused(work, labels, reuse_logits=True) * 1.7, scratch)
+    assert torch.equal(g_inplace, g_got)
