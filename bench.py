@@ -855,6 +855,16 @@ def run_profile_case(name: str):
         for _ in range(3):
             quantize_transposed_impl(x.view(-1, 4096), 128)
             token_shift_lerp_quantized(x, state, mu, (0, 2, 3))
+    elif name == "output_cotangent":
+        # the first step of a Linear's backward pass: dY [8192, 4096] f32 (134 MB) through the output's dequantize rule into its two
+        # fp8 forms, one call; beside it the plain token-major quantizer on the same array
+        g = torch.Generator(device="cuda").manual_seed(0)
+        y = torch.randn(8192, 4096, device="cuda", generator=g)
+        _, y_sc8, y_sc32 = quantize_impl(y, (1, 128))
+        dy = torch.randn(8192, 4096, device="cuda", generator=g) * 1e-3
+        for _ in range(3):
+            _ops.dequantize_bwd_quantize_dual_impl(y_sc8, y_sc32, dy)
+            quantize_transposed_impl(dy, 128)
     elif name == "dequantize":
         x = torch.randn(16384, 4096, device="cuda", dtype=torch.bfloat16)
         t = quantize_impl(x, (1, 128))
@@ -935,7 +945,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--headline-only", action="store_true",
                     help="only the headline step and its per-kernel pass (for launch lists under a profiler): no e2e, triple, scaleout or CPU leg")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "transposed", "activation_f32", "dequantize", "wkv7", "wkv7_backward", "glue"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm_full", "quantize", "transposed", "activation_f32", "output_cotangent", "dequantize", "wkv7", "wkv7_backward", "glue"],
                     help="run a few launches of one kernel on a reduced case (for ncu) and exit")
     ap.add_argument("--skip-model-step", action="store_true", help="leave out the end-to-end training-step record (about half a minute)")
     ap.add_argument("--cpu-child", action="store_true", help=argparse.SUPPRESS)

@@ -282,6 +282,15 @@ PB_API size_t pb_token_shift_lerp_bwd_workspace_size(int64_t batch, int64_t step
 PB_API int pb_token_shift_lerp_bwd(const float* const* g, const float* x, const float* state, const float* mu,
                             int64_t batch, int64_t steps, int64_t channels, int n_mix,
                             float* dx, float* dstate, float* dmu, void* workspace, size_t workspace_bytes, void* stream);
+/* The first step of a Linear's backward pass in one call (pratchya/_qualia/_qarr.py:575-601 followed by the quantizations of
+ * :784-789): the cotangent g [rows, cols] f32 of the layer's fake-quantized output is scaled by the cotangent rule of that
+ * output's dequantize, g' = (g * x_sc) / 128 with x_sc = e8m0(y_sc8) * y_sc32 of the OUTPUT's (1,128) triple (what pb_dequantize_bwd
+ * computes), and g' leaves as the triple of quantize_impl(g', (1,128)) (q, sc8, sc32: the dgrad operand) and as the triple of
+ * quantize_impl(g'^T, (1,128)) (q_t [cols, rows], sc8_t, sc32_t: the wgrad operand).  g' itself is not written.  The bytes are
+ * those of pb_dequantize_bwd followed by pb_quantize and pb_quantize_transposed.  rows and cols multiples of 1024; g 16-byte,
+ * q_t 32-byte aligned; out_format PB_E4M3 or PB_E5M2. */
+PB_API int pb_dequantize_bwd_quantize_dual(const float* g, const uint8_t* y_sc8, const float* y_sc32, int64_t rows, int64_t cols, int out_format,
+                                    uint8_t* q, uint8_t* sc8, float* sc32, uint8_t* q_t, uint8_t* sc8_t, float* sc32_t, void* stream);
 /* Token shift and lerps fused into the activation quantizers of the Linears that consume the mixes
  * (Linear.__call__, pratchya/_nnx_impl/_module.py:46-47, applied to the mixes of :137-151 and :240-247): with
  * v_k = x + (prev - x) * mu[k] as above, every mix k < n_mix leaves as the triple of quantize_impl(v_k, (1,128)),

@@ -217,12 +217,17 @@ class _LinearFn(torch.autograd.Function):
         if ctx.have_xt:
             xt, pos = saved[6:9], 9
         g = g_y.reshape(-1, g_y.shape[-1]).contiguous()
-        if ctx.fake:                                    # cotangent of the output's dequantize, :575-601
-            g = _ops.dequantize_impl_bwd(saved[pos], saved[pos + 1], g, (1, b))
         m, k = xq[0].shape
         n = wq[0].shape[1]
+        if ctx.fake and xt is not None and b == 128:
+            # the cotangent of the output's dequantize (:575-601) as the prologue of dY's two quantizers
+            gq, gt = _ops.dequantize_bwd_quantize_dual_impl(saved[pos], saved[pos + 1], g, out_format=ctx.grad_format)
+        else:
+            if ctx.fake:                                # cotangent of the output's dequantize, :575-601
+                g = _ops.dequantize_impl_bwd(saved[pos], saved[pos + 1], g, (1, b))
+            if xt is not None:
+                gq, gt = _ops.quantize_dual_impl(g, out_format=ctx.grad_format)
         if xt is not None:
-            gq, gt = _ops.quantize_dual_impl(g, out_format=ctx.grad_format)
             op = _ops._operand
             gx = _ops.gemm_tn(op(gq[0], gq[1], gq[2], m, n, (1, 128)), op(wq[0], wq[1], wq[2], k, n, (128, 128)), torch.float32, g.device)
             gw = _ops.gemm_tn(op(xt[0], xt[1], xt[2], k, m, (1, 128)), op(gt[0], gt[1], gt[2], n, m, (1, 128)), torch.float32, g.device)

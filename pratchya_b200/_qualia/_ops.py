@@ -231,6 +231,32 @@ def dequantize_impl_bwd(sc_fp8: torch.Tensor, sc_fp32: torch.Tensor, g_out: torc
     return out.to(g_out.dtype)
 
 
+def dequantize_bwd_quantize_dual_impl(sc_fp8: torch.Tensor, sc_fp32: torch.Tensor, g_out: torch.Tensor, out_format: str = "e4m3"):
+    """quantize_dual_impl(dequantize_impl_bwd(sc_fp8, sc_fp32, g_out, (1,128))): the cotangent of a Linear's fake-quantized output
+    through that output's dequantize rule and into the two fp8 forms the layer's backward products take (_qarr.py:575-601, then
+    :784-789), in one call that never writes the scaled cotangent.  One call (a row pass and a token-major pass over g_out)
+    where it applies (f32, 2-D, rows and cols multiples of 1024); otherwise the two steps.  Same bits either way."""
+    _require_cuda(g_out, "dequantize_bwd_quantize_dual_impl input")
+    rows, cols = g_out.shape[-2], g_out.shape[-1]
+    if not (g_out.dim() == 2 and g_out.dtype == torch.float32 and rows % 1024 == 0 and cols % 1024 == 0 and g_out.numel() > 0):
+        return quantize_dual_impl(dequantize_impl_bwd(sc_fp8, sc_fp32, g_out, (1, 128)), out_format=out_format)
+    lib = _lib.load()
+    g = g_out.contiguous()
+    groups = rows * cols // 1024
+    dev = g.device
+    with torch.cuda.device(dev):
+        q = torch.empty((rows, cols), dtype=_FMT_DTYPE[out_format], device=dev)
+        sc8 = torch.empty((groups, 8), dtype=E8M0, device=dev)
+        sc32 = torch.empty((groups, 1, 1), dtype=torch.float32, device=dev)
+        q_t = torch.empty((cols, rows), dtype=_FMT_DTYPE[out_format], device=dev)
+        sc8_t = torch.empty((groups, 8), dtype=E8M0, device=dev)
+        sc32_t = torch.empty((groups, 1, 1), dtype=torch.float32, device=dev)
+        check(lib.pb_dequantize_bwd_quantize_dual(g.data_ptr(), sc_fp8.contiguous().data_ptr(), sc_fp32.contiguous().data_ptr(), rows, cols,
+                                                  _FMT_CODE[out_format], q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(),
+                                                  q_t.data_ptr(), sc8_t.data_ptr(), sc32_t.data_ptr(), _stream(g)))
+    return (q, sc8, sc32), (q_t, sc8_t, sc32_t)
+
+
 def quantize_impl_bwd(g_out, tgrid):
     """Cotangent rule of quantize_impl, _qarr.py:514-526.  `g_out` is the cotangent of the quantized
     triple: a dense array (any dtype but e4m3) passes through unchanged (:519-520); an e4m3 triple

@@ -393,6 +393,57 @@ fake_quantize_row128_f32_kernel(const float4* __restrict__ x, typename Out4<OutT
   }
 }
 
+// The backward pass of a Linear starts from the cotangent g of its fake-quantized output: the output's dequantize rule
+// scales it, g' = (g * x_sc) / 128 with x_sc = e8m0(y_sc8) * y_sc32 of the OUTPUT's (1,128) triple (dequantize_impl_bwd,
+// _qarr.py:575-601), and g' is then quantized for the two products of the backward pass.  This is the row quantizer with that
+// scaling as its prologue: the output's super-groups are the cotangent's, so a warp has its eight multipliers in lanes 0-7.
+template <int FMT>
+__global__ void __launch_bounds__(kRowThreads)
+scaled_quantize_row128_f32_kernel(const float4* __restrict__ g, const uint8_t* __restrict__ y_sc8, const float* __restrict__ y_sc32,
+                                  uint32_t* __restrict__ q, uint8_t* __restrict__ sc8, float* __restrict__ sc32, int64_t n_groups) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = (int64_t)gridDim.x * (kRowThreads / 32);
+  for (int64_t gi = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); gi < n_groups; gi += warps_total) {
+    const float4* src = g + gi * (kGroupElems / 4);
+    float4 w[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) w[it] = __ldcs(src + it * 32 + lane);
+    float xs = 0.0f;
+    if (lane < 8) xs = __fmul_rn(e8m0_to_f32(__ldg(y_sc8 + gi * 8 + lane)), __ldg(y_sc32 + gi));
+    float m[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {        // load `it` holds elements of block `it`
+      const float x_sc = __shfl_sync(0xffffffffu, xs, it);
+      const float k128 = 0.0078125f;
+      w[it] = make_float4(__fmul_rn(__fmul_rn(w[it].x, x_sc), k128), __fmul_rn(__fmul_rn(w[it].y, x_sc), k128),
+                          __fmul_rn(__fmul_rn(w[it].z, x_sc), k128), __fmul_rn(__fmul_rn(w[it].w, x_sc), k128));
+      m[it] = fmaxf(fmaxf(fabsf(w[it].x), fabsf(w[it].y)), fmaxf(fabsf(w[it].z), fabsf(w[it].w)));
+    }
+    butterfly_max<8, 2>(m, lane);                 // m[0]: amax of block it_own over the warp
+    const int it_own = bitrev<3>(lane & 7);
+    float Mj = m[0];
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 1));
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 2));
+    Mj = fmaxf(Mj, __shfl_xor_sync(0xffffffffu, Mj, 4));
+    uint32_t sb; float D;
+    block_scale(m[0], Mj, sb, D);
+    const float r = __frcp_rn(D);
+    if (lane < 8) sc8[gi * 8 + it_own] = (uint8_t)sb;
+    if (lane == 0) sc32[gi] = Mj;
+    uint32_t* dst = q + gi * (kGroupElems / 4);
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int srcl = bitrev<3>(it);
+      const float Di = __shfl_sync(0xffffffffu, D, srcl);
+      const float ri = __shfl_sync(0xffffffffu, r, srcl);
+      const float2 nD2 = make_float2(-Di, -Di), r2 = make_float2(ri, ri);
+      const uint32_t p0 = div_hoisted_pack2(w[it].x, w[it].y, nD2, r2);
+      const uint32_t p1 = div_hoisted_pack2(w[it].z, w[it].w, nD2, r2);
+      __stcs(dst + it * 32 + lane, bf16x2_to_fp8x2<FMT>(p0) | (bf16x2_to_fp8x2<FMT>(p1) << 16));
+    }
+  }
+}
+
 // The head of TimeMix and of ChannelMix (pratchya/_nnx_impl/_module.py:126-134, 235-237) fused into the activation
 // quantizers of the Linears that follow (Linear.__call__, :46-47): for mix k
 //     v_k[r][c] = x[r][c] + (prev[r][c] - x[r][c]) * mu[k][c],   prev = the token before, the carried state for a first token,
@@ -863,6 +914,32 @@ extern "C" int pb_relu2_requantize(const void* y, int64_t rows, int64_t cols, in
   }
   PB_LAUNCH_CHECK("relu2_requantize_row128_f32_kernel");
   return PB_OK;
+}
+
+namespace pb {   // transpose_quantize.cu
+int launch_scaled_transposed(const float* g, const uint8_t* y_sc8, const float* y_sc32, int out_format, uint8_t* q_t, uint8_t* sc8, float* sc32,
+                             int64_t rows, int64_t cols, cudaStream_t st);
+}
+
+extern "C" int pb_dequantize_bwd_quantize_dual(const float* g, const uint8_t* y_sc8, const float* y_sc32, int64_t rows, int64_t cols, int out_format,
+                                               uint8_t* q, uint8_t* sc8, float* sc32, uint8_t* q_t, uint8_t* sc8_t, float* sc32_t, void* stream) {
+  if (!g || !y_sc8 || !y_sc32 || !q || !sc8 || !sc32 || !q_t || !sc8_t || !sc32_t)
+    return fail(PB_ERR_NULL_POINTER, "pb_dequantize_bwd_quantize_dual: null argument");
+  if (out_format != PB_E4M3 && out_format != PB_E5M2) return fail(PB_ERR_BAD_DTYPE, "pb_dequantize_bwd_quantize_dual: out_format %d is neither PB_E4M3 nor PB_E5M2", out_format);
+  if (rows <= 0 || cols <= 0 || cols % 1024 != 0 || rows % 1024 != 0)
+    return fail(PB_ERR_UNSUPPORTED, "pb_dequantize_bwd_quantize_dual: [%lld, %lld]: rows and cols must be positive multiples of 1024", (long long)rows, (long long)cols);
+  if (rows * (cols / 128) > kMaxIndexed) return fail(PB_ERR_UNSUPPORTED, "pb_dequantize_bwd_quantize_dual: too many blocks");
+  if ((reinterpret_cast<uintptr_t>(g) & 15) || (reinterpret_cast<uintptr_t>(q) & 3) || (reinterpret_cast<uintptr_t>(q_t) & 31))
+    return fail(PB_ERR_MISALIGNED, "pb_dequantize_bwd_quantize_dual: g must be 16-byte, q 4-byte and q_t 32-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t n_groups = rows * (cols / 1024);
+  const int grid = grid_for(n_groups * 32, kRowThreads, 8);
+  if (out_format == PB_E4M3)
+    scaled_quantize_row128_f32_kernel<PB_E4M3><<<grid, kRowThreads, 0, st>>>(reinterpret_cast<const float4*>(g), y_sc8, y_sc32, reinterpret_cast<uint32_t*>(q), sc8, sc32, n_groups);
+  else
+    scaled_quantize_row128_f32_kernel<PB_E5M2><<<grid, kRowThreads, 0, st>>>(reinterpret_cast<const float4*>(g), y_sc8, y_sc32, reinterpret_cast<uint32_t*>(q), sc8, sc32, n_groups);
+  PB_LAUNCH_CHECK("scaled_quantize_row128_f32_kernel");
+  return pb::launch_scaled_transposed(g, y_sc8, y_sc32, out_format, q_t, sc8_t, sc32_t, rows, cols, st);
 }
 
 namespace pb {   // transpose_quantize.cu

@@ -529,11 +529,19 @@ transpose_quantize1024_bf16_ring_kernel(const __grid_constant__ CUtensorMap map_
 // value quantized is v[r][c] = x[r][c] + (prev[r][c] - x[r][c]) * mu[c] with prev the row before (the carried state for the
 // first row of a sequence; sequences are whole tiles long), three roundings as in the op-by-op form.  The row before a
 // thread's first row is in the tile, except for the tile's first row, which sixteen threads fetch with a plain load.
+//
+// SCALE (LERP == 2): the cotangent rule of a (1,128) dequantize as a prologue (dequantize_impl_bwd, _qarr.py:575-601): the value
+// quantized is (x[r][c] * x_sc(r, c / 128)) / 128 with x_sc = e8m0(y_sc8) * y_sc32 of another array's (1,128) triple (the forward
+// output whose cotangent x is).  A tile's 16 columns lie in one block, so it needs one multiplier per row: the group's
+// threads form the 1024 of them in shared memory (rows 128 apart one bank apart) before they read the tile.
 struct LerpPrologue {
   const float* x; const float* state; const float* mu; int steps;
+  const uint8_t* y_sc8; const float* y_sc32;
 };
+constexpr int kRingScaleFloats = 1024 + 8;             // one multiplier per tile row, index r + (r >> 7)
+constexpr int kRingScaleBytes = 2 * kRingScaleFloats * 4;   // per group
 
-template <int FMT, bool LERP>
+template <int FMT, int LERP>
 __global__ void __launch_bounds__(1024, 1)
 transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x, uint8_t* __restrict__ q_t, uint8_t* __restrict__ sc8,
                                        float* __restrict__ sc32, int rows, int cols, int tiles_x, int tiles_y, int n_tiles,
@@ -570,12 +578,34 @@ transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x
   const int swap = (gt >> 4) & 1;                 // upper half-warp: rows in swapped pairs
   const int nsg = rows >> 10;
   int local = 0;
+  uint32_t nb0 = 0, nb1 = 0;                      // SCALE: the e8m0 bytes and fp32 factors of rows gt and gt + 512 of the group's next tile
+  float nf0 = 0.0f, nf1 = 0.0f;
+  auto fetch_scales = [&](int tile_index) {
+    const int cx = tile_index % tiles_x, rest = tile_index / tiles_x, ry = rest % tiles_y, z = rest / tiles_y;
+    const int64_t row = (int64_t)z * rows + ry * 1024 + gt;
+    const int c0 = cx * 16;
+    nb0 = __ldg(lerp.y_sc8 + row * (cols >> 7) + (c0 >> 7));
+    nf0 = __ldg(lerp.y_sc32 + row * (cols >> 10) + (c0 >> 10));
+    nb1 = __ldg(lerp.y_sc8 + (row + 512) * (cols >> 7) + (c0 >> 7));
+    nf1 = __ldg(lerp.y_sc32 + (row + 512) * (cols >> 10) + (c0 >> 10));
+  };
   for (int seq = grp; blockIdx.x + seq * (int)gridDim.x < n_tiles; seq += 2, ++local) {
     const int tl = blockIdx.x + seq * gridDim.x;
     const int cx = tl % tiles_x, rest = tl / tiles_x, ry = rest % tiles_y, z = rest / tiles_y;
     const int c0 = cx * 16, r0 = ry * 1024;
     float before = 0.0f, mu_c = 0.0f;             // LERP: the row before the tile's first row (threads of rows 0..31), mu of the column
-    if (LERP) {
+    float* xs = reinterpret_cast<float*>(smem + kRingBufs * kRingTileBytes + kRingPartBytes + kRingBlockBytes + 64) + grp * kRingScaleFloats;
+    if (LERP == 2) {
+      // This thread's two multipliers of the tile (rows gt and gt + 512) were fetched while the group's previous tile was being
+      // worked on; every thread of the group is past both barriers of that tile, so nobody still reads the old table.
+      if (local == 0) fetch_scales(tl);
+      xs[gt + (gt >> 7)] = __fmul_rn(e8m0_to_f32(nb0), nf0);
+      xs[gt + 512 + ((gt + 512) >> 7)] = __fmul_rn(e8m0_to_f32(nb1), nf1);
+      asm volatile("barrier.cta.sync %0, 512;" ::"r"(grp + 1) : "memory");
+      const int next = blockIdx.x + (seq + 2) * gridDim.x;
+      if (next < n_tiles) fetch_scales(next);       // in flight under this tile's arithmetic
+    }
+    if (LERP == 1) {
       mu_c = __ldg(lerp.mu + c0 + cp);
       if (row_first == 0) {
         const int64_t row = (int64_t)z * rows + r0;
@@ -588,7 +618,14 @@ transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x
     const uint8_t* tile = smem + (size_t)(seq % kRingBufs) * kRingTileBytes;
     float w[32];
     float cm = 0.0f;
-    if (LERP) {
+    if (LERP == 2) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int r = row_first + (i ^ swap);
+        w[i] = __fmul_rn(__fmul_rn(*reinterpret_cast<const float*>(tile + r * 64 + cp * 4), xs[r + (r >> 7)]), 0.0078125f);
+        cm = fmaxf(cm, fabsf(w[i]));
+      }
+    } else if (LERP == 1) {
       if (row_first != 0) before = *reinterpret_cast<const float*>(tile + (row_first - 1) * 64 + cp * 4);
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {           // the two loads of a pair in the half-warp's own order, then rows in their natural order
@@ -609,7 +646,7 @@ transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x
         cm = fmaxf(cm, fabsf(w[i]));
       }
     }
-    const int qswap = LERP ? 0 : swap;            // LERP leaves the registers in row order
+    const int qswap = LERP == 1 ? 0 : swap;       // the lerp prologue leaves the registers in row order
     float (*pa)[16] = part_amax[grp * 2 + (local & 1)];
     pa[blk * 4 + quarter][cp] = cm;
     int give_up;
@@ -650,9 +687,9 @@ transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x
   }
 }
 
-template <int FMT, bool LERP>
+template <int FMT, int LERP>
 int launch_one_pass_f32_ring(const void* x, uint8_t* q_t, uint8_t* sc8, float* sc32, int64_t batch, int64_t rows, int64_t cols, cudaStream_t st,
-                             const LerpPrologue lerp = LerpPrologue{nullptr, nullptr, nullptr, 1}) {
+                             const LerpPrologue lerp = LerpPrologue{nullptr, nullptr, nullptr, 1, nullptr, nullptr}) {
   using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -674,14 +711,14 @@ int launch_one_pass_f32_ring(const void* x, uint8_t* q_t, uint8_t* sc8, float* s
   {
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-      PB_CUDA_TRY(cudaFuncSetAttribute(transpose_quantize1024_f32_ring_kernel<FMT, LERP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem));
+      PB_CUDA_TRY(cudaFuncSetAttribute(transpose_quantize1024_f32_ring_kernel<FMT, LERP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem + kRingScaleBytes));
       configured[dev] = true;
     }
   }
   const int tiles_x = (int)(cols / 16), tiles_y = (int)(rows / 1024);
   const int64_t n_tiles = (int64_t)tiles_x * tiles_y * batch;
   const int grid = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
-  transpose_quantize1024_f32_ring_kernel<FMT, LERP><<<grid, 1024, kRingSmem, st>>>(map, q_t, sc8, sc32, (int)rows, (int)cols, tiles_x, tiles_y, (int)n_tiles, lerp);
+  transpose_quantize1024_f32_ring_kernel<FMT, LERP><<<grid, 1024, kRingSmem + kRingScaleBytes, st>>>(map, q_t, sc8, sc32, (int)rows, (int)cols, tiles_x, tiles_y, (int)n_tiles, lerp);
   PB_LAUNCH_CHECK("transpose_quantize1024_f32_ring_kernel");
   return PB_OK;
 }
@@ -763,7 +800,18 @@ int launch_shift_lerp_transposed(const float* x, const float* state, const float
                                  int64_t rows, int64_t steps, int64_t cols, cudaStream_t st) {
   if (rows % 1024 != 0 || steps % 1024 != 0 || cols % 16 != 0 || rows >= (1ll << 31) || (cols / 16) * (rows / 1024) >= (1ll << 31))
     return fail(PB_ERR_UNSUPPORTED, "shift-lerp transposed quantizer: rows=%lld steps=%lld cols=%lld", (long long)rows, (long long)steps, (long long)cols);
-  return launch_one_pass_f32_ring<PB_E4M3, true>(x, q_t, sc8, sc32, 1, rows, cols, st, LerpPrologue{x, state, mu, (int)steps});
+  return launch_one_pass_f32_ring<PB_E4M3, 1>(x, q_t, sc8, sc32, 1, rows, cols, st, LerpPrologue{x, state, mu, (int)steps, nullptr, nullptr});
+}
+
+// quantize_impl(g'^T, (1,128)) of g' = (g * x_sc) / 128, x_sc from the (1,128) triple (y_sc8, y_sc32) of an array of g's shape
+// [rows, cols] (rows a multiple of 1024, cols of 128): the persistent f32 kernel with that scaling as its prologue.
+int launch_scaled_transposed(const float* g, const uint8_t* y_sc8, const float* y_sc32, int out_format, uint8_t* q_t, uint8_t* sc8, float* sc32,
+                             int64_t rows, int64_t cols, cudaStream_t st) {
+  if (rows % 1024 != 0 || cols % 1024 != 0 || rows >= (1ll << 31) || (cols / 16) * (rows / 1024) >= (1ll << 31))
+    return fail(PB_ERR_UNSUPPORTED, "scaled transposed quantizer: rows=%lld cols=%lld", (long long)rows, (long long)cols);
+  const LerpPrologue pro{nullptr, nullptr, nullptr, 1, y_sc8, y_sc32};
+  return out_format == PB_E4M3 ? launch_one_pass_f32_ring<PB_E4M3, 2>(g, q_t, sc8, sc32, 1, rows, cols, st, pro)
+                               : launch_one_pass_f32_ring<PB_E5M2, 2>(g, q_t, sc8, sc32, 1, rows, cols, st, pro);
 }
 
 // Reads and clears the transposed quantizer's device status word (see pb_gemm_check).
@@ -812,8 +860,8 @@ extern "C" int pb_quantize_transposed(const void* x, int x_dtype, int64_t batch,
       }
       const bool ring32 = batch * rows < (1ll << 31) && (cols / 16) * (rows / 1024) * batch >= 2 * sm_count() && env_switch("PB_TQ_RING", 1) != 0;
       if (ring32)
-        return out_format == PB_E4M3 ? launch_one_pass_f32_ring<PB_E4M3, false>(x, o, sc8, sc32, batch, rows, cols, st)
-                                     : launch_one_pass_f32_ring<PB_E5M2, false>(x, o, sc8, sc32, batch, rows, cols, st);
+        return out_format == PB_E4M3 ? launch_one_pass_f32_ring<PB_E4M3, 0>(x, o, sc8, sc32, batch, rows, cols, st)
+                                     : launch_one_pass_f32_ring<PB_E5M2, 0>(x, o, sc8, sc32, batch, rows, cols, st);
       return out_format == PB_E4M3 ? launch_one_pass<float, PB_E4M3>(x, o, sc8, sc32, batch, rows, cols, st)
                                    : launch_one_pass<float, PB_E5M2>(x, o, sc8, sc32, batch, rows, cols, st);
     }

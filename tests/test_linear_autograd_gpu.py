@@ -145,3 +145,27 @@ def test_literal_dot_precision_switch(built_lib):
         assert torch.equal(a, b)
     with pytest.raises(ValueError):
         set_literal_dot_precision("bf16")
+
+
+@pytest.mark.parametrize("rows,cols,fmt", [(1024, 1024, "e4m3"), (4096, 2048, "e5m2"), (32768, 2048, "e4m3"), (8192, 8192, "e4m3")])
+def test_output_cotangent_scaling_fused_into_its_quantizers(built_lib, rows, cols, fmt):
+    """The first step of a Linear's backward pass: dY through the cotangent rule of the output's dequantize and into its
+    two fp8 forms.  The one-call form (the scaling as a prologue of the row quantizer and of the persistent token-major
+    quantizer) against the three calls it replaces, byte for byte; fewer tiles than SMs, and many."""
+    from pratchya_b200 import _lib
+    from pratchya_b200._qualia import _ops, quantize_impl
+    gen = torch.Generator(device="cuda").manual_seed(rows + cols)
+    y = torch.randn(rows, cols, device="cuda", generator=gen) * 3.0
+    y[:, 128:256] *= 1e-3                                        # blocks of very different scale
+    y[5] = 0.0                                                   # all-zero super-groups in the output: multiplier zero
+    _, y_sc8, y_sc32 = quantize_impl(y, (1, 128))
+    g = torch.randn(rows, cols, device="cuda", generator=gen) * 1e-3
+    g.view(-1)[::4099] *= 300.0
+    got = _ops.dequantize_bwd_quantize_dual_impl(y_sc8, y_sc32, g, out_format=fmt)
+    torch.cuda.synchronize()
+    _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+    want = _ops.quantize_dual_impl(_ops.dequantize_impl_bwd(y_sc8, y_sc32, g, (1, 128)), out_format=fmt)
+    as_bytes = lambda t: t.contiguous().view(torch.uint8)
+    for form, a, b in (("row", got[0], want[0]), ("token-major", got[1], want[1])):
+        for part, u, v in zip(("fp8", "e8m0", "fp32"), a, b):
+            assert u.shape == v.shape and torch.equal(as_bytes(u), as_bytes(v)), f"{form} form, {part}"
