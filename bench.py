@@ -575,7 +575,18 @@ def run_ours(args):
     big_q_ms = time_alone(big_quant)          # leaves the row form's triple in (bq, b8, b32) for the dequantizer
     big_dq_ms = time_alone(big_dequant)
     quant_bytes = qm * qk * QUANT_BYTES_PER_ELEM
-    del big, bq, bqt, back, tws
+    del big, back
+    # the same token-major quantizer on f32 input (the end-to-end model's activations are f32): 4 + 1 + scales bytes per element
+    big32 = [torch.randn(qm, qk, device=dev, dtype=torch.float32) for _ in range(2)]
+
+    def big_quant_t32(i):
+        _lib.check(lib.pb_quantize_transposed(big32[i % 2].data_ptr(), _lib.PB_F32, 1, qm, qk, 128, _lib.PB_E4M3,
+                                              bqt.data_ptr(), b8.data_ptr(), b32.data_ptr(), tws.data_ptr(), tws_bytes, stream))
+
+    big_qt32_ms = time_alone(big_quant_t32)
+    quant32_bytes = qm * qk * (QUANT_BYTES_PER_ELEM + 2.0)
+    _lib.check(lib.pb_gemm_check(stream))
+    del big32, bq, bqt, tws
 
     if args.headline_only:
         if rank == 0:
@@ -714,10 +725,10 @@ def run_ours(args):
         _lib.check(lib.pb_gemm_check(stream))
 
     times = torch.tensor([total_ms, e2e_ms, g_ms, q_ms, big_q_ms, big_qt_ms, big_dq_ms, copy_only_ms, scale["ms"], scale["gemm_ms"],
-                          allreduce["ms"] if allreduce else 0.0], device=dev, dtype=torch.float64)
+                          allreduce["ms"] if allreduce else 0.0, big_qt32_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, g_ms, q_ms, big_q_ms, big_qt_ms, big_dq_ms, copy_only_ms, scale_ms, scale_gemm_ms, ar_ms = times.tolist()
+    total_ms, e2e_ms, g_ms, q_ms, big_q_ms, big_qt_ms, big_dq_ms, copy_only_ms, scale_ms, scale_gemm_ms, ar_ms, big_qt32_ms = times.tolist()
 
     # ---- the end-to-end training step (configs[4]); its own record, not the headline.  It comes last, and after it the ranks only
     # talk through the host group: a rank that failed in it cannot be asked for another GPU collective.
@@ -772,6 +783,9 @@ def run_ours(args):
             "roofline_quantize": hbm("quantize_row128_bf16_kernel", big_q_ms, QUANT_DRAM_TRAFFIC_BYTES),
             "roofline_transposed": hbm("transpose_quantize1024_bf16_kernel", big_qt_ms),
             "roofline_dequantize": hbm("dequantize_row128_kernel", big_dq_ms),
+            "roofline_transposed_f32": dict(hbm("transpose_quantize1024_f32_ring_kernel", big_qt32_ms), workload=f"X[{qm},{qk}] f32",
+                                            achieved=quant32_bytes / (big_qt32_ms * 1e-3) / 1e9,
+                                            frac=quant32_bytes / (big_qt32_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]),
             "e2e": {"value": world * FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": d2h_bytes,
                     "api": "pratchya_b200._nnx_impl.Linear.product (= QArrayImpl(x,(1,128)) @ kernel, the (1,128)-quantized product the "
