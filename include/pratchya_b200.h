@@ -282,6 +282,12 @@ PB_API size_t pb_token_shift_lerp_bwd_workspace_size(int64_t batch, int64_t step
 PB_API int pb_token_shift_lerp_bwd(const float* const* g, const float* x, const float* state, const float* mu,
                             int64_t batch, int64_t steps, int64_t channels, int n_mix,
                             float* dx, float* dstate, float* dmu, void* workspace, size_t workspace_bytes, void* stream);
+/* relu(k)^2 (ChannelMix's activation, pratchya/_nnx_impl/_module.py:249) as the prologue of the second Linear's two input
+ * quantizers: from k [rows, cols] f32 the triples of quantize_impl(relu(k)^2, (1,128)) (q, sc8, sc32) and of its transpose
+ * (q_t [cols, rows], sc8_t, sc32_t), e4m3, without writing relu(k)^2.  The bytes are those of pb_relu2 followed by pb_quantize
+ * and pb_quantize_transposed.  rows and cols multiples of 1024; k 16-byte, q_t 32-byte aligned. */
+PB_API int pb_relu2_quantize_dual(const float* k, int64_t rows, int64_t cols, uint8_t* q, uint8_t* sc8, float* sc32,
+                           uint8_t* q_t, uint8_t* sc8_t, float* sc32_t, void* stream);
 /* The first step of a Linear's backward pass in one call (pratchya/_qualia/_qarr.py:575-601 followed by the quantizations of
  * :784-789): the cotangent g [rows, cols] f32 of the layer's fake-quantized output is scaled by the cotangent rule of that
  * output's dequantize, g' = (g * x_sc) / 128 with x_sc = e8m0(y_sc8) * y_sc32 of the OUTPUT's (1,128) triple (what pb_dequantize_bwd

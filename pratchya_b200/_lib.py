@@ -66,6 +66,7 @@ _SIGNATURES = {
     "pb_token_shift_lerp": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr, _ptr]),
     "pb_token_shift_lerp_bwd_workspace_size": (_sz, [_i64, _i64, _i64, _int]),
     "pb_token_shift_lerp_bwd": (_int, [_ptr] * 4 + [_i64, _i64, _i64, _int] + [_ptr] * 4 + [_sz, _ptr]),
+    "pb_relu2_quantize_dual": (_int, [_ptr, _i64, _i64] + [_ptr] * 7),
     "pb_dequantize_bwd_quantize_dual": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _int] + [_ptr] * 7),
     "pb_shift_lerp_quantize": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr, _ptr, _ptr, C.c_uint, _ptr, _ptr, _ptr, _ptr]),
     "pb_wkv_prepare": (_int, [_ptr] * 11 + [_i64, _i64, _i64, _int] + [_ptr] * 8),

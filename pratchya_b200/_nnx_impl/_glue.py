@@ -281,6 +281,50 @@ def relu2(x):
     return _Relu2Fn.apply(_f32c(x))
 
 
+class _Relu2QuantFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, k):
+        lib = _lib.load()
+        cols = k.shape[-1]
+        rows = k.numel() // cols
+        groups = rows * cols // 1024
+        dev = k.device
+        with torch.cuda.device(dev):
+            q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=dev)
+            sc8 = torch.empty((groups, 8), dtype=torch.float8_e8m0fnu, device=dev)
+            sc32 = torch.empty((groups, 1, 1), dtype=torch.float32, device=dev)
+            q_t = torch.empty((cols, rows), dtype=torch.float8_e4m3fn, device=dev)
+            sc8_t = torch.empty((groups, 8), dtype=torch.float8_e8m0fnu, device=dev)
+            sc32_t = torch.empty((groups, 1, 1), dtype=torch.float32, device=dev)
+            check(lib.pb_relu2_quantize_dual(k.data_ptr(), rows, cols, q.data_ptr(), sc8.data_ptr(), sc32.data_ptr(),
+                                             q_t.data_ptr(), sc8_t.data_ptr(), sc32_t.data_ptr(), _stream(dev)))
+            handle = torch.zeros(1, dtype=torch.float32, device=dev).expand(k.shape)
+        ctx.save_for_backward(k)
+        ctx.mark_non_differentiable(q, sc8, sc32, q_t, sc8_t, sc32_t)
+        ctx.set_materialize_grads(False)
+        return handle, q, sc8, sc32, q_t, sc8_t, sc32_t
+
+    @staticmethod
+    def backward(ctx, g, *_):
+        if g is None:
+            return None
+        return _Relu2Fn.backward(ctx, g)
+
+
+def relu2_quantized(k):
+    """relu(k) ** 2 (_module.py:249) for a consumer that is a (128,128) Linear with a backward pass to follow: the result
+    leaves as a QuantizedMix (the (1,128) triple and the triple of the transpose) and is never written as f32.  k [..., C] f32
+    with C and the number of rows multiples of 1024.  The bytes are those of relu2 + quantize_impl / quantize_transposed_impl."""
+    if not k.is_cuda:
+        raise RuntimeError("relu2_quantized needs CUDA tensors: pratchya_b200 has no CPU path")
+    out = _Relu2QuantFn.apply(_f32c(k))
+    return QuantizedMix(out[0], (out[1], out[2], out[3]), (out[4], out[5], out[6]))
+
+
+def can_quantize_relu2(k):
+    return k.is_cuda and k.dim() >= 2 and k.shape[-1] % 1024 == 0 and k.numel() > 0 and (k.numel() // k.shape[-1]) % 1024 == 0
+
+
 class _WkvFinishFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y, r, k, v, gate, gn_scale, gn_bias, bonus_mult, eps, n_head):

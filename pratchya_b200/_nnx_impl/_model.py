@@ -19,7 +19,7 @@ from dataclasses import dataclass
 import torch
 
 from .._qualia import _ops
-from ._glue import QuantizedMix, can_quantize_mixes, relu2, rms_norm, token_shift_lerp, token_shift_lerp_quantized, wkv_finish, wkv_prepare
+from ._glue import QuantizedMix, can_quantize_mixes, can_quantize_relu2, relu2, relu2_quantized, rms_norm, token_shift_lerp, token_shift_lerp_quantized, wkv_finish, wkv_prepare
 from ._glue import smoothed_cross_entropy as fused_cross_entropy
 from ._module import linear_fp8
 from ._wkv7 import wkv_state_scan
@@ -249,7 +249,10 @@ class ChannelMix(torch.nn.Module):                   # _module.py:228-258
             k = QuantizedMix(y.new_zeros(1).expand(y.shape), _ops.relu2_requantize_impl(y), None)
             return self.w_v(k), cm_state
         k = self.w_k(x_k).to(torch.float32)
-        k = relu2(k) if self.fused_glue else torch.relu(k) ** 2
+        if self.fused_glue and torch.is_grad_enabled() and can_quantize_relu2(k) and self.w_v.tgrid == (128, 128):
+            k = relu2_quantized(k)       # relu^2 as the prologue of w_v's two input quantizers
+        else:
+            k = relu2(k) if self.fused_glue else torch.relu(k) ** 2
         return self.w_v(k), cm_state
 
 

@@ -397,7 +397,10 @@ fake_quantize_row128_f32_kernel(const float4* __restrict__ x, typename Out4<OutT
 // scales it, g' = (g * x_sc) / 128 with x_sc = e8m0(y_sc8) * y_sc32 of the OUTPUT's (1,128) triple (dequantize_impl_bwd,
 // _qarr.py:575-601), and g' is then quantized for the two products of the backward pass.  This is the row quantizer with that
 // scaling as its prologue: the output's super-groups are the cotangent's, so a warp has its eight multipliers in lanes 0-7.
-template <int FMT>
+//
+// RELU2 instead of the scaling: the value quantized is relu(g)^2, the activation between ChannelMix's two Linears
+// (pratchya/_nnx_impl/_module.py:249) as the prologue of the second Linear's input quantizer.
+template <int FMT, bool RELU2>
 __global__ void __launch_bounds__(kRowThreads)
 scaled_quantize_row128_f32_kernel(const float4* __restrict__ g, const uint8_t* __restrict__ y_sc8, const float* __restrict__ y_sc32,
                                   uint32_t* __restrict__ q, uint8_t* __restrict__ sc8, float* __restrict__ sc32, int64_t n_groups) {
@@ -409,14 +412,19 @@ scaled_quantize_row128_f32_kernel(const float4* __restrict__ g, const uint8_t* _
 #pragma unroll
     for (int it = 0; it < 8; ++it) w[it] = __ldcs(src + it * 32 + lane);
     float xs = 0.0f;
-    if (lane < 8) xs = __fmul_rn(e8m0_to_f32(__ldg(y_sc8 + gi * 8 + lane)), __ldg(y_sc32 + gi));
+    if (!RELU2 && lane < 8) xs = __fmul_rn(e8m0_to_f32(__ldg(y_sc8 + gi * 8 + lane)), __ldg(y_sc32 + gi));
     float m[8];
 #pragma unroll
     for (int it = 0; it < 8; ++it) {        // load `it` holds elements of block `it`
-      const float x_sc = __shfl_sync(0xffffffffu, xs, it);
-      const float k128 = 0.0078125f;
-      w[it] = make_float4(__fmul_rn(__fmul_rn(w[it].x, x_sc), k128), __fmul_rn(__fmul_rn(w[it].y, x_sc), k128),
-                          __fmul_rn(__fmul_rn(w[it].z, x_sc), k128), __fmul_rn(__fmul_rn(w[it].w, x_sc), k128));
+      if (RELU2) {
+        const float a = fmaxf(w[it].x, 0.f), b = fmaxf(w[it].y, 0.f), c = fmaxf(w[it].z, 0.f), d = fmaxf(w[it].w, 0.f);
+        w[it] = make_float4(__fmul_rn(a, a), __fmul_rn(b, b), __fmul_rn(c, c), __fmul_rn(d, d));
+      } else {
+        const float x_sc = __shfl_sync(0xffffffffu, xs, it);
+        const float k128 = 0.0078125f;
+        w[it] = make_float4(__fmul_rn(__fmul_rn(w[it].x, x_sc), k128), __fmul_rn(__fmul_rn(w[it].y, x_sc), k128),
+                            __fmul_rn(__fmul_rn(w[it].z, x_sc), k128), __fmul_rn(__fmul_rn(w[it].w, x_sc), k128));
+      }
       m[it] = fmaxf(fmaxf(fabsf(w[it].x), fabsf(w[it].y)), fmaxf(fabsf(w[it].z), fabsf(w[it].w)));
     }
     butterfly_max<8, 2>(m, lane);                 // m[0]: amax of block it_own over the warp
@@ -935,11 +943,32 @@ extern "C" int pb_dequantize_bwd_quantize_dual(const float* g, const uint8_t* y_
   const int64_t n_groups = rows * (cols / 1024);
   const int grid = grid_for(n_groups * 32, kRowThreads, 8);
   if (out_format == PB_E4M3)
-    scaled_quantize_row128_f32_kernel<PB_E4M3><<<grid, kRowThreads, 0, st>>>(reinterpret_cast<const float4*>(g), y_sc8, y_sc32, reinterpret_cast<uint32_t*>(q), sc8, sc32, n_groups);
+    scaled_quantize_row128_f32_kernel<PB_E4M3, false><<<grid, kRowThreads, 0, st>>>(reinterpret_cast<const float4*>(g), y_sc8, y_sc32, reinterpret_cast<uint32_t*>(q), sc8, sc32, n_groups);
   else
-    scaled_quantize_row128_f32_kernel<PB_E5M2><<<grid, kRowThreads, 0, st>>>(reinterpret_cast<const float4*>(g), y_sc8, y_sc32, reinterpret_cast<uint32_t*>(q), sc8, sc32, n_groups);
+    scaled_quantize_row128_f32_kernel<PB_E5M2, false><<<grid, kRowThreads, 0, st>>>(reinterpret_cast<const float4*>(g), y_sc8, y_sc32, reinterpret_cast<uint32_t*>(q), sc8, sc32, n_groups);
   PB_LAUNCH_CHECK("scaled_quantize_row128_f32_kernel");
   return pb::launch_scaled_transposed(g, y_sc8, y_sc32, out_format, q_t, sc8_t, sc32_t, rows, cols, st);
+}
+
+namespace pb {   // transpose_quantize.cu
+int launch_relu2_transposed(const float* k, uint8_t* q_t, uint8_t* sc8, float* sc32, int64_t rows, int64_t cols, cudaStream_t st);
+}
+
+extern "C" int pb_relu2_quantize_dual(const float* k, int64_t rows, int64_t cols, uint8_t* q, uint8_t* sc8, float* sc32,
+                                      uint8_t* q_t, uint8_t* sc8_t, float* sc32_t, void* stream) {
+  if (!k || !q || !sc8 || !sc32 || !q_t || !sc8_t || !sc32_t) return fail(PB_ERR_NULL_POINTER, "pb_relu2_quantize_dual: null argument");
+  if (rows <= 0 || cols <= 0 || cols % 1024 != 0 || rows % 1024 != 0)
+    return fail(PB_ERR_UNSUPPORTED, "pb_relu2_quantize_dual: [%lld, %lld]: rows and cols must be positive multiples of 1024", (long long)rows, (long long)cols);
+  if (rows * (cols / 128) > kMaxIndexed) return fail(PB_ERR_UNSUPPORTED, "pb_relu2_quantize_dual: too many blocks");
+  if ((reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(q) & 3) || (reinterpret_cast<uintptr_t>(q_t) & 31))
+    return fail(PB_ERR_MISALIGNED, "pb_relu2_quantize_dual: k must be 16-byte, q 4-byte and q_t 32-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t n_groups = rows * (cols / 1024);
+  const int grid = grid_for(n_groups * 32, kRowThreads, 8);
+  scaled_quantize_row128_f32_kernel<PB_E4M3, true><<<grid, kRowThreads, 0, st>>>(reinterpret_cast<const float4*>(k), nullptr, nullptr,
+                                                                               reinterpret_cast<uint32_t*>(q), sc8, sc32, n_groups);
+  PB_LAUNCH_CHECK("scaled_quantize_row128_f32_kernel");
+  return pb::launch_relu2_transposed(k, q_t, sc8_t, sc32_t, rows, cols, st);
 }
 
 namespace pb {   // transpose_quantize.cu

@@ -530,7 +530,7 @@ transpose_quantize1024_bf16_ring_kernel(const __grid_constant__ CUtensorMap map_
 // first row of a sequence; sequences are whole tiles long), three roundings as in the op-by-op form.  The row before a
 // thread's first row is in the tile, except for the tile's first row, which sixteen threads fetch with a plain load.
 //
-// SCALE (LERP == 2): the cotangent rule of a (1,128) dequantize as a prologue (dequantize_impl_bwd, _qarr.py:575-601): the value
+// RELU2 (LERP == 3): relu(x)^2 on the way to the registers.  SCALE (LERP == 2): the cotangent rule of a (1,128) dequantize as a prologue (dequantize_impl_bwd, _qarr.py:575-601): the value
 // quantized is (x[r][c] * x_sc(r, c / 128)) / 128 with x_sc = e8m0(y_sc8) * y_sc32 of another array's (1,128) triple (the forward
 // output whose cotangent x is).  A tile's 16 columns lie in one block, so it needs one multiplier per row: the group's
 // threads form the 1024 of them in shared memory (rows 128 apart one bank apart) before they read the tile.
@@ -618,7 +618,14 @@ transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x
     const uint8_t* tile = smem + (size_t)(seq % kRingBufs) * kRingTileBytes;
     float w[32];
     float cm = 0.0f;
-    if (LERP == 2) {
+    if (LERP == 3) {                              // RELU2: relu(x)^2, ChannelMix's activation, on the way to the registers
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float a = fmaxf(*reinterpret_cast<const float*>(tile + (row_first + (i ^ swap)) * 64 + cp * 4), 0.0f);
+        w[i] = __fmul_rn(a, a);
+        cm = fmaxf(cm, w[i]);
+      }
+    } else if (LERP == 2) {
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         const int r = row_first + (i ^ swap);
@@ -801,6 +808,13 @@ int launch_shift_lerp_transposed(const float* x, const float* state, const float
   if (rows % 1024 != 0 || steps % 1024 != 0 || cols % 16 != 0 || rows >= (1ll << 31) || (cols / 16) * (rows / 1024) >= (1ll << 31))
     return fail(PB_ERR_UNSUPPORTED, "shift-lerp transposed quantizer: rows=%lld steps=%lld cols=%lld", (long long)rows, (long long)steps, (long long)cols);
   return launch_one_pass_f32_ring<PB_E4M3, 1>(x, q_t, sc8, sc32, 1, rows, cols, st, LerpPrologue{x, state, mu, (int)steps, nullptr, nullptr});
+}
+
+// quantize_impl((relu(k)^2)^T, (1,128)) from k [rows, cols] f32 (rows and cols multiples of 1024)
+int launch_relu2_transposed(const float* k, uint8_t* q_t, uint8_t* sc8, float* sc32, int64_t rows, int64_t cols, cudaStream_t st) {
+  if (rows % 1024 != 0 || cols % 16 != 0 || rows >= (1ll << 31) || (cols / 16) * (rows / 1024) >= (1ll << 31))
+    return fail(PB_ERR_UNSUPPORTED, "relu^2 transposed quantizer: rows=%lld cols=%lld", (long long)rows, (long long)cols);
+  return launch_one_pass_f32_ring<PB_E4M3, 3>(k, q_t, sc8, sc32, 1, rows, cols, st);
 }
 
 // quantize_impl(g'^T, (1,128)) of g' = (g * x_sc) / 128, x_sc from the (1,128) triple (y_sc8, y_sc32) of an array of g's shape

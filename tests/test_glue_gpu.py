@@ -168,6 +168,38 @@ def test_rms_norm_matches_torch(built_lib, shape):
         close(a, b, name, 2e-5)
 
 
+@pytest.mark.parametrize("shape", [(1024, 1024), (2, 1024, 2048), (8, 512, 8192)])
+def test_relu2_quantized_gives_the_bytes_of_relu2_then_quantize(built_lib, shape):
+    """relu^2 as the prologue of the row and the token-major quantizer: byte for byte the triples of the quantizers run on
+    the array the relu2 kernel writes, and the same gradient through a Linear."""
+    from pratchya_b200 import _lib
+    from pratchya_b200._qualia import quantize_impl, quantize_transposed_impl
+    from pratchya_b200._nnx_impl import linear_fp8
+    from pratchya_b200._nnx_impl._glue import relu2, relu2_quantized
+    gen = torch.Generator(device="cuda").manual_seed(sum(shape))
+    k = torch.randn(shape, device="cuda", generator=gen) * 2.0
+    k.view(-1)[::4099] *= 40.0
+    mix = relu2_quantized(k)
+    torch.cuda.synchronize()
+    _lib.check(built_lib.pb_gemm_check(torch.cuda.current_stream().cuda_stream))
+    k2 = relu2(k).reshape(-1, shape[-1])
+    as_bytes = lambda t: t.contiguous().view(torch.uint8)
+    for got, want in zip(mix.row, quantize_impl(k2, (1, 128))):
+        assert got.shape == want.shape and torch.equal(as_bytes(got), as_bytes(want))
+    for got, want in zip(mix.tokens, quantize_transposed_impl(k2, 128)):
+        assert got.shape == want.shape and torch.equal(as_bytes(got), as_bytes(want))
+    w = (torch.randn(shape[-1], 256, device="cuda", generator=gen) * 0.03).requires_grad_(True)
+    g = torch.randn(*shape[:-1], 256, device="cuda", generator=gen)
+    results = []
+    for fused in (True, False):
+        kk = k.clone().requires_grad_(True)
+        y = linear_fp8(relu2_quantized(kk) if fused else relu2(kk), w, (128, 128))
+        results.append((y.detach(), torch.autograd.grad(y, [kk, w], g)))
+    assert torch.equal(results[0][0], results[1][0])
+    for a, b in zip(results[0][1], results[1][1]):
+        assert torch.equal(a, b)
+
+
 def test_relu2_matches_torch(built_lib):
     from pratchya_b200._nnx_impl._glue import relu2
     gen = torch.Generator(device="cuda").manual_seed(9)
