@@ -407,6 +407,31 @@ __device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Waits for fill number `fill` (0, 1, 2, ... of this buffer) to land.  The two groups take a buffer's fills in turn, so the
+// group that waits here did not consume the buffer's previous fill and may arrive before that one has even landed; a
+// parity wait alone would then take the phase BEFORE the previous fill's (same parity as the awaited one, and over) for
+// the awaited one, read a tile that is still arriving and arm the barrier a second time within one phase.  So the
+// thread that arms a fill publishes its number in shared memory afterwards (release), and a waiter first sees that
+// number (acquire): from then on the barrier is in the awaited fill's own phase and the parity wait means what it says.
+// Both waits are bounded.
+__device__ __noinline__ bool ring_wait_armed(uint32_t armed_addr, uint32_t fill) {      // the rare case: the fill is not armed yet
+  for (uint32_t n = 0; n < kRingWaitPolls; ++n) {
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(armed_addr) : "memory");
+    if (v > fill) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ bool ring_wait_tile(uint32_t bar, uint32_t armed_addr, uint32_t fill) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(armed_addr) : "memory");
+  if (v <= fill && !ring_wait_armed(armed_addr, fill)) return false;
+  return ring_wait(bar, fill & 1u);
+}
+__device__ __forceinline__ void ring_publish_fill(uint32_t armed_addr, uint32_t fill) {
+  asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(armed_addr), "r"(fill + 1u) : "memory");
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(1024, 1)
 transpose_quantize1024_bf16_ring_kernel(const __grid_constant__ CUtensorMap map_x, uint8_t* __restrict__ q_t, uint8_t* __restrict__ sc8,
@@ -420,7 +445,10 @@ transpose_quantize1024_bf16_ring_kernel(const __grid_constant__ CUtensorMap map_
   const int tid = threadIdx.x, grp = tid >> 9, gt = tid & 511;
 
   if (tid == 0) {
-    for (int b = 0; b < kRingBufs; ++b) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_bar + 8u * b));
+    for (int b = 0; b < kRingBufs; ++b) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_bar + 8u * b));
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_bar + 32u + 4u * b), "r"(0u) : "memory");      // fills armed so far
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -437,6 +465,7 @@ transpose_quantize1024_bf16_ring_kernel(const __grid_constant__ CUtensorMap map_
     for (int j = 0; j < 4; ++j)
       asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                    ::"r"(dst + j * 16384u), "l"(&map_x), "r"(cx * 32), "r"(z * rows + ry * 1024 + j * 256), "r"(bar) : "memory");
+    ring_publish_fill(s_bar + 32u + 4u * (seq % kRingBufs), (uint32_t)(seq / kRingBufs));
   };
   if (tid == 0) { issue(0); issue(1); issue(2); }
 
@@ -450,7 +479,7 @@ transpose_quantize1024_bf16_ring_kernel(const __grid_constant__ CUtensorMap map_
     const int tl = blockIdx.x + seq * gridDim.x;
     const int cx = tl % tiles_x, rest = tl / tiles_x, ry = rest % tiles_y, z = rest / tiles_y;
     const int c0 = cx * 32, r0 = ry * 1024;
-    const bool landed = ring_wait(s_bar + 8u * (seq % kRingBufs), (uint32_t)(seq / kRingBufs) & 1u);
+    const bool landed = ring_wait_tile(s_bar + 8u * (seq % kRingBufs), s_bar + 32u + 4u * (seq % kRingBufs), (uint32_t)(seq / kRingBufs));
     if (!landed) atomicExch(&g_tq_status, (unsigned int)PB_ERR_DEVICE_TIMEOUT);
     const uint8_t* tile = smem + (size_t)(seq % kRingBufs) * kRingTileBytes;
     uint32_t w[32];
@@ -555,7 +584,10 @@ transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x
   const int tid = threadIdx.x, grp = tid >> 9, gt = tid & 511;
 
   if (tid == 0) {
-    for (int b = 0; b < kRingBufs; ++b) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_bar + 8u * b));
+    for (int b = 0; b < kRingBufs; ++b) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_bar + 8u * b));
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_bar + 32u + 4u * b), "r"(0u) : "memory");      // fills armed so far
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -570,6 +602,7 @@ transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x
     for (int j = 0; j < 4; ++j)
       asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                    ::"r"(dst + j * 16384u), "l"(&map_x), "r"(cx * 16), "r"(z * rows + ry * 1024 + j * 256), "r"(bar) : "memory");
+    ring_publish_fill(s_bar + 32u + 4u * (seq % kRingBufs), (uint32_t)(seq / kRingBufs));
   };
   if (tid == 0) { issue(0); issue(1); issue(2); }
 
@@ -613,7 +646,7 @@ transpose_quantize1024_f32_ring_kernel(const __grid_constant__ CUtensorMap map_x
         else if (lerp.state) before = __ldg(lerp.state + (row / lerp.steps) * cols + c0 + cp);
       }
     }
-    const bool landed = ring_wait(s_bar + 8u * (seq % kRingBufs), (uint32_t)(seq / kRingBufs) & 1u);
+    const bool landed = ring_wait_tile(s_bar + 8u * (seq % kRingBufs), s_bar + 32u + 4u * (seq % kRingBufs), (uint32_t)(seq / kRingBufs));
     if (!landed) atomicExch(&g_tq_status, (unsigned int)PB_ERR_DEVICE_TIMEOUT);
     const uint8_t* tile = smem + (size_t)(seq % kRingBufs) * kRingTileBytes;
     float w[32];
